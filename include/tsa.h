@@ -1,0 +1,197 @@
+/* tsa.h - C ABI of the B200 (sm_100a) quantized attention path.
+ *
+ * Drop-in boundary for TScale's attention kernels: each entry point enqueues work on a CUDA stream
+ * and takes the same kind of arguments the reference passes to its own kernels through
+ * CudaCall(...) (code/gpt/compute/gpt_cuda.cu:503-515,747-751,796-845): caller-owned 2-D device
+ * buffers with a byte stride, per-head scale planes indexed [head][row], grouped span lists for
+ * the mask, the ALiBi slope, and a sumWeightLog side output.  Nothing here allocates device
+ * memory; scratch is passed in by the caller (tsa_*_workspace_bytes gives the size).
+ *
+ * Every function returns a tsa_status and never aborts.  Device-side problems (a bounded wait
+ * that ran out) are reported through the optional int *statusWord in device memory: the kernels
+ * OR a non-zero code into it and return normally.
+ *
+ * Naming follows the reference (code/gpt/model_params/model_params.h:8-12):
+ *   qk = query vectors ("attention current token"), qv = key vectors ("attention remote"),
+ *   v = value vectors, out = ValLookup, sumWeightLog = log2-sum-exp including the implicit sink.
+ */
+#ifndef TSA_H
+#define TSA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *tsa_stream_t; /* == cudaStream_t */
+
+enum tsa_status {
+    TSA_OK = 0,
+    TSA_BAD_ARG = 1,
+    TSA_UNSUPPORTED = 2,
+    TSA_CUDA_ERROR = 3,
+    TSA_TIMEOUT = 4
+};
+
+enum tsa_dtype {
+    TSA_I8 = 0,   /* int8 (reference type i8) */
+    TSA_E4M3 = 1, /* fp8 e4m3 (reference type e4m3, code/util/fp8.h:122-139) */
+    TSA_F16 = 2,
+    TSA_BF16 = 3,
+    TSA_F32 = 4
+};
+
+/* Mirrors TCuda2DPtr<T> (code/lib/cuda/cuda_arrays.h:203-237): row y starts at data + y * stride_bytes.
+ * xsize / ysize are the extents in elements / rows and are used for argument validation and as the
+ * bounds of TMA tensor maps; data == NULL means "argument not given" where the entry point allows it. */
+typedef struct {
+    void *data;
+    int stride_bytes;
+    int xsize;
+    int ysize;
+} tsa_ptr2d;
+
+/* Mirrors TAttentionSpanGroup<64> (code/gpt/att/att.h:56-64): one record per 64-row query block and
+ * round; Start/Finish are 128-aligned key-block bounds, SpanStart/SpanFinish the inclusive key span
+ * of each of the 64 rows (unused rows: SpanStart = 1e9, SpanFinish = 1e9 - 1). */
+#define TSA_ATT_GROUP 64
+#define TSA_ATT_ALIGN 128
+typedef struct {
+    int Start;
+    int Finish;
+    int SpanStart[TSA_ATT_GROUP];
+    int SpanFinish[TSA_ATT_GROUP];
+} tsa_span_group;
+
+/* Replaces the compile-time switches of code/gpt/compute/cfg_precision.h:9-12,46-58 (ATT_TYPE,
+ * TAttVecFloat) and the constants of gpt_cuda.cu:40-45 (QK_VEC_SCALE, V_VEC_SCALE). */
+typedef struct {
+    int qk_dtype;       /* TSA_I8 or TSA_E4M3: type of qk and qv */
+    int v_dtype;        /* TSA_I8 or TSA_E4M3 */
+    int out_dtype;      /* TSA_F16, TSA_BF16 or TSA_F32: type of out (forward) */
+    int grad_dtype;     /* TSA_F16, TSA_BF16 or TSA_F32: type of dOut, dQK, dQV, dV (backward) */
+    int head_dim_qk;    /* Q_DIM */
+    int head_dim_v;     /* TT_DIM */
+    float qk_vec_scale; /* query scale used when qkScale is not given (QK_VEC_SCALE) */
+    float v_vec_scale;  /* value scale used when vScale is not given; 1 returns "stored-V units" like Fp8Att */
+    int flags;          /* TSA_FLAG_* */
+} tsa_att_cfg;
+
+#define TSA_FLAG_FORCE_GENERIC 1 /* use the SIMT kernels that accept any mask and head size */
+
+const char *tsa_version(void);
+/* text of the last error raised on the calling thread ("" if none) */
+const char *tsa_last_error(void);
+
+/* ---- forward ---------------------------------------------------------------------------------
+ * Replaces Fp8Att (code/gpt/compute/gpt_att_fp8.cuh:43-46) and Fp16Att (gpt_att_fp16.cuh:121-127).
+ *   qk, qv        [len][H*Dqk] 8-bit;   qkScale, qvScale  f32 [H][len] (qkScale may be absent)
+ *   v             [len][H*Dv] 8-bit, NOT transposed;  vScale f32 [H][len] (may be absent)
+ *   attSpans / attSpanPtr: grouped spans of lenAttTiles 64-row blocks, device memory (gpt_cuda.cu:362-363)
+ *   out           [len][H*Dv] of cfg->out_dtype; sumWeightLog f32 [H][len] (may be absent)
+ * logit(i,j) = dot(qk_i, qv_j) * qkScale_i * qvScale_j * sqrt(1/Dqk) * 0.5/0.693147 * (*qvGlobalScale)
+ *              - alibiSlope * (i - j);  softmax base 2 with an extra logit-0 / value-0 sink;
+ * rows without keys give 0.  qvGlobalScale: device scalar, NULL = 1. */
+int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    tsa_ptr2d out, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len);
+
+/* ---- backward --------------------------------------------------------------------------------
+ * Replaces Fp8AttGradQK + Fp8AttGradQV (gpt_att_fp8.cuh:277-284, 599-606) and Fp16AttGradQK/QV
+ * (gpt_att_fp16.cuh:332, 459).  Additional inputs: dOut [len][H*Dv] of cfg->grad_dtype, out (forward
+ * result, used when dScale is absent), dScale f32 [H][len] = sum_x dOut*out (absent: computed into the
+ * workspace), sumWeightLog from the forward, revAttSpans / revAttSpanPtr = grouped spans of the
+ * transposed mask (gpt_cuda.cu:812).  Outputs dQK, dQV [len][H*Dqk], dV [len][H*Dv] of
+ * cfg->grad_dtype: gradients with respect to the true-scale (dequantised) vectors, times attGradMult
+ * (the rope / normalise back-propagation of the reference epilogues is not part of this entry). */
+int tsa_att_bwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    tsa_ptr2d dOut, tsa_ptr2d out, tsa_ptr2d dScale, tsa_ptr2d sumWeightLog,
+    const tsa_span_group *attSpans, const int *attSpanPtr,
+    const tsa_span_group *revAttSpans, const int *revAttSpanPtr,
+    float alibiSlope, float attGradMult,
+    tsa_ptr2d dQK, tsa_ptr2d dQV, tsa_ptr2d dV, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+size_t tsa_att_bwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len);
+
+/* dScale[head][t] = sum_x out[t][head*Dv + x] * dOut[t][head*Dv + x].
+ * Replaces CalcDScale (gpt_att_fp16.cuh:621-643) and the dScale part of KVProductBackpropE4fused
+ * (gpt_combiner.cuh:184-217).  outDtype / gradDtype: TSA_F16, TSA_BF16 or TSA_F32. */
+int tsa_calc_dscale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa_ptr2d dScale,
+    int headCount, int headDimV, int len, tsa_stream_t stream);
+
+/* raw integer scores S[head][i][j] = sum_x qk[i][x] * qv[j][x] for i < lenQ, j < lenK, computed by the
+ * same tcgen05 kind::i8 tile path the int8 forward uses (int32 [H][lenQ][lenK], dense).  Parity hook
+ * for the exactness of the integer QK^T accumulators (s8 -> s32 tiles of gpt_att_fp16.cuh:76-101). */
+int tsa_qk_scores_i32(tsa_ptr2d qk, tsa_ptr2d qv, int headCount, int headDim, int lenQ, int lenK,
+    int32_t *scores, int *statusWord, tsa_stream_t stream);
+
+/* ---- per-row quantisers ----------------------------------------------------------------------
+ * Replaces NormalizeVecsRowTile / NormalizeVecsRowTileMax (code/gpt/compute/row_tile_scale.cuh:11-34,
+ * 59-82) and the stand-alone use of the TStoreRowTileNormalize epilogue (lib/cuda/cuda_matmul.cuh:147-204).
+ * Per row and per tile of `tile` elements: TSA_QUANT_RMS: scale = sqrt(mean(x^2)) * vecScale;
+ * TSA_QUANT_ABSMAX: scale = max|x| / 127 (i8) or / 256 (e4m3); dst = sat_rne(x / scale);
+ * scale plane f32 [xsize/tile][len]; all-zero tiles give scale 0 and zeros.  Rows in [len, dst.ysize)
+ * are written with zeros like the reference's padding rows.  srcDtype: TSA_F32, TSA_F16 or TSA_BF16. */
+enum tsa_quant_kind { TSA_QUANT_RMS = 0, TSA_QUANT_ABSMAX = 1 };
+int tsa_quant_rows(int kind, int srcDtype, int dstDtype, float vecScale, tsa_ptr2d src, tsa_ptr2d dst,
+    tsa_ptr2d scale, int len, int tile, tsa_stream_t stream);
+
+/* ---- KV-cache decode -------------------------------------------------------------------------
+ * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
+ * batched over sequences.  Per sequence the cache is caller-owned device memory:
+ *   k, v    int8 [capacity][H*D] (row stride H*D bytes);  kScale, vScale scaleDtype [capacity][H].
+ * tsa_kv_append writes each sequence's new token at row ctxLens[s] and then increments ctxLens[s]
+ * (AddVectors, cpu_infer.cpp:403-408).  tsa_att_decode then attends, like the reference, to the keys
+ * [cur - window, cur - 1] with cur = ctxLens[s] - 1 (window 0: the new token itself); logits use the exact
+ * int32 dot, an extra logit-0 sink, and out = sum softmax * vScale * v. */
+typedef struct {
+    void *k;
+    void *v;
+    void *kScale;
+    void *vScale;
+} tsa_kv_seq;
+
+typedef struct {
+    int head_dim;       /* 64 or 128 */
+    int scale_dtype;    /* TSA_F16 or TSA_F32: type of kScale / vScale planes */
+    int out_dtype;      /* TSA_F32, TSA_F16 or TSA_BF16 */
+    float qk_vec_scale; /* query scale when qScale is absent (VEC_SCALE of cpu_infer.cpp:16) */
+} tsa_decode_cfg;
+
+int tsa_kv_append(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, int *ctxLens, int nSeq, int capacity,
+    tsa_ptr2d kNew, tsa_ptr2d kScaleNew, tsa_ptr2d vNew, tsa_ptr2d vScaleNew, int headCount,
+    int *statusWord, tsa_stream_t stream);
+/* q int8 [nSeq][H*D]; qScale f32 [nSeq][H] (may be absent); out [nSeq][H*D].  maxCtx: host-side upper
+ * bound of ctxLens, only used to size the launch.  seqs and ctxLens are device arrays. */
+int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+    tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+size_t tsa_att_decode_workspace_bytes(const tsa_decode_cfg *cfg, int nSeq, int headCount, int maxCtx);
+
+/* ---- host-side span preprocessing (CPU) ------------------------------------------------------
+ * tsa_make_window_spans: causal window mask of AddAttSpans (code/gpt/att/sliding_window.cpp:80-87):
+ *   row i of a fragment starting at f0 attends [max(f0, i - window), i - 1]; window <= 0: whole prefix.
+ *   spans: (start, finish) int pairs, spanPtr: len + 1 offsets.  Returns the span count, or -(needed) if
+ *   maxSpans is too small.
+ * tsa_transpose_attention: TransposeAttention (code/gpt/att/att.cpp:26-56).
+ * tsa_group_attention: GroupAttention<64,128> (code/gpt/att/att.h:95-181); groupPtr has ceil(len/64)+1 entries.
+ * tsa_group_window_spans: closed form of the two above for window masks: writes grouped spans of the mask
+ *   (transposed = 0) or of its transpose (transposed = 1) without enumerating pairs. */
+int tsa_make_window_spans(int fragCount, const int *fragLens, int window, int maxSpans, int *spans, int *spanPtr);
+int tsa_transpose_attention(int len, const int *spans, const int *spanPtr, int maxSpans, int *resSpans, int *resSpanPtr);
+int tsa_group_attention(int len, const int *spans, const int *spanPtr, int maxGroups, tsa_span_group *groups, int *groupPtr);
+int tsa_group_window_spans(int fragCount, const int *fragLens, int window, int transposed, int maxGroups,
+    tsa_span_group *groups, int *groupPtr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,286 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+ctypes front-end of the CPU oracle (oracle/libtsa_oracle.so, our restatement of TScale's
+attention path) and, when it has been built from a reference checkout, of the reference's own
+CPU code (oracle/_ref/libtsa_ref.so).  Only tests/, __graft_entry__.smoke() and the CPU-baseline
+legs of bench.py import this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_SO = os.path.join(_HERE, "libtsa_oracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libtsa_ref.so")
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+_fp = ctypes.POINTER(ctypes.c_float)
+_ip = ctypes.POINTER(ctypes.c_int)
+_bp = ctypes.POINTER(ctypes.c_int8)
+
+
+def build(reference=True):
+    """Compile the oracle (and the reference shim when a reference checkout is present)."""
+    subprocess.run(["make", "-C", _HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
+    if reference and os.path.exists("/root/reference/code/gpt/compute/gpt_cpu.cpp"):
+        subprocess.run(["make", "-C", _HERE, "ref", "-j8"], check=True, stdout=subprocess.DEVNULL)
+
+
+def _f(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(_fp)
+
+
+def _i(a):
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    return a, a.ctypes.data_as(_ip)
+
+
+def _b(a):
+    a = np.ascontiguousarray(a).view(np.int8)
+    return a, a.ctypes.data_as(_bp)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_ORACLE_SO):
+            build(reference=False)
+        _lib = ctypes.CDLL(_ORACLE_SO)
+        _lib.oracle_e4m3_to_f32.restype = c_float
+        _lib.oracle_e4m3_to_f32.argtypes = [c_int]
+        _lib.oracle_f32_to_e4m3.argtypes = [c_float]
+        _lib.oracle_f32_to_i8.argtypes = [c_float]
+    return _lib
+
+
+def _cpu_has(*flags):
+    try:
+        txt = open("/proc/cpuinfo").read()
+    except OSError:
+        return False
+    line = next((l for l in txt.splitlines() if l.startswith("flags")), "")
+    have = set(line.split())
+    return all(f in have for f in flags)
+
+
+_ref = None
+
+
+def ref():
+    """The reference's own CPU attention, or None when it was not built or this CPU cannot run it
+    (the decode path uses AVX-VNNI intrinsics)."""
+    global _ref
+    if _ref is None:
+        if not os.path.exists(_REF_SO) or not _cpu_has("avx2", "fma", "avx_vnni"):
+            _ref = False
+        else:
+            r = ctypes.CDLL(_REF_SO)
+            r.ref_vec_scale.restype = c_float
+            r.ref_e4m3_to_float.restype = c_float
+            r.ref_float2i8.argtypes = [c_float]
+            _ref = r
+    return _ref or None
+
+
+def set_threads(n):
+    lib().oracle_set_threads(int(n))
+
+
+# ------------------------------------------------------------------------------------------------
+# 8-bit formats
+E4M3_TABLE = None
+
+
+def e4m3_table():
+    """float value of each of the 256 e4m3 bytes (0x7f/0xff are NaN codes and map to +-480 here
+    only so that the table stays finite; the quantisers never emit them)."""
+    global E4M3_TABLE
+    if E4M3_TABLE is None:
+        E4M3_TABLE = np.array([lib().oracle_e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+    return E4M3_TABLE
+
+
+def e4m3_to_f32(a):
+    return e4m3_table()[np.asarray(a).view(np.uint8)]
+
+
+def dequant(a8, dtype):
+    if dtype == "i8":
+        return np.asarray(a8).view(np.int8).astype(np.float32)
+    if dtype == "e4m3":
+        return e4m3_to_f32(a8)
+    raise ValueError(dtype)
+
+
+def quant_rows(kind, dst, vec_scale, src, tile):
+    """kind: 'rms' | 'absmax' | 'rms_clamp127'; dst: 'i8' | 'e4m3'.
+    Returns (bytes [len][x] int8, scale [x/tile][len] f32)."""
+    src, sp = _f(src)
+    ln, xs = src.shape
+    out = np.zeros((ln, xs), dtype=np.int8)
+    scale = np.zeros((xs // tile, ln), dtype=np.float32)
+    lib().oracle_quant_rows(
+        {"rms": 0, "absmax": 1, "rms_clamp127": 2}[kind], {"i8": 0, "e4m3": 1}[dst], c_float(vec_scale),
+        ln, xs, tile, sp, out.ctypes.data_as(_bp), scale.ctypes.data_as(_fp))
+    return out, scale
+
+
+# ------------------------------------------------------------------------------------------------
+# spans
+def window_spans(frag_lens, window):
+    """Causal window spans of TScale (att/sliding_window.cpp:80-87,211-222): row i of a fragment
+    starting at f0 attends [max(f0, i - window), i - 1]; the row itself is excluded; the first row
+    of a fragment has no span.  window <= 0 or None means the whole fragment prefix."""
+    spans, ptr = [], [0]
+    base = 0
+    for fl in frag_lens:
+        for i in range(base, base + fl):
+            lo = base if not window or window <= 0 else max(base, i - window)
+            if i - 1 >= lo:
+                spans.append((lo, i - 1))
+            ptr.append(len(spans))
+        base += fl
+    return np.array(spans, dtype=np.int32).reshape(-1, 2), np.array(ptr, dtype=np.int32)
+
+
+def transpose_attention(spans, span_ptr, use_ref=False):
+    spans, sp = _i(spans)
+    span_ptr, pp = _i(span_ptr)
+    ln = len(span_ptr) - 1
+    fn = ref().ref_transpose_attention if use_ref else lib().oracle_transpose_attention
+    cap = max(16, 2 * len(spans) + ln)
+    while True:
+        res = np.zeros((cap, 2), dtype=np.int32)
+        rptr = np.zeros(ln + 1, dtype=np.int32)
+        n = fn(ln, sp, pp, cap, res.ctypes.data_as(_ip), rptr.ctypes.data_as(_ip))
+        if n >= 0:
+            return res[:n].copy(), rptr
+        cap = -n
+
+
+def group_attention(spans, span_ptr, use_ref=False):
+    """GroupAttention<64,128>: returns (groups [n][130] int32, group_ptr [ceil(len/64)+1])."""
+    spans, sp = _i(spans)
+    span_ptr, pp = _i(span_ptr)
+    ln = len(span_ptr) - 1
+    fn = ref().ref_group_attention_64_128 if use_ref else lib().oracle_group_attention_64_128
+    cap = max(16, (ln + 63) // 64 * 2)
+    while True:
+        groups = np.zeros((cap, 130), dtype=np.int32)
+        gptr = np.zeros((ln + 63) // 64 + 1, dtype=np.int32)
+        n = fn(ln, sp, pp, cap, groups.ctypes.data_as(_ip), gptr.ctypes.data_as(_ip))
+        if n >= 0:
+            return groups[:n].copy(), gptr
+        cap = -n
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+def att_fwd(q, k, v, spans, span_ptr, heads, slope, global_scale=1.0, use_ref=False):
+    """fp32 forward on true-scale vectors q,k [len][H*Dq], v [len][H*Dv].
+    Returns dict(out, sum_weight [H][len], max_dp [H][len], lse [H][len])."""
+    q, qp = _f(q)
+    k, kp = _f(k)
+    v, vp = _f(v)
+    spans, sp = _i(spans)
+    span_ptr, pp = _i(span_ptr)
+    ln = q.shape[0]
+    dq, dv = q.shape[1] // heads, v.shape[1] // heads
+    out = np.zeros_like(v)
+    sw = np.zeros((heads, ln), dtype=np.float32)
+    mx = np.zeros((heads, ln), dtype=np.float32)
+    if use_ref:
+        assert global_scale == 1.0
+        ref().ref_att_fwd(ln, heads, dq, dv, c_float(slope), qp, kp, vp, sp, pp,
+                          out.ctypes.data_as(_fp), sw.ctypes.data_as(_fp), mx.ctypes.data_as(_fp))
+        lse = mx + np.log2(sw)
+    else:
+        lse = np.zeros((heads, ln), dtype=np.float32)
+        lib().oracle_att_fwd(ln, heads, dq, dv, c_float(global_scale), c_float(slope), qp, kp, vp, sp, pp,
+                             out.ctypes.data_as(_fp), sw.ctypes.data_as(_fp), mx.ctypes.data_as(_fp),
+                             lse.ctypes.data_as(_fp))
+    return dict(out=out, sum_weight=sw, max_dp=mx, lse=lse)
+
+
+def dscale(out, d_out, heads):
+    out, op = _f(out)
+    d_out, dp = _f(d_out)
+    ln = out.shape[0]
+    res = np.zeros((heads, ln), dtype=np.float32)
+    lib().oracle_dscale(ln, heads, out.shape[1] // heads, op, dp, res.ctypes.data_as(_fp))
+    return res
+
+
+def att_bwd(q, k, v, d_out, spans, span_ptr, heads, slope, global_scale=1.0, use_ref=False, fwd=None,
+            rev=None):
+    """fp32 backward.  Returns dict(dq, dk, dv, dscale)."""
+    q, qp = _f(q)
+    k, kp = _f(k)
+    v, vp = _f(v)
+    d_out, dop = _f(d_out)
+    spans, sp = _i(spans)
+    span_ptr, pp = _i(span_ptr)
+    ln = q.shape[0]
+    dq_, dv_ = q.shape[1] // heads, v.shape[1] // heads
+    if fwd is None:
+        fwd = att_fwd(q, k, v, spans, span_ptr, heads, slope, global_scale, use_ref=use_ref)
+    ds = dscale(fwd["out"], d_out, heads)
+    if rev is None:
+        rev = transpose_attention(spans, span_ptr)
+    rs, rsp = _i(rev[0])
+    rp, rpp = _i(rev[1])
+    dq = np.zeros_like(q)
+    dk = np.zeros_like(k)
+    dv = np.zeros_like(v)
+    if use_ref:
+        assert global_scale == 1.0
+        ref().ref_att_bwd(ln, heads, dq_, dv_, c_float(slope), qp, kp, vp, dop, ds.ctypes.data_as(_fp),
+                          sp, pp, rsp, rpp, dq.ctypes.data_as(_fp), dk.ctypes.data_as(_fp),
+                          dv.ctypes.data_as(_fp))
+    else:
+        sw, swp = _f(fwd["sum_weight"])
+        mx, mxp = _f(fwd["max_dp"])
+        lib().oracle_att_bwd(ln, heads, dq_, dv_, c_float(global_scale), c_float(slope), qp, kp, vp, dop,
+                             ds.ctypes.data_as(_fp), swp, mxp, sp, pp, rsp, rpp,
+                             dq.ctypes.data_as(_fp), dk.ctypes.data_as(_fp), dv.ctypes.data_as(_fp))
+    return dict(dq=dq, dk=dk, dv=dv, dscale=ds)
+
+
+def qk_int32(q8, k8, heads):
+    q8, qp = _b(q8)
+    k8, kp = _b(k8)
+    lq, lk = q8.shape[0], k8.shape[0]
+    d = q8.shape[1] // heads
+    s = np.zeros((heads, lq, lk), dtype=np.int32)
+    lib().oracle_qk_int32(lq, lk, heads, d, qp, kp, s.ctypes.data_as(_ip))
+    return s
+
+
+def decode_step(k_cache, k_scale, v_cache, v_scale, q8, q_scale, heads, width, slope, exp_mode="exact",
+                use_ref=False):
+    """One decode step of one sequence; the cache already holds the new token (see tsa_oracle.cpp).
+    k_cache, v_cache int8 [ctx][H*D]; k_scale, v_scale f32 [ctx][H]; q8 int8 [H*D]; q_scale f32 [H]."""
+    k_cache, kp = _b(k_cache)
+    v_cache, vp = _b(v_cache)
+    k_scale, ksp = _f(k_scale)
+    q8, qp = _b(q8)
+    k_cache = k_cache.reshape(k_cache.shape[0], -1)
+    ctx = k_cache.shape[0]
+    d = k_cache.shape[1] // heads
+    out = np.zeros(heads * d, dtype=np.float32)
+    if use_ref:
+        # the reference has constant q and v scales (VEC_SCALE)
+        ref().ref_decode_step(ctx, heads, d, width, c_float(slope), kp, ksp, vp, qp, out.ctypes.data_as(_fp))
+        return out
+    v_scale, vsp = _f(v_scale)
+    q_scale, qsp = _f(q_scale)
+    lib().oracle_decode_step(ctx, heads, d, width, c_float(slope), 0 if exp_mode == "poly" else 1,
+                             kp, ksp, vp, vsp, qp, qsp, out.ctypes.data_as(_fp))
+    return out

@@ -1,0 +1,155 @@
+"""GPU parity of the attention forward / backward against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _setup(seed, frag_lens, heads, d, qk_dtype, v_dtype, scale=1.0, spans=None):
+    from tscale_b200 import ops
+    length = sum(frag_lens)
+    q, k, v = util.make_qkv(seed, length, heads, d, d, scale)
+    q8, sq, qd = util.quantize(q, qk_dtype, d)
+    k8, sk, kd = util.quantize(k, qk_dtype, d)
+    v8, sv, vd = util.quantize(v, v_dtype, d)
+    dev = _dev()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    g = dict(q8=t(q8.view(np.uint8)), k8=t(k8.view(np.uint8)), v8=t(v8.view(np.uint8)), sq=t(sq), sk=t(sk), sv=t(sv))
+    return g, (qd, kd, vd)
+
+
+def _run_fwd(seed, frag_lens, window, slope, heads, d, qk_dtype, v_dtype, out_dtype=torch.float32, scale=1.0,
+             force_generic=False, custom=None):
+    from tscale_b200 import ops
+    g, (qd, kd, vd) = _setup(seed, frag_lens, heads, d, qk_dtype, v_dtype, scale)
+    if custom is None:
+        spans, ptr = O.window_spans(frag_lens, window)
+        mask = ops.Mask.window(frag_lens, window)
+    else:
+        spans, ptr = custom
+        mask = ops.Mask.from_spans(spans, ptr)
+    ref = O.att_fwd(qd, kd, vd, spans, ptr, heads, slope)
+    cfg = ops.make_cfg(qk_dtype, v_dtype, d, d, out_dtype=out_dtype, force_generic=force_generic)
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out, lse = ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"],
+                           status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "device status %#x" % int(status.item())
+    return util.to_np(out), util.to_np(lse), ref, (g, mask, cfg, spans, ptr, (qd, kd, vd))
+
+
+@pytest.mark.parametrize("window,slope", [(64, 0.5), (64, 0.0), (0, 0.0)])
+def test_fwd_generic_int8_config1_shape(window, slope):
+    # configs[0] at reduced length: int8 Q/K/V with per-row absmax scales, D=64, fp32 output
+    out, lse, ref, _ = _run_fwd(0, [320, 192], window, slope, 4, 64, "i8", "i8", force_generic=True)
+    mx, mean = util.err_stats(out, ref["out"])
+    assert mx < 1e-4 and mean < 1e-5, (mx, mean)
+    assert util.err_stats(lse, ref["lse"])[0] < 1e-4
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window,slope", [(64, 0.5), (0, 0.0), (256, 0.0)])
+@pytest.mark.parametrize("qk_dtype", ["e4m3", "i8"])
+def test_fwd_tcgen05(d, window, slope, qk_dtype):
+    out, lse, ref, _ = _run_fwd(1, [384, 256, 128], window, slope, 3, d, qk_dtype, "e4m3", out_dtype=torch.bfloat16, scale=0.5)
+    mx, mean = util.err_stats(out, ref["out"])
+    assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, (mx, mean)
+    assert util.err_stats(lse, ref["lse"])[0] < 2e-3
+
+
+def test_fwd_tcgen05_large_logits_rescale():
+    # logits of several units so that the running floor(max) moves and the accumulator is rescaled
+    out, lse, ref, _ = _run_fwd(2, [512], 0, 0.0, 2, 64, "e4m3", "e4m3", out_dtype=torch.float32, scale=2.5)
+    assert ref["max_dp"].max() > 4
+    mx, mean = util.err_stats(out, ref["out"])
+    assert mx < 0.1 and mean < 1e-2, (mx, mean)   # values are 5x larger than in the unit-scale cases
+    assert util.err_stats(lse, ref["lse"])[0] < 5e-3
+
+
+def test_fwd_tcgen05_ragged_and_multispan():
+    # ragged length (not a multiple of 64), rows with no span, rows with two spans (two rounds)
+    length = 300
+    rows = []
+    for i in range(length):
+        if i % 7 == 0:
+            rows.append([])
+        elif i > 140 and i % 5 == 0:
+            rows.append([(3, 40), (i - 20, i - 1)])
+        else:
+            rows.append([(max(0, i - 90), i - 1)] if i > 0 else [])
+    spans, ptr = [], [0]
+    for r in rows:
+        spans.extend(r)
+        ptr.append(len(spans))
+    custom = (np.array(spans, dtype=np.int32).reshape(-1, 2), np.array(ptr, dtype=np.int32))
+    for force in (True, False):
+        out, lse, ref, _ = _run_fwd(3, [length], None, 0.25, 2, 64, "e4m3", "e4m3", out_dtype=torch.float32, scale=0.5,
+                                    force_generic=force, custom=custom)
+        mx, mean = util.err_stats(out, ref["out"])
+        assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, (force, mx, mean)
+        empty = [i for i, r in enumerate(rows) if not r]
+        assert np.all(out[empty] == 0)
+
+
+def test_fwd_matches_golden_fixture(golden_dir):
+    # the reference's own output on a committed fixture, inputs int8-quantised here
+    import os
+    from tscale_b200 import ops
+    z = np.load(os.path.join(golden_dir, "att_w64_slope05.npz"))
+    heads, d = int(z["heads"]), z["q"].shape[1] // int(z["heads"])
+    mask = ops.Mask.from_spans(z["spans"], z["span_ptr"])
+    q8, sq, qd = util.quantize(z["q"], "i8", d)
+    k8, sk, kd = util.quantize(z["k"], "i8", d)
+    v8, sv, vd = util.quantize(z["v"], "i8", d)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(_dev())
+    cfg = ops.make_cfg("i8", "i8", d, d, out_dtype=torch.float32)
+    out, lse = ops.att_fwd(cfg, t(q8.view(np.uint8)), t(k8.view(np.uint8)), t(v8.view(np.uint8)), t(sk), mask,
+                           float(z["slope"]), heads, qk_scale=t(sq), v_scale=t(sv))
+    # int8 quantisation error of the inputs dominates: compare to the fp32 fixture loosely and to the
+    # oracle on the same quantised inputs tightly
+    ref_q = O.att_fwd(qd, kd, vd, z["spans"], z["span_ptr"], heads, float(z["slope"]))
+    assert util.err_stats(util.to_np(out), ref_q["out"])[0] < 1e-4
+    assert util.err_stats(util.to_np(out), z["out"])[1] < 2e-2
+
+
+@pytest.mark.parametrize("window,slope,d", [(64, 0.5, 64), (0, 0.0, 128), (256, 0.0, 128)])
+def test_bwd_against_oracle(window, slope, d):
+    from tscale_b200 import ops
+    frag_lens, heads = [256, 192], 2
+    out, lse, ref, (g, mask, cfg, spans, ptr, (qd, kd, vd)) = _run_fwd(
+        4, frag_lens, window, slope, heads, d, "i8", "e4m3", out_dtype=torch.float32, scale=0.5)
+    rng = np.random.default_rng(5)
+    d_out = (rng.standard_normal(out.shape) * 1e-2).astype(np.float32)
+    gref = O.att_bwd(qd, kd, vd, d_out, spans, ptr, heads, slope, fwd=ref)
+    cfg.grad_dtype = 4  # f32
+    out_t = torch.from_numpy(ref["out"]).to(_dev())
+    lse_t = torch.from_numpy(ref["lse"]).to(_dev())
+    dq, dk, dv = ops.att_bwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], torch.from_numpy(d_out).to(_dev()), out_t, lse_t,
+                             mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"])
+    torch.cuda.synchronize()
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        r = util.rel_l2(util.to_np(got), gref[name])
+        assert r < util.GRAD_REL_L2, (name, r)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_int8_scores_bit_exact(d):
+    from tscale_b200 import ops
+    rng = np.random.default_rng(6)
+    heads, lq, lk = 3, 200, 333
+    q8 = rng.integers(-128, 128, (lq, heads * d)).astype(np.int8)
+    k8 = rng.integers(-128, 128, (lk, heads * d)).astype(np.int8)
+    ref = O.qk_int32(q8, k8, heads)
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    got = ops.qk_scores_i32(torch.from_numpy(q8).to(_dev()), torch.from_numpy(k8).to(_dev()), heads, d, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(got.cpu().numpy(), ref)

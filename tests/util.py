@@ -1,0 +1,46 @@
+"""Shared helpers of the parity tests: seeded inputs, quantisation through the oracle, error metrics."""
+import numpy as np
+
+from oracle import oracle as O
+
+# tolerances of the path (softmax outputs / fp8 paths against the fp32-accumulated oracle)
+OUT_MAX_ABS = 2e-2
+OUT_MEAN_ABS = 2e-3
+GRAD_REL_L2 = 1e-2
+
+
+def make_qkv(seed, length, heads, dq, dv, scale=1.0):
+    rng = np.random.default_rng(seed)
+    q = (rng.standard_normal((length, heads * dq)) * scale).astype(np.float32)
+    k = (rng.standard_normal((length, heads * dq)) * scale).astype(np.float32)
+    v = (rng.standard_normal((length, heads * dv)) * scale).astype(np.float32)
+    return q, k, v
+
+
+def quantize(x, dtype, tile):
+    """abs-max per (row, head) quantisation through the oracle; returns bytes, scale [H][len], dequantised."""
+    b, s = O.quant_rows("absmax", dtype, 0.0, x, tile)
+    ln, xs = x.shape
+    deq = (O.dequant(b, dtype).reshape(ln, xs // tile, tile) * s.T[:, :, None]).reshape(ln, xs)
+    return b, s, deq.astype(np.float32)
+
+
+def err_stats(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    d = np.abs(a - b)
+    return float(d.max()) if d.size else 0.0, float(d.mean()) if d.size else 0.0
+
+
+def rel_l2(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    den = np.sqrt((b * b).sum())
+    return float(np.sqrt(((a - b) ** 2).sum()) / max(den, 1e-30))
+
+
+def to_np(t):
+    import torch
+    if t.dtype == torch.bfloat16:
+        t = t.float()
+    return t.detach().cpu().numpy()

@@ -1,0 +1,330 @@
+// KV-cache decode step: a bandwidth-bound stream over the int8 K and V rows of each sequence.
+//
+// Reference behaviour: NCPUInfer::ComputeValLookup (code/gpt/train/cpu_infer.cpp:413-460): for the
+// newest token cur of a sequence, keys to = cur - dt, dt = 1..min(cur, width) (width 0: to = cur),
+// logit = int32dot(q, k[to]) * kScale[to][h] * attDotScale * qScale - slope * (cur - to), a sink with
+// logit 0, softmax in base 2, out = sum softmax * vScale[to][h] * v[to].
+//
+// Layout: per sequence K and V are [capacity][H*D] int8 with the heads of one token contiguous, so a
+// token range of a sequence is one contiguous byte range.  A CTA owns (sequence, chunk of DEC_CHUNK
+// tokens) and all heads: a 128-bit load per lane covers 512 contiguous bytes per warp = 32/LPH heads
+// of one token (LPH = D/16 lanes per head).  The int8 dot uses dp4a (exact int32), partial sums are
+// reduced over the LPH lanes of a head with shuffles.  Each CTA keeps an online (max, sum, acc[D])
+// per head and writes it to the scratch buffer; a second kernel merges the chunks of a sequence and
+// adds the sink.  Algorithmic traffic per key: 2*D bytes + 2 scales per head.
+#include "tsa_common.cuh"
+
+namespace tsa {
+
+constexpr int DEC_CHUNK = 256;  // tokens per CTA
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_UNROLL = 4;   // tokens in flight per lane (4 x 16 B K + 4 x 16 B V)
+
+struct TDecodeParams {
+    const tsa_kv_seq *Seqs;
+    const int *CtxLens;
+    int NSeq;
+    int HeadCount;
+    int Window;
+    int ScaleDtype;
+    int OutDtype;
+    float Slope;
+    float DotScale;  // attDotScale
+    float QVecScale; // constant query scale when QScale is absent
+    P2D<int8_t> Q;
+    P2D<float> QScale;
+    P2D<char> Out;
+    float *Partial;  // [nSeq][maxChunks][H][D + 4]
+    int MaxChunks;
+};
+
+__device__ __forceinline__ float LoadScale(const void *base, size_t idx, int dt)
+{
+    return dt == TSA_F16 ? __half2float(((const __half *)base)[idx]) : ((const float *)base)[idx];
+}
+
+__device__ __forceinline__ void KeyRange(int ctxLen, int window, int *j0, int *j1)
+{
+    int cur = ctxLen - 1;
+    if (window == 0) {
+        *j0 = cur;
+        *j1 = cur + 1;
+    } else {
+        *j0 = max(0, cur - window);
+        *j1 = cur;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32) DecodePartialKernel(TDecodeParams p)
+{
+    constexpr int LPH = D / 16;       // lanes per head
+    constexpr int HPW = 32 / LPH;     // heads per warp-wide load
+    int seq = blockIdx.y;
+    int chunk = blockIdx.x;
+    int ctxLen = p.CtxLens[seq];
+    if (ctxLen <= 0) {
+        return;
+    }
+    int j0, j1;
+    KeyRange(ctxLen, p.Window, &j0, &j1);
+    int cBeg = j0 + chunk * DEC_CHUNK;
+    int cEnd = min(cBeg + DEC_CHUNK, j1);
+    if (cBeg >= cEnd) {
+        return;
+    }
+    int cur = ctxLen - 1;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int sub = lane % LPH;             // 16-byte slice inside the head
+    int H = p.HeadCount;
+    size_t rowBytes = (size_t)H * D;
+    tsa_kv_seq sq = p.Seqs[seq];
+    const int8_t *kBase = (const int8_t *)sq.k;
+    const int8_t *vBase = (const int8_t *)sq.v;
+
+    int headGroups = (H + HPW - 1) / HPW;
+    for (int hg = warp; hg < headGroups; hg += DEC_WARPS) {
+        int head = hg * HPW + lane / LPH;
+        bool headOk = head < H;
+        int headC = headOk ? head : H - 1;
+        size_t colOff = (size_t)headC * D + sub * 16;
+        int4 qv = *reinterpret_cast<const int4 *>(p.Q.Row(seq) + colOff);
+        float qs = p.QScale.Valid() ? p.QScale.Row(seq)[headC] : p.QVecScale;
+        float logitMult = p.DotScale * qs;
+
+        float m = -1e30f, l = 0;
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            acc[i] = 0;
+        }
+        for (int tBase = cBeg; tBase < cEnd; tBase += DEC_UNROLL) {
+            int4 kv[DEC_UNROLL], vv[DEC_UNROLL];
+            float ks[DEC_UNROLL], vs[DEC_UNROLL];
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                int t = min(tBase + u, cEnd - 1);
+                kv[u] = __ldg(reinterpret_cast<const int4 *>(kBase + (size_t)t * rowBytes + colOff));
+                vv[u] = __ldg(reinterpret_cast<const int4 *>(vBase + (size_t)t * rowBytes + colOff));
+                ks[u] = LoadScale(sq.kScale, (size_t)t * H + headC, p.ScaleDtype);
+                vs[u] = LoadScale(sq.vScale, (size_t)t * H + headC, p.ScaleDtype);
+            }
+            float z[DEC_UNROLL];
+            float cm = m;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                int dot = __dp4a(qv.x, kv[u].x, 0);
+                dot = __dp4a(qv.y, kv[u].y, dot);
+                dot = __dp4a(qv.z, kv[u].z, dot);
+                dot = __dp4a(qv.w, kv[u].w, dot);
+#pragma unroll
+                for (int o = LPH / 2; o > 0; o >>= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                }
+                int t = tBase + u;
+                // same association as the reference: ((dot * kScale) * attDotScale) * qScale - slope * dist
+                float zz = (float)dot * ks[u] * logitMult - p.Slope * (float)(cur - t);
+                z[u] = (t < cEnd) ? zz : -1e30f;
+                cm = fmaxf(cm, z[u]);
+            }
+            float corr = exp2f(m - cm);
+            m = cm;
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                acc[i] *= corr;
+            }
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                float w = exp2f(z[u] - m);
+                l += w;
+                float wv = w * vs[u];
+                const int words[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        int s8 = (int)(int8_t)(words[wi] >> (8 * b));
+                        acc[wi * 4 + b] = fmaf(wv, (float)s8, acc[wi * 4 + b]);
+                    }
+                }
+            }
+        }
+        if (headOk) {
+            float *dst = p.Partial + (((size_t)seq * p.MaxChunks + chunk) * H + head) * (D + 4);
+            if (sub == 0) {
+                dst[D] = m;
+                dst[D + 1] = l;
+            }
+            float4 *d4 = reinterpret_cast<float4 *>(dst + sub * 16);
+            d4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            d4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            d4[2] = make_float4(acc[8], acc[9], acc[10], acc[11]);
+            d4[3] = make_float4(acc[12], acc[13], acc[14], acc[15]);
+        }
+    }
+}
+
+// merge chunk partials of one (sequence, head): block = D threads
+template <int D>
+__global__ void __launch_bounds__(D) DecodeCombineKernel(TDecodeParams p)
+{
+    int seq = blockIdx.y, head = blockIdx.x, x = threadIdx.x;
+    int ctxLen = p.CtxLens[seq];
+    float res = 0;
+    if (ctxLen > 0) {
+        int j0, j1;
+        KeyRange(ctxLen, p.Window, &j0, &j1);
+        int chunks = (j1 - j0 + DEC_CHUNK - 1) / DEC_CHUNK;
+        const float *base = p.Partial + ((size_t)seq * p.MaxChunks * p.HeadCount + head) * (D + 4);
+        size_t cstride = (size_t)p.HeadCount * (D + 4);
+        float m = 0; // the sink has logit 0 (softMax.Add(0), cpu_infer.cpp:444)
+        for (int c = 0; c < chunks; ++c) {
+            m = fmaxf(m, base[c * cstride + D]);
+        }
+        float l = exp2f(-m);
+        float acc = 0;
+        for (int c = 0; c < chunks; ++c) {
+            float f = exp2f(base[c * cstride + D] - m);
+            l += f * base[c * cstride + D + 1];
+            acc += f * base[c * cstride + x];
+        }
+        res = acc / l;
+    }
+    StoreFromFloat(p.Out.Row(seq), head * D + x, p.OutDtype, res);
+}
+
+__global__ void KvAppendKernel(const tsa_kv_seq *seqs, int *ctxLens, int nSeq, int capacity, int rowBytes, int headCount, int scaleBytes,
+    P2D<int8_t> kNew, P2D<char> kScaleNew, P2D<int8_t> vNew, P2D<char> vScaleNew, int *statusWord)
+{
+    int seq = blockIdx.x;
+    int pos = ctxLens[seq];
+    if (pos >= capacity || pos < 0) {
+        if (threadIdx.x == 0 && statusWord) {
+            atomicOr(statusWord, kDevBadSpan);
+        }
+        return;
+    }
+    tsa_kv_seq sq = seqs[seq];
+    for (int i = threadIdx.x * 16; i < rowBytes; i += blockDim.x * 16) {
+        *reinterpret_cast<int4 *>((int8_t *)sq.k + (size_t)pos * rowBytes + i) = *reinterpret_cast<const int4 *>(kNew.Row(seq) + i);
+        *reinterpret_cast<int4 *>((int8_t *)sq.v + (size_t)pos * rowBytes + i) = *reinterpret_cast<const int4 *>(vNew.Row(seq) + i);
+    }
+    int sb = headCount * scaleBytes;
+    for (int i = threadIdx.x; i < sb; i += blockDim.x) {
+        ((char *)sq.kScale)[(size_t)pos * sb + i] = kScaleNew.Row(seq)[i];
+        ((char *)sq.vScale)[(size_t)pos * sb + i] = vScaleNew.Row(seq)[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ctxLens[seq] = pos + 1;
+    }
+}
+
+static int MaxChunksFor(int maxCtx)
+{
+    return (maxCtx + DEC_CHUNK - 1) / DEC_CHUNK + 1;
+}
+
+size_t DecodeWorkspaceBytes(int headDim, int nSeq, int headCount, int maxCtx)
+{
+    return (size_t)nSeq * MaxChunksFor(maxCtx) * headCount * (headDim + 4) * sizeof(float);
+}
+
+int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStream_t stream)
+{
+    p.MaxChunks = MaxChunksFor(maxCtx);
+    dim3 grid(p.MaxChunks, p.NSeq);
+    dim3 gridC(p.HeadCount, p.NSeq);
+    if (cfg->head_dim == 128) {
+        DecodePartialKernel<128><<<grid, DEC_WARPS * 32, 0, stream>>>(p);
+        DecodeCombineKernel<128><<<gridC, 128, 0, stream>>>(p);
+    } else {
+        DecodePartialKernel<64><<<grid, DEC_WARPS * 32, 0, stream>>>(p);
+        DecodeCombineKernel<64><<<gridC, 64, 0, stream>>>(p);
+    }
+    return CheckCuda(cudaGetLastError(), "tsa_att_decode launch");
+}
+
+} // namespace tsa
+
+using namespace tsa;
+
+static int CheckDecodeCfg(const tsa_decode_cfg *cfg, const char *fn)
+{
+    TSA_REQUIRE(cfg != nullptr, "%s: null cfg", fn);
+    TSA_REQUIRE(cfg->head_dim == 64 || cfg->head_dim == 128, "%s: head_dim %d must be 64 or 128", fn, cfg->head_dim);
+    TSA_REQUIRE(cfg->scale_dtype == TSA_F16 || cfg->scale_dtype == TSA_F32, "%s: scale dtype must be f16 or f32", fn);
+    TSA_REQUIRE(cfg->out_dtype >= TSA_F16 && cfg->out_dtype <= TSA_F32, "%s: out dtype must be f16, bf16 or f32", fn);
+    return TSA_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) size_t tsa_att_decode_workspace_bytes(const tsa_decode_cfg *cfg, int nSeq, int headCount, int maxCtx)
+{
+    if (!cfg || nSeq <= 0 || headCount <= 0 || maxCtx < 0) {
+        return 0;
+    }
+    return DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+    tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+{
+    int rc = CheckDecodeCfg(cfg, "tsa_att_decode");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    TSA_REQUIRE(seqs && ctxLens && q.data && out.data, "tsa_att_decode: null buffer");
+    TSA_REQUIRE(nSeq >= 0 && headCount > 0 && maxCtx >= 0 && window >= 0, "tsa_att_decode: negative size");
+    if (nSeq == 0) {
+        return TSA_OK;
+    }
+    int rowSize = headCount * cfg->head_dim;
+    TSA_REQUIRE(q.xsize >= rowSize && q.ysize >= nSeq && out.xsize >= rowSize && out.ysize >= nSeq, "tsa_att_decode: q/out extents");
+    TSA_REQUIRE((uintptr_t)q.data % 16 == 0 && q.stride_bytes % 16 == 0, "tsa_att_decode: q must be 16-byte aligned");
+    if (qScale.data) {
+        TSA_REQUIRE(qScale.xsize >= headCount && qScale.ysize >= nSeq, "tsa_att_decode: qScale extents");
+    }
+    size_t need = DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
+    TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_decode: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
+    TSA_REQUIRE((uintptr_t)workspace % 16 == 0, "tsa_att_decode: workspace must be 16-byte aligned");
+    (void)statusWord;
+    TDecodeParams p;
+    p.Seqs = seqs;
+    p.CtxLens = ctxLens;
+    p.NSeq = nSeq;
+    p.HeadCount = headCount;
+    p.Window = window;
+    p.ScaleDtype = cfg->scale_dtype;
+    p.OutDtype = cfg->out_dtype;
+    p.Slope = alibiSlope;
+    p.DotScale = HostAttDotScale(cfg->head_dim);
+    p.QVecScale = cfg->qk_vec_scale;
+    p.Q = P2D<int8_t>(q);
+    p.QScale = P2D<float>(qScale);
+    p.Out = P2D<char>(out);
+    p.Partial = (float *)workspace;
+    return LaunchDecode(cfg, p, maxCtx, (cudaStream_t)stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_kv_append(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, int *ctxLens, int nSeq, int capacity,
+    tsa_ptr2d kNew, tsa_ptr2d kScaleNew, tsa_ptr2d vNew, tsa_ptr2d vScaleNew, int headCount,
+    int *statusWord, tsa_stream_t stream)
+{
+    int rc = CheckDecodeCfg(cfg, "tsa_kv_append");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    TSA_REQUIRE(seqs && ctxLens && kNew.data && vNew.data && kScaleNew.data && vScaleNew.data, "tsa_kv_append: null buffer");
+    if (nSeq <= 0) {
+        return nSeq == 0 ? TSA_OK : Fail(TSA_BAD_ARG, "tsa_kv_append: negative nSeq");
+    }
+    int rowBytes = headCount * cfg->head_dim;
+    TSA_REQUIRE(kNew.xsize >= rowBytes && vNew.xsize >= rowBytes && kNew.ysize >= nSeq && vNew.ysize >= nSeq, "tsa_kv_append: kNew/vNew extents");
+    TSA_REQUIRE((uintptr_t)kNew.data % 16 == 0 && kNew.stride_bytes % 16 == 0 && (uintptr_t)vNew.data % 16 == 0 && vNew.stride_bytes % 16 == 0,
+        "tsa_kv_append: kNew/vNew must be 16-byte aligned");
+    KvAppendKernel<<<nSeq, 128, 0, (cudaStream_t)stream>>>(seqs, ctxLens, nSeq, capacity, rowBytes, headCount, DtypeSize(cfg->scale_dtype),
+        P2D<int8_t>(kNew), P2D<char>(kScaleNew), P2D<int8_t>(vNew), P2D<char>(vScaleNew), statusWord);
+    return CheckCuda(cudaGetLastError(), "tsa_kv_append launch");
+}

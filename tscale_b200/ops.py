@@ -1,0 +1,224 @@
+"""Torch-tensor front-end of the C ABI: builds tsa_ptr2d views of CUDA tensors and calls the library.
+
+Names follow the reference's attention operators (code/gpt/compute/gpt_cuda.cu:445-564, 618-894):
+qk = queries, qv = keys, v = values, per-head scale planes [H][len], grouped spans for the mask.
+Everything runs on the GPU through libtsa_b200.so; torch only owns the memory and the stream.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import abi
+from .abi import Ptr2D, check
+
+_DT = {"i8": abi.TSA_I8, "e4m3": abi.TSA_E4M3, torch.float16: abi.TSA_F16, torch.bfloat16: abi.TSA_BF16,
+       torch.float32: abi.TSA_F32}
+
+
+def p2d(t, xsize=None, ysize=None):
+    """tsa_ptr2d view of a 2-D tensor whose last dimension is contiguous (None -> absent argument)."""
+    if t is None:
+        return Ptr2D(None, 0, 0, 0)
+    assert t.dim() == 2 and t.stride(1) == 1, "expected a row-major 2-D tensor"
+    return Ptr2D(t.data_ptr(), t.stride(0) * t.element_size(), xsize or t.shape[1], ysize or t.shape[0])
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _np_ip(a):
+    return a.ctypes.data_as(abi.c_int_p)
+
+
+class Mask:
+    """Attention mask in the grouped form the kernels take (TAttentionSpanGroup<64> records), for the
+    mask itself and for its transpose.  Built on the host by the library's span helpers."""
+
+    def __init__(self, length, groups, group_ptr, rev_groups, rev_group_ptr):
+        self.len = length
+        self.len_att_tiles = (length + abi.ATT_GROUP - 1) // abi.ATT_GROUP
+        self.groups, self.group_ptr = groups, group_ptr          # numpy int32 [n][130], [tiles+1]
+        self.rev_groups, self.rev_group_ptr = rev_groups, rev_group_ptr
+        self._dev = {}
+
+    @staticmethod
+    def _run_grouper(fn, cap):
+        while True:
+            groups = np.zeros((max(cap, 1), 130), dtype=np.int32)
+            n = fn(cap, groups)
+            if n >= 0:
+                return groups[:n].copy()
+            cap = -n
+
+    @classmethod
+    def window(cls, frag_lens, window):
+        """Causal window mask of concatenated fragments; window <= 0 means full causal."""
+        L = abi.lib()
+        fl = np.ascontiguousarray(frag_lens, dtype=np.int32)
+        length = int(fl.sum())
+        tiles = (length + abi.ATT_GROUP - 1) // abi.ATT_GROUP
+        res = []
+        for transposed in (0, 1):
+            gptr = np.zeros(tiles + 1, dtype=np.int32)
+            groups = cls._run_grouper(
+                lambda cap, g: L.tsa_group_window_spans(len(fl), _np_ip(fl), int(window or 0), transposed, cap,
+                                                        g.ctypes.data, _np_ip(gptr)), tiles + 1)
+            res += [groups, gptr]
+        return cls(length, *res)
+
+    @classmethod
+    def from_spans(cls, spans, span_ptr):
+        """General mask from per-row inclusive spans in CSR form."""
+        L = abi.lib()
+        spans = np.ascontiguousarray(spans, dtype=np.int32).reshape(-1, 2)
+        span_ptr = np.ascontiguousarray(span_ptr, dtype=np.int32)
+        length = len(span_ptr) - 1
+        tiles = (length + abi.ATT_GROUP - 1) // abi.ATT_GROUP
+        cap = max(16, 2 * len(spans) + length)
+        while True:
+            rev = np.zeros((cap, 2), dtype=np.int32)
+            rev_ptr = np.zeros(length + 1, dtype=np.int32)
+            n = L.tsa_transpose_attention(length, _np_ip(spans), _np_ip(span_ptr), cap, _np_ip(rev), _np_ip(rev_ptr))
+            if n >= 0:
+                rev = rev[:n].copy()
+                break
+            cap = -n
+        res = []
+        for sp, pt in ((spans, span_ptr), (rev, rev_ptr)):
+            gptr = np.zeros(tiles + 1, dtype=np.int32)
+            groups = cls._run_grouper(
+                lambda cap, g: L.tsa_group_attention(length, _np_ip(sp), _np_ip(pt), cap, g.ctypes.data, _np_ip(gptr)),
+                tiles + 1)
+            res += [groups, gptr]
+        m = cls(length, *res)
+        m.rev_spans, m.rev_span_ptr = rev, rev_ptr
+        return m
+
+    def dev(self, device):
+        key = str(device)
+        if key not in self._dev:
+            self._dev[key] = tuple(torch.from_numpy(np.ascontiguousarray(a)).to(device)
+                                   for a in (self.groups, self.group_ptr, self.rev_groups, self.rev_group_ptr))
+        return self._dev[key]
+
+
+def quant_rows(src, kind, dst, tile, vec_scale=0.0, length=None):
+    """Per-row, per-tile quantiser.  kind 'rms' | 'absmax'; dst 'i8' | 'e4m3'.
+    Returns (bytes uint8 [rows][x], scale f32 [x/tile][rows])."""
+    rows, xs = src.shape
+    length = rows if length is None else length
+    out = torch.empty((rows, xs), dtype=torch.uint8, device=src.device)
+    scale = torch.empty((xs // tile, rows), dtype=torch.float32, device=src.device)
+    check(abi.lib().tsa_quant_rows(abi.TSA_QUANT_RMS if kind == "rms" else abi.TSA_QUANT_ABSMAX, _DT[src.dtype], _DT[dst],
+                                   vec_scale, p2d(src), p2d(out), p2d(scale), length, tile, _stream()))
+    return out, scale
+
+
+def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat16, grad_dtype=torch.bfloat16,
+             qk_vec_scale=1.0, v_vec_scale=1.0, force_generic=False):
+    return abi.AttCfg(_DT[qk_dtype], _DT[v_dtype], _DT[out_dtype], _DT[grad_dtype], head_dim_qk, head_dim_v,
+                      qk_vec_scale, v_vec_scale, abi.TSA_FLAG_FORCE_GENERIC if force_generic else 0)
+
+
+def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale=None, global_scale=None,
+            out=None, lse=None, workspace=None, status=None):
+    """Forward.  Returns (out [len][H*Dv], sumWeightLog f32 [H][len])."""
+    L = abi.lib()
+    dev = qk.device
+    rows = qk.shape[0]
+    out_t = {abi.TSA_F16: torch.float16, abi.TSA_BF16: torch.bfloat16, abi.TSA_F32: torch.float32}[cfg.out_dtype]
+    if out is None:
+        out = torch.empty((rows, heads * cfg.head_dim_v), dtype=out_t, device=dev)
+    if lse is None:
+        lse = torch.empty((heads, rows), dtype=torch.float32, device=dev)
+    if workspace is None:
+        workspace = torch.empty(max(1, L.tsa_att_fwd_workspace_bytes(ctypes.byref(cfg), heads, rows)), dtype=torch.uint8, device=dev)
+    groups, gptr, _, _ = mask.dev(dev)
+    check(L.tsa_att_fwd(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
+                        p2d(v), p2d(v_scale), _ptr(groups), _ptr(gptr), slope, p2d(out), p2d(lse), heads,
+                        mask.len_att_tiles, _ptr(workspace), workspace.numel(), _ptr(status), _stream()))
+    return out, lse
+
+
+def att_bwd(cfg, qk, qv, v, qv_scale, d_out, out, lse, mask, slope, heads, qk_scale=None, v_scale=None,
+            global_scale=None, d_scale=None, grad_mult=1.0, workspace=None, status=None):
+    """Backward.  Returns (dQK, dQV, dV) with respect to the true-scale vectors."""
+    L = abi.lib()
+    dev = qk.device
+    rows = qk.shape[0]
+    gt = {abi.TSA_F16: torch.float16, abi.TSA_BF16: torch.bfloat16, abi.TSA_F32: torch.float32}[cfg.grad_dtype]
+    dq = torch.empty((rows, heads * cfg.head_dim_qk), dtype=gt, device=dev)
+    dk = torch.empty((rows, heads * cfg.head_dim_qk), dtype=gt, device=dev)
+    dv = torch.empty((rows, heads * cfg.head_dim_v), dtype=gt, device=dev)
+    if workspace is None:
+        workspace = torch.empty(max(1, L.tsa_att_bwd_workspace_bytes(ctypes.byref(cfg), heads, rows)), dtype=torch.uint8, device=dev)
+    groups, gptr, rgroups, rgptr = mask.dev(dev)
+    check(L.tsa_att_bwd(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
+                        p2d(v), p2d(v_scale), p2d(d_out), p2d(out), p2d(d_scale), p2d(lse),
+                        _ptr(groups), _ptr(gptr), _ptr(rgroups), _ptr(rgptr), slope, grad_mult,
+                        p2d(dq), p2d(dk), p2d(dv), heads, mask.len_att_tiles,
+                        _ptr(workspace), workspace.numel(), _ptr(status), _stream()))
+    return dq, dk, dv
+
+
+def calc_dscale(out, d_out, heads, head_dim_v):
+    rows = out.shape[0]
+    res = torch.empty((heads, rows), dtype=torch.float32, device=out.device)
+    check(abi.lib().tsa_calc_dscale(_DT[out.dtype], _DT[d_out.dtype], p2d(out), p2d(d_out), p2d(res), heads, head_dim_v,
+                                    rows, _stream()))
+    return res
+
+
+def qk_scores_i32(qk, qv, heads, head_dim, status=None):
+    """Raw int32 QK^T scores [H][lenQ][lenK] from the tcgen05 kind::i8 path."""
+    len_q, len_k = qk.shape[0], qv.shape[0]
+    res = torch.empty((heads, len_q, len_k), dtype=torch.int32, device=qk.device)
+    check(abi.lib().tsa_qk_scores_i32(p2d(qk), p2d(qv), heads, head_dim, len_q, len_k, _ptr(res), _ptr(status), _stream()))
+    return res
+
+
+class KVCache:
+    """Caller-owned int8 KV cache of nSeq sequences (the reference's TAttentionVecHistory,
+    code/gpt/train/cpu_infer.cpp:397-410), one contiguous [capacity][H*D] block per sequence."""
+
+    def __init__(self, n_seq, capacity, heads, head_dim, device, scale_dtype=torch.float16, out_dtype=torch.float32,
+                 qk_vec_scale=1.0):
+        self.n_seq, self.capacity, self.heads, self.head_dim = n_seq, capacity, heads, head_dim
+        row = heads * head_dim
+        self.k = torch.zeros((n_seq, capacity, row), dtype=torch.int8, device=device)
+        self.v = torch.zeros((n_seq, capacity, row), dtype=torch.int8, device=device)
+        self.k_scale = torch.zeros((n_seq, capacity, heads), dtype=scale_dtype, device=device)
+        self.v_scale = torch.zeros((n_seq, capacity, heads), dtype=scale_dtype, device=device)
+        self.ctx_lens = torch.zeros(n_seq, dtype=torch.int32, device=device)
+        table = np.zeros((n_seq, 4), dtype=np.uint64)
+        for s in range(n_seq):
+            table[s] = (self.k[s].data_ptr(), self.v[s].data_ptr(), self.k_scale[s].data_ptr(), self.v_scale[s].data_ptr())
+        self.seqs = torch.from_numpy(table.view(np.int64)).to(device)
+        self.cfg = abi.DecodeCfg(head_dim, _DT[scale_dtype], _DT[out_dtype], qk_vec_scale)
+        self.out_dtype = out_dtype
+        self.workspace = None
+        self.max_ctx = 0
+
+    def append(self, k_new, k_scale_new, v_new, v_scale_new, status=None):
+        check(abi.lib().tsa_kv_append(ctypes.byref(self.cfg), _ptr(self.seqs), _ptr(self.ctx_lens), self.n_seq, self.capacity,
+                                      p2d(k_new), p2d(k_scale_new), p2d(v_new), p2d(v_scale_new), self.heads,
+                                      _ptr(status), _stream()))
+        self.max_ctx = min(self.capacity, self.max_ctx + 1)
+
+    def decode(self, q, q_scale, window, slope, out=None, status=None):
+        L = abi.lib()
+        if out is None:
+            out = torch.empty((self.n_seq, self.heads * self.head_dim), dtype=self.out_dtype, device=q.device)
+        need = L.tsa_att_decode_workspace_bytes(ctypes.byref(self.cfg), self.n_seq, self.heads, self.capacity)
+        if self.workspace is None or self.workspace.numel() < need:
+            self.workspace = torch.empty(max(1, need), dtype=torch.uint8, device=q.device)
+        check(L.tsa_att_decode(ctypes.byref(self.cfg), _ptr(self.seqs), _ptr(self.ctx_lens), self.n_seq, self.max_ctx,
+                               p2d(q), p2d(q_scale), window, slope, p2d(out), self.heads,
+                               _ptr(self.workspace), self.workspace.numel(), _ptr(status), _stream()))
+        return out
