@@ -61,17 +61,55 @@ def test_fwd_generic_int8_config1_shape(window, slope):
 def test_fwd_tcgen05(d, window, slope, qk_dtype):
     out, lse, ref, _ = _run_fwd(1, [384, 256, 128], window, slope, 3, d, qk_dtype, "e4m3", out_dtype=torch.bfloat16, scale=0.5)
     mx, mean = util.err_stats(out, ref["out"])
-    assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, (mx, mean)
-    assert util.err_stats(lse, ref["lse"])[0] < 2e-3
+    assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, util.describe(out, ref["out"])
+    assert util.err_stats(lse, ref["lse"])[0] < 2e-3, util.describe(lse, ref["lse"])
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_fwd_tcgen05_constant_scales(d):
+    # the reference's call shape: constant query and value scales (QK_VEC_SCALE / V_VEC_SCALE), per-row key scale
+    from tscale_b200 import ops
+    frag_lens, heads, window, slope = [256, 128], 2, 0, 0.0
+    length = sum(frag_lens)
+    rng = np.random.default_rng(7)
+    k = (rng.standard_normal((length, heads * d)) * 0.5).astype(np.float32)
+    k8, sk, kd = util.quantize(k, "e4m3", d)
+    # q and v are stored directly as e4m3 codes with a constant scale of 1/24
+    qf = rng.standard_normal((length, heads * d)).astype(np.float32) * 8
+    vf = rng.standard_normal((length, heads * d)).astype(np.float32) * 8
+    enc = np.vectorize(lambda x: O.lib().oracle_f32_to_e4m3(float(x)))
+    q8 = enc(qf).astype(np.uint8)
+    v8 = enc(vf).astype(np.uint8)
+    qd = O.e4m3_to_f32(q8) / 24.0
+    vd = O.e4m3_to_f32(v8) / 24.0
+    spans, ptr = O.window_spans(frag_lens, window)
+    ref = O.att_fwd(qd, kd, vd, spans, ptr, heads, slope)
+    cfg = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.float32, qk_vec_scale=1 / 24.0, v_vec_scale=1 / 24.0)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out, lse = ops.att_fwd(cfg, t(q8), t(k8.view(np.uint8)), t(v8), t(sk), ops.Mask.window(frag_lens, window), slope, heads,
+                           status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    out = util.to_np(out)
+    mx, mean = util.err_stats(out, ref["out"])
+    assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, util.describe(out, ref["out"])
 
 
 def test_fwd_tcgen05_large_logits_rescale():
     # logits of several units so that the running floor(max) moves and the accumulator is rescaled
     out, lse, ref, _ = _run_fwd(2, [512], 0, 0.0, 2, 64, "e4m3", "e4m3", out_dtype=torch.float32, scale=2.5)
     assert ref["max_dp"].max() > 4
+    # peaked softmax: a few e4m3-rounded weights (3 mantissa bits, like the reference's fp8 kernel) carry each row,
+    # so the error is a few percent of the value range (|v| up to ~10 here) instead of being averaged out
     mx, mean = util.err_stats(out, ref["out"])
-    assert mx < 0.1 and mean < 1e-2, (mx, mean)   # values are 5x larger than in the unit-scale cases
+    vmax = float(np.abs(ref["out"]).max())
+    assert mx < 0.06 * vmax and mean < 0.01 * vmax, util.describe(out, ref["out"])
     assert util.err_stats(lse, ref["lse"])[0] < 5e-3
+    # the same data through the generic kernel (exact fp32 weights) pins the rescale logic itself
+    out_g, lse_g, _, _ = _run_fwd(2, [512], 0, 0.0, 2, 64, "e4m3", "e4m3", out_dtype=torch.float32, scale=2.5, force_generic=True)
+    assert util.err_stats(out_g, ref["out"])[0] < 1e-3
+    assert util.err_stats(lse, lse_g)[0] < 5e-3
 
 
 def test_fwd_tcgen05_ragged_and_multispan():
@@ -94,7 +132,7 @@ def test_fwd_tcgen05_ragged_and_multispan():
         out, lse, ref, _ = _run_fwd(3, [length], None, 0.25, 2, 64, "e4m3", "e4m3", out_dtype=torch.float32, scale=0.5,
                                     force_generic=force, custom=custom)
         mx, mean = util.err_stats(out, ref["out"])
-        assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, (force, mx, mean)
+        assert mx < util.OUT_MAX_ABS and mean < util.OUT_MEAN_ABS, (force, util.describe(out, ref["out"]))
         empty = [i for i, r in enumerate(rows) if not r]
         assert np.all(out[empty] == 0)
 

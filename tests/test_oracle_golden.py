@@ -1,0 +1,92 @@
+"""The CPU oracle against the committed known-answer files (produced by the reference's own CPU code,
+tests/golden/make_golden.py).  Integer / index work and the fp32 attention are compared bit for bit."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+
+def _cases(golden_dir, prefix):
+    return sorted(glob.glob(os.path.join(golden_dir, prefix + "*.npz")))
+
+
+def test_golden_files_present(golden_dir):
+    assert len(_cases(golden_dir, "att_")) >= 4 and len(_cases(golden_dir, "decode_")) >= 4
+
+
+@pytest.mark.parametrize("name", ["att_w64_slope05", "att_full_slope0", "att_w1_d32", "att_handmade"])
+def test_attention_forward_backward_bit_exact(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    heads, slope = int(z["heads"]), float(z["slope"])
+    fwd = O.att_fwd(z["q"], z["k"], z["v"], z["spans"], z["span_ptr"], heads, slope)
+    assert np.array_equal(fwd["out"], z["out"])
+    assert np.array_equal(fwd["sum_weight"], z["sum_weight"])
+    assert np.array_equal(fwd["max_dp"], z["max_dp"])
+    bwd = O.att_bwd(z["q"], z["k"], z["v"], z["d_out"], z["spans"], z["span_ptr"], heads, slope, fwd=fwd)
+    assert np.array_equal(bwd["dscale"], z["dscale"])
+    for n in ("dq", "dk", "dv"):
+        assert np.array_equal(bwd[n], z[n]), n
+
+
+@pytest.mark.parametrize("name", ["att_w64_slope05", "att_full_slope0", "att_w1_d32", "att_handmade"])
+def test_span_preprocessing_matches_reference(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    rev, rev_ptr = O.transpose_attention(z["spans"], z["span_ptr"])
+    assert np.array_equal(rev, z["rev_spans"]) and np.array_equal(rev_ptr, z["rev_span_ptr"])
+    g, gp = O.group_attention(z["spans"], z["span_ptr"])
+    assert np.array_equal(g, z["groups"]) and np.array_equal(gp, z["group_ptr"])
+    g, gp = O.group_attention(z["rev_spans"], z["rev_span_ptr"])
+    assert np.array_equal(g, z["rev_groups"]) and np.array_equal(gp, z["rev_group_ptr"])
+
+
+def test_rows_without_keys_give_zero(golden_dir):
+    z = np.load(os.path.join(golden_dir, "att_handmade.npz"))
+    empty = np.nonzero(np.diff(z["span_ptr"]) == 0)[0]
+    assert len(empty) >= 3
+    fwd = O.att_fwd(z["q"], z["k"], z["v"], z["spans"], z["span_ptr"], int(z["heads"]), float(z["slope"]))
+    assert np.all(fwd["out"][empty] == 0) and np.all(fwd["sum_weight"][:, empty] == 1)
+
+
+@pytest.mark.parametrize("name", ["decode_w64", "decode_wide", "decode_w0", "decode_first"])
+def test_decode_bit_exact(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    heads = int(z["heads"])
+    ctx = z["k_cache"].shape[0]
+    vs = np.full((ctx, heads), z["vec_scale"], dtype=np.float32)
+    qs = np.full((heads,), z["vec_scale"], dtype=np.float32)
+    got = O.decode_step(z["k_cache"], z["k_scale"], z["v_cache"], vs, z["q8"], qs, heads, int(z["width"]), float(z["slope"]),
+                        exp_mode="poly")
+    assert np.array_equal(got, z["out"])
+    exact = O.decode_step(z["k_cache"], z["k_scale"], z["v_cache"], vs, z["q8"], qs, heads, int(z["width"]), float(z["slope"]),
+                          exp_mode="exact")
+    assert np.abs(exact - z["out"]).max() < 1e-4 * max(1.0, np.abs(z["out"]).max())
+
+
+def test_code_points(golden_dir):
+    z = np.load(os.path.join(golden_dir, "codes.npz"))
+    tab = O.e4m3_table()
+    # the reference's host decoder maps the byte 0x80 (negative zero) to -2^-7; every other code agrees
+    idx = np.array([i for i in range(256) if i != 0x80 and (i & 0x7f) != 0x7f])
+    assert np.array_equal(tab[idx], z["e4m3"][idx])
+    got = np.array([O.lib().oracle_f32_to_i8(float(x)) for x in z["i8_grid"]], dtype=np.int32)
+    assert np.array_equal(got, z["i8"])
+    # encode(decode(code)) is the identity on finite codes
+    for i in idx:
+        if i == 0x80:
+            continue
+        assert (O.lib().oracle_f32_to_e4m3(float(tab[i])) & 0xff) == i, i
+
+
+def test_quantisers_small():
+    x = np.array([[1.0, -2.0, 0.5, 4.0] * 8, [0.0] * 32], dtype=np.float32)
+    b, s = O.quant_rows("absmax", "i8", 0.0, x, 32)
+    assert s[0, 0] == np.float32(4.0) / 127 and s[0, 1] == 0 and np.all(b[1] == 0)
+    assert b[0, 3] == 127 and b[0, 1] == -64   # -2 * (127/4) = -63.5 rounds to even -64
+    b, s = O.quant_rows("absmax", "e4m3", 0.0, x, 32)
+    assert np.allclose(O.dequant(b, "e4m3")[0, :4] * s[0, 0], [1.0, -2.0, 0.5, 4.0])
+    b, s = O.quant_rows("rms", "i8", 1 / 24.0, x, 32)
+    rms = np.sqrt(np.mean(x[0] ** 2))
+    assert np.isclose(s[0, 0], rms / 24.0, rtol=1e-6)

@@ -44,3 +44,15 @@ def to_np(t):
     if t.dtype == torch.bfloat16:
         t = t.float()
     return t.detach().cpu().numpy()
+
+
+def describe(got, want):
+    """Short diagnosis of a mismatch: error stats, median ratio, worst rows."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    d = np.abs(got - want)
+    big = np.abs(want) > 0.05
+    ratio = np.median(got[big] / want[big]) if big.any() else float("nan")
+    rows = np.argsort(d.max(axis=1))[-4:][::-1]
+    return "max %.3g mean %.3g median ratio %.4g worst rows %s (err %s) nan %d" % (
+        d.max(), d.mean(), ratio, rows.tolist(), np.round(d.max(axis=1)[rows], 4).tolist(), int(np.isnan(got).sum()))

@@ -69,7 +69,7 @@ struct TFwdSmem {
 
 struct TFwdMisc {
     float2 ColTerm[TILE_N]; // (sk_j, slope * jl)
-    float SvTerm[TILE_N];   // 128 * sv_j / svRef
+    float SvTerm[TILE_N];   // sv_j / svRef
     uint64_t BarQ;
     uint64_t BarFull[4];
     uint64_t BarMma;
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(FWD_THREADS) FwdSm100Kernel(const __grid_const
     }
     const float rowMult = sq * p.C * g;
     const float vRef = HAS_VSCALE ? p.VRef[head] : 0.0f;
-    const float svMult = (HAS_VSCALE && vRef > 0) ? 128.0f / vRef : 0.0f;
+    const float svMult = (HAS_VSCALE && vRef > 0) ? 1.0f / vRef : 0.0f; // sv_j / svRef <= 1; the factor 128 sits in the exponent
 
     const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
     bool failed = false;
@@ -561,26 +561,25 @@ __global__ void __launch_bounds__(FWD_THREADS) FwdSm100Kernel(const __grid_const
     }
 }
 
-// per head maximum of the V scale plane (normalises the weights' e4m3 range)
+// per head maximum of the V scale plane (normalises the weights' e4m3 range).  Scales are non-negative, so
+// the float maximum is the maximum of the bit patterns; the workspace is zeroed before the launch.
+constexpr int VREF_CHUNK = 2048;
 __global__ void __launch_bounds__(256) VRefKernel(P2D<float> vScale, int keyRows, float *vRef)
 {
-    __shared__ float red[8];
-    int head = blockIdx.x;
+    int head = blockIdx.y;
     const float *rowp = vScale.Row(head);
+    int t0 = blockIdx.x * VREF_CHUNK;
     float mx = 0;
-    for (int t = threadIdx.x; t < keyRows; t += blockDim.x) {
-        mx = fmaxf(mx, rowp[t]);
+#pragma unroll
+    for (int k = 0; k < VREF_CHUNK / 256; ++k) {
+        int t = t0 + k * 256 + threadIdx.x;
+        if (t < keyRows) {
+            mx = fmaxf(mx, rowp[t]);
+        }
     }
     mx = WarpMax(mx);
-    if ((threadIdx.x & 31) == 0) {
-        red[threadIdx.x >> 5] = mx;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < 8; ++w) {
-            mx = fmaxf(mx, red[w]);
-        }
-        vRef[head] = mx;
+    if ((threadIdx.x & 31) == 0 && mx > 0) {
+        atomicMax(reinterpret_cast<int *>(vRef + head), __float_as_int(mx));
     }
 }
 
@@ -779,7 +778,12 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     const bool hasVs = p.VScale.Data != nullptr;
     if (hasVs) {
         fp.VRef = (const float *)workspace;
-        VRefKernel<<<p.HeadCount, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
+        rc = CheckCuda(cudaMemsetAsync(workspace, 0, p.HeadCount * sizeof(float), stream), "clearing the V-scale maxima");
+        if (rc != TSA_OK) {
+            return rc;
+        }
+        dim3 vgrid((keyRows + VREF_CHUNK - 1) / VREF_CHUNK, p.HeadCount);
+        VRefKernel<<<vgrid, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
     }
     const int qTiles = (lenAttTiles + 1) / 2;
     const bool i8 = cfg->qk_dtype == TSA_I8;
