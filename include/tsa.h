@@ -176,6 +176,23 @@ int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int 
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
 size_t tsa_att_decode_workspace_bytes(const tsa_decode_cfg *cfg, int nSeq, int headCount, int maxCtx);
 
+/* Same decode step for callers that cannot give the library a scratch buffer.  It has no counterpart in the
+ * reference.  Meant for hosts that fix all device memory when they start and never allocate again: a runtime
+ * built like TScale's, which hands out buffers from pools sized at context creation and then only replays
+ * kernel launches, or a server whose memory budget is fully committed to its caches, where a cudaMalloc in
+ * the token loop would fail or stall the GPU.  The per-chunk partial results live in a fixed 32 MiB array in
+ * the library image instead of a workspace argument; every GPU that loads the library holds that array until
+ * the process ends.  The call allocates nothing and returns TSA_UNSUPPORTED, with a message, when
+ * tsa_att_decode_workspace_bytes(cfg, nSeq, headCount, maxCtx) exceeds tsa_att_decode_static_capacity_bytes().
+ * The first call on each device looks up the array's device address (a one-time set-up step on the host);
+ * make that first call outside any stream capture.  All calls on a device share the one array and it keeps
+ * whatever the previous call left there (each call overwrites every slot it later reads, so nothing has to be
+ * cleared); two such calls that overlap in time on the same GPU, e.g. on different streams, race on it. */
+int tsa_att_decode_static(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+    tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
+    int *statusWord, tsa_stream_t stream);
+size_t tsa_att_decode_static_capacity_bytes(void);
+
 /* ---- host-side span preprocessing (CPU) ------------------------------------------------------
  * tsa_make_window_spans: causal window mask of AddAttSpans (code/gpt/att/sliding_window.cpp:80-87):
  *   row i of a fragment starting at f0 attends [max(f0, i - window), i - 1]; window <= 0: whole prefix.

@@ -52,7 +52,7 @@ EXPORTS = [
     "tsa_version", "tsa_last_error", "tsa_att_fwd", "tsa_att_fwd_workspace_bytes", "tsa_att_bwd",
     "tsa_att_bwd_workspace_bytes", "tsa_calc_dscale", "tsa_qk_scores_i32", "tsa_quant_rows", "tsa_kv_append",
     "tsa_att_decode", "tsa_att_decode_workspace_bytes", "tsa_make_window_spans", "tsa_transpose_attention",
-    "tsa_group_attention", "tsa_group_window_spans",
+    "tsa_group_attention", "tsa_group_window_spans", "tsa_att_decode_static", "tsa_att_decode_static_capacity_bytes",
 ]
 
 
@@ -78,6 +78,10 @@ def _declare(lib):
                                    P, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
     lib.tsa_att_decode_workspace_bytes.restype = c_size_t
     lib.tsa_att_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeCfg), c_int, c_int, c_int]
+    lib.tsa_att_decode_static.argtypes = [ctypes.POINTER(DecodeCfg), c_void_p, c_void_p, c_int, c_int, P, P, c_int, c_float,
+                                          P, c_int, c_void_p, c_void_p]
+    lib.tsa_att_decode_static_capacity_bytes.restype = c_size_t
+    lib.tsa_att_decode_static_capacity_bytes.argtypes = []
     lib.tsa_make_window_spans.argtypes = [c_int, c_int_p, c_int, c_int, c_int_p, c_int_p]
     lib.tsa_transpose_attention.argtypes = [c_int, c_int_p, c_int_p, c_int, c_int_p, c_int_p]
     lib.tsa_group_attention.argtypes = [c_int, c_int_p, c_int_p, c_int, c_void_p, c_int_p]

@@ -13,6 +13,7 @@
 // per head and writes it to the scratch buffer; a second kernel merges the chunks of a sequence and
 // adds the sink.  Algorithmic traffic per key: 2*D bytes + 2 scales per head.
 #include "tsa_common.cuh"
+#include <mutex>
 
 namespace tsa {
 
@@ -327,4 +328,100 @@ extern "C" __attribute__((visibility("default"))) int tsa_kv_append(const tsa_de
     KvAppendKernel<<<nSeq, 128, 0, (cudaStream_t)stream>>>(seqs, ctxLens, nSeq, capacity, rowBytes, headCount, DtypeSize(cfg->scale_dtype),
         P2D<int8_t>(kNew), P2D<char>(kScaleNew), P2D<int8_t>(vNew), P2D<char>(vScaleNew), statusWord);
     return CheckCuda(cudaGetLastError(), "tsa_kv_append launch");
+}
+
+// ---- decode without any allocation -------------------------------------------------------------------
+// Some hosts cannot hand this library a scratch buffer at call time: TScale's own runtime carves all device
+// memory out of pools when a context is created and afterwards only replays a fixed list of kernel launches
+// (code/lib/cuda/cuda_graph.cuh:131-349, cuda_memory.h), and a serving loop that already owns the whole
+// memory budget has nothing left to ask cudaMalloc for (which would also stall the device while it runs).
+// For them the chunk partials of the decode live in this fixed array inside the library image; every GPU
+// that loads the library keeps these 32 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
+static __device__ __align__(256) unsigned char g_decodeScratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratchLock;
+void *g_scratchAddr[kMaxDevices]; // device address of g_decodeScratch, per device, filled on first use
+
+// The array's name is only a host-side handle; the address a kernel can use has to be asked for, on the
+// device that is current, once per device.
+int StaticScratchAddress(void **out)
+{
+    int dev = -1;
+    int rc = tsa::CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        return tsa::Fail(TSA_UNSUPPORTED, "tsa_att_decode_static: device index %d not supported", dev);
+    }
+    std::lock_guard<std::mutex> guard(g_scratchLock);
+    if (!g_scratchAddr[dev]) {
+        void *ptr = nullptr;
+        rc = tsa::CheckCuda(cudaGetSymbolAddress((void **)&ptr, g_decodeScratch), "cudaGetSymbolAddress(decode scratch)");
+        if (rc != TSA_OK) {
+            return rc;
+        }
+        g_scratchAddr[dev] = ptr;
+    }
+    *out = g_scratchAddr[dev];
+    return TSA_OK;
+}
+} // namespace
+
+extern "C" __attribute__((visibility("default"))) size_t tsa_att_decode_static_capacity_bytes(void)
+{
+    return kStaticScratchBytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_decode_static(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+    tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
+    int *statusWord, tsa_stream_t stream)
+{
+    int rc = CheckDecodeCfg(cfg, "tsa_att_decode_static");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    TSA_REQUIRE(seqs && ctxLens && q.data && out.data, "tsa_att_decode_static: null buffer");
+    TSA_REQUIRE(nSeq >= 0 && headCount > 0 && maxCtx >= 0 && window >= 0, "tsa_att_decode_static: negative size");
+    if (nSeq == 0) {
+        return TSA_OK;
+    }
+    int rowSize = headCount * cfg->head_dim;
+    TSA_REQUIRE(q.xsize >= rowSize && q.ysize >= nSeq && out.xsize >= rowSize && out.ysize >= nSeq, "tsa_att_decode_static: q/out extents");
+    TSA_REQUIRE((uintptr_t)q.data % 16 == 0 && q.stride_bytes % 16 == 0, "tsa_att_decode_static: q must be 16-byte aligned");
+    if (qScale.data) {
+        TSA_REQUIRE(qScale.xsize >= headCount && qScale.ysize >= nSeq, "tsa_att_decode_static: qScale extents");
+    }
+    size_t need = DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
+    if (need > kStaticScratchBytes) {
+        return Fail(TSA_UNSUPPORTED,
+            "tsa_att_decode_static: nSeq %d x maxCtx %d x %d heads needs %zu bytes of chunk partials, the built-in scratch holds %zu; "
+            "use tsa_att_decode with a caller workspace",
+            nSeq, maxCtx, headCount, need, kStaticScratchBytes);
+    }
+    void *scratch = nullptr;
+    rc = StaticScratchAddress(&scratch);
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    (void)statusWord;
+    TDecodeParams p;
+    p.Seqs = seqs;
+    p.CtxLens = ctxLens;
+    p.NSeq = nSeq;
+    p.HeadCount = headCount;
+    p.Window = window;
+    p.ScaleDtype = cfg->scale_dtype;
+    p.OutDtype = cfg->out_dtype;
+    p.Slope = alibiSlope;
+    p.DotScale = HostAttDotScale(cfg->head_dim);
+    p.QVecScale = cfg->qk_vec_scale;
+    p.Q = P2D<int8_t>(q);
+    p.QScale = P2D<float>(qScale);
+    p.Out = P2D<char>(out);
+    p.Partial = (float *)scratch;
+    return LaunchDecode(cfg, p, maxCtx, (cudaStream_t)stream);
 }

@@ -222,3 +222,12 @@ class KVCache:
                                p2d(q), p2d(q_scale), window, slope, p2d(out), self.heads,
                                _ptr(self.workspace), self.workspace.numel(), _ptr(status), _stream()))
         return out
+
+    def decode_static(self, q, q_scale, window, slope, out=None, status=None):
+        """The same step through tsa_att_decode_static: no workspace, the library's built-in scratch array."""
+        if out is None:
+            out = torch.empty((self.n_seq, self.heads * self.head_dim), dtype=self.out_dtype, device=q.device)
+        check(abi.lib().tsa_att_decode_static(ctypes.byref(self.cfg), _ptr(self.seqs), _ptr(self.ctx_lens), self.n_seq,
+                                              self.max_ctx, p2d(q), p2d(q_scale), window, slope, p2d(out), self.heads,
+                                              _ptr(status), _stream()))
+        return out
