@@ -29,17 +29,19 @@ __device__ __forceinline__ void MbarExpectTx(uint64_t *bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
 }
+// upper bound, in nanoseconds, for which one try_wait may keep the thread suspended before it returns false
+constexpr uint32_t kTryWaitHintNs = 200000;
 __device__ __forceinline__ bool MbarTryWait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(SmemAddr(bar)), "r"(parity)
+        : "r"(SmemAddr(bar)), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return ok != 0;
 }

@@ -70,7 +70,16 @@ __device__ __forceinline__ uint32_t PackE4M3x2(float lo, float hi)
 }
 __device__ __forceinline__ uint32_t PackE4M3x4(float a, float b, float c, float d)
 {
-    return PackE4M3x2(a, b) | (PackE4M3x2(c, d) << 16);
+    uint32_t r;
+    asm("{\n\t"
+        ".reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t"
+        "}"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+    return r;
 }
 __device__ __forceinline__ float2 UnpackE4M3x2(uint32_t pair)
 {
