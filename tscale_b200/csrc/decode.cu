@@ -17,9 +17,7 @@
 
 namespace tsa {
 
-constexpr int DEC_CHUNK = 256;  // tokens per CTA
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_UNROLL = 4;   // tokens in flight per lane (4 x 16 B K + 4 x 16 B V)
 
 struct TDecodeParams {
     const tsa_kv_seq *Seqs;
@@ -35,8 +33,11 @@ struct TDecodeParams {
     P2D<int8_t> Q;
     P2D<float> QScale;
     P2D<char> Out;
-    float *Partial;  // [nSeq][maxChunks][H][D + 4]
-    int MaxChunks;
+    float *Partial;  // [chunk slot][H][D + 4]
+    int *Plan;       // workspace header: Plan[0] = tokens per chunk, Plan[1 + s] = first chunk slot of sequence s
+    int TargetCtas;  // chunk slots the keys of all sequences are spread over
+    int *Status;     // device status word (may be null)
+    int MaxSlots;    // TargetCtas + nSeq
 };
 
 __device__ __forceinline__ float LoadScale(const void *base, size_t idx, int dt)
@@ -56,42 +57,157 @@ __device__ __forceinline__ void KeyRange(int ctxLen, int window, int *j0, int *j
     }
 }
 
-template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32) DecodePartialKernel(TDecodeParams p)
+constexpr int DEC_MIN_CHUNK = 64;
+
+__device__ __forceinline__ int SeqKeys(const int *ctxLens, int s, int window)
+{
+    int ctxLen = ctxLens[s];
+    if (ctxLen <= 0) {
+        return 0;
+    }
+    int j0, j1;
+    KeyRange(ctxLen, window, &j0, &j1);
+    return j1 - j0;
+}
+
+// Balanced plan: all keys of all sequences are cut into chunks of (nearly) the same size C = total / TargetCtas, so
+// that every CTA streams the same number of bytes whatever the mix of context lengths.  Chunk slots are numbered
+// sequence by sequence.  Every CTA derives the plan from ctxLens itself (a block-wide sum and scan); CTA 0 also
+// writes it to the workspace header for the merge kernel.  Returns false if this CTA has no chunk.
+// barrier of the DEC_WARPS * 32 planning threads (the producer warp does not take part)
+__device__ __forceinline__ void PlanSync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory");
+}
+
+__device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBeg, int *pEnd)
+{
+    __shared__ int red[DEC_WARPS];
+    __shared__ int sliceBase[DEC_WARPS * 32 + 1];
+    __shared__ int found[3];
+    const int tid = threadIdx.x, nThreads = DEC_WARPS * 32;
+    // total number of keys
+    int sum = 0;
+    for (int s = tid; s < p.NSeq; s += nThreads) {
+        sum += SeqKeys(p.CtxLens, s, p.Window);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    }
+    if ((tid & 31) == 0) {
+        red[tid >> 5] = sum;
+    }
+    PlanSync();
+    int total = 0;
+    for (int w = 0; w < DEC_WARPS; ++w) {
+        total += red[w];
+    }
+    int chunk = (total + p.TargetCtas - 1) / p.TargetCtas;
+    chunk = max((chunk + 7) & ~7, DEC_MIN_CHUNK);
+    // chunk slots per contiguous slice of sequences, then an exclusive scan over the slices
+    const int per = (p.NSeq + nThreads - 1) / nThreads;
+    const int s0 = tid * per, s1 = min(s0 + per, p.NSeq);
+    int mine = 0;
+    for (int s = s0; s < s1; ++s) {
+        mine += (SeqKeys(p.CtxLens, s, p.Window) + chunk - 1) / chunk;
+    }
+    sliceBase[tid + 1] = mine;
+    if (tid == 0) {
+        sliceBase[0] = 0;
+        found[0] = -1;
+    }
+    PlanSync();
+    if (tid == 0) {
+        for (int i = 1; i <= nThreads; ++i) {
+            sliceBase[i] += sliceBase[i - 1];
+        }
+    }
+    PlanSync();
+    int base = sliceBase[tid];
+    const bool writePlan = blockIdx.x == 0;
+    if (writePlan && tid == 0) {
+        p.Plan[0] = chunk;
+    }
+    for (int s = s0; s < s1; ++s) {
+        int keys = SeqKeys(p.CtxLens, s, p.Window);
+        int n = (keys + chunk - 1) / chunk;
+        if (writePlan) {
+            p.Plan[1 + s] = base;
+        }
+        if (slot >= base && slot < base + n) {
+            int ctxLen = p.CtxLens[s];
+            int j0, j1;
+            KeyRange(ctxLen, p.Window, &j0, &j1);
+            found[0] = s;
+            found[1] = j0 + (slot - base) * chunk;
+            found[2] = min(found[1] + chunk, j1);
+        }
+        base += n;
+    }
+    if (writePlan && tid == nThreads - 1) {
+        p.Plan[1 + p.NSeq] = sliceBase[nThreads];
+    }
+    PlanSync();
+    *pSeq = found[0];
+    *pBeg = found[1];
+    *pEnd = found[2];
+    return found[0] >= 0;
+}
+
+template <bool F16>
+struct TScaleOf {
+    typedef __half T;
+};
+template <>
+struct TScaleOf<false> {
+    typedef float T;
+};
+__device__ __forceinline__ float LoadScaleT(const __half *p) { return __half2float(__ldg(p)); }
+__device__ __forceinline__ float LoadScaleT(const float *p) { return __ldg(p); }
+// sum of four (unsigned byte of a) x (signed byte of b) products, plus c
+__device__ __forceinline__ int Dp4aUS(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// One CTA = one chunk slot of the balanced plan, four warps, all heads.  Each lane keeps DEC_UNROLL tokens of K and
+// V (16 bytes each) in flight; four such CTAs are resident per SM.
+template <int D, int DEC_UNROLL, bool SCALE_F16>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecodeParams p)
 {
     constexpr int LPH = D / 16;       // lanes per head
     constexpr int HPW = 32 / LPH;     // heads per warp-wide load
-    int seq = blockIdx.y;
-    int chunk = blockIdx.x;
-    int ctxLen = p.CtxLens[seq];
-    if (ctxLen <= 0) {
+    const int chunk = blockIdx.x;     // chunk slot
+    int seq, cBeg, cEnd;
+    if (!DecodePlan(p, chunk, &seq, &cBeg, &cEnd)) {
         return;
     }
-    int j0, j1;
-    KeyRange(ctxLen, p.Window, &j0, &j1);
-    int cBeg = j0 + chunk * DEC_CHUNK;
-    int cEnd = min(cBeg + DEC_CHUNK, j1);
-    if (cBeg >= cEnd) {
-        return;
-    }
-    int cur = ctxLen - 1;
-    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int sub = lane % LPH;             // 16-byte slice inside the head
-    int H = p.HeadCount;
-    size_t rowBytes = (size_t)H * D;
-    tsa_kv_seq sq = p.Seqs[seq];
-    const int8_t *kBase = (const int8_t *)sq.k;
-    const int8_t *vBase = (const int8_t *)sq.v;
+    const int ctxLen = p.CtxLens[seq];
+    const int cur = ctxLen - 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPH;             // 16-byte slice inside the head
+    const int H = p.HeadCount;
+    const int rowInt4 = H * D / 16;          // int4 words per token row
+    const tsa_kv_seq sq = p.Seqs[seq];
+    typedef typename TScaleOf<SCALE_F16>::T TScale;
 
-    int headGroups = (H + HPW - 1) / HPW;
+    const int headGroups = (H + HPW - 1) / HPW;
     for (int hg = warp; hg < headGroups; hg += DEC_WARPS) {
-        int head = hg * HPW + lane / LPH;
-        bool headOk = head < H;
-        int headC = headOk ? head : H - 1;
-        size_t colOff = (size_t)headC * D + sub * 16;
-        int4 qv = *reinterpret_cast<const int4 *>(p.Q.Row(seq) + colOff);
-        float qs = p.QScale.Valid() ? p.QScale.Row(seq)[headC] : p.QVecScale;
-        float logitMult = p.DotScale * qs;
+        const int head = hg * HPW + lane / LPH;
+        const bool headOk = head < H;
+        const int headC = headOk ? head : H - 1;
+        const int colOff = headC * D + sub * 16;
+        const int4 qv = *reinterpret_cast<const int4 *>(p.Q.Row(seq) + colOff);
+        const float qs = p.QScale.Valid() ? p.QScale.Row(seq)[headC] : p.QVecScale;
+        const float logitMult = p.DotScale * qs;
+        // running pointers: one add per token instead of a 64-bit multiply
+        const int4 *kp = reinterpret_cast<const int4 *>((const int8_t *)sq.k + (size_t)cBeg * H * D + colOff);
+        const int4 *vp = reinterpret_cast<const int4 *>((const int8_t *)sq.v + (size_t)cBeg * H * D + colOff);
+        const TScale *ksp = (const TScale *)sq.kScale + (size_t)cBeg * H + headC;
+        const TScale *vsp = (const TScale *)sq.vScale + (size_t)cBeg * H + headC;
 
         float m = -1e30f, l = 0;
         float acc[16];
@@ -102,14 +218,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) DecodePartialKernel(TDecodePar
         for (int tBase = cBeg; tBase < cEnd; tBase += DEC_UNROLL) {
             int4 kv[DEC_UNROLL], vv[DEC_UNROLL];
             float ks[DEC_UNROLL], vs[DEC_UNROLL];
+            const int cnt = cEnd - tBase; // tokens left, >= 1
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
-                int t = min(tBase + u, cEnd - 1);
-                kv[u] = __ldg(reinterpret_cast<const int4 *>(kBase + (size_t)t * rowBytes + colOff));
-                vv[u] = __ldg(reinterpret_cast<const int4 *>(vBase + (size_t)t * rowBytes + colOff));
-                ks[u] = LoadScale(sq.kScale, (size_t)t * H + headC, p.ScaleDtype);
-                vs[u] = LoadScale(sq.vScale, (size_t)t * H + headC, p.ScaleDtype);
+                const int tt = u < cnt ? u : cnt - 1;
+                kv[u] = __ldg(kp + tt * rowInt4);
+                vv[u] = __ldg(vp + tt * rowInt4);
+                ks[u] = LoadScaleT(ksp + tt * H);
+                vs[u] = LoadScaleT(vsp + tt * H);
             }
+            kp += DEC_UNROLL * rowInt4;
+            vp += DEC_UNROLL * rowInt4;
+            ksp += DEC_UNROLL * H;
+            vsp += DEC_UNROLL * H;
             float z[DEC_UNROLL];
             float cm = m;
 #pragma unroll
@@ -122,37 +243,38 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) DecodePartialKernel(TDecodePar
                 for (int o = LPH / 2; o > 0; o >>= 1) {
                     dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 }
-                int t = tBase + u;
                 // same association as the reference: ((dot * kScale) * attDotScale) * qScale - slope * dist
-                float zz = (float)dot * ks[u] * logitMult - p.Slope * (float)(cur - t);
-                z[u] = (t < cEnd) ? zz : -1e30f;
+                const float zz = (float)dot * ks[u] * logitMult - p.Slope * (float)(cur - (tBase + u));
+                z[u] = (u < cnt) ? zz : -1e30f;
                 cm = fmaxf(cm, z[u]);
             }
-            float corr = exp2f(m - cm);
-            m = cm;
-            l *= corr;
+            if (cm != m) {
+                const float corr = exp2f(m - cm);
+                m = cm;
+                l *= corr;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                acc[i] *= corr;
+                for (int i = 0; i < 16; ++i) {
+                    acc[i] *= corr;
+                }
             }
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
-                float w = exp2f(z[u] - m);
+                const float w = exp2f(z[u] - m);
                 l += w;
-                float wv = w * vs[u];
+                const float wv = w * vs[u];
                 const int words[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) {
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        int s8 = (int)(int8_t)(words[wi] >> (8 * b));
+                        const int s8 = (int)(int8_t)(words[wi] >> (8 * b));
                         acc[wi * 4 + b] = fmaf(wv, (float)s8, acc[wi * 4 + b]);
                     }
                 }
             }
         }
         if (headOk) {
-            float *dst = p.Partial + (((size_t)seq * p.MaxChunks + chunk) * H + head) * (D + 4);
+            float *dst = p.Partial + ((size_t)chunk * H + head) * (D + 4);
             if (sub == 0) {
                 dst[D] = m;
                 dst[D + 1] = l;
@@ -174,10 +296,9 @@ __global__ void __launch_bounds__(D) DecodeCombineKernel(TDecodeParams p)
     int ctxLen = p.CtxLens[seq];
     float res = 0;
     if (ctxLen > 0) {
-        int j0, j1;
-        KeyRange(ctxLen, p.Window, &j0, &j1);
-        int chunks = (j1 - j0 + DEC_CHUNK - 1) / DEC_CHUNK;
-        const float *base = p.Partial + ((size_t)seq * p.MaxChunks * p.HeadCount + head) * (D + 4);
+        const int first = p.Plan[1 + seq];
+        const int chunks = p.Plan[2 + seq] - first;
+        const float *base = p.Partial + ((size_t)first * p.HeadCount + head) * (D + 4);
         size_t cstride = (size_t)p.HeadCount * (D + 4);
         float m = 0; // the sink has logit 0 (softMax.Add(0), cpu_infer.cpp:444)
         for (int c = 0; c < chunks; ++c) {
@@ -222,26 +343,58 @@ __global__ void KvAppendKernel(const tsa_kv_seq *seqs, int *ctxLens, int nSeq, i
     }
 }
 
-static int MaxChunksFor(int maxCtx)
+constexpr int DEC_MAX_TARGET_CTAS = 1024; // workspace is sized for this many chunk slots plus one per sequence
+
+static size_t DecodeHeaderBytes(int nSeq)
 {
-    return (maxCtx + DEC_CHUNK - 1) / DEC_CHUNK + 1;
+    return ((size_t)(nSeq + 2) * sizeof(int) + 255) / 256 * 256;
 }
 
 size_t DecodeWorkspaceBytes(int headDim, int nSeq, int headCount, int maxCtx)
 {
-    return (size_t)nSeq * MaxChunksFor(maxCtx) * headCount * (headDim + 4) * sizeof(float);
+    (void)maxCtx;
+    return DecodeHeaderBytes(nSeq) + (size_t)(DEC_MAX_TARGET_CTAS + nSeq) * headCount * (headDim + 4) * sizeof(float);
 }
 
 int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStream_t stream)
 {
-    p.MaxChunks = MaxChunksFor(maxCtx);
-    dim3 grid(p.MaxChunks, p.NSeq);
-    dim3 gridC(p.HeadCount, p.NSeq);
+    (void)maxCtx;
+    int dev = 0, sms = 0;
+    int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc == TSA_OK) {
+        rc = CheckCuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+    }
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    const bool f16 = cfg->scale_dtype == TSA_F16;
+    const void *kern = nullptr;
     if (cfg->head_dim == 128) {
-        DecodePartialKernel<128><<<grid, DEC_WARPS * 32, 0, stream>>>(p);
+        kern = f16 ? (const void *)DecodePartialKernel<128, 8, true> : (const void *)DecodePartialKernel<128, 8, false>;
+    } else {
+        kern = f16 ? (const void *)DecodePartialKernel<64, 8, true> : (const void *)DecodePartialKernel<64, 8, false>;
+    }
+    // one full wave of equal chunks: as many chunk slots as CTAs are resident at once
+    int perSm = 0;
+    rc = CheckCuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kern, DEC_WARPS * 32, 0), "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    perSm = perSm < 1 ? 1 : perSm;
+    p.TargetCtas = sms * perSm < DEC_MAX_TARGET_CTAS ? sms * perSm : DEC_MAX_TARGET_CTAS;
+    p.MaxSlots = p.TargetCtas + p.NSeq;
+    p.Plan = (int *)p.Partial;
+    p.Partial = (float *)((char *)p.Partial + DecodeHeaderBytes(p.NSeq));
+    dim3 grid(p.MaxSlots);
+    dim3 gridC(p.HeadCount, p.NSeq);
+    void *args[] = {&p};
+    rc = CheckCuda(cudaLaunchKernel(kern, grid, dim3(DEC_WARPS * 32), args, 0, stream), "decode launch");
+    if (rc != TSA_OK) {
+        return rc;
+    }
+    if (cfg->head_dim == 128) {
         DecodeCombineKernel<128><<<gridC, 128, 0, stream>>>(p);
     } else {
-        DecodePartialKernel<64><<<grid, DEC_WARPS * 32, 0, stream>>>(p);
         DecodeCombineKernel<64><<<gridC, 64, 0, stream>>>(p);
     }
     return CheckCuda(cudaGetLastError(), "tsa_att_decode launch");
@@ -290,8 +443,8 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_decode(const tsa_d
     size_t need = DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
     TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_decode: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
     TSA_REQUIRE((uintptr_t)workspace % 16 == 0, "tsa_att_decode: workspace must be 16-byte aligned");
-    (void)statusWord;
     TDecodeParams p;
+    p.Status = statusWord;
     p.Seqs = seqs;
     p.CtxLens = ctxLens;
     p.NSeq = nSeq;
@@ -407,8 +560,8 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_decode_static(cons
     if (rc != TSA_OK) {
         return rc;
     }
-    (void)statusWord;
     TDecodeParams p;
+    p.Status = statusWord;
     p.Seqs = seqs;
     p.CtxLens = ctxLens;
     p.NSeq = nSeq;
