@@ -217,11 +217,16 @@ def main():
             item["d_out"] = (torch.randn((length, hd), generator=gen, device=dev, dtype=torch.float32) * 1e-2).to(grad_dtype)
         layers.append(item)
     workspace = torch.empty(1 << 20, dtype=torch.uint8, device=dev)
-    bwd_ws = torch.empty(max(1, heads * ((length * 4 + 255) // 256 * 256)), dtype=torch.uint8, device=dev) if w["bwd"] else None
+    bwd_ws = None
+    if w["bwd"]:
+        from tscale_b200 import abi
+        import ctypes
+        bwd_ws = torch.empty(max(1, abi.lib().tsa_att_bwd_workspace_bytes(ctypes.byref(cfg), heads, length)), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     gathered = None
+    pending = []
     if args.gather and world > 1:
-        gathered = torch.empty((world, length, hd), dtype=torch.bfloat16, device=dev)
+        gathered = [torch.empty((world, length, hd), dtype=torch.bfloat16, device=dev) for _ in layers]
 
     launches = [0]
     dom = max(range(len(layers)), key=lambda i: layer_flops(w, layers[i]["window"]))  # dominant layer
@@ -244,11 +249,14 @@ def main():
                         status=status)
             launches[0] += 3  # dScale + dQ kernel + dK/dV kernel
         if gathered is not None:
-            dist.all_gather_into_tensor(gathered.view(-1), item["out"].view(-1))
+            # NCCL runs the gather on its own stream: the next layer's kernels overlap with it
+            pending.append(dist.all_gather_into_tensor(gathered[len(pending) % len(gathered)].view(-1), item["out"].view(-1), async_op=True))
 
     def step(record=None):
         for i, item in enumerate(layers):
             run_layer(item, record if i == dom else None)
+        while pending:
+            pending.pop().wait()
 
     def barrier():
         torch.cuda.synchronize()

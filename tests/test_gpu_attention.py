@@ -170,12 +170,22 @@ def test_bwd_against_oracle(window, slope, d):
     cfg.grad_dtype = 4  # f32
     out_t = torch.from_numpy(ref["out"]).to(_dev())
     lse_t = torch.from_numpy(ref["lse"]).to(_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
     dq, dk, dv = ops.att_bwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], torch.from_numpy(d_out).to(_dev()), out_t, lse_t,
-                             mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"])
+                             mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status)
     torch.cuda.synchronize()
+    assert int(status.item()) == 0
     for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
         r = util.rel_l2(util.to_np(got), gref[name])
         assert r < util.GRAD_REL_L2, (name, r)
+    # the SIMT kernels (every head size, the path odd shapes take) against the same oracle
+    cfg.flags |= 1
+    dq, dk, dv = ops.att_bwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], torch.from_numpy(d_out).to(_dev()), out_t, lse_t,
+                             mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status)
+    torch.cuda.synchronize()
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        r = util.rel_l2(util.to_np(got), gref[name])
+        assert r < util.GRAD_REL_L2, ("generic " + name, r)
 
 
 @pytest.mark.parametrize("d", [64, 128])

@@ -25,9 +25,7 @@
 // Every barrier wait is bounded; when one runs out the kernel records a code in *statusWord, drains its
 // outstanding copies, frees its tensor memory and returns.
 #include "att_internal.cuh"
-#include "sm100_ptx.cuh"
-#include <cuda.h>
-#include <type_traits>
+#include "att_sm100_common.cuh"
 
 namespace tsa {
 
@@ -41,7 +39,6 @@ constexpr int TILE_M = 128;
 constexpr int TILE_N = 128;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O_COL = 128;
-constexpr long long WAIT_CYCLES = 1ll << 31; // about a second
 
 struct TFwdParams {
     int HeadCount;
@@ -86,156 +83,6 @@ struct TFwdMisc {
     uint64_t BarP;           // softmax -> control: P(it) written, 256 arrivals
     uint32_t TmemBase;
 };
-
-__device__ __forceinline__ bool WaitBar(uint64_t *bar, uint32_t parity)
-{
-    long long t0 = clock64();
-    for (;;) {
-        if (MbarWaitBounded(bar, parity, 64)) {
-            return true;
-        }
-        if (clock64() - t0 > WAIT_CYCLES) {
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void MbarArrive(uint64_t *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
-}
-
-// named barrier over `count` threads with an OR reduction of a predicate
-__device__ __forceinline__ bool BarRedOr(int id, int count, bool flag)
-{
-    uint32_t res;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %3, 0;\n\t"
-        "bar.red.or.pred p, %1, %2, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(res)
-        : "r"(id), "r"(count), "r"((uint32_t)flag)
-        : "memory");
-    return res != 0;
-}
-__device__ __forceinline__ void BarSync(int id, int count)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-// iterator over the key tiles of a 128-row query tile: rounds of the two 64-row blocks' span groups
-struct TTileIter {
-    const tsa_span_group *G0, *G1; // first group of each block (null: block absent)
-    int N0, N1;
-    int KeyRows;
-    int Round, J0, Hi;
-    bool Valid;
-
-    __device__ void LoadRound()
-    {
-        int rounds = max(N0, N1);
-        for (; Round < rounds; ++Round) {
-            int lo = 0x7fffffff, hi = -1;
-            if (Round < N0) {
-                lo = min(lo, G0[Round].Start);
-                hi = max(hi, G0[Round].Finish);
-            }
-            if (Round < N1) {
-                lo = min(lo, G1[Round].Start);
-                hi = max(hi, G1[Round].Finish);
-            }
-            lo = max(lo, 0) & ~(TILE_N - 1);
-            hi = min(hi, KeyRows - 1) & ~(TILE_N - 1);
-            if (lo <= hi) {
-                J0 = lo;
-                Hi = hi;
-                Valid = true;
-                return;
-            }
-        }
-        Valid = false;
-    }
-    __device__ void Init(const tsa_span_group *spans, const int *spanPtr, int lenAttTiles, int qTile, int keyRows)
-    {
-        int b0 = qTile * 2, b1 = qTile * 2 + 1;
-        G0 = G1 = nullptr;
-        N0 = N1 = 0;
-        if (b0 < lenAttTiles) {
-            int a = spanPtr[b0], b = spanPtr[b0 + 1];
-            G0 = spans + a;
-            N0 = b - a;
-        }
-        if (b1 < lenAttTiles) {
-            int a = spanPtr[b1], b = spanPtr[b1 + 1];
-            G1 = spans + a;
-            N1 = b - a;
-        }
-        KeyRows = keyRows;
-        Round = 0;
-        Valid = false;
-        LoadRound();
-    }
-    __device__ void Advance()
-    {
-        J0 += TILE_N;
-        if (J0 > Hi) {
-            ++Round;
-            LoadRound();
-        }
-    }
-};
-
-template <int N>
-__device__ __forceinline__ void TmemStN(uint32_t taddr, const uint32_t *r);
-template <>
-__device__ __forceinline__ void TmemStN<8>(uint32_t taddr, const uint32_t *r)
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 :
-                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-
-__device__ __forceinline__ float FastExp2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float Max3(float a, float b, float c)
-{
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
-__device__ __forceinline__ uint32_t PackHalf2(float a, float b)
-{
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-// residual of a pair after e4m3 rounding, again as an e4m3 pair
-__device__ __forceinline__ uint32_t ResidualE4M3x2(float a, float b, uint32_t hiPair)
-{
-    uint32_t hb;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hb) : "h"((uint16_t)hiPair));
-    uint32_t ef = PackHalf2(a, b);
-    uint32_t diff;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(diff) : "r"(ef), "r"(hb));
-    uint16_t r;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(diff));
-    return r;
-}
-
-// exact int32 -> float for |x| < 2^22 without the conversion pipe: bits(1.5 * 2^23 + x) - 1.5 * 2^23
-__device__ __forceinline__ float2 IntPairToFloat(uint32_t a, uint32_t b)
-{
-    float2 t = make_float2(__uint_as_float(a + 0x4B400000u), __uint_as_float(b + 0x4B400000u));
-    return __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
-}
 
 // Thread layout: warps 0-7 are softmax warps, two threads per query row: thread (half, row) with half = tid / 128
 // owns columns [64 * half, 64 * half + 64) of the row's scores and columns [half * D/2, (half + 1) * D/2) of its
@@ -832,42 +679,6 @@ __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_con
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-typedef CUresult (*TEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static TEncodeTiled GetEncodeTiled()
-{
-    static TEncodeTiled fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
-            fn = (TEncodeTiled)ptr;
-        }
-    }
-    return fn;
-}
-
-// rows x (xsize bytes) matrix of bytes, box = 128 rows x headDim bytes, swizzle = headDim bytes
-static int MakeTileMap(CUtensorMap *map, tsa_ptr2d a, int headDim, const char *what)
-{
-    TEncodeTiled enc = GetEncodeTiled();
-    if (!enc) {
-        return Fail(TSA_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)a.xsize, (cuuint64_t)a.ysize};
-    cuuint64_t strides[1] = {(cuuint64_t)a.stride_bytes};
-    cuuint32_t box[2] = {(cuuint32_t)headDim, 128};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.data, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        headDim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        return Fail(TSA_CUDA_ERROR, "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
-    }
-    return TSA_OK;
-}
-
 static bool TmaCompatible(tsa_ptr2d a)
 {
     return a.data && ((uintptr_t)a.data % 16 == 0) && (a.stride_bytes % 16 == 0) && a.xsize > 0 && a.ysize > 0;

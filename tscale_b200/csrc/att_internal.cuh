@@ -45,4 +45,11 @@ size_t Sm100FwdWorkspaceBytes(int headCount);
 int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v,
     int lenAttTiles, int keyRows, void *workspace, int *statusWord, cudaStream_t stream);
 
+// tcgen05 backward (att_bwd_sm100.cu): two launches of one kernel (dQ pass, dK/dV pass) after widening the stored
+// vectors to bf16 in the workspace
+bool Sm100BwdSupports(const tsa_att_cfg *cfg, int headCount);
+size_t Sm100BwdWorkspaceBytes(int headCount, int headDim, int rows);
+int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v, tsa_ptr2d dOut,
+    int lenAttTiles, void *workspace, int *statusWord, cudaStream_t stream);
+
 } // namespace tsa

@@ -196,6 +196,31 @@ __device__ __forceinline__ void MmaF8TS(uint32_t dTmem, uint32_t aTmem, uint64_t
         : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// bf16 operands, f32 accumulation
+__device__ __forceinline__ void MmaF16SS(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void MmaF16TS(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // arrive on the mbarrier when all MMAs issued so far by this thread have completed
 __device__ __forceinline__ void MmaCommit(uint64_t *bar)
 {

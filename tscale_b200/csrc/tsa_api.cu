@@ -155,7 +155,12 @@ extern "C" __attribute__((visibility("default"))) size_t tsa_att_bwd_workspace_b
         return 0;
     }
     size_t rowBytes = ((size_t)len * sizeof(float) + 255) / 256 * 256;
-    return rowBytes * headCount; // dScale plane when the caller does not supply one
+    size_t bytes = rowBytes * headCount; // dScale plane when the caller does not supply one
+    if (cfg && Sm100BwdSupports(cfg, headCount)) {
+        int rows = (len + TSA_ATT_GROUP - 1) / TSA_ATT_GROUP * TSA_ATT_GROUP;
+        bytes += Sm100BwdWorkspaceBytes(headCount, cfg->head_dim_qk, rows); // bf16 copies of Q, K, V, dOut
+    }
+    return bytes;
 }
 
 extern "C" __attribute__((visibility("default"))) int tsa_att_bwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
@@ -168,7 +173,6 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_bwd(const tsa_att_
     tsa_ptr2d dQK, tsa_ptr2d dQV, tsa_ptr2d dV, int headCount, int lenAttTiles,
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
 {
-    (void)statusWord;
     TGenParams p;
     int rc = FillCommon("tsa_att_bwd", cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, headCount, lenAttTiles, &p);
     if (rc != TSA_OK) {
@@ -187,14 +191,21 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_bwd(const tsa_att_
         return TSA_OK;
     }
     cudaStream_t s = (cudaStream_t)stream;
+    const bool tensorPath = Sm100BwdSupports(cfg, headCount) && (uintptr_t)dQK.data % 16 == 0 && dQK.stride_bytes % 16 == 0 &&
+        (uintptr_t)dQV.data % 16 == 0 && dQV.stride_bytes % 16 == 0 && (uintptr_t)dV.data % 16 == 0 && dV.stride_bytes % 16 == 0;
+    const size_t dsRowBytes = ((size_t)len * sizeof(float) + 255) / 256 * 256;
+    const size_t dsBytes = dsRowBytes * headCount;
+    const size_t need = dsBytes + (tensorPath ? Sm100BwdWorkspaceBytes(headCount, cfg->head_dim_qk, len) : 0);
+    if (tensorPath || !dScale.data) {
+        TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_bwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
+        TSA_REQUIRE((uintptr_t)workspace % 256 == 0, "tsa_att_bwd: workspace must be 256-byte aligned");
+    }
     tsa_ptr2d ds = dScale;
     if (!ds.data) {
         TSA_REQUIRE(out.data && IsFloatType(cfg->out_dtype) && out.ysize >= len && out.xsize >= headCount * cfg->head_dim_v,
             "tsa_att_bwd: without dScale the forward result `out` is required");
-        size_t need = tsa_att_bwd_workspace_bytes(cfg, headCount, len);
-        TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_bwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
         ds.data = workspace;
-        ds.stride_bytes = (int)(need / headCount);
+        ds.stride_bytes = (int)dsRowBytes;
         ds.xsize = len;
         ds.ysize = headCount;
         rc = LaunchDScale(cfg->out_dtype, cfg->grad_dtype, out, dOut, ds, headCount, cfg->head_dim_v, len, s);
@@ -213,6 +224,9 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_bwd(const tsa_att_
     p.DV = P2D<char>(dV);
     p.RevSpans = revAttSpans;
     p.RevSpanPtr = revAttSpanPtr;
+    if (tensorPath) {
+        return LaunchSm100Bwd(cfg, p, qk, qv, v, dOut, lenAttTiles, (char *)workspace + dsBytes, statusWord, s);
+    }
     return LaunchGenericBwd(p, s);
 }
 
