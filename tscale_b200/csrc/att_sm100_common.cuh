@@ -26,6 +26,30 @@ __device__ __forceinline__ bool WaitBar(uint64_t *bar, uint32_t parity)
     }
 }
 
+// the same with an abort flag of the CTA: returns false as soon as another thread has given up.
+// FAST polls without a suspend hint (the waiting thread's wake-up latency is on the critical path).
+template <bool FAST = false>
+__device__ __forceinline__ bool WaitBarA(uint64_t *bar, uint32_t parity, const int *abortFlag)
+{
+    if (FAST ? MbarTryWaitFast(bar, parity) : MbarTryWait(bar, parity)) {
+        return true;
+    }
+    long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            if (FAST ? MbarTryWaitFast(bar, parity) : MbarTryWait(bar, parity)) {
+                return true;
+            }
+        }
+        if (*(const volatile int *)abortFlag) {
+            return false;
+        }
+        if (clock64() - t0 > WAIT_CYCLES) {
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void MbarArrive(uint64_t *bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");

@@ -29,6 +29,37 @@ __device__ __forceinline__ void MbarExpectTx(uint64_t *bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
 }
+// adds to the transaction count of the current phase without arriving (the arrival follows separately)
+__device__ __forceinline__ void MbarExpectTxOnly(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+}
+// one poll with the default (short) suspend time: for the thread whose wake-up latency is on the critical path
+__device__ __forceinline__ bool MbarTryWaitFast(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(SmemAddr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// register reallocation between the warpgroups of a CTA (all four warps of the warpgroup execute it)
+template <int N>
+__device__ __forceinline__ void RegDealloc()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void RegAlloc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
 // upper bound, in nanoseconds, for which one try_wait may keep the thread suspended before it returns false
 constexpr uint32_t kTryWaitHintNs = 200000;
 __device__ __forceinline__ bool MbarTryWait(uint64_t *bar, uint32_t parity)
