@@ -64,6 +64,20 @@ def test_dscale():
     assert np.allclose(got, ref, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("heads,d", [(6, 64), (3, 128), (5, 32)])
+def test_dscale_16bit_vector_path(dt, heads, d):
+    """16-bit out / dOut take the 16-byte-load kernel; the oracle sees the same rounded values."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(12)
+    out_t = torch.from_numpy(rng.standard_normal((333, heads * d)).astype(np.float32)).to(dt)
+    d_out_t = torch.from_numpy(rng.standard_normal((333, heads * d)).astype(np.float32)).to(dt)
+    ref = O.dscale(out_t.float().numpy(), d_out_t.float().numpy(), heads)
+    got = ops.calc_dscale(out_t.to(DEV), d_out_t.to(DEV), heads, d).cpu().numpy()
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-4)
+
+
 def _decode_case(seed, ctx_lens, heads, d, window, slope, steps=2, scale_dtype=torch.float16):
     from tscale_b200 import ops
     rng = np.random.default_rng(seed)

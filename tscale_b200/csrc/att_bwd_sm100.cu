@@ -542,7 +542,11 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qk), rows, cols, qb);
     ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qv), rows, cols, kb);
     ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->v_dtype, P2D<char>(v), rows, cols, vb);
-    ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->grad_dtype, P2D<char>(dOut), rows, cols, dob);
+    // dO that already is bf16 in a TMA-compatible layout is read where it lies
+    const bool dOutInPlace = cfg->grad_dtype == TSA_BF16 && (uintptr_t)dOut.data % 16 == 0 && dOut.stride_bytes % 16 == 0 && dOut.xsize >= cols;
+    if (!dOutInPlace) {
+        ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->grad_dtype, P2D<char>(dOut), rows, cols, dob);
+    }
     int rc = CheckCuda(cudaGetLastError(), "bf16 widening launch");
     if (rc != TSA_OK) {
         return rc;
@@ -560,7 +564,12 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
         rc = mapOf(&mv, vb, "v bf16");
     }
     if (rc == TSA_OK) {
-        rc = mapOf(&mdo, dob, "dOut bf16");
+        if (dOutInPlace) {
+            tsa_ptr2d a = {dOut.data, dOut.stride_bytes, cols, rows};
+            rc = MakeTileMapEx(&mdo, a, 2, 64, 128, "dOut bf16 (in place)");
+        } else {
+            rc = mapOf(&mdo, dob, "dOut bf16");
+        }
     }
     if (rc != TSA_OK) {
         return rc;

@@ -392,15 +392,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
 #pragma unroll
                     for (int ks = 0; ks < TILE_N / 32; ++ks) {
                         uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                        // D = 64: P is one 32-column block; D = 128: P of half h sits at S columns 64h .. 64h+15
-                        uint32_t aCol = SEP_P ? TMEM_P_COL + ks * 8 : (uint32_t)((ks >> 1) * HALF_N + (ks & 1) * 8);
+                        // D = 64: P is one 32-column block; D = 128: P of chunk ks sits at S columns 32 ks .. 32 ks + 7
+                        uint32_t aCol = SEP_P ? TMEM_P_COL + ks * 8 : (uint32_t)(ks * 32);
                         MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
                     }
                     if (withResidual) {
 #pragma unroll
                         for (int ks = 0; ks < TILE_N / 32; ++ks) {
                             uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                            uint32_t aCol = SEP_P ? TMEM_P_COL + 32 + ks * 8 : (uint32_t)((ks >> 1) * HALF_N + 16 + (ks & 1) * 8);
+                            uint32_t aCol = SEP_P ? TMEM_P_COL + 32 + ks * 8 : (uint32_t)(ks * 32 + 8);
                             MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, 1u);
                         }
                     }
@@ -518,8 +518,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
         const int colBase = half * HALF_N;
         const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int pairBar = BAR_PAIR0 + (warp & 3);
-        const uint32_t pHiCol = SEP_P ? TMEM_P_COL + half * 16 : (uint32_t)colBase;
-        const uint32_t pLoCol = SEP_P ? TMEM_P_COL + 32 + half * 16 : (uint32_t)(colBase + 16);
+        // packed weights of chunk ch: 8 columns (plus 8 for the residual); D = 128: inside the chunk's own S columns
+        auto PHiCol = [](int ch) { return SEP_P ? TMEM_P_COL + (uint32_t)ch * 8 : (uint32_t)ch * 32; };
+        auto PLoCol = [](int ch) { return SEP_P ? TMEM_P_COL + 32 + (uint32_t)ch * 8 : (uint32_t)ch * 32 + 8; };
         const float g = p.GlobalScale ? *p.GlobalScale : 1.0f;
 
         int t = 0; // tiles processed by this CTA (barrier parities, ring position)
@@ -579,19 +580,48 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                 }
                 const int stage = t % STAGES;
                 const int j0 = cur.J0;
-                const int ls = spanS - j0, lf = spanF - j0; // span in tile-local columns
-                const bool rowFull = ls <= 0 && lf >= TILE_N - 1;
-                const bool warpMasked = !__all_sync(0xffffffffu, rowFull);
-                // 32-column chunks of this thread's half that some row of the warp attends
-                const bool any0 = __any_sync(0xffffffffu, ls <= colBase + 31 && lf >= colBase && ls <= lf);
-                const bool any1 = __any_sync(0xffffffffu, ls <= colBase + 63 && lf >= colBase + 32 && ls <= lf);
                 // P carries a residual part on every tile that is not interior to all 128 rows (same rule in the MMA warp)
                 const bool tileMasked = !(cur.Round == round0 && j0 >= maxS && j0 + TILE_N - 1 <= minF);
-                // span in half-local columns, clipped so that (unsigned)(c - lsH) <= spanW  <=>  ls <= c <= lf
-                const int lsC = max(ls, colBase), lfC = min(lf, colBase + HALF_N - 1);
-                const int lsH = lsC - colBase;
-                const unsigned spanW = (lsC <= lfC) ? (unsigned)(lfC - lsC) : 0u;
-                const bool rowEmpty = lsC > lfC;
+                // The four 32-column chunks of the tile are shared between the two threads of a row.  On an interior tile
+                // thread h takes chunks h and h + 2.  On a masked tile only the chunks some row of the warp attends are
+                // computed (both warps of a pair hold the same rows, so they agree) and they are dealt out alternately,
+                // which keeps the pair balanced on window layers where the attended band covers two or three chunks.
+                int ls = 0, lf = TILE_N - 1; // the row's span in tile-local columns
+                bool warpMasked = false;
+                int chKeep = half, chAgain = half + 2; // chunk kept in registers / chunk read twice (-1: none)
+                unsigned zeroMask = 0;                 // chunks this thread fills with zero weights
+                if (tileMasked) {
+                    ls = spanS - j0;
+                    lf = spanF - j0;
+                    warpMasked = !__all_sync(0xffffffffu, ls <= 0 && lf >= TILE_N - 1);
+                    if (warpMasked) {
+                        unsigned need = 0;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            if (__any_sync(0xffffffffu, ls <= ch * 32 + 31 && lf >= ch * 32 && ls <= lf)) {
+                                need |= 1u << ch;
+                            }
+                        }
+                        chKeep = -1;
+                        chAgain = -1;
+                        int pos = 0;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            if (need & (1u << ch)) {
+                                if ((pos & 1) == half) {
+                                    if (chKeep < 0) {
+                                        chKeep = ch;
+                                    } else {
+                                        chAgain = ch;
+                                    }
+                                }
+                                ++pos;
+                            } else if ((ch & 1) == half) {
+                                zeroMask |= 1u << ch;
+                            }
+                        }
+                    }
+                }
 
                 // the staged key scales (the wait also makes the loader's shared-memory writes visible), then S(t)
                 // A thread whose wait ran out does not leave alone: it carries `failed` to the next barrier of its
@@ -601,53 +631,82 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                     giveUp(kDevTimeoutMma);
                 }
                 TcFenceAfter();
-                const float *skBuf = misc.Sk[stage] + colBase;
-                const float *svBuf = misc.Sv[stage] + colBase;
-                const float *alBuf = misc.Al + colBase;
+                const float *skBuf = misc.Sk[stage];
+                const float *svBuf = misc.Sv[stage];
+                const float *alBuf = misc.Al;
 
-                // Register budget: only 32 of the thread's 64 scores stay in registers.  Chunk 1 (columns 32-63 of the
-                // half) is read for the maximum, dropped, and read again for the weights; chunk 0 is read once and kept.
-                // S is released to the MMA warp after the second read of chunk 1, about half-way through the tile.
-                uint32_t s[32];
-                // u = S * sk (+ ALiBi, then already multiplied by the row factor), masked, left in s[]; running maximum
-                auto scaleChunk = [&](auto maskedTag, int ch, float mxIn) {
+                // Register budget: only 32 scores stay in registers.  Chunk chAgain is read for the maximum, dropped, and
+                // read again for the weights; chunk chKeep is read once and kept.  S is released to the MMA warp after the
+                // last read, about half-way through the tile.
+                float2 s[16];
+                // u = S * sk (+ ALiBi, then already multiplied by the row factor), masked, left in s[]; returns the maximum
+                auto scaleChunk = [&](auto maskedTag, int ch) {
                     constexpr bool MASKED = decltype(maskedTag)::value;
-                    float mx = mxIn;
+                    // span in chunk-local columns, clipped so that (unsigned)(c - lsH) <= spanW  <=>  ls <= col <= lf
+                    const int lsC = max(ls, ch * 32), lfC = min(lf, ch * 32 + 31);
+                    const int lsH = lsC - ch * 32;
+                    const unsigned spanW = (lsC <= lfC) ? (unsigned)(lfC - lsC) : 0u;
+                    const float4 *sk4 = reinterpret_cast<const float4 *>(skBuf + ch * 32);
+                    const float4 *al4 = reinterpret_cast<const float4 *>(alBuf + ch * 32);
+                    float mx = -INFINITY;
 #pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        const int lc = ch * 32 + c; // column inside this thread's half
-                        float2 a = QK_I8 ? IntPairToFloat(s[c], s[c + 1]) : make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-                        float2 x = __fmul2_rn(a, *reinterpret_cast<const float2 *>(skBuf + lc));
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 k4 = sk4[c >> 2];
+                        float2 x0 = s[c >> 1], x1 = s[(c >> 1) + 1];
+                        if (QK_I8) {
+                            x0 = IntPairToFloat(__float_as_uint(x0.x), __float_as_uint(x0.y));
+                            x1 = IntPairToFloat(__float_as_uint(x1.x), __float_as_uint(x1.y));
+                        }
+                        x0 = __fmul2_rn(x0, make_float2(k4.x, k4.y));
+                        x1 = __fmul2_rn(x1, make_float2(k4.z, k4.w));
                         if (HAS_ALIBI) {
-                            x = __ffma2_rn(x, rowMult2, *reinterpret_cast<const float2 *>(alBuf + lc));
+                            const float4 a4 = al4[c >> 2];
+                            x0 = __ffma2_rn(x0, rowMult2, make_float2(a4.x, a4.y));
+                            x1 = __ffma2_rn(x1, rowMult2, make_float2(a4.z, a4.w));
                         }
                         if (MASKED) {
-                            x.x = ((unsigned)(lc - lsH) <= spanW) ? x.x : -INFINITY;
-                            x.y = ((unsigned)(lc + 1 - lsH) <= spanW) ? x.y : -INFINITY;
+                            x0.x = ((unsigned)(c - lsH) <= spanW) ? x0.x : -INFINITY;
+                            x0.y = ((unsigned)(c + 1 - lsH) <= spanW) ? x0.y : -INFINITY;
+                            x1.x = ((unsigned)(c + 2 - lsH) <= spanW) ? x1.x : -INFINITY;
+                            x1.y = ((unsigned)(c + 3 - lsH) <= spanW) ? x1.y : -INFINITY;
                         }
-                        s[c] = __float_as_uint(x.x);
-                        s[c + 1] = __float_as_uint(x.y);
-                        mx = Max3(mx, x.x, x.y);
+                        s[c >> 1] = x0;
+                        s[(c >> 1) + 1] = x1;
+                        mx = Max3(mx, x0.x, x0.y);
+                        mx = Max3(mx, x1.x, x1.y);
+                    }
+                    if (MASKED && lsC > lfC) {
+                        mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
                     }
                     return mx;
                 };
                 auto loadChunk = [&](int ch) {
-                    TmemLd32(tLane + colBase + ch * 32, s);
+                    TmemLd32Pairs(tLane + ch * 32, s);
                     TmemWaitLd();
                 };
-                const bool use0 = !warpMasked || any0, use1 = !warpMasked || any1;
+                auto releaseS = [&]() {
+                    if (SEP_P) {
+                        TcFenceBefore();
+                        __syncwarp();
+                        if (lane == 0) {
+                            MbarArrive(&misc.BarSRead);
+                        }
+                    }
+                };
                 float mx = -INFINITY;
                 if (!failed) {
-                    if (use1) {
-                        loadChunk(1);
-                        mx = warpMasked ? scaleChunk(std::true_type(), 1, mx) : scaleChunk(std::false_type(), 1, mx);
+                    if (chAgain >= 0) {
+                        loadChunk(chAgain);
+                        mx = warpMasked ? scaleChunk(std::true_type(), chAgain) : scaleChunk(std::false_type(), chAgain);
                     }
-                    if (use0) {
-                        loadChunk(0);
-                        mx = warpMasked ? scaleChunk(std::true_type(), 0, mx) : scaleChunk(std::false_type(), 0, mx);
-                    }
-                    if (warpMasked && rowEmpty) {
-                        mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
+                    if (chKeep >= 0) {
+                        loadChunk(chKeep);
+                        if (chAgain < 0) {
+                            releaseS(); // nothing is read twice
+                        }
+                        mx = fmaxf(mx, warpMasked ? scaleChunk(std::true_type(), chKeep) : scaleChunk(std::false_type(), chKeep));
+                    } else {
+                        releaseS();
                     }
                 }
                 const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
@@ -691,84 +750,74 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                 lacc2.x *= alpha;
                 lacc2.y *= alpha;
                 m = newM;
-                // weights, packed e4m3; an empty row gets eoff = -inf so that every weight is 0 whatever the compare let through
-                const float eoff = rowEmpty && warpMasked ? -INFINITY : rowOff - m + 7.0f;
-                const float2 eoff2 = make_float2(eoff, eoff);
+                // weights, packed e4m3.  A row that attends nothing in a chunk gets an offset of -inf there, so every
+                // weight is 0 whatever the masking compare let through.
+                const float eoff = rowOff - m + 7.0f;
                 auto weightChunk = [&](auto residTag, int ch) {
                     constexpr bool RESID = decltype(residTag)::value;
+                    const bool chunkEmpty = warpMasked && max(ls, ch * 32) > min(lf, ch * 32 + 31);
+                    const float eo = chunkEmpty ? -INFINITY : eoff;
+                    const float2 eoff2 = make_float2(eo, eo);
+                    const float4 *sv4 = reinterpret_cast<const float4 *>(svBuf + ch * 32);
                     uint32_t pk[8], pl[8];
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
-                        float2 e[2];
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            const int lc = c + 2 * q;
-                            const float2 u = make_float2(__uint_as_float(s[lc]), __uint_as_float(s[lc + 1]));
-                            float2 tt = HAS_ALIBI ? __fadd2_rn(u, eoff2) : __ffma2_rn(u, rowMult2, eoff2);
-                            float2 w = make_float2(FastExp2(tt.x), FastExp2(tt.y));
-                            lacc2 = __fadd2_rn(lacc2, w);
-                            e[q] = HAS_VSCALE ? __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + ch * 32 + lc)) : w;
+                        float2 t0 = HAS_ALIBI ? __fadd2_rn(s[c >> 1], eoff2) : __ffma2_rn(s[c >> 1], rowMult2, eoff2);
+                        float2 t1 = HAS_ALIBI ? __fadd2_rn(s[(c >> 1) + 1], eoff2) : __ffma2_rn(s[(c >> 1) + 1], rowMult2, eoff2);
+                        float2 w0 = FastExp2Pair(t0), w1 = FastExp2Pair(t1);
+                        lacc2 = __fadd2_rn(lacc2, w0);
+                        lacc2 = __fadd2_rn(lacc2, w1);
+                        if (HAS_VSCALE) {
+                            const float4 v4 = sv4[c >> 2];
+                            w0 = __fmul2_rn(w0, make_float2(v4.x, v4.y));
+                            w1 = __fmul2_rn(w1, make_float2(v4.z, v4.w));
                         }
-                        const uint32_t hi4 = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
+                        const uint32_t hi4 = PackE4M3x4(w0.x, w0.y, w1.x, w1.y);
                         pk[c >> 2] = hi4;
                         if (RESID) {
-                            pl[c >> 2] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
+                            pl[c >> 2] = ResidualE4M3x2(w0.x, w0.y, hi4 & 0xffff) | (ResidualE4M3x2(w1.x, w1.y, hi4 >> 16) << 16);
                         }
                     }
-                    TmemStN<8>(tLane + pHiCol + ch * 8, pk);
+                    TmemStN<8>(tLane + PHiCol(ch), pk);
                     if (RESID) {
-                        TmemStN<8>(tLane + pLoCol + ch * 8, pl);
+                        TmemStN<8>(tLane + PLoCol(ch), pl);
                     }
                 };
-                auto zeroChunk = [&](int ch) {
+                if (chKeep >= 0) {
+                    if (tileMasked) {
+                        weightChunk(std::true_type(), chKeep);
+                    } else {
+                        weightChunk(std::false_type(), chKeep);
+                    }
+                }
+                if (chAgain >= 0) {
+                    // second read of this chunk's scores, after which S belongs to the next QK^T
+                    loadChunk(chAgain);
+                    releaseS();
+                    if (warpMasked) {
+                        scaleChunk(std::true_type(), chAgain);
+                    } else {
+                        scaleChunk(std::false_type(), chAgain);
+                    }
+                    if (tileMasked) {
+                        weightChunk(std::true_type(), chAgain);
+                    } else {
+                        weightChunk(std::false_type(), chAgain);
+                    }
+                }
+                if (zeroMask) {
                     uint32_t z[8];
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         z[q] = 0;
                     }
-                    TmemStN<8>(tLane + pHiCol + ch * 8, z);
-                    TmemStN<8>(tLane + pLoCol + ch * 8, z);
-                };
-                auto releaseS = [&]() {
-                    if (SEP_P) {
-                        TcFenceBefore();
-                        __syncwarp();
-                        if (lane == 0) {
-                            MbarArrive(&misc.BarSRead);
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        if (zeroMask & (1u << ch)) {
+                            TmemStN<8>(tLane + PHiCol(ch), z);
+                            TmemStN<8>(tLane + PLoCol(ch), z);
                         }
                     }
-                };
-                // chunk 0 from the registers
-                if (warpMasked) {
-                    // a masked warp implies a masked tile: the residual part is always written
-                    if (any0) {
-                        weightChunk(std::true_type(), 0);
-                    } else {
-                        zeroChunk(0);
-                    }
-                } else if (tileMasked) {
-                    weightChunk(std::true_type(), 0);
-                } else {
-                    weightChunk(std::false_type(), 0);
-                }
-                // chunk 1: second read of its scores, after which S belongs to the next QK^T
-                if (use1) {
-                    loadChunk(1);
-                    releaseS();
-                    if (warpMasked) {
-                        scaleChunk(std::true_type(), 1, 0.0f);
-                        weightChunk(std::true_type(), 1);
-                    } else {
-                        scaleChunk(std::false_type(), 1, 0.0f);
-                        if (tileMasked) {
-                            weightChunk(std::true_type(), 1);
-                        } else {
-                            weightChunk(std::false_type(), 1);
-                        }
-                    }
-                } else {
-                    releaseS();
-                    zeroChunk(1);
                 }
                 TmemWaitSt();
                 TcFenceBefore();

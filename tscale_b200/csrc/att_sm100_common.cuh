@@ -160,6 +160,58 @@ __device__ __forceinline__ void TmemSt16(uint32_t taddr, const uint32_t *r)
         : "memory");
 }
 
+// 32 consecutive columns of this thread's lane as 16 register pairs (for packed f32x2 arithmetic without
+// re-pairing moves); includes the wait for the load.
+__device__ __forceinline__ void TmemLd32Pairs(uint32_t taddr, float2 *s)
+{
+    uint64_t v[16];
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 t<32>;\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, t16, t17, t18, t19, t20, t21, t22, t23, t24, t25, t26, t27, t28, t29, t30, t31}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t"
+        "mov.b64 %0, {t0, t1};\n\t"
+        "mov.b64 %1, {t2, t3};\n\t"
+        "mov.b64 %2, {t4, t5};\n\t"
+        "mov.b64 %3, {t6, t7};\n\t"
+        "mov.b64 %4, {t8, t9};\n\t"
+        "mov.b64 %5, {t10, t11};\n\t"
+        "mov.b64 %6, {t12, t13};\n\t"
+        "mov.b64 %7, {t14, t15};\n\t"
+        "mov.b64 %8, {t16, t17};\n\t"
+        "mov.b64 %9, {t18, t19};\n\t"
+        "mov.b64 %10, {t20, t21};\n\t"
+        "mov.b64 %11, {t22, t23};\n\t"
+        "mov.b64 %12, {t24, t25};\n\t"
+        "mov.b64 %13, {t26, t27};\n\t"
+        "mov.b64 %14, {t28, t29};\n\t"
+        "mov.b64 %15, {t30, t31};\n\t"
+        "}"
+        : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]), "=l"(v[4]), "=l"(v[5]), "=l"(v[6]), "=l"(v[7]), "=l"(v[8]), "=l"(v[9]), "=l"(v[10]), "=l"(v[11]), "=l"(v[12]), "=l"(v[13]), "=l"(v[14]), "=l"(v[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        s[i] = make_float2(__uint_as_float((uint32_t)v[i]), __uint_as_float((uint32_t)(v[i] >> 32)));
+    }
+}
+
+// 2^x of a register pair, result again a pair
+__device__ __forceinline__ float2 FastExp2Pair(float2 x)
+{
+    uint64_t in = (uint64_t)__float_as_uint(x.x) | ((uint64_t)__float_as_uint(x.y) << 32), out;
+    asm("{\n\t"
+        ".reg .f32 a, b;\n\t"
+        "mov.b64 {a, b}, %1;\n\t"
+        "ex2.approx.ftz.f32 a, a;\n\t"
+        "ex2.approx.ftz.f32 b, b;\n\t"
+        "mov.b64 %0, {a, b};\n\t"
+        "}"
+        : "=l"(out)
+        : "l"(in));
+    return make_float2(__uint_as_float((uint32_t)out), __uint_as_float((uint32_t)(out >> 32)));
+}
+
 __device__ __forceinline__ float FastExp2(float x)
 {
     float y;

@@ -4,6 +4,7 @@
 // Reference behaviour: NormalizeVecsRowTile / NormalizeVecsRowTileMax
 // (code/gpt/compute/row_tile_scale.cuh:11-34, 59-82), CalcDScale (gpt_att_fp16.cuh:621-643).
 #include "tsa_common.cuh"
+#include <type_traits>
 
 namespace tsa {
 
@@ -168,12 +169,67 @@ __global__ void __launch_bounds__(256) DScaleKernel(int outDt, int gradDt, int l
     }
 }
 
+// dScale for 16-bit out / dOut: every thread takes 8 consecutive elements of both (one 16-byte load each), the
+// headDim / 8 lanes of a head add up by shuffles.  A warp covers 256 consecutive elements of one row.
+template <class T16>
+__global__ void __launch_bounds__(256) DScaleVecKernel(int len, int headCount, int headDim, int chunksPerRow,
+    P2D<char> out, P2D<char> dOut, P2D<float> dScale)
+{
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long long)len * chunksPerRow) {
+        return;
+    }
+    const int t = (int)(warp / chunksPerRow);
+    const int x = ((int)(warp - (long long)t * chunksPerRow) * 32 + lane) * 8; // first element of this thread
+    const int width = headCount * headDim;
+    float sum = 0;
+    if (x < width) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(out.Row(t) + (size_t)x * 2));
+        const uint4 b = __ldg(reinterpret_cast<const uint4 *>(dOut.Row(t) + (size_t)x * 2));
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 fa, fb;
+            if (std::is_same<T16, __half>::value) {
+                fa = __half22float2(*reinterpret_cast<const __half2 *>(&aw[k]));
+                fb = __half22float2(*reinterpret_cast<const __half2 *>(&bw[k]));
+            } else {
+                fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&aw[k]));
+                fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&bw[k]));
+            }
+            sum = fmaf(fa.x, fb.x, sum);
+            sum = fmaf(fa.y, fb.y, sum);
+        }
+    }
+    const int lanesPerHead = headDim / 8; // 2, 4, 8, 16 or 32
+    for (int o = lanesPerHead >> 1; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    }
+    if (x < width && (lane & (lanesPerHead - 1)) == 0) {
+        dScale.Row(x / headDim)[t] = sum;
+    }
+}
+
 int LaunchDScale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa_ptr2d dScale,
     int headCount, int headDimV, int len, cudaStream_t stream)
 {
     long long warps = (long long)len * headCount;
     if (warps == 0) {
         return TSA_OK;
+    }
+    const bool pow2 = (headDimV & (headDimV - 1)) == 0 && headDimV >= 16 && headDimV <= 256;
+    const bool aligned = (uintptr_t)out.data % 16 == 0 && out.stride_bytes % 16 == 0 && (uintptr_t)dOut.data % 16 == 0 && dOut.stride_bytes % 16 == 0;
+    if (outDtype == gradDtype && (outDtype == TSA_F16 || outDtype == TSA_BF16) && pow2 && aligned) {
+        const int chunksPerRow = (headCount * headDimV + 255) / 256;
+        const long long vecWarps = (long long)len * chunksPerRow;
+        const int vblocks = (int)((vecWarps * 32 + 255) / 256);
+        if (outDtype == TSA_F16) {
+            DScaleVecKernel<__half><<<vblocks, 256, 0, stream>>>(len, headCount, headDimV, chunksPerRow, P2D<char>(out), P2D<char>(dOut), P2D<float>(dScale));
+        } else {
+            DScaleVecKernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(len, headCount, headDimV, chunksPerRow, P2D<char>(out), P2D<char>(dOut), P2D<float>(dScale));
+        }
+        return CheckCuda(cudaGetLastError(), "tsa_calc_dscale launch");
     }
     int blocks = (int)((warps * 32 + 255) / 256);
     DScaleKernel<<<blocks, 256, 0, stream>>>(outDtype, gradDtype, len, headCount, headDimV, P2D<char>(out), P2D<char>(dOut), P2D<float>(dScale));
