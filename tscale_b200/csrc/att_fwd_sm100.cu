@@ -13,26 +13,17 @@
 // e4m3(P) + e4m3(P - e4m3(P)) and multiplied in two MMAs, which removes the 3-bit-mantissa rounding of the
 // weights where it is not averaged out over many keys.
 //
-// Work item = one head x 128 query rows (two 64-row span blocks).  CTAs are persistent: two per SM, each takes
-// items from a counter in the workspace (late, long rows first) until none is left, so barrier set-up, tensor
-// memory allocation and the pipeline fill are paid once per CTA and one item's output store overlaps the next
-// item's first MMAs.  Twelve warps in three warpgroups:
-//   warps 0-7  softmax, two threads per query row (a row is one tensor-memory lane; each thread owns 64 of the
-//              128 score columns of a tile and keeps them in registers between the maximum and the weights);
-//   warp  8    lane 0 issues every MMA;
-//   warp  9    loader: takes the next item, stages its spans / query scales in shared memory, issues the TMA
-//              copies of Q and of the K/V ring (which runs on across item boundaries) and stages the key scales;
-//   warps 10-11 only take part in the register reallocation (setmaxnreg hands their registers to the softmax warps).
-// Tensor memory (256 columns, so two CTAs share an SM): S [0,128) f32 / s32, O [128, 128 + D) f32.  For D = 64 the
-// weights have their own columns [192, 256), so S is free again as soon as every thread has loaded its scores:
-// QK^T of the next tile runs while the softmax of this one is still computing, and P V follows when P arrives.
-// For D = 128 P is written back over the thread's own S columns and the next QK^T follows P V.
-// Shared memory: 2 Q tiles, STAGES x (K tile, V tile, key scales) filled by TMA with the 128 B (D = 128) or 64 B
-// (D = 64) swizzle the MMA descriptors expect.  Softmax arithmetic uses packed f32x2 multiply-adds and 3-input max.
+// One CTA = one head x 128 query rows (two 64-row span blocks).  Eight softmax warps, two threads per row
+// (each owns 64 of the row's 128 score columns; a row is one tensor-memory lane), plus a control warp whose
+// lane 0 issues every TMA copy and every MMA.  Tensor memory: columns [0,128) S (f32 / s32); each half writes its
+// packed e4m3 weights (16 columns, plus 16 for the residual) back over its own S columns; columns [128, 128 + D)
+// hold O (f32).  256 columns are allocated so two CTAs share an SM and one CTA's softmax overlaps the other's
+// MMAs.  Shared memory: Q tile, STAGES x (K tile, V tile) filled by TMA with the 128 B (D = 128) or 64 B (D = 64)
+// swizzle the MMA descriptors expect.  Softmax arithmetic uses packed f32x2 multiply-adds and 3-input max.
 // Key tiles follow the reference's grouped spans: for round r the tiles [Start, Finish] of the two blocks'
 // r-th groups; 32-column chunks no row of a warp attends cost no exponentials (window layers).
-// Every barrier wait is bounded; when one runs out the kernel records a code in *statusWord, every role leaves
-// its loop, outstanding copies are drained, tensor memory is freed and the CTA returns.
+// Every barrier wait is bounded; when one runs out the kernel records a code in *statusWord, drains its
+// outstanding copies, frees its tensor memory and returns.
 #include "att_internal.cuh"
 #include "att_sm100_common.cuh"
 
@@ -41,32 +32,23 @@ namespace tsa {
 using namespace sm100;
 
 constexpr int SOFTMAX_THREADS = 256;
-constexpr int SOFTMAX_WARPS = SOFTMAX_THREADS / 32;
-constexpr int MMA_WARP = 8;
-constexpr int LOAD_WARP = 9;
-constexpr int FWD_THREADS = 384;
-constexpr int SOFTMAX_REGS = 104; // after setmaxnreg: (384 * 80 - 128 * 32) / 256 = 104
-constexpr int CONTROL_REGS = 32;
+constexpr int CTRL_WARP = SOFTMAX_THREADS / 32;
+constexpr int FWD_THREADS = SOFTMAX_THREADS + 32;
 constexpr int SCORE_THREADS = 128;
 constexpr int TILE_M = 128;
 constexpr int TILE_N = 128;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O_COL = 128;
-constexpr uint32_t TMEM_P_COL = 192; // D = 64 only
-constexpr int ITEM_RING = 4;
-constexpr int MAX_STAGES = 4;
 
 struct TFwdParams {
     int HeadCount;
     int OutRows;      // rows of out that may be written
     int KeyRows;      // rows of K / V
     int LenAttTiles;  // number of 64-row span blocks
-    int QTiles;       // 128-row query tiles
     const tsa_span_group *Spans;
     const int *SpanPtr;
     P2D<float> QScale, KScale, VScale;
     const float *VRef; // per head max of VScale (workspace), null without VScale
-    int *Counter;      // next work item (workspace, zeroed before the launch)
     P2D<char> Out;
     P2D<float> Lse;
     const float *GlobalScale;
@@ -77,75 +59,46 @@ struct TFwdParams {
     int *Status;
 };
 
-// what the loader publishes about a work item: everything the other warps would otherwise fetch from global
-// memory at the start of the item
-struct TItemSlot {
-    int QTile, Head;     // QTile < 0: no more work
-    int N0, N1;          // number of span groups (rounds) of the two 64-row blocks
-    int A0, A1;          // index of each block's first group
-    int Round0, J0, Hi;  // first non-empty round and its key-tile range; Valid = 0: the item has no key tile
-    int Valid;
-    int MaxS, MinF;      // max span start / min span finish over the 128 rows in round Round0
-    float VRef;
-    int Pad[3];
-    int SpanS[TILE_M], SpanF[TILE_M]; // the rows' spans in round Round0
-    float SQ[TILE_M];                 // the rows' query scales (0 beyond the last row)
+template <int D>
+struct TFwdSmem {
+    static constexpr int STAGES = (D == 64) ? 3 : 2;
+    static constexpr int TILE_BYTES = 128 * D;
+    static constexpr int Q_OFF = 0;
+    static constexpr int K_OFF = TILE_BYTES;
+    static constexpr int V_OFF = K_OFF + STAGES * TILE_BYTES;
+    static constexpr int MISC_OFF = V_OFF + STAGES * TILE_BYTES;
+    static constexpr int TOTAL = MISC_OFF + 4096 + 1024; // misc + alignment slack
 };
 
 struct TFwdMisc {
-    TItemSlot Item[ITEM_RING];
-    float Sk[MAX_STAGES][TILE_N]; // key scale of each column of the staged tile
-    float Sv[MAX_STAGES][TILE_N]; // value scale / per-head maximum
-    float Al[TILE_N];             // ALiBi term slope * column (tile invariant)
-    float RowX[2][2][TILE_M];     // exchange between the two threads of a row, double buffered by tile parity
-    uint64_t BarItem[ITEM_RING];      // loader -> all: item slot written
-    uint64_t BarItemEmpty[ITEM_RING]; // softmax warps + MMA lane -> loader: slot read
-    uint64_t BarQFull[2], BarQEmpty[2];
-    uint64_t BarFull[MAX_STAGES], BarEmpty[MAX_STAGES];
-    uint64_t BarS;     // MMA -> softmax: S(t) complete
-    uint64_t BarSRead; // softmax -> MMA: S(t) is in registers (D = 64)
-    uint64_t BarP;     // softmax -> MMA: P(t) written
-    uint64_t BarPV;    // MMA -> softmax: P V(t) retired: O current, P columns free
+    float Sk[2][TILE_N];     // key scale of each column of the tile, double buffered by tile parity: fast warps
+    float Sv[2][TILE_N];     // stage the next tile's scales while slower warps still read the current ones
+    float Al[TILE_N];        // ALiBi term slope * column (tile invariant)
+    float RowX[2][TILE_M];   // exchange between the two threads of a row (tile max, final sum)
+    int TileMasked[2];       // softmax -> control warp: P has a residual part for this tile
+    int Abort;               // a bounded wait ran out somewhere in the CTA
+    uint64_t BarQ;
+    uint64_t BarFull[4];
+    uint64_t BarMma;         // control -> softmax: S(it) ready (and PV(it-1) retired)
+    uint64_t BarP;           // softmax -> control: P(it) written, 256 arrivals
     uint32_t TmemBase;
-    int Abort;         // a bounded wait ran out somewhere in the CTA
 };
 
-template <int D>
-struct TFwdSmem {
-    static constexpr int STAGES = (D == 64) ? 4 : 2;
-    static constexpr int TILE_BYTES = 128 * D;
-    static constexpr int Q_OFF = 0;
-    static constexpr int K_OFF = 2 * TILE_BYTES;
-    static constexpr int V_OFF = K_OFF + STAGES * TILE_BYTES;
-    static constexpr int MISC_OFF = V_OFF + STAGES * TILE_BYTES;
-    static constexpr int TOTAL = MISC_OFF + (int)((sizeof(TFwdMisc) + 1023) / 1024 * 1024);
-};
-
-__device__ __forceinline__ void IterFromSlot(TTileIter &it, const TItemSlot &s, const tsa_span_group *spans, int keyRows)
-{
-    it.G0 = spans + s.A0;
-    it.G1 = spans + s.A1;
-    it.N0 = s.N0;
-    it.N1 = s.N1;
-    it.KeyRows = keyRows;
-    it.Round = s.Round0;
-    it.J0 = s.J0;
-    it.Hi = s.Hi;
-    it.Valid = s.Valid != 0;
-}
-
+// Thread layout: warps 0-7 are softmax warps, two threads per query row: thread (half, row) with half = tid / 128
+// owns columns [64 * half, 64 * half + 64) of the row's scores and columns [half * D/2, (half + 1) * D/2) of its
+// output.  Warp 8 is the control warp: lane 0 issues every TMA copy and every MMA.
 template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
 __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TFwdParams p)
 {
     using SM = TFwdSmem<D>;
     constexpr int STAGES = SM::STAGES;
-    constexpr bool SEP_P = (D == 64); // P has its own tensor-memory columns
     constexpr int SWZ = (D == 128) ? 128 : 64;
     constexpr uint32_t GROUP_BYTES = 8 * D; // 8 rows of a tile
     constexpr uint32_t IDESC_QK = QK_I8 ? MakeInstrDesc(2, 1, 1, 0, 0, TILE_M, TILE_N) : MakeInstrDesc(1, 0, 0, 0, 0, TILE_M, TILE_N);
     constexpr uint32_t IDESC_PV = MakeInstrDesc(1, 0, 0, 0, 1, TILE_M, D);
-    constexpr int BAR_PAIR0 = 1;     // + (warp & 3): the two warps that share 32 rows
+    constexpr int BAR_STAGE = 1;     // named barrier of the 256 softmax threads
+    constexpr int BAR_PAIR0 = 2;     // + (warp & 3): the two warps that share 32 rows
     constexpr int HALF_N = TILE_N / 2;
     constexpr int HALF_D = D / 2;
 
@@ -155,7 +108,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     uint8_t *sV = smem + SM::V_OFF;
     TFwdMisc &misc = *reinterpret_cast<TFwdMisc *>(smem + SM::MISC_OFF);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int head = blockIdx.y;
+    const int qTile = gridDim.x - 1 - blockIdx.x; // late (long) rows first
 
     if ((SmemAddr(smem) & 1023u) != 0) {
         // the launch did not honour the alignment: report instead of computing on mis-swizzled tiles
@@ -165,26 +120,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
         return;
     }
     if (tid == 0) {
-        for (int s = 0; s < ITEM_RING; ++s) {
-            MbarInit(&misc.BarItem[s], 1);
-            MbarInit(&misc.BarItemEmpty[s], SOFTMAX_WARPS + 1);
-        }
-        for (int s = 0; s < 2; ++s) {
-            MbarInit(&misc.BarQFull[s], 1);
-            MbarInit(&misc.BarQEmpty[s], 1);
-        }
+        MbarInit(&misc.BarQ, 1);
         for (int s = 0; s < STAGES; ++s) {
             MbarInit(&misc.BarFull[s], 1);
-            MbarInit(&misc.BarEmpty[s], 1);
         }
-        MbarInit(&misc.BarS, 1);
-        MbarInit(&misc.BarSRead, SOFTMAX_WARPS);
-        MbarInit(&misc.BarP, SOFTMAX_WARPS);
-        MbarInit(&misc.BarPV, 1);
+        MbarInit(&misc.BarMma, 1);
+        MbarInit(&misc.BarP, SOFTMAX_THREADS);
         misc.Abort = 0;
         FenceBarrierInit();
     }
-    if (warp == MMA_WARP) {
+    if (warp == CTRL_WARP) {
         TmemAlloc(&misc.TmemBase, TMEM_COLS);
         TmemRelinquish();
     }
@@ -195,656 +140,385 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     __syncthreads();
     TcFenceAfter();
     const uint32_t tmem = misc.TmemBase;
-    const int totalItems = p.QTiles * p.HeadCount;
-    const int *abortFlag = &misc.Abort;
-    auto giveUp = [&](int code) {
-        *(volatile int *)&misc.Abort = 1;
-        if (p.Status) {
-            atomicOr(p.Status, code);
-        }
-    };
 
-    if (warp >= SOFTMAX_WARPS) {
-        RegDealloc<CONTROL_REGS>();
-        if (warp == LOAD_WARP) {
-            // ------------------------------------------------------------ loader warp
-            if (lane == 0) {
-                PrefetchTensorMap(&tmQ);
-                PrefetchTensorMap(&tmK);
-                PrefetchTensorMap(&tmV);
-            }
-            int g = 0;          // tiles issued into the K/V ring
-            int nq = 0;         // Q tiles requested (items that have key tiles)
+    TTileIter cur;
+    cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, qTile, p.KeyRows);
+
+    if (warp == CTRL_WARP) {
+        // ---------------------------------------------------------------- control warp
+        if ((tid & 31) == 0 && cur.Valid) {
+            PrefetchTensorMap(&tmQ);
+            PrefetchTensorMap(&tmK);
+            PrefetchTensorMap(&tmV);
+            const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
+            TTileIter prod = cur;
+            int issued = 0, landed = 0;
             bool failed = false;
-            for (int k = 0; !failed; ++k) {
-                int item = 0;
-                if (lane == 0) {
-                    item = atomicAdd(p.Counter, 1);
-                }
-                item = __shfl_sync(0xffffffffu, item, 0);
-                const bool last = item >= totalItems;
-                const int qTile = last ? -1 : p.QTiles - 1 - item / p.HeadCount; // late (long) rows first
-                const int head = last ? 0 : item % p.HeadCount;
-                TTileIter iter;
-                iter.Valid = false;
-                int a0 = 0, a1 = 0;
-                int ss[4], sf[4];
-                float sqv[4];
-                float vRef = 0;
-                if (!last) {
-                    iter.Init(p.Spans, p.SpanPtr, p.LenAttTiles, qTile, p.KeyRows);
-                    a0 = iter.G0 ? (int)(iter.G0 - p.Spans) : 0;
-                    a1 = iter.G1 ? (int)(iter.G1 - p.Spans) : 0;
+            auto issueLoad = [&](int slot, int j0) {
+                MbarExpectTx(&misc.BarFull[slot], 2 * SM::TILE_BYTES);
+                TmaLoad2D(sK + slot * SM::TILE_BYTES, &tmK, head * D, j0, &misc.BarFull[slot]);
+                TmaLoad2D(sV + slot * SM::TILE_BYTES, &tmV, head * D, j0, &misc.BarFull[slot]);
+            };
+            auto issuePV = [&](int slot, bool accumulate, bool withResidual) {
+                const uint32_t vAddr = sVa + slot * SM::TILE_BYTES;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int r = lane + 32 * q;
-                        const tsa_span_group *gp = (r < 64) ? iter.G0 : iter.G1;
-                        const int n = (r < 64) ? iter.N0 : iter.N1;
-                        ss[q] = 1;
-                        sf[q] = 0;
-                        if (iter.Valid && iter.Round < n) {
-                            ss[q] = gp[iter.Round].SpanStart[r & 63];
-                            sf[q] = gp[iter.Round].SpanFinish[r & 63];
-                        }
-                        const int row = qTile * TILE_M + r;
-                        sqv[q] = 0;
-                        if (row < p.OutRows) {
-                            sqv[q] = p.QScale.Valid() ? p.QScale.Row(head)[row] : p.QkVecScale;
-                        }
-                    }
-                    if (HAS_VSCALE) {
-                        vRef = p.VRef[head];
-                    }
+                for (int ks = 0; ks < TILE_N / 32; ++ks) {
+                    uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
+                    uint32_t aCol = (ks >> 1) * HALF_N + (ks & 1) * 8; // P of half h sits at columns 64h .. 64h+15
+                    MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
                 }
-                const float svMult = (HAS_VSCALE && vRef > 0) ? 1.0f / vRef : 0.0f; // sv_j / svRef <= 1; the factor 128 sits in the exponent
-                const int slotIdx = k & (ITEM_RING - 1);
-                if (lane == 0) {
-                    if (k >= ITEM_RING && !WaitBarA(&misc.BarItemEmpty[slotIdx], ((k / ITEM_RING) - 1) & 1, abortFlag)) {
-                        failed = true;
-                        giveUp(kDevTimeoutMma);
-                    }
-                }
-                failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
-                if (failed) {
-                    break;
-                }
-                TItemSlot &slot = misc.Item[slotIdx];
-                if (!last) {
-                    int maxS = max(max(ss[0], ss[1]), max(ss[2], ss[3]));
-                    int minF = min(min(sf[0], sf[1]), min(sf[2], sf[3]));
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        maxS = max(maxS, __shfl_xor_sync(0xffffffffu, maxS, o));
-                        minF = min(minF, __shfl_xor_sync(0xffffffffu, minF, o));
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        slot.SpanS[lane + 32 * q] = ss[q];
-                        slot.SpanF[lane + 32 * q] = sf[q];
-                        slot.SQ[lane + 32 * q] = sqv[q];
-                    }
-                    if (lane == 0) {
-                        slot.Head = head;
-                        slot.N0 = iter.N0;
-                        slot.N1 = iter.N1;
-                        slot.A0 = a0;
-                        slot.A1 = a1;
-                        slot.Round0 = iter.Round;
-                        slot.J0 = iter.J0;
-                        slot.Hi = iter.Hi;
-                        slot.Valid = iter.Valid ? 1 : 0;
-                        slot.MaxS = maxS;
-                        slot.MinF = minF;
-                        slot.VRef = vRef;
-                    }
-                }
-                if (lane == 0) {
-                    slot.QTile = qTile;
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    MbarArrive(&misc.BarItem[slotIdx]);
-                }
-                if (last) {
-                    break;
-                }
-                if (iter.Valid) {
-                    if (lane == 0) {
-                        const int qb = nq & 1;
-                        // the buffer was last read by the QK^T products of the item two Q tiles back
-                        if (nq >= 2 && !WaitBarA(&misc.BarQEmpty[qb], ((nq >> 1) - 1) & 1, abortFlag)) {
-                            failed = true;
-                            giveUp(kDevTimeoutMma);
-                        } else {
-                            MbarExpectTx(&misc.BarQFull[qb], SM::TILE_BYTES);
-                            TmaLoad2D(sQ + qb * SM::TILE_BYTES, &tmQ, head * D, qTile * TILE_M, &misc.BarQFull[qb]);
-                        }
-                    }
-                    ++nq;
-                    failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
-                }
-                while (iter.Valid && !failed) {
-                    const int stage = g % STAGES;
-                    if (lane == 0) {
-                        if (g >= STAGES && !WaitBarA(&misc.BarEmpty[stage], ((g / STAGES) - 1) & 1, abortFlag)) {
-                            failed = true;
-                            giveUp(kDevTimeoutMma);
-                        } else {
-                            MbarExpectTxOnly(&misc.BarFull[stage], 2 * SM::TILE_BYTES);
-                            TmaLoad2D(sK + stage * SM::TILE_BYTES, &tmK, head * D, iter.J0, &misc.BarFull[stage]);
-                            TmaLoad2D(sV + stage * SM::TILE_BYTES, &tmV, head * D, iter.J0, &misc.BarFull[stage]);
-                        }
-                    }
-                    failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
-                    if (failed) {
-                        break;
-                    }
-                    {
-                        const float *ksRow = p.KScale.Row(head);
-                        const float *vsRow = HAS_VSCALE ? p.VScale.Row(head) : nullptr;
-                        float kq[4], vq[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int j = iter.J0 + lane + 32 * q;
-                            kq[q] = 0;
-                            vq[q] = 0;
-                            if (j < p.KeyRows) {
-                                kq[q] = ksRow[j];
-                                if (HAS_VSCALE) {
-                                    vq[q] = vsRow[j];
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            misc.Sk[stage][lane + 32 * q] = kq[q];
-                            if (HAS_VSCALE) {
-                                misc.Sv[stage][lane + 32 * q] = vq[q] * svMult;
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) {
-                        MbarArrive(&misc.BarFull[stage]);
-                    }
-                    ++g;
-                    iter.Advance();
-                }
-            }
-            if (*(volatile int *)&misc.Abort) {
-                // drain copies that were requested, so none lands after the CTA is gone
-                if (lane == 0) {
-                    for (int t = max(0, g - STAGES); t < g; ++t) {
-                        WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
-                    }
-                    if (nq > 0) {
-                        WaitBar(&misc.BarQFull[(nq - 1) & 1], ((nq - 1) >> 1) & 1);
-                    }
-                }
-            }
-            __syncwarp();
-        } else if (warp == MMA_WARP) {
-            // ------------------------------------------------------------ MMA warp
-            if (lane == 0) {
-                const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
-                auto issuePV = [&](int stage, bool accumulate, bool withResidual) {
-                    const uint32_t vAddr = sVa + stage * SM::TILE_BYTES;
+                if (withResidual) {
 #pragma unroll
                     for (int ks = 0; ks < TILE_N / 32; ++ks) {
                         uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                        // D = 64: P is one 32-column block; D = 128: P of chunk ks sits at S columns 32 ks .. 32 ks + 7
-                        uint32_t aCol = SEP_P ? TMEM_P_COL + ks * 8 : (uint32_t)(ks * 32);
-                        MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+                        uint32_t aCol = (ks >> 1) * HALF_N + 16 + (ks & 1) * 8;
+                        MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, 1u);
                     }
-                    if (withResidual) {
+                }
+            };
+            auto issueQK = [&](int slot) {
+                const uint32_t kAddr = sKa + slot * SM::TILE_BYTES;
 #pragma unroll
-                        for (int ks = 0; ks < TILE_N / 32; ++ks) {
-                            uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                            uint32_t aCol = SEP_P ? TMEM_P_COL + 32 + ks * 8 : (uint32_t)(ks * 32 + 8);
-                            MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, 1u);
-                        }
+                for (int ks = 0; ks < D / 32; ++ks) {
+                    uint64_t aDesc = MakeSmemDesc(sQa + ks * 32, 16, GROUP_BYTES, SWZ);
+                    uint64_t bDesc = MakeSmemDesc(kAddr + ks * 32, 16, GROUP_BYTES, SWZ);
+                    if (QK_I8) {
+                        MmaI8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
+                    } else {
+                        MmaF8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
                     }
-                };
-                auto issueQK = [&](int qb, int stage) {
-                    const uint32_t qAddr = sQa + qb * SM::TILE_BYTES;
-                    const uint32_t kAddr = sKa + stage * SM::TILE_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < D / 32; ++ks) {
-                        uint64_t aDesc = MakeSmemDesc(qAddr + ks * 32, 16, GROUP_BYTES, SWZ);
-                        uint64_t bDesc = MakeSmemDesc(kAddr + ks * 32, 16, GROUP_BYTES, SWZ);
-                        if (QK_I8) {
-                            MmaI8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
-                        } else {
-                            MmaF8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
-                        }
-                    }
-                };
-                int t = 0;  // tiles issued so far (parity of BarS / BarSRead / BarP / BarPV and ring position)
-                int nq = 0; // items with key tiles so far (Q buffer and its barriers' parity)
-                bool pending = false, pendAccum = false, pendMasked = false;
-                int pendStage = 0;
-                bool failed = false;
-                // P V of the previous tile: needs its weights; frees the ring stage and the P columns when it retires
-                auto flushPV = [&]() {
-                    if (!WaitBarA<true>(&misc.BarP, (t - 1) & 1, abortFlag)) {
-                        failed = true;
-                        giveUp(kDevTimeoutMma);
-                        return;
+                }
+            };
+            auto fail = [&](int code) {
+                failed = true;
+                *(volatile int *)&misc.Abort = 1;
+                if (p.Status) {
+                    atomicOr(p.Status, code);
+                }
+            };
+
+            MbarExpectTx(&misc.BarQ, SM::TILE_BYTES);
+            TmaLoad2D(sQ, &tmQ, head * D, qTile * TILE_M, &misc.BarQ);
+            for (int s = 0; s < STAGES && prod.Valid; ++s) {
+                issueLoad(s, prod.J0);
+                prod.Advance();
+                ++issued;
+            }
+            if (!WaitBar(&misc.BarQ, 0)) {
+                fail(kDevTimeoutTma);
+            }
+            int it = 0;
+            TTileIter ctl = cur;
+            for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
+                const int slot = it % STAGES;
+                if (!WaitBar(&misc.BarFull[slot], (it / STAGES) & 1)) {
+                    fail(kDevTimeoutTma);
+                    break;
+                }
+                ++landed;
+                if (it > 0) {
+                    // P(it-1) written by all softmax threads
+                    if (!WaitBar(&misc.BarP, (it - 1) & 1)) {
+                        fail(kDevTimeoutMma);
+                        break;
                     }
                     TcFenceAfter();
-                    issuePV(pendStage, pendAccum, pendMasked);
-                    MmaCommit(&misc.BarPV);
-                    MmaCommit(&misc.BarEmpty[pendStage]);
-                    pending = false;
-                };
-                for (int k = 0; !failed; ++k) {
-                    const int slotIdx = k & (ITEM_RING - 1);
-                    if (!WaitBarA(&misc.BarItem[slotIdx], (k / ITEM_RING) & 1, abortFlag)) {
-                        failed = true;
-                        giveUp(kDevTimeoutTma);
-                        break;
-                    }
-                    const TItemSlot &slot = misc.Item[slotIdx];
-                    const int qTile = slot.QTile;
-                    TTileIter iter;
-                    iter.Valid = false;
-                    int maxS = 0, minF = 0, round0 = 0;
-                    if (qTile >= 0) {
-                        IterFromSlot(iter, slot, p.Spans, p.KeyRows);
-                        maxS = slot.MaxS;
-                        minF = slot.MinF;
-                        round0 = slot.Round0;
-                    }
-                    MbarArrive(&misc.BarItemEmpty[slotIdx]);
-                    if (qTile < 0) {
-                        break;
-                    }
-                    if (!iter.Valid) {
-                        continue;
-                    }
-                    const int qb = nq & 1;
-                    for (int it = 0; iter.Valid && !failed; ++it, iter.Advance()) {
-                        const int stage = t % STAGES;
-                        if (!WaitBarA(&misc.BarFull[stage], (t / STAGES) & 1, abortFlag) ||
-                            (it == 0 && !WaitBarA(&misc.BarQFull[qb], (nq >> 1) & 1, abortFlag))) {
-                            failed = true;
-                            giveUp(kDevTimeoutTma);
-                            break;
-                        }
-                        if (SEP_P) {
-                            if (t > 0 && !WaitBarA<true>(&misc.BarSRead, (t - 1) & 1, abortFlag)) {
-                                failed = true;
-                                giveUp(kDevTimeoutMma);
-                                break;
-                            }
-                            TcFenceAfter();
-                            issueQK(qb, stage);
-                            MmaCommit(&misc.BarS);
-                            if (pending) {
-                                flushPV();
-                            }
-                        } else {
-                            if (pending) {
-                                flushPV();
-                                if (failed) {
-                                    break;
-                                }
-                            }
-                            TcFenceAfter();
-                            issueQK(qb, stage);
-                            MmaCommit(&misc.BarS);
-                        }
-                        pending = true;
-                        pendStage = stage;
-                        pendAccum = it > 0;
-                        pendMasked = !(iter.Round == round0 && iter.J0 >= maxS && iter.J0 + TILE_N - 1 <= minF);
-                        ++t;
-                    }
-                    // the Q buffer is free once this item's QK^T products have retired
-                    MmaCommit(&misc.BarQEmpty[qb]);
-                    ++nq;
+                    issuePV((it - 1) % STAGES, it - 1 > 0, misc.TileMasked[(it - 1) & 1] != 0);
                 }
-                if (pending && !failed) {
-                    flushPV();
+                TcFenceAfter();
+                issueQK(slot);
+                MmaCommit(&misc.BarMma);
+                if (it > 0 && prod.Valid) {
+                    // the slot of tile it-1 is free once PV(it-1) has retired, i.e. when this commit completes
+                    if (!WaitBar(&misc.BarMma, it & 1)) {
+                        fail(kDevTimeoutMma);
+                        break;
+                    }
+                    issueLoad((it - 1) % STAGES, prod.J0);
+                    prod.Advance();
+                    ++issued;
+                }
+                if (*(volatile int *)&misc.Abort) {
+                    failed = true;
                 }
             }
-            __syncwarp();
+            if (!failed && it > 0) {
+                if (WaitBar(&misc.BarP, (it - 1) & 1)) {
+                    TcFenceAfter();
+                    issuePV((it - 1) % STAGES, it - 1 > 0, misc.TileMasked[(it - 1) & 1] != 0);
+                } else {
+                    fail(kDevTimeoutMma);
+                }
+            }
+            MmaCommit(&misc.BarMma); // final phase (also releases softmax threads waiting after a failure)
+            if (failed) {
+                // drain copies that were requested but never consumed, so none lands after the CTA is gone
+                for (int t = landed; t < issued; ++t) {
+                    WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
+                }
+            }
         }
+        __syncwarp();
     } else {
-        RegAlloc<SOFTMAX_REGS>();
         // ---------------------------------------------------------------- softmax warps
         const int half = tid >> 7;
         const int r = tid & (TILE_M - 1);
+        const int row = qTile * TILE_M + r;
         const int colBase = half * HALF_N;
         const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int pairBar = BAR_PAIR0 + (warp & 3);
-        // packed weights of chunk ch: 8 columns (plus 8 for the residual); D = 128: inside the chunk's own S columns
-        auto PHiCol = [](int ch) { return SEP_P ? TMEM_P_COL + (uint32_t)ch * 8 : (uint32_t)ch * 32; };
-        auto PLoCol = [](int ch) { return SEP_P ? TMEM_P_COL + 32 + (uint32_t)ch * 8 : (uint32_t)ch * 32 + 8; };
+
+        const bool rowOk = row < p.OutRows;
         const float g = p.GlobalScale ? *p.GlobalScale : 1.0f;
+        float sq = 0;
+        if (rowOk) {
+            sq = p.QScale.Valid() ? p.QScale.Row(head)[row] : p.QkVecScale;
+        }
+        // a zero query scale would turn masked (-inf) scores into NaN; a tiny positive one keeps every logit at ~0
+        const float rowMult = fmaxf(sq * p.C * g, 1e-30f);
+        const float2 rowMult2 = make_float2(rowMult, rowMult);
+        const float vRef = HAS_VSCALE ? p.VRef[head] : 0.0f;
+        const float svMult = (HAS_VSCALE && vRef > 0) ? 1.0f / vRef : 0.0f; // sv_j / svRef <= 1; the factor 128 sits in the exponent
 
-        int t = 0; // tiles processed by this CTA (barrier parities, ring position)
+        int spanS = 1, spanF = 0, spanRound = -1;
+        float m = 0;
+        float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this thread's weights
+        float pfSk = 0, pfSv = 0;
+        auto fetchScales = [&](int j0) {
+            pfSk = 0;
+            pfSv = 0;
+            int j = j0 + tid;
+            if (tid < TILE_N && j < p.KeyRows) {
+                pfSk = p.KScale.Row(head)[j];
+                if (HAS_VSCALE) {
+                    pfSv = p.VScale.Row(head)[j] * svMult;
+                }
+            }
+        };
+        if (cur.Valid) {
+            fetchScales(cur.J0);
+        }
         bool failed = false;
-        for (int k = 0; !failed; ++k) {
-            const int slotIdx = k & (ITEM_RING - 1);
-            if (!WaitBarA(&misc.BarItem[slotIdx], (k / ITEM_RING) & 1, abortFlag)) {
+        int it = 0;
+        while (cur.Valid) {
+            if (cur.Round != spanRound) {
+                spanS = 1;
+                spanF = 0;
+                const tsa_span_group *gp = (r < 64) ? cur.G0 : cur.G1;
+                const int n = (r < 64) ? cur.N0 : cur.N1;
+                if (cur.Round < n) {
+                    spanS = gp[cur.Round].SpanStart[r & 63];
+                    spanF = gp[cur.Round].SpanFinish[r & 63];
+                }
+                spanRound = cur.Round;
+            }
+            const int buf = it & 1;
+            if (tid < TILE_N) {
+                misc.Sk[buf][tid] = pfSk;
+                if (HAS_VSCALE) {
+                    misc.Sv[buf][tid] = pfSv;
+                }
+            }
+            const int j0 = cur.J0;
+            const int ls = spanS - j0, lf = spanF - j0; // span in tile-local columns
+            const bool rowFull = ls <= 0 && lf >= TILE_N - 1;
+            const bool warpMasked = !__all_sync(0xffffffffu, rowFull);
+            // 32-column chunks of this thread's half that some row of the warp attends
+            const bool any0 = __any_sync(0xffffffffu, ls <= colBase + 31 && lf >= colBase && ls <= lf);
+            const bool any1 = __any_sync(0xffffffffu, ls <= colBase + 63 && lf >= colBase + 32 && ls <= lf);
+            if (failed) {
+                *(volatile int *)&misc.Abort = 1;
+            }
+            const bool tileMasked = BarRedOr(BAR_STAGE, SOFTMAX_THREADS, warpMasked);
+            if (*(volatile int *)&misc.Abort) {
                 failed = true;
-                giveUp(kDevTimeoutTma);
                 break;
             }
-            const TItemSlot &slot = misc.Item[slotIdx];
-            const int qTile = slot.QTile;
-            TTileIter cur;
-            cur.Valid = false;
-            int head = 0, round0 = 0, maxS = 0, minF = 0, span0S = 1, span0F = 0;
-            float sq = 0, vRef = 0;
-            if (qTile >= 0) {
-                IterFromSlot(cur, slot, p.Spans, p.KeyRows);
-                head = slot.Head;
-                round0 = slot.Round0;
-                maxS = slot.MaxS;
-                minF = slot.MinF;
-                span0S = slot.SpanS[r];
-                span0F = slot.SpanF[r];
-                sq = slot.SQ[r];
-                vRef = slot.VRef;
+            TTileIter nxt = cur;
+            nxt.Advance();
+            if (nxt.Valid) {
+                fetchScales(nxt.J0);
             }
-            __syncwarp();
-            if (lane == 0) {
-                MbarArrive(&misc.BarItemEmpty[slotIdx]);
+            if (!WaitBar(&misc.BarMma, it & 1)) {
+                failed = true;
+                if (p.Status) {
+                    atomicOr(p.Status, kDevTimeoutMma);
+                }
             }
-            if (qTile < 0) {
-                break;
+            TcFenceAfter();
+
+            // The scores are read from tensor memory twice, 32 columns at a time (first for the row maximum, then for
+            // the weights), which keeps the live registers of a thread at one chunk instead of its whole half row.
+            // Masked and unmasked tiles run separate copies of the code (warp-uniform branches), so the common
+            // unmasked tile pays for no compare / select.
+            // span in half-local columns, clipped so that (unsigned)(c - lsH) <= spanW  <=>  ls <= c <= lf
+            const int lsC = max(ls, colBase), lfC = min(lf, colBase + HALF_N - 1);
+            const int lsH = lsC - colBase;
+            const unsigned spanW = (lsC <= lfC) ? (unsigned)(lfC - lsC) : 0u;
+            const bool rowEmpty = lsC > lfC;
+            const float *skBuf = misc.Sk[buf] + colBase;
+            const float *svBuf = misc.Sv[buf] + colBase;
+            const float *alBuf = misc.Al + colBase;
+            auto loadScaled = [&](auto maskedTag, int ch, float2 *u) {
+                constexpr bool MASKED = decltype(maskedTag)::value;
+                uint32_t sreg[32];
+                TmemLd32(tLane + colBase + ch * 32, sreg);
+                TmemWaitLd();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const int lc = ch * 32 + c; // column inside this thread's half
+                    float2 a = QK_I8 ? IntPairToFloat(sreg[c], sreg[c + 1]) : make_float2(__uint_as_float(sreg[c]), __uint_as_float(sreg[c + 1]));
+                    float2 x = __fmul2_rn(a, *reinterpret_cast<const float2 *>(skBuf + lc));
+                    if (HAS_ALIBI) {
+                        x = __ffma2_rn(x, rowMult2, *reinterpret_cast<const float2 *>(alBuf + lc));
+                    }
+                    if (MASKED) {
+                        // lsH / lfH: span in columns of this half; unsigned compare folds both bounds
+                        x.x = ((unsigned)(lc - lsH) <= spanW) ? x.x : -INFINITY;
+                        x.y = ((unsigned)(lc + 1 - lsH) <= spanW) ? x.y : -INFINITY;
+                    }
+                    u[c >> 1] = x;
+                }
+            };
+            auto chunkMax = [&](auto maskedTag, int ch, float mxIn) {
+                float2 u[16];
+                loadScaled(maskedTag, ch, u);
+                float mx = mxIn;
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    mx = Max3(mx, u[k].x, u[k].y);
+                }
+                return mx;
+            };
+            float mx = -INFINITY;
+            if (warpMasked) {
+                if (any0) {
+                    mx = chunkMax(std::true_type(), 0, mx);
+                }
+                if (any1) {
+                    mx = chunkMax(std::true_type(), 1, mx);
+                }
+                if (rowEmpty) {
+                    mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
+                }
+            } else {
+                mx = chunkMax(std::false_type(), 0, mx);
+                mx = chunkMax(std::false_type(), 1, mx);
             }
-            const int row = qTile * TILE_M + r;
-            const bool rowOk = row < p.OutRows;
-            // a zero query scale would turn masked (-inf) scores into NaN; a tiny positive one keeps every logit at ~0
-            const float rowMult = fmaxf(sq * p.C * g, 1e-30f);
-            const float2 rowMult2 = make_float2(rowMult, rowMult);
-
-            int spanS = span0S, spanF = span0F, spanRound = round0;
-            float m = 0;
-            float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this thread's weights
-            int it = 0;
-            while (cur.Valid) {
-                if (cur.Round != spanRound) {
-                    spanS = 1;
-                    spanF = 0;
-                    const tsa_span_group *gp = (r < 64) ? cur.G0 : cur.G1;
-                    const int n = (r < 64) ? cur.N0 : cur.N1;
-                    if (cur.Round < n) {
-                        spanS = gp[cur.Round].SpanStart[r & 63];
-                        spanF = gp[cur.Round].SpanFinish[r & 63];
-                    }
-                    spanRound = cur.Round;
-                }
-                const int stage = t % STAGES;
-                const int j0 = cur.J0;
-                // P carries a residual part on every tile that is not interior to all 128 rows (same rule in the MMA warp)
-                const bool tileMasked = !(cur.Round == round0 && j0 >= maxS && j0 + TILE_N - 1 <= minF);
-                // The four 32-column chunks of the tile are shared between the two threads of a row.  On an interior tile
-                // thread h takes chunks h and h + 2.  On a masked tile only the chunks some row of the warp attends are
-                // computed (both warps of a pair hold the same rows, so they agree) and they are dealt out alternately,
-                // which keeps the pair balanced on window layers where the attended band covers two or three chunks.
-                int ls = 0, lf = TILE_N - 1; // the row's span in tile-local columns
-                bool warpMasked = false;
-                int chKeep = half, chAgain = half + 2; // chunk kept in registers / chunk read twice (-1: none)
-                unsigned zeroMask = 0;                 // chunks this thread fills with zero weights
-                if (tileMasked) {
-                    ls = spanS - j0;
-                    lf = spanF - j0;
-                    warpMasked = !__all_sync(0xffffffffu, ls <= 0 && lf >= TILE_N - 1);
-                    if (warpMasked) {
-                        unsigned need = 0;
+            const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
+            float zmax = mx;
+            if (!HAS_ALIBI) {
+                zmax = (mx == -INFINITY) ? mx : mx * rowMult;
+            }
+            misc.RowX[half][r] = zmax + rowOff;
+            BarSync(pairBar, 64);
+            const float tileMax = fmaxf(zmax + rowOff, misc.RowX[half ^ 1][r]);
+            const float newM = fmaxf(m, floorf(tileMax)); // -inf stays below m
+            const float alpha = exp2f(m - newM);
+            if (it > 0 && __any_sync(0xffffffffu, newM != m)) {
 #pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            if (__any_sync(0xffffffffu, ls <= ch * 32 + 31 && lf >= ch * 32 && ls <= lf)) {
-                                need |= 1u << ch;
-                            }
-                        }
-                        chKeep = -1;
-                        chAgain = -1;
-                        int pos = 0;
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            if (need & (1u << ch)) {
-                                if ((pos & 1) == half) {
-                                    if (chKeep < 0) {
-                                        chKeep = ch;
-                                    } else {
-                                        chAgain = ch;
-                                    }
-                                }
-                                ++pos;
-                            } else if ((ch & 1) == half) {
-                                zeroMask |= 1u << ch;
-                            }
-                        }
-                    }
-                }
-
-                // the staged key scales (the wait also makes the loader's shared-memory writes visible), then S(t)
-                // A thread whose wait ran out does not leave alone: it carries `failed` to the next barrier of its
-                // pair (a reduction), so both threads of a row leave together and no named barrier is left waiting.
-                if (!failed && (!WaitBarA(&misc.BarFull[stage], (t / STAGES) & 1, abortFlag) || !WaitBarA(&misc.BarS, t & 1, abortFlag))) {
-                    failed = true;
-                    giveUp(kDevTimeoutMma);
-                }
-                TcFenceAfter();
-                const float *skBuf = misc.Sk[stage];
-                const float *svBuf = misc.Sv[stage];
-                const float *alBuf = misc.Al;
-
-                // Register budget: only 32 scores stay in registers.  Chunk chAgain is read for the maximum, dropped, and
-                // read again for the weights; chunk chKeep is read once and kept.  S is released to the MMA warp after the
-                // last read, about half-way through the tile.
-                float2 s[16];
-                // u = S * sk (+ ALiBi, then already multiplied by the row factor), masked, left in s[]; returns the maximum
-                auto scaleChunk = [&](auto maskedTag, int ch) {
-                    constexpr bool MASKED = decltype(maskedTag)::value;
-                    // span in chunk-local columns, clipped so that (unsigned)(c - lsH) <= spanW  <=>  ls <= col <= lf
-                    const int lsC = max(ls, ch * 32), lfC = min(lf, ch * 32 + 31);
-                    const int lsH = lsC - ch * 32;
-                    const unsigned spanW = (lsC <= lfC) ? (unsigned)(lfC - lsC) : 0u;
-                    const float4 *sk4 = reinterpret_cast<const float4 *>(skBuf + ch * 32);
-                    const float4 *al4 = reinterpret_cast<const float4 *>(alBuf + ch * 32);
-                    float mx = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        const float4 k4 = sk4[c >> 2];
-                        float2 x0 = s[c >> 1], x1 = s[(c >> 1) + 1];
-                        if (QK_I8) {
-                            x0 = IntPairToFloat(__float_as_uint(x0.x), __float_as_uint(x0.y));
-                            x1 = IntPairToFloat(__float_as_uint(x1.x), __float_as_uint(x1.y));
-                        }
-                        x0 = __fmul2_rn(x0, make_float2(k4.x, k4.y));
-                        x1 = __fmul2_rn(x1, make_float2(k4.z, k4.w));
-                        if (HAS_ALIBI) {
-                            const float4 a4 = al4[c >> 2];
-                            x0 = __ffma2_rn(x0, rowMult2, make_float2(a4.x, a4.y));
-                            x1 = __ffma2_rn(x1, rowMult2, make_float2(a4.z, a4.w));
-                        }
-                        if (MASKED) {
-                            x0.x = ((unsigned)(c - lsH) <= spanW) ? x0.x : -INFINITY;
-                            x0.y = ((unsigned)(c + 1 - lsH) <= spanW) ? x0.y : -INFINITY;
-                            x1.x = ((unsigned)(c + 2 - lsH) <= spanW) ? x1.x : -INFINITY;
-                            x1.y = ((unsigned)(c + 3 - lsH) <= spanW) ? x1.y : -INFINITY;
-                        }
-                        s[c >> 1] = x0;
-                        s[(c >> 1) + 1] = x1;
-                        mx = Max3(mx, x0.x, x0.y);
-                        mx = Max3(mx, x1.x, x1.y);
-                    }
-                    if (MASKED && lsC > lfC) {
-                        mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
-                    }
-                    return mx;
-                };
-                auto loadChunk = [&](int ch) {
-                    TmemLd32Pairs(tLane + ch * 32, s);
+                for (int c0 = 0; c0 < HALF_D; c0 += 32) {
+                    uint32_t o[32];
+                    TmemLd32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
                     TmemWaitLd();
-                };
-                auto releaseS = [&]() {
-                    if (SEP_P) {
-                        TcFenceBefore();
-                        __syncwarp();
-                        if (lane == 0) {
-                            MbarArrive(&misc.BarSRead);
-                        }
-                    }
-                };
-                float mx = -INFINITY;
-                if (!failed) {
-                    if (chAgain >= 0) {
-                        loadChunk(chAgain);
-                        mx = warpMasked ? scaleChunk(std::true_type(), chAgain) : scaleChunk(std::false_type(), chAgain);
-                    }
-                    if (chKeep >= 0) {
-                        loadChunk(chKeep);
-                        if (chAgain < 0) {
-                            releaseS(); // nothing is read twice
-                        }
-                        mx = fmaxf(mx, warpMasked ? scaleChunk(std::true_type(), chKeep) : scaleChunk(std::false_type(), chKeep));
-                    } else {
-                        releaseS();
-                    }
-                }
-                const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
-                float zmax = mx;
-                if (!HAS_ALIBI) {
-                    zmax = (mx == -INFINITY) ? mx : mx * rowMult;
-                }
-                misc.RowX[t & 1][half][r] = zmax + rowOff;
-                if (BarRedOr(pairBar, 64, failed)) {
-                    failed = true;
-                    break;
-                }
-                const float tileMax = fmaxf(zmax + rowOff, misc.RowX[t & 1][half ^ 1][r]);
-                const float newM = fmaxf(m, floorf(tileMax)); // -inf stays below m
-                const float alpha = exp2f(m - newM);
-                // P V(t-1) retired: O is current and the P columns may be overwritten
-                if (t > 0) {
-                    if (!WaitBarA(&misc.BarPV, (t - 1) & 1, abortFlag)) {
-                        failed = true;
-                        giveUp(kDevTimeoutMma);
-                        cur.Advance();
-                        ++it;
-                        ++t;
-                        continue; // to the next barrier of the pair
-                    }
-                    TcFenceAfter();
-                }
-                if (it > 0 && __any_sync(0xffffffffu, newM != m)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-                        uint32_t o[32];
-                        TmemLd32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
-                        TmemWaitLd();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                        }
-                        TmemSt32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
+                    for (int c = 0; c < 32; ++c) {
+                        o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
                     }
+                    TmemSt32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
                 }
-                lacc2.x *= alpha;
-                lacc2.y *= alpha;
-                m = newM;
-                // weights, packed e4m3.  A row that attends nothing in a chunk gets an offset of -inf there, so every
-                // weight is 0 whatever the masking compare let through.
-                const float eoff = rowOff - m + 7.0f;
-                auto weightChunk = [&](auto residTag, int ch) {
-                    constexpr bool RESID = decltype(residTag)::value;
-                    const bool chunkEmpty = warpMasked && max(ls, ch * 32) > min(lf, ch * 32 + 31);
-                    const float eo = chunkEmpty ? -INFINITY : eoff;
-                    const float2 eoff2 = make_float2(eo, eo);
-                    const float4 *sv4 = reinterpret_cast<const float4 *>(svBuf + ch * 32);
-                    uint32_t pk[8], pl[8];
+            }
+            lacc2.x *= alpha;
+            lacc2.y *= alpha;
+            m = newM;
+            // weights, packed e4m3 into this half's own S columns (both chunks are re-read before the first store)
+            // an empty row gets eoff = -inf so that every weight is 0 whatever the compare above let through
+            const float eoff = rowEmpty && warpMasked ? -INFINITY : rowOff - m + 7.0f;
+            const float2 eoff2 = make_float2(eoff, eoff);
+            uint32_t pk[2][8], pl[2][8];
+            auto chunkWeights = [&](auto maskedTag, auto residTag, int ch) {
+                constexpr bool RESID = decltype(residTag)::value;
+                float2 u[16];
+                loadScaled(maskedTag, ch, u);
 #pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float2 t0 = HAS_ALIBI ? __fadd2_rn(s[c >> 1], eoff2) : __ffma2_rn(s[c >> 1], rowMult2, eoff2);
-                        float2 t1 = HAS_ALIBI ? __fadd2_rn(s[(c >> 1) + 1], eoff2) : __ffma2_rn(s[(c >> 1) + 1], rowMult2, eoff2);
-                        float2 w0 = FastExp2Pair(t0), w1 = FastExp2Pair(t1);
-                        lacc2 = __fadd2_rn(lacc2, w0);
-                        lacc2 = __fadd2_rn(lacc2, w1);
-                        if (HAS_VSCALE) {
-                            const float4 v4 = sv4[c >> 2];
-                            w0 = __fmul2_rn(w0, make_float2(v4.x, v4.y));
-                            w1 = __fmul2_rn(w1, make_float2(v4.z, v4.w));
-                        }
-                        const uint32_t hi4 = PackE4M3x4(w0.x, w0.y, w1.x, w1.y);
-                        pk[c >> 2] = hi4;
-                        if (RESID) {
-                            pl[c >> 2] = ResidualE4M3x2(w0.x, w0.y, hi4 & 0xffff) | (ResidualE4M3x2(w1.x, w1.y, hi4 >> 16) << 16);
-                        }
+                for (int c = 0; c < 16; c += 2) {
+                    float2 e[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        float2 t = HAS_ALIBI ? __fadd2_rn(u[c + k], eoff2) : __ffma2_rn(u[c + k], rowMult2, eoff2);
+                        float2 w = make_float2(FastExp2(t.x), FastExp2(t.y));
+                        lacc2 = __fadd2_rn(lacc2, w);
+                        e[k] = HAS_VSCALE ? __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + ch * 32 + 2 * (c + k))) : w;
                     }
-                    TmemStN<8>(tLane + PHiCol(ch), pk);
+                    const uint32_t hi4 = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
+                    pk[ch][c >> 1] = hi4;
                     if (RESID) {
-                        TmemStN<8>(tLane + PLoCol(ch), pl);
-                    }
-                };
-                if (chKeep >= 0) {
-                    if (tileMasked) {
-                        weightChunk(std::true_type(), chKeep);
-                    } else {
-                        weightChunk(std::false_type(), chKeep);
+                        pl[ch][c >> 1] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
                     }
                 }
-                if (chAgain >= 0) {
-                    // second read of this chunk's scores, after which S belongs to the next QK^T
-                    loadChunk(chAgain);
-                    releaseS();
-                    if (warpMasked) {
-                        scaleChunk(std::true_type(), chAgain);
-                    } else {
-                        scaleChunk(std::false_type(), chAgain);
-                    }
-                    if (tileMasked) {
-                        weightChunk(std::true_type(), chAgain);
-                    } else {
-                        weightChunk(std::false_type(), chAgain);
-                    }
-                }
-                if (zeroMask) {
-                    uint32_t z[8];
+            };
+            auto zeroChunk = [&](int ch) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        z[q] = 0;
-                    }
+                for (int k = 0; k < 8; ++k) {
+                    pk[ch][k] = 0;
+                    pl[ch][k] = 0;
+                }
+            };
+            if (warpMasked) {
+                // masked tiles always carry the residual (tileMasked is true whenever any warp is masked)
+                if (any0) {
+                    chunkWeights(std::true_type(), std::true_type(), 0);
+                } else {
+                    zeroChunk(0);
+                }
+                if (any1) {
+                    chunkWeights(std::true_type(), std::true_type(), 1);
+                } else {
+                    zeroChunk(1);
+                }
+            } else if (tileMasked) {
+                chunkWeights(std::false_type(), std::true_type(), 0);
+                chunkWeights(std::false_type(), std::true_type(), 1);
+            } else {
+                chunkWeights(std::false_type(), std::false_type(), 0);
+                chunkWeights(std::false_type(), std::false_type(), 1);
+            }
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        if (zeroMask & (1u << ch)) {
-                            TmemStN<8>(tLane + PHiCol(ch), z);
-                            TmemStN<8>(tLane + PLoCol(ch), z);
-                        }
-                    }
+            for (int ch = 0; ch < 2; ++ch) {
+                TmemStN<8>(tLane + colBase + ch * 8, pk[ch]);
+                if (tileMasked) {
+                    TmemStN<8>(tLane + colBase + 16 + ch * 8, pl[ch]);
                 }
-                TmemWaitSt();
-                TcFenceBefore();
-                __syncwarp();
-                if (lane == 0) {
-                    MbarArrive(&misc.BarP);
-                }
-                cur.Advance();
-                ++it;
-                ++t;
             }
-            const int tiles = it;
-            if (!failed && tiles > 0) {
-                if (!WaitBarA(&misc.BarPV, (t - 1) & 1, abortFlag)) {
-                    failed = true;
-                    giveUp(kDevTimeoutMma);
-                }
-                TcFenceAfter();
+            TmemWaitSt();
+            TcFenceBefore();
+            if (tid == 0) {
+                misc.TileMasked[it & 1] = tileMasked ? 1 : 0;
             }
-            // total weight of the row: both halves (the exchange buffer of the parity no tile is using)
-            misc.RowX[t & 1][half][r] = lacc2.x + lacc2.y;
-            if (BarRedOr(pairBar, 64, failed)) {
+            MbarArrive(&misc.BarP);
+            cur = nxt;
+            ++it;
+        }
+
+        const int tiles = it;
+        if (tiles > 0 && !failed) {
+            if (!WaitBar(&misc.BarMma, tiles & 1)) {
                 failed = true;
-                break;
+                if (p.Status) {
+                    atomicOr(p.Status, kDevTimeoutMma);
+                }
             }
-            const float lTot = (lacc2.x + lacc2.y + misc.RowX[t & 1][half ^ 1][r]) * (1.0f / 128.0f) + exp2f(-m);
-            BarSync(pairBar, 64); // the partner has read before the next item's first tile may write this buffer
+            TcFenceAfter();
+        }
+        if (failed) {
+            *(volatile int *)&misc.Abort = 1;
+        }
+        // total weight of the row: both halves
+        misc.RowX[half][r] = lacc2.x + lacc2.y;
+        BarSync(BAR_STAGE, SOFTMAX_THREADS);
+        failed = failed || (*(volatile int *)&misc.Abort != 0);
+        if (!failed) {
+            const float lTot = (lacc2.x + lacc2.y + misc.RowX[half ^ 1][r]) * (1.0f / 128.0f) + exp2f(-m);
             const float outMult = (HAS_VSCALE ? vRef : p.VVecScale) * (1.0f / 128.0f) / lTot;
             if (rowOk && half == 0 && p.Lse.Valid()) {
                 p.Lse.Row(head)[row] = m + log2f(lTot);
@@ -877,13 +551,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                         for (int c = 0; c < 32; c += 8) {
                             uint32_t w[4];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                float a = __uint_as_float(o[c + 2 * q]) * outMult, b = __uint_as_float(o[c + 2 * q + 1]) * outMult;
+                            for (int k = 0; k < 4; ++k) {
+                                float a = __uint_as_float(o[c + 2 * k]) * outMult, b = __uint_as_float(o[c + 2 * k + 1]) * outMult;
                                 if (p.OutDtype == TSA_BF16) {
                                     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                                    w[q] = *reinterpret_cast<uint32_t *>(&h);
+                                    w[k] = *reinterpret_cast<uint32_t *>(&h);
                                 } else {
-                                    w[q] = PackHalf2(a, b);
+                                    w[k] = PackHalf2(a, b);
                                 }
                             }
                             dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -891,13 +565,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                     }
                 }
             }
-            // the next item's first P V overwrites O: its P arrival (after these loads in program order) orders it
-            TcFenceBefore();
         }
     }
     TcFenceBefore();
     __syncthreads();
-    if (warp == MMA_WARP) {
+    if (warp == CTRL_WARP) {
         TmemDealloc(tmem, TMEM_COLS);
     }
 }
@@ -925,11 +597,6 @@ __global__ void __launch_bounds__(256) VRefKernel(P2D<float> vScale, int keyRows
 }
 
 // ---- raw int32 score tiles (parity hook for the kind::i8 accumulators) -------------------------
-struct TScoreMisc {
-    uint64_t BarQ, BarMma;
-    uint32_t TmemBase;
-};
-
 template <int D>
 __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, int lenQ, int lenK, int32_t *scores, int *status)
@@ -940,7 +607,7 @@ __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_con
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem, *sK = smem + 128 * D;
-    TScoreMisc &misc = *reinterpret_cast<TScoreMisc *>(smem + 2 * 128 * D);
+    TFwdMisc &misc = *reinterpret_cast<TFwdMisc *>(smem + 2 * 128 * D);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int head = blockIdx.z, qTile = blockIdx.y, kTile = blockIdx.x;
     if (tid == 0) {
@@ -1031,31 +698,9 @@ bool Sm100FwdSupports(const tsa_att_cfg *cfg, tsa_ptr2d qk, tsa_ptr2d qv, tsa_pt
     return TmaCompatible(qk) && TmaCompatible(qv) && TmaCompatible(v);
 }
 
-// per-head V-scale maxima, then the work-item counter
-static size_t VRefBytes(int headCount)
-{
-    return (size_t)((headCount * sizeof(float) + 255) / 256 * 256);
-}
 size_t Sm100FwdWorkspaceBytes(int headCount)
 {
-    return VRefBytes(headCount) + 256;
-}
-
-static int SmCount()
-{
-    static int count[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-        return 148;
-    }
-    if (count[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-            n = 148;
-        }
-        count[dev] = n;
-    }
-    return count[dev];
+    return (size_t)((headCount * sizeof(float) + 255) / 256 * 256);
 }
 
 template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
@@ -1067,9 +712,7 @@ static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtens
     if (rc != TSA_OK) {
         return rc;
     }
-    const int items = qTiles * fp.HeadCount;
-    const int resident = 2 * SmCount();
-    dim3 grid(items < resident ? items : resident);
+    dim3 grid(qTiles, fp.HeadCount);
     kern<<<grid, FWD_THREADS, smemBytes, stream>>>(mq, mk, mv, fp);
     return CheckCuda(cudaGetLastError(), "tcgen05 forward launch");
 }
@@ -1110,18 +753,16 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     fp.OutDtype = p.OutDtype;
     fp.Status = statusWord;
     const bool hasVs = p.VScale.Data != nullptr;
-    const int qTiles = (lenAttTiles + 1) / 2;
-    fp.QTiles = qTiles;
-    fp.Counter = (int *)((char *)workspace + VRefBytes(p.HeadCount));
-    rc = CheckCuda(cudaMemsetAsync(workspace, 0, Sm100FwdWorkspaceBytes(p.HeadCount), stream), "clearing the forward workspace");
-    if (rc != TSA_OK) {
-        return rc;
-    }
     if (hasVs) {
         fp.VRef = (const float *)workspace;
+        rc = CheckCuda(cudaMemsetAsync(workspace, 0, p.HeadCount * sizeof(float), stream), "clearing the V-scale maxima");
+        if (rc != TSA_OK) {
+            return rc;
+        }
         dim3 vgrid((keyRows + VREF_CHUNK - 1) / VREF_CHUNK, p.HeadCount);
         VRefKernel<<<vgrid, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
     }
+    const int qTiles = (lenAttTiles + 1) / 2;
     const bool i8 = cfg->qk_dtype == TSA_I8;
     const bool alibi = p.Slope != 0.0f;
 #define TSA_FWD_CASE(DD, I8, VS)                                                                         \
