@@ -17,13 +17,19 @@
 //                 transposed spans:  S^T = R1 C1^T, dP^T = R2 C2^T, A1 = dS * sq_i, A2 = P,  dK += A1 C1, dV += A2 C2
 // Tensor memory (512 columns): [0,128) S, [128,256) dP, [256,256+D) first output, [256+D,256+2D) second output.
 // A1 / A2 (bf16, two per column) are written back over the S / dP columns the writing thread has already consumed.
-// 256 arithmetic threads, two per tile row, 64 columns each in chunks of 32; a control warp issues TMA and MMA.
-// Row tiles stay in shared memory, column tiles stream through a TMA ring.  All waits are bounded.
+//
+// A tile is worked on as two 64-column halves with their own barriers, so the tensor pipe and the arithmetic
+// overlap: while the 8 warps of one half turn S / dP into A1 / A2, the MMAs of the other half (its output
+// products, then its S / dP of the next tile) run.  512 arithmetic threads, four per tile row, 32 columns each in
+// two steps of 16; packed f32x2 arithmetic on per-column factors staged in shared memory by each half's own warps;
+// a control warp issues TMA and MMA.  Row tiles stay in shared memory, column tiles stream through a TMA ring.
+// All waits are bounded; a failed wait is carried to the half's next named barrier so its threads leave together.
 #include "att_sm100_common.cuh"
 
 namespace tsa {
 
-constexpr int BWD_ARITH_THREADS = 256;
+constexpr int BWD_ARITH_THREADS = 512;
+constexpr int BWD_HALF_THREADS = 256;
 constexpr int BWD_CTRL_WARP = BWD_ARITH_THREADS / 32;
 constexpr int BWD_THREADS = BWD_ARITH_THREADS + 32;
 constexpr uint32_t BWD_TMEM_COLS = 512;
@@ -59,17 +65,19 @@ struct TBwdSmem {
 };
 
 struct TBwdMisc {
-    float ColA[2][TILE_ROWS]; // per column of the tile, double buffered by tile parity
-    float ColB[2][TILE_ROWS];
-    float ColC[2][TILE_ROWS];
-    float Al[TILE_ROWS];      // slope * column
+    // per column of the tile, double buffered by tile parity, written by the half that uses them:
+    float ColA[2][TILE_ROWS]; // scale of the column vector (dQ: sk_j, dK/dV: sq_i)
+    float ColT[2][TILE_ROWS]; // additive term of the exponent (dQ: ALiBi column part, dK/dV: -lse_i - ALiBi column part)
+    float ColB[2][TILE_ROWS]; // dQ: sv_j c ln2;  dK/dV: -delta_i c ln2
     int Abort;
     uint64_t BarR;            // TMA: row tiles landed
     uint64_t BarFull[4];      // TMA: column stage landed
-    uint64_t BarMma;          // control -> arithmetic: S and dP of tile t ready (and the outputs of tile t-1 issued before)
-    uint64_t BarP;            // arithmetic -> control: A1 / A2 of tile t written, 256 arrivals
+    uint64_t BarS[2];         // control -> half h: S and dP columns of the half ready
+    uint64_t BarP[2];         // half h -> control: A1 / A2 of the half written (8 warp arrivals)
+    uint64_t BarDone;         // control -> all: every output product has retired
     uint32_t TmemBase;
 };
+static_assert(sizeof(TBwdMisc) <= 8192, "misc block");
 
 __device__ __forceinline__ uint32_t PackBf16x2(float lo, float hi)
 {
@@ -87,11 +95,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     constexpr int STAGES = SM::STAGES;
     constexpr int KBLOCKS = D / 64;                     // 64-element (128-byte) blocks along the head dimension
     constexpr uint32_t BLOCK_BYTES = 128 * 128;         // one [128 rows][128 bytes] block of a tile
-    constexpr uint32_t IDESC_SS = MakeInstrDesc(1, 1, 1, 0, 0, TILE_ROWS, TILE_ROWS); // bf16 x bf16 -> f32, both K-major
-    constexpr uint32_t IDESC_OUT = MakeInstrDesc(1, 1, 1, 0, 1, TILE_ROWS, D);         // A from tensor memory, B MN-major
-    constexpr int BAR_STAGE = 1;
-    constexpr int HALF_N = TILE_ROWS / 2;
-    constexpr int HALF_D = D / 2;
+    constexpr uint32_t IDESC_SS = MakeInstrDesc(1, 1, 1, 0, 0, TILE_ROWS, 64); // bf16 x bf16 -> f32, both K-major, 64 columns
+    constexpr uint32_t IDESC_OUT = MakeInstrDesc(1, 1, 1, 0, 1, TILE_ROWS, D); // A from tensor memory, B MN-major
+    constexpr int BAR_HALF0 = 1;                        // + h: named barrier of the 256 threads of half h
+    constexpr int QUARTER_D = D / 4;
     constexpr int OUTPUTS = MODE_DKV ? 2 : 1;
 
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -100,7 +107,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     uint8_t *sC = smem + SM::C_OFF;
     TBwdMisc &misc = *reinterpret_cast<TBwdMisc *>(smem + SM::MISC_OFF);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y;
     const int rowTile = gridDim.x - 1 - blockIdx.x;
 
@@ -115,8 +122,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         for (int s = 0; s < STAGES; ++s) {
             MbarInit(&misc.BarFull[s], 1);
         }
-        MbarInit(&misc.BarMma, 1);
-        MbarInit(&misc.BarP, BWD_ARITH_THREADS);
+        for (int h = 0; h < 2; ++h) {
+            MbarInit(&misc.BarS[h], 1);
+            MbarInit(&misc.BarP[h], BWD_HALF_THREADS / 32);
+        }
+        MbarInit(&misc.BarDone, 1);
         misc.Abort = 0;
         FenceBarrierInit();
     }
@@ -124,20 +134,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         TmemAlloc(&misc.TmemBase, BWD_TMEM_COLS);
         TmemRelinquish();
     }
-    if (tid < TILE_ROWS) {
-        misc.Al[tid] = p.Slope * (float)tid;
-    }
     TcFenceBefore();
     __syncthreads();
     TcFenceAfter();
     const uint32_t tmem = misc.TmemBase;
+    const int *abortFlag = &misc.Abort;
 
     TTileIter cur;
     cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, rowTile, p.Rows);
 
     if (warp == BWD_CTRL_WARP) {
         // ---------------------------------------------------------------- control warp
-        if ((tid & 31) == 0 && cur.Valid) {
+        if (lane == 0 && cur.Valid) {
             PrefetchTensorMap(&tmR1);
             PrefetchTensorMap(&tmR2);
             PrefetchTensorMap(&tmC1);
@@ -157,36 +165,39 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 loadTile(sC + slot * 2 * SM::TILE_BYTES, &tmC1, c0, &misc.BarFull[slot]);
                 loadTile(sC + slot * 2 * SM::TILE_BYTES + SM::TILE_BYTES, &tmC2, c0, &misc.BarFull[slot]);
             };
-            // S = R1 C1^T and dP = R2 C2^T: both operands K-major, D / 16 steps of 16 elements (32 bytes)
-            auto issueScores = [&](int slot) {
-                const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES, c2 = c1 + SM::TILE_BYTES;
+            // columns [64h, 64h + 64) of S = R1 C1^T and dP = R2 C2^T: both operands K-major, D / 16 steps of 16
+            // elements (32 bytes); the B operand starts 64 rows (8 KB per 128-byte block) into the column tile
+            auto issueScores = [&](int slot, int h) {
+                const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES + h * 8192, c2 = c1 + SM::TILE_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * BLOCK_BYTES + (ks & 3) * 32;
-                    MmaF16SS(tmem + BWD_S_COL, MakeSmemDesc(sR1a + off, 16, 1024, 128), MakeSmemDesc(c1 + off, 16, 1024, 128), IDESC_SS, ks > 0);
+                    MmaF16SS(tmem + BWD_S_COL + h * 64, MakeSmemDesc(sR1a + off, 16, 1024, 128), MakeSmemDesc(c1 + off, 16, 1024, 128), IDESC_SS, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * BLOCK_BYTES + (ks & 3) * 32;
-                    MmaF16SS(tmem + BWD_DP_COL, MakeSmemDesc(sR2a + off, 16, 1024, 128), MakeSmemDesc(c2 + off, 16, 1024, 128), IDESC_SS, ks > 0);
+                    MmaF16SS(tmem + BWD_DP_COL + h * 64, MakeSmemDesc(sR2a + off, 16, 1024, 128), MakeSmemDesc(c2 + off, 16, 1024, 128), IDESC_SS, ks > 0);
                 }
             };
-            // out1 += A1 C1 (and out2 += A2 C2): A from tensor memory (bf16, 8 columns per 16 rows of the tile's
-            // column dimension), B = the column tile read MN-major: 16 rows per step, D columns over KBLOCKS blocks
-            auto issueOutputs = [&](int slot, bool accumulate) {
+            // out1 += A1 C1 (and out2 += A2 C2) over the half's 64 tile columns = 4 steps of 16: A from tensor memory
+            // (quarter q of the tile keeps its bf16 pairs in columns 32q .. 32q+15), B = the column tile read MN-major
+            auto issueOutputs = [&](int slot, int h, bool accumulate) {
                 const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES, c2 = c1 + SM::TILE_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < TILE_ROWS / 16; ++ks) {
-                    const uint32_t aCol = (ks >> 2) * HALF_N + (ks & 3) * 8;
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int ks = h * 4 + k4;
+                    const uint32_t aCol = (ks >> 1) * 32 + (ks & 1) * 8;
                     MmaF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + aCol, MakeSmemDesc(c1 + ks * 16 * 128, BLOCK_BYTES, 1024, 128), IDESC_OUT,
-                        (accumulate || ks > 0) ? 1u : 0u);
+                        (accumulate || k4 > 0) ? 1u : 0u);
                 }
                 if (MODE_DKV) {
 #pragma unroll
-                    for (int ks = 0; ks < TILE_ROWS / 16; ++ks) {
-                        const uint32_t aCol = (ks >> 2) * HALF_N + (ks & 3) * 8;
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int ks = h * 4 + k4;
+                        const uint32_t aCol = (ks >> 1) * 32 + (ks & 1) * 8;
                         MmaF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + aCol, MakeSmemDesc(c2 + ks * 16 * 128, BLOCK_BYTES, 1024, 128), IDESC_OUT,
-                            (accumulate || ks > 0) ? 1u : 0u);
+                            (accumulate || k4 > 0) ? 1u : 0u);
                     }
                 }
             };
@@ -206,32 +217,40 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 prod.Advance();
                 ++issued;
             }
-            if (!WaitBar(&misc.BarR, 0)) {
+            if (!WaitBarA(&misc.BarR, 0, abortFlag)) {
                 fail(kDevTimeoutTma);
             }
+            // Tensor-pipe order per tile: out(h0, it-1), scores(h0, it), out(h1, it-1), scores(h1, it).  The outputs of a
+            // half must read its A columns before the next scores of that half overwrite them; the pipe runs in order.
             int it = 0;
             TTileIter ctl = cur;
             for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
                 const int slot = it % STAGES;
-                if (!WaitBar(&misc.BarFull[slot], (it / STAGES) & 1)) {
+                if (!WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag)) {
                     fail(kDevTimeoutTma);
                     break;
                 }
                 ++landed;
-                if (it > 0) {
-                    if (!WaitBar(&misc.BarP, (it - 1) & 1)) {
-                        fail(kDevTimeoutMma);
-                        break;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (it > 0) {
+                        if (!WaitBarA<true>(&misc.BarP[h], (it - 1) & 1, abortFlag)) {
+                            fail(kDevTimeoutMma);
+                            break;
+                        }
+                        TcFenceAfter();
+                        issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
                     }
                     TcFenceAfter();
-                    issueOutputs((it - 1) % STAGES, it - 1 > 0);
+                    issueScores(slot, h);
+                    MmaCommit(&misc.BarS[h]);
                 }
-                TcFenceAfter();
-                issueScores(slot);
-                MmaCommit(&misc.BarMma);
+                if (failed) {
+                    break;
+                }
                 if (it > 0 && prod.Valid) {
-                    // the slot of tile it-1 is free once its output MMAs have retired, i.e. when this commit completes
-                    if (!WaitBar(&misc.BarMma, it & 1)) {
+                    // the slot of tile it-1 is free once its output products have retired: the commit just made covers them
+                    if (!WaitBarA(&misc.BarS[1], it & 1, abortFlag)) {
                         fail(kDevTimeoutMma);
                         break;
                     }
@@ -239,19 +258,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     prod.Advance();
                     ++issued;
                 }
-                if (*(volatile int *)&misc.Abort) {
-                    failed = true;
-                }
             }
             if (!failed && it > 0) {
-                if (WaitBar(&misc.BarP, (it - 1) & 1)) {
-                    TcFenceAfter();
-                    issueOutputs((it - 1) % STAGES, it - 1 > 0);
-                } else {
-                    fail(kDevTimeoutMma);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (WaitBarA<true>(&misc.BarP[h], (it - 1) & 1, abortFlag)) {
+                        TcFenceAfter();
+                        issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                    } else {
+                        fail(kDevTimeoutMma);
+                        break;
+                    }
                 }
             }
-            MmaCommit(&misc.BarMma); // final phase (also releases arithmetic threads waiting after a failure)
+            MmaCommit(&misc.BarDone);
             if (failed) {
                 for (int t = landed; t < issued; ++t) {
                     WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
@@ -261,14 +281,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- arithmetic warps
-        const int half = tid >> 7;
+        const int quarter = tid >> 7;          // 32-column block of the tile
+        const int h = quarter >> 1;            // half: its own barriers and staging
+        const int hl = tid & (BWD_HALF_THREADS - 1);
         const int r = tid & (TILE_ROWS - 1);
         const int row = rowTile * TILE_ROWS + r;
-        const int colBase = half * HALF_N;
         const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const bool rowOk = row < p.Rows;
         const float g = p.GlobalScale ? *p.GlobalScale : 1.0f;
         const float cg = p.C * g;
+        const float dsMult = cg * kLog2;
         // per-row constants.  dQ pass: the row is a query (scale sq, lse, delta); dK/dV pass: the row is a key (sk, sv)
         float rowScale = 0, rowLse = 0, rowDelta = 0, rowSv = 0;
         if (rowOk) {
@@ -282,24 +304,28 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             }
         }
         const float rowMult = rowScale * cg;
-        const float dsMult = cg * kLog2;
-        const float alSign = MODE_DKV ? -1.0f : 1.0f;
+        const float2 rowMult2 = make_float2(rowMult, rowMult);
+        const float2 rowSvM2 = make_float2(rowSv * dsMult, rowSv * dsMult);
+        const float2 negDeltaM2 = make_float2(-rowDelta * dsMult, -rowDelta * dsMult);
 
         int spanS = 1, spanF = 0, spanRound = -1;
-        float pfA = 0, pfB = 0, pfC = 0;
+        // columns [64h, 64h + 64) of the tile are staged by the first 64 threads of the half, one tile ahead
+        float pfA = 0, pfT = 0, pfB = 0;
         auto fetchCols = [&](int c0) {
             pfA = 0;
+            pfT = 0;
             pfB = 0;
-            pfC = 0;
-            const int c = c0 + tid;
-            if (tid < TILE_ROWS && c < p.Rows) {
+            const int lc = h * 64 + hl;
+            const int c = c0 + lc;
+            if (hl < 64 && c < p.Rows) {
                 if (!MODE_DKV) {
                     pfA = p.KScale.Row(head)[c];
-                    pfB = p.VScale.Valid() ? p.VScale.Row(head)[c] : p.VVecScale;
+                    pfT = p.Slope * (float)lc;
+                    pfB = (p.VScale.Valid() ? p.VScale.Row(head)[c] : p.VVecScale) * dsMult;
                 } else {
                     pfA = p.QScale.Valid() ? p.QScale.Row(head)[c] : p.QkVecScale;
-                    pfB = p.Lse.Row(head)[c];
-                    pfC = p.DScale.Row(head)[c];
+                    pfT = -p.Lse.Row(head)[c] - p.Slope * (float)lc;
+                    pfB = -p.DScale.Row(head)[c] * dsMult;
                 }
             }
         };
@@ -307,7 +333,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             fetchCols(cur.J0);
         }
         bool failed = false;
-        bool aborted = false;
         int it = 0;
         while (cur.Valid) {
             if (cur.Round != spanRound) {
@@ -322,17 +347,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 spanRound = cur.Round;
             }
             const int buf = it & 1;
-            if (tid < TILE_ROWS) {
-                misc.ColA[buf][tid] = pfA;
-                misc.ColB[buf][tid] = pfB;
-                misc.ColC[buf][tid] = pfC;
+            if (hl < 64) {
+                misc.ColA[buf][h * 64 + hl] = pfA;
+                misc.ColT[buf][h * 64 + hl] = pfT;
+                misc.ColB[buf][h * 64 + hl] = pfB;
             }
             const int c0 = cur.J0;
             const int ls = spanS - c0, lf = min(spanF, p.Rows - 1) - c0; // span in tile-local columns
             const bool rowFull = ls <= 0 && lf >= TILE_ROWS - 1;
             const bool warpMasked = !__all_sync(0xffffffffu, rowFull);
-            aborted = BarRedOr(BAR_STAGE, BWD_ARITH_THREADS, failed || (*(volatile int *)&misc.Abort != 0));
-            if (aborted) {
+            // publishes the staged columns to the half; a failed wait is carried here so the half leaves together
+            if (BarRedOr(BAR_HALF0 + h, BWD_HALF_THREADS, failed || (*(volatile int *)&misc.Abort != 0))) {
+                failed = true;
                 break;
             }
             {
@@ -342,81 +368,87 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     fetchCols(nxt.J0);
                 }
             }
-            if (!WaitBar(&misc.BarMma, it & 1)) {
+            if (!WaitBarA(&misc.BarS[h], it & 1, abortFlag)) {
                 failed = true;
+                *(volatile int *)&misc.Abort = 1;
                 if (p.Status) {
                     atomicOr(p.Status, kDevTimeoutMma);
                 }
+                cur.Advance();
+                ++it;
+                continue; // to the half's next barrier
             }
             TcFenceAfter();
 
+            // exponent = u * rowMult + (ColT + rowConst):  dQ: ALiBi + rowOff - lse_i;  dK/dV: -lse_i - ALiBi with the sign of the
+            // transposed tile
             const float rowOff = -p.Slope * (float)(row - c0);
-            const float *colA = misc.ColA[buf] + colBase;
-            const float *colB = misc.ColB[buf] + colBase;
-            const float *colC = misc.ColC[buf] + colBase;
-            const float *alBuf = misc.Al + colBase;
+            const float rowConst = MODE_DKV ? -rowOff : rowOff - rowLse;
+            const float2 rowConst2 = make_float2(rowConst, rowConst);
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                // span clipped to this chunk, chunk-local: (unsigned)(c - lsQ) <= spanW  <=>  inside the span
-                const int cb = colBase + ch * 32;
-                const int lsC = max(ls, cb), lfC = min(lf, cb + 31);
+            for (int sc = 0; sc < 2; ++sc) {
+                const int cb = quarter * 32 + sc * 16; // first tile column of this step
+                // span clipped to this step, step-local: (unsigned)(c - lsQ) <= spanW  <=>  inside the span
+                const int lsC = max(ls, cb), lfC = min(lf, cb + 15);
                 const bool rowEmpty = lsC > lfC;
                 const int lsQ = lsC - cb;
                 const unsigned spanW = rowEmpty ? 0u : (unsigned)(lfC - lsC);
                 const bool anyCh = !warpMasked || __any_sync(0xffffffffu, !rowEmpty);
-                uint32_t a1[16], a2[16];
+                uint32_t a1[8], a2[8];
                 if (anyCh) {
-                    uint32_t sreg[32], preg[32];
-                    TmemLd32(tLane + BWD_S_COL + cb, sreg);
-                    TmemLd32(tLane + BWD_DP_COL + cb, preg);
-                    TmemWaitLd();
+                    float2 s[8], d[8];
+                    TmemLd16x2Pairs(tLane + BWD_S_COL + cb, tLane + BWD_DP_COL + cb, s, d);
+                    const float4 *A4 = reinterpret_cast<const float4 *>(misc.ColA[buf] + cb);
+                    const float4 *T4 = reinterpret_cast<const float4 *>(misc.ColT[buf] + cb);
+                    const float4 *B4 = reinterpret_cast<const float4 *>(misc.ColB[buf] + cb);
 #pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        const int lc = ch * 32 + c;
-                        float pv[2], dsv[2];
+                    for (int c = 0; c < 16; c += 4) {
+                        const float4 a4 = A4[c >> 2], t4 = T4[c >> 2], b4 = B4[c >> 2];
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
-                            const float ca = colA[lc + k];
-                            const float u = __uint_as_float(sreg[c + k]) * ca;
-                            const float z = fmaf(u, rowMult, alSign * (alBuf[lc + k] + rowOff));
-                            const float lse = MODE_DKV ? colB[lc + k] : rowLse;
-                            const float delta = MODE_DKV ? colC[lc + k] : rowDelta;
-                            const float sv = MODE_DKV ? rowSv : colB[lc + k];
-                            float pij = FastExp2(z - lse);
+                            const int i = (c >> 1) + k;
+                            const float2 ca = k ? make_float2(a4.z, a4.w) : make_float2(a4.x, a4.y);
+                            const float2 ct = k ? make_float2(t4.z, t4.w) : make_float2(t4.x, t4.y);
+                            const float2 cbv = k ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y);
+                            const float2 u = __fmul2_rn(s[i], ca);
+                            const float2 e = __ffma2_rn(u, rowMult2, __fadd2_rn(ct, rowConst2));
+                            float2 pij = FastExp2Pair(e);
                             if (warpMasked) {
-                                pij = (!rowEmpty && (unsigned)(c + k - lsQ) <= spanW) ? pij : 0.0f;
+                                pij.x = (!rowEmpty && (unsigned)(c + 2 * k - lsQ) <= spanW) ? pij.x : 0.0f;
+                                pij.y = (!rowEmpty && (unsigned)(c + 2 * k + 1 - lsQ) <= spanW) ? pij.y : 0.0f;
                             }
-                            const float dp = __uint_as_float(preg[c + k]) * sv;
-                            const float ds = pij * (dp - delta) * dsMult;
-                            pv[k] = pij;
-                            dsv[k] = ds * (MODE_DKV ? ca : ca); // dQ: dS * sk_j; dK: dS * sq_i (both are the column scale)
+                            const float2 dpv = MODE_DKV ? __ffma2_rn(d[i], rowSvM2, cbv) : __ffma2_rn(d[i], cbv, negDeltaM2);
+                            const float2 ds = __fmul2_rn(__fmul2_rn(pij, dpv), ca);
+                            a1[i] = PackBf16x2(ds.x, ds.y);
+                            a2[i] = PackBf16x2(pij.x, pij.y);
                         }
-                        a1[c >> 1] = PackBf16x2(dsv[0], dsv[1]);
-                        a2[c >> 1] = PackBf16x2(pv[0], pv[1]);
                     }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) {
+                    for (int k = 0; k < 8; ++k) {
                         a1[k] = 0;
                         a2[k] = 0;
                     }
                 }
-                // 32 bf16 values = 16 columns, written over columns this thread has already read
-                TmemSt16(tLane + BWD_S_COL + colBase + ch * 16, a1);
+                // 16 bf16 values = 8 columns, written over columns this thread has already read
+                TmemStN<8>(tLane + BWD_S_COL + quarter * 32 + sc * 8, a1);
                 if (MODE_DKV) {
-                    TmemSt16(tLane + BWD_DP_COL + colBase + ch * 16, a2);
+                    TmemStN<8>(tLane + BWD_DP_COL + quarter * 32 + sc * 8, a2);
                 }
             }
             TmemWaitSt();
             TcFenceBefore();
-            MbarArrive(&misc.BarP);
+            __syncwarp();
+            if (lane == 0) {
+                MbarArrive(&misc.BarP[h]);
+            }
             cur.Advance();
             ++it;
         }
 
         const int tiles = it;
-        if (!aborted && tiles > 0 && !failed) {
-            if (!WaitBar(&misc.BarMma, tiles & 1)) {
+        if (!failed && tiles > 0) {
+            if (!WaitBarA(&misc.BarDone, 0, abortFlag)) {
                 failed = true;
                 if (p.Status) {
                     atomicOr(p.Status, kDevTimeoutMma);
@@ -424,44 +456,46 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             }
             TcFenceAfter();
         }
-        if (!aborted && !failed) {
+        if (!failed) {
+            // each of the four threads of a row stores a quarter of the output columns
             const int esz = (p.GradDtype == TSA_F32) ? 4 : 2;
 #pragma unroll
             for (int o = 0; o < OUTPUTS; ++o) {
                 const P2D<char> &outp = (o == 0) ? p.Out1 : p.Out2;
-                char *oRow = outp.Row(rowOk ? row : 0) + ((size_t)head * D + half * HALF_D) * esz;
-#pragma unroll
-                for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-                    uint32_t v[32];
-                    if (tiles > 0) {
-                        TmemLd32(tLane + BWD_OUT_COL + o * D + half * HALF_D + c0, v);
-                        TmemWaitLd();
+                char *oRow = outp.Row(rowOk ? row : 0) + ((size_t)head * D + quarter * QUARTER_D) * esz;
+                uint32_t v[QUARTER_D];
+                if (tiles > 0) {
+                    if (QUARTER_D == 32) {
+                        TmemLd32(tLane + BWD_OUT_COL + o * D + quarter * QUARTER_D, v);
                     } else {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            v[c] = 0;
-                        }
+                        TmemLd16(tLane + BWD_OUT_COL + o * D + quarter * QUARTER_D, v);
                     }
-                    if (rowOk) {
-                        if (p.GradDtype == TSA_F32) {
-                            float4 *dst = reinterpret_cast<float4 *>(oRow + c0 * 4);
+                    TmemWaitLd();
+                } else {
 #pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                dst[c >> 2] = make_float4(__uint_as_float(v[c]) * p.GradMult, __uint_as_float(v[c + 1]) * p.GradMult,
-                                    __uint_as_float(v[c + 2]) * p.GradMult, __uint_as_float(v[c + 3]) * p.GradMult);
+                    for (int c = 0; c < QUARTER_D; ++c) {
+                        v[c] = 0;
+                    }
+                }
+                if (rowOk) {
+                    if (p.GradDtype == TSA_F32) {
+                        float4 *dst = reinterpret_cast<float4 *>(oRow);
+#pragma unroll
+                        for (int c = 0; c < QUARTER_D; c += 4) {
+                            dst[c >> 2] = make_float4(__uint_as_float(v[c]) * p.GradMult, __uint_as_float(v[c + 1]) * p.GradMult,
+                                __uint_as_float(v[c + 2]) * p.GradMult, __uint_as_float(v[c + 3]) * p.GradMult);
+                        }
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(oRow);
+#pragma unroll
+                        for (int c = 0; c < QUARTER_D; c += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float a = __uint_as_float(v[c + 2 * k]) * p.GradMult, b = __uint_as_float(v[c + 2 * k + 1]) * p.GradMult;
+                                w[k] = (p.GradDtype == TSA_BF16) ? PackBf16x2(a, b) : PackHalf2(a, b);
                             }
-                        } else {
-                            uint4 *dst = reinterpret_cast<uint4 *>(oRow + c0 * 2);
-#pragma unroll
-                            for (int c = 0; c < 32; c += 8) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const float a = __uint_as_float(v[c + 2 * k]) * p.GradMult, b = __uint_as_float(v[c + 2 * k + 1]) * p.GradMult;
-                                    w[k] = (p.GradDtype == TSA_BF16) ? PackBf16x2(a, b) : PackHalf2(a, b);
-                                }
-                                dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
+                            dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
                 }

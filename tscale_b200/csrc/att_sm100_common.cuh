@@ -196,6 +196,44 @@ __device__ __forceinline__ void TmemLd32Pairs(uint32_t taddr, float2 *s)
     }
 }
 
+// 16 consecutive columns from each of two tensor-memory addresses (same lane) as register pairs, one wait for both
+__device__ __forceinline__ void TmemLd16x2Pairs(uint32_t taddrA, uint32_t taddrB, float2 *a, float2 *b)
+{
+    uint64_t v[16];
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 s<16>;\n\t"
+        ".reg .b32 d<16>;\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {s0, s1, s2, s3, s4, s5, s6, s7, s8, s9, s10, s11, s12, s13, s14, s15}, [%16];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {d0, d1, d2, d3, d4, d5, d6, d7, d8, d9, d10, d11, d12, d13, d14, d15}, [%17];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t"
+        "mov.b64 %0, {s0, s1};\n\t"
+        "mov.b64 %1, {s2, s3};\n\t"
+        "mov.b64 %2, {s4, s5};\n\t"
+        "mov.b64 %3, {s6, s7};\n\t"
+        "mov.b64 %4, {s8, s9};\n\t"
+        "mov.b64 %5, {s10, s11};\n\t"
+        "mov.b64 %6, {s12, s13};\n\t"
+        "mov.b64 %7, {s14, s15};\n\t"
+        "mov.b64 %8, {d0, d1};\n\t"
+        "mov.b64 %9, {d2, d3};\n\t"
+        "mov.b64 %10, {d4, d5};\n\t"
+        "mov.b64 %11, {d6, d7};\n\t"
+        "mov.b64 %12, {d8, d9};\n\t"
+        "mov.b64 %13, {d10, d11};\n\t"
+        "mov.b64 %14, {d12, d13};\n\t"
+        "mov.b64 %15, {d14, d15};\n\t"
+        "}"
+        : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]), "=l"(v[4]), "=l"(v[5]), "=l"(v[6]), "=l"(v[7]), "=l"(v[8]), "=l"(v[9]), "=l"(v[10]), "=l"(v[11]), "=l"(v[12]), "=l"(v[13]), "=l"(v[14]), "=l"(v[15])
+        : "r"(taddrA), "r"(taddrB)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        a[i] = make_float2(__uint_as_float((uint32_t)v[i]), __uint_as_float((uint32_t)(v[i] >> 32)));
+        b[i] = make_float2(__uint_as_float((uint32_t)v[8 + i]), __uint_as_float((uint32_t)(v[8 + i] >> 32)));
+    }
+}
+
 // 2^x of a register pair, result again a pair
 __device__ __forceinline__ float2 FastExp2Pair(float2 x)
 {
