@@ -22,7 +22,7 @@
 // overlap: while the 8 warps of one half turn S / dP into A1 / A2, the MMAs of the other half (its output
 // products, then its S / dP of the next tile) run.  512 arithmetic threads, four per tile row, 32 columns each in
 // two steps of 16; packed f32x2 arithmetic on per-column factors staged in shared memory by each half's own warps;
-// a control warp issues TMA and MMA.  Row tiles stay in shared memory, column tiles stream through a TMA ring.
+// one warp issues the MMAs, one the TMA copies.  Row tiles stay in shared memory, column tiles stream through a TMA ring.
 // All waits are bounded; a failed wait is carried to the half's next named barrier so its threads leave together.
 #include "att_sm100_common.cuh"
 
@@ -31,9 +31,19 @@ namespace tsa {
 constexpr int BWD_ARITH_THREADS = 512;
 constexpr int BWD_HALF_THREADS = 256;
 constexpr int BWD_CTRL_WARP = BWD_ARITH_THREADS / 32;
-constexpr int BWD_THREADS = BWD_ARITH_THREADS + 32;
+constexpr int BWD_LOAD_WARP = BWD_CTRL_WARP + 1;
+constexpr int BWD_THREADS = BWD_ARITH_THREADS + 64;
 constexpr uint32_t BWD_TMEM_COLS = 512;
 constexpr uint32_t BWD_S_COL = 0, BWD_DP_COL = 128, BWD_OUT_COL = 256;
+
+// Phase trace for profiling builds (-DTSA_BWD_TRACE): clock64() per tile from lane 0 of the first warp of each half
+// and of the control warp of one CTA; tsa_debug_trace_bwd copies the buffer out.
+#ifdef TSA_BWD_TRACE
+__device__ long long g_traceBwd[4096];
+#define TRB(T, e) do { if (traceOn && (T) < 64) g_traceBwd[(T) * 16 + (e)] = clock64(); } while (0)
+#else
+#define TRB(T, e) do { } while (0)
+#endif
 
 struct TBwdParams {
     int HeadCount;
@@ -72,6 +82,7 @@ struct TBwdMisc {
     int Abort;
     uint64_t BarR;            // TMA: row tiles landed
     uint64_t BarFull[4];      // TMA: column stage landed
+    uint64_t BarEmpty[4];     // MMA warp -> loader: the stage's last output product has retired
     uint64_t BarS[2];         // control -> half h: S and dP columns of the half ready
     uint64_t BarP[2];         // half h -> control: A1 / A2 of the half written (8 warp arrivals)
     uint64_t BarDone;         // control -> all: every output product has retired
@@ -121,6 +132,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         MbarInit(&misc.BarR, 1);
         for (int s = 0; s < STAGES; ++s) {
             MbarInit(&misc.BarFull[s], 1);
+            MbarInit(&misc.BarEmpty[s], 1);
         }
         for (int h = 0; h < 2; ++h) {
             MbarInit(&misc.BarS[h], 1);
@@ -139,32 +151,59 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     TcFenceAfter();
     const uint32_t tmem = misc.TmemBase;
     const int *abortFlag = &misc.Abort;
+#ifdef TSA_BWD_TRACE
+    const bool traceOn = blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (warp == 0 || warp == 8 || warp == BWD_CTRL_WARP);
+#endif
 
     TTileIter cur;
     cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, rowTile, p.Rows);
 
-    if (warp == BWD_CTRL_WARP) {
-        // ---------------------------------------------------------------- control warp
+    if (warp == BWD_LOAD_WARP) {
+        // ---------------------------------------------------------------- loader warp: every TMA copy
         if (lane == 0 && cur.Valid) {
             PrefetchTensorMap(&tmR1);
             PrefetchTensorMap(&tmR2);
             PrefetchTensorMap(&tmC1);
             PrefetchTensorMap(&tmC2);
-            const uint32_t sR1a = SmemAddr(sR1), sR2a = SmemAddr(sR2), sCa = SmemAddr(sC);
-            TTileIter prod = cur;
-            int issued = 0, landed = 0;
-            bool failed = false;
             auto loadTile = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
 #pragma unroll
                 for (int kb = 0; kb < KBLOCKS; ++kb) {
                     TmaLoad2D(dst + kb * BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
                 }
             };
-            auto issueLoad = [&](int slot, int c0) {
+            MbarExpectTx(&misc.BarR, 2 * SM::TILE_BYTES);
+            loadTile(sR1, &tmR1, rowTile * TILE_ROWS, &misc.BarR);
+            loadTile(sR2, &tmR2, rowTile * TILE_ROWS, &misc.BarR);
+            int g = 0;
+            bool failed = false;
+            for (TTileIter prod = cur; prod.Valid && !failed; prod.Advance(), ++g) {
+                const int slot = g % STAGES;
+                if (g >= STAGES && !WaitBarA(&misc.BarEmpty[slot], ((g / STAGES) - 1) & 1, abortFlag)) {
+                    failed = true;
+                    *(volatile int *)&misc.Abort = 1;
+                    if (p.Status) {
+                        atomicOr(p.Status, kDevTimeoutMma);
+                    }
+                    break;
+                }
                 MbarExpectTx(&misc.BarFull[slot], 2 * SM::TILE_BYTES);
-                loadTile(sC + slot * 2 * SM::TILE_BYTES, &tmC1, c0, &misc.BarFull[slot]);
-                loadTile(sC + slot * 2 * SM::TILE_BYTES + SM::TILE_BYTES, &tmC2, c0, &misc.BarFull[slot]);
-            };
+                loadTile(sC + slot * 2 * SM::TILE_BYTES, &tmC1, prod.J0, &misc.BarFull[slot]);
+                loadTile(sC + slot * 2 * SM::TILE_BYTES + SM::TILE_BYTES, &tmC2, prod.J0, &misc.BarFull[slot]);
+            }
+            if (*(volatile int *)&misc.Abort) {
+                // drain copies that were requested, so none lands after the CTA is gone
+                WaitBar(&misc.BarR, 0);
+                for (int t = max(0, g - STAGES); t < g; ++t) {
+                    WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == BWD_CTRL_WARP) {
+        // ---------------------------------------------------------------- MMA warp: lane 0 issues every MMA
+        if (lane == 0 && cur.Valid) {
+            const uint32_t sR1a = SmemAddr(sR1), sR2a = SmemAddr(sR2), sCa = SmemAddr(sC);
+            bool failed = false;
             // columns [64h, 64h + 64) of S = R1 C1^T and dP = R2 C2^T: both operands K-major, D / 16 steps of 16
             // elements (32 bytes); the B operand starts 64 rows (8 KB per 128-byte block) into the column tile
             auto issueScores = [&](int slot, int h) {
@@ -208,29 +247,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     atomicOr(p.Status, code);
                 }
             };
-
-            MbarExpectTx(&misc.BarR, 2 * SM::TILE_BYTES);
-            loadTile(sR1, &tmR1, rowTile * TILE_ROWS, &misc.BarR);
-            loadTile(sR2, &tmR2, rowTile * TILE_ROWS, &misc.BarR);
-            for (int s = 0; s < STAGES && prod.Valid; ++s) {
-                issueLoad(s, prod.J0);
-                prod.Advance();
-                ++issued;
-            }
             if (!WaitBarA(&misc.BarR, 0, abortFlag)) {
                 fail(kDevTimeoutTma);
             }
             // Tensor-pipe order per tile: out(h0, it-1), scores(h0, it), out(h1, it-1), scores(h1, it).  The outputs of a
             // half must read its A columns before the next scores of that half overwrite them; the pipe runs in order.
+            // This thread never waits for its own MMAs, so the pipe stays fed; the loader refills a stage when the
+            // commit made after the stage's last output product completes.
             int it = 0;
             TTileIter ctl = cur;
             for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
                 const int slot = it % STAGES;
-                if (!WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag)) {
-                    fail(kDevTimeoutTma);
-                    break;
-                }
-                ++landed;
+                TRB(it, 8);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (it > 0) {
@@ -239,24 +267,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                             break;
                         }
                         TcFenceAfter();
+                        TRB(it, 9 + 2 * h);
                         issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                        if (h == 1) {
+                            MmaCommit(&misc.BarEmpty[(it - 1) % STAGES]);
+                        }
+                    }
+                    if (h == 0 && !WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag)) {
+                        fail(kDevTimeoutTma);
+                        break;
                     }
                     TcFenceAfter();
                     issueScores(slot, h);
                     MmaCommit(&misc.BarS[h]);
-                }
-                if (failed) {
-                    break;
-                }
-                if (it > 0 && prod.Valid) {
-                    // the slot of tile it-1 is free once its output products have retired: the commit just made covers them
-                    if (!WaitBarA(&misc.BarS[1], it & 1, abortFlag)) {
-                        fail(kDevTimeoutMma);
-                        break;
-                    }
-                    issueLoad((it - 1) % STAGES, prod.J0);
-                    prod.Advance();
-                    ++issued;
+                    TRB(it, 10 + 2 * h);
                 }
             }
             if (!failed && it > 0) {
@@ -272,11 +296,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 }
             }
             MmaCommit(&misc.BarDone);
-            if (failed) {
-                for (int t = landed; t < issued; ++t) {
-                    WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
-                }
-            }
         }
         __syncwarp();
     } else {
@@ -346,6 +365,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 }
                 spanRound = cur.Round;
             }
+            TRB(it, 4 * h);
             const int buf = it & 1;
             if (hl < 64) {
                 misc.ColA[buf][h * 64 + hl] = pfA;
@@ -361,6 +381,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 failed = true;
                 break;
             }
+            TRB(it, 4 * h + 1);
             {
                 TTileIter nxt = cur;
                 nxt.Advance();
@@ -379,6 +400,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 continue; // to the half's next barrier
             }
             TcFenceAfter();
+            TRB(it, 4 * h + 2);
 
             // exponent = u * rowMult + (ColT + rowConst):  dQ: ALiBi + rowOff - lse_i;  dK/dV: -lse_i - ALiBi with the sign of the
             // transposed tile
@@ -442,6 +464,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             if (lane == 0) {
                 MbarArrive(&misc.BarP[h]);
             }
+            TRB(it, 4 * h + 3);
             cur.Advance();
             ++it;
         }
@@ -644,3 +667,10 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
 }
 
 } // namespace tsa
+
+#ifdef TSA_BWD_TRACE
+extern "C" __attribute__((visibility("default"))) int tsa_debug_trace_bwd(long long *dst, int n)
+{
+    return (int)cudaMemcpyFromSymbol(dst, tsa::g_traceBwd, n * sizeof(long long));
+}
+#endif
