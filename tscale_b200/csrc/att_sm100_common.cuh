@@ -196,6 +196,61 @@ __device__ __forceinline__ void TmemLd32Pairs(uint32_t taddr, float2 *s)
     }
 }
 
+// 64 consecutive columns of this thread's lane as 32 register pairs, one wait for both loads
+__device__ __forceinline__ void TmemLd64Pairs(uint32_t taddr, float2 *s)
+{
+    uint64_t v[32];
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 t<32>;\n\t"
+        ".reg .b32 u<32>;\n\t"
+        ".reg .b32 a2;\n\t"
+        "add.u32 a2, %32, 32;\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, t16, t17, t18, t19, t20, t21, t22, t23, t24, t25, t26, t27, t28, t29, t30, t31}, [%32];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {u0, u1, u2, u3, u4, u5, u6, u7, u8, u9, u10, u11, u12, u13, u14, u15, u16, u17, u18, u19, u20, u21, u22, u23, u24, u25, u26, u27, u28, u29, u30, u31}, [a2];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t"
+        "mov.b64 %0, {t0, t1};\n\t"
+        "mov.b64 %1, {t2, t3};\n\t"
+        "mov.b64 %2, {t4, t5};\n\t"
+        "mov.b64 %3, {t6, t7};\n\t"
+        "mov.b64 %4, {t8, t9};\n\t"
+        "mov.b64 %5, {t10, t11};\n\t"
+        "mov.b64 %6, {t12, t13};\n\t"
+        "mov.b64 %7, {t14, t15};\n\t"
+        "mov.b64 %8, {t16, t17};\n\t"
+        "mov.b64 %9, {t18, t19};\n\t"
+        "mov.b64 %10, {t20, t21};\n\t"
+        "mov.b64 %11, {t22, t23};\n\t"
+        "mov.b64 %12, {t24, t25};\n\t"
+        "mov.b64 %13, {t26, t27};\n\t"
+        "mov.b64 %14, {t28, t29};\n\t"
+        "mov.b64 %15, {t30, t31};\n\t"
+        "mov.b64 %16, {u0, u1};\n\t"
+        "mov.b64 %17, {u2, u3};\n\t"
+        "mov.b64 %18, {u4, u5};\n\t"
+        "mov.b64 %19, {u6, u7};\n\t"
+        "mov.b64 %20, {u8, u9};\n\t"
+        "mov.b64 %21, {u10, u11};\n\t"
+        "mov.b64 %22, {u12, u13};\n\t"
+        "mov.b64 %23, {u14, u15};\n\t"
+        "mov.b64 %24, {u16, u17};\n\t"
+        "mov.b64 %25, {u18, u19};\n\t"
+        "mov.b64 %26, {u20, u21};\n\t"
+        "mov.b64 %27, {u22, u23};\n\t"
+        "mov.b64 %28, {u24, u25};\n\t"
+        "mov.b64 %29, {u26, u27};\n\t"
+        "mov.b64 %30, {u28, u29};\n\t"
+        "mov.b64 %31, {u30, u31};\n\t"
+        "}"
+        : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]), "=l"(v[4]), "=l"(v[5]), "=l"(v[6]), "=l"(v[7]), "=l"(v[8]), "=l"(v[9]), "=l"(v[10]), "=l"(v[11]), "=l"(v[12]), "=l"(v[13]), "=l"(v[14]), "=l"(v[15]), "=l"(v[16]), "=l"(v[17]), "=l"(v[18]), "=l"(v[19]), "=l"(v[20]), "=l"(v[21]), "=l"(v[22]), "=l"(v[23]), "=l"(v[24]), "=l"(v[25]), "=l"(v[26]), "=l"(v[27]), "=l"(v[28]), "=l"(v[29]), "=l"(v[30]), "=l"(v[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        s[i] = make_float2(__uint_as_float((uint32_t)v[i]), __uint_as_float((uint32_t)(v[i] >> 32)));
+    }
+}
+
 // 16 consecutive columns from each of two tensor-memory addresses (same lane) as register pairs, one wait for both
 __device__ __forceinline__ void TmemLd16x2Pairs(uint32_t taddrA, uint32_t taddrB, float2 *a, float2 *b)
 {
