@@ -247,7 +247,7 @@ def main():
             ops.att_bwd(cfg, item["q"], item["k"], item["v"], item["sk"], item["d_out"], item["out"], item["lse"],
                         masks[item["window"]], item["slope"], heads, qk_scale=item["sq"], v_scale=item["sv"], workspace=bwd_ws,
                         status=status)
-            launches[0] += 3  # dScale + dQ kernel + dK/dV kernel
+            launches[0] += 6  # dScale, bf16 widening of Q / K / V, dQ kernel, dK/dV kernel
         if gathered is not None:
             # NCCL runs the gather on its own stream: the next layer's kernels overlap with it
             pending.append(dist.all_gather_into_tensor(gathered[len(pending) % len(gathered)].view(-1), item["out"].view(-1), async_op=True))
@@ -298,7 +298,7 @@ def main():
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, status, world, dist, fl_step)
+        e2e = run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step)
 
     if rank != 0:
         if world > 1:
@@ -315,7 +315,14 @@ def main():
         "peak_fp8_measured": fp8_peak, "frac_fp8_measured": (achieved / fp8_peak) if fp8_peak else None,
         "peak_fp8_nominal": 4500.0, "frac_fp8_nominal": achieved / 4500.0,
         "ms_per_launch": dom_ms, "algorithmic_flops_per_launch": dom_flops, "traffic": None,
+        "timed": "CUDA events around the layer's tsa_att_fwd call (V-scale maximum kernel of a few microseconds + the attention kernel)",
     }
+    if args.workload == "prefill125m":
+        # ncu capture of this kernel on 2 fragments (profiles/fwd_sm100_e4m3_d64_fullcausal_2frag.md): 20.2 MB read, 0 written
+        # to DRAM while the kernel runs; traffic grows with the fragment count
+        roofline["traffic"] = 20.2e6 / 2 * w["frags"]
+        roofline["traffic_source"] = "dram bytes of a 2-fragment ncu capture scaled by fragments; algorithmic input bytes %.1f MB" % (
+            3 * w["frags"] * w["seq"] * heads * d / 1e6)
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
         sample = make_cpu_sample(w)
@@ -357,24 +364,24 @@ def measure_fp8_peak(torch, dev):
         return None
 
 
-def run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, status, world, dist, fl_step):
-    """Same step through the public call with HOST buffers: every step copies the layer inputs from pinned host
-    memory to the device, runs the layer, and copies the bf16 result back to pinned host memory."""
+def run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step):
+    """Same step through the public call with HOST buffers: every step copies the layer inputs (and dOut for the
+    training workload) from pinned host memory to the device, runs the layer, and copies the bf16 result (forward:
+    out; training: dQ, dK, dV) back to pinned host memory."""
     dev = layers[0]["q"].device
-    names = ("q", "k", "v", "sq", "sk", "sv")
+    names = ("q", "k", "v", "sq", "sk", "sv") + (("d_out",) if w["bwd"] else ())
     host_in = [{n: it[n].cpu().pin_memory() for n in names} for it in layers]
-    host_out = [torch.empty(it["out"].shape, dtype=it["out"].dtype).pin_memory() for it in layers]
+    n_out = 3 if w["bwd"] else 1
+    host_out = [[torch.empty(it["out"].shape, dtype=it["out"].dtype).pin_memory() for _ in range(n_out)] for it in layers]
     stage = [{n: torch.empty_like(layers[0][n]) for n in names} for _ in range(2)]
     out_stage = [torch.empty_like(layers[0]["out"]) for _ in range(2)]
+    grad_stage = [None, None]
     lse = layers[0]["lse"]
     h2d = torch.cuda.Stream(device=dev)
     d2h = torch.cuda.Stream(device=dev)
     main_s = torch.cuda.current_stream()
     h2d_bytes = sum(sum(t.numel() * t.element_size() for t in hi.values()) for hi in host_in)
-    d2h_bytes = sum(t.numel() * t.element_size() for t in host_out)
-    if w["bwd"]:
-        return {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                "note": "end-to-end leg implemented for forward workloads"}
+    d2h_bytes = sum(sum(t.numel() * t.element_size() for t in ho) for ho in host_out)
 
     def step():
         free_in = [None, None]
@@ -394,12 +401,19 @@ def run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, status, w
             s = stage[sl]
             ops.att_fwd(cfg, s["q"], s["k"], s["v"], s["sk"], masks[it["window"]], it["slope"], heads, qk_scale=s["sq"],
                         v_scale=s["sv"], out=out_stage[sl], lse=lse, workspace=workspace, status=status)
+            results = [out_stage[sl]]
+            if w["bwd"]:
+                grad_stage[sl] = ops.att_bwd(cfg, s["q"], s["k"], s["v"], s["sk"], s["d_out"], out_stage[sl], lse, masks[it["window"]],
+                                             it["slope"], heads, qk_scale=s["sq"], v_scale=s["sv"], workspace=bwd_ws, status=status)
+                results = list(grad_stage[sl])
             done = torch.cuda.Event()
             done.record(main_s)
             free_in[sl] = done
             with torch.cuda.stream(d2h):
                 d2h.wait_event(done)
-                host_out[i].copy_(out_stage[sl], non_blocking=True)
+                for dst, src in zip(host_out[i], results):
+                    dst.copy_(src, non_blocking=True)
+                    src.record_stream(d2h)
                 fo = torch.cuda.Event()
                 fo.record(d2h)
             free_out[sl] = fo

@@ -211,7 +211,9 @@ def run(args, rank, world, local_rank):
     roofline = {"bound": "hbm", "kernel": "DecodePartialKernel<128> + DecodeCombineKernel<128>", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_source": "MEASURED_PEAKS.json copy bandwidth (%s)" % peaks["_source"], "frac_of_8tbs_nominal": achieved / 8000.0,
-                "ms_per_launch": k_ms, "algorithmic_bytes_per_launch": k_bytes, "traffic": None}
+                "ms_per_launch": k_ms, "algorithmic_bytes_per_launch": k_bytes,
+                # ncu capture at this size (profiles/decode_partial_i8_d128_64seq.md): 1.1588 GB of DRAM traffic for 1.166 GB algorithmic
+                "traffic": 0.994 * k_bytes, "traffic_source": "dram bytes / algorithmic bytes = 0.994 in the ncu capture of this workload"}
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
