@@ -402,8 +402,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                     mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
                 }
             } else {
-                mx = chunkMax(std::false_type(), 0, mx);
-                mx = chunkMax(std::false_type(), 1, mx);
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    mx = chunkMax(std::false_type(), ch, mx);
+                }
             }
             const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
             float zmax = mx;
@@ -435,9 +437,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
             // an empty row gets eoff = -inf so that every weight is 0 whatever the compare above let through
             const float eoff = rowEmpty && warpMasked ? -INFINITY : rowOff - m + 7.0f;
             const float2 eoff2 = make_float2(eoff, eoff);
-            uint32_t pk[2][8], pl[2][8];
             auto chunkWeights = [&](auto maskedTag, auto residTag, int ch) {
                 constexpr bool RESID = decltype(residTag)::value;
+                uint32_t pk[8], pl[8];
                 float2 u[16];
                 loadScaled(maskedTag, ch, u);
 #pragma unroll
@@ -451,18 +453,25 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                         e[k] = HAS_VSCALE ? __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + ch * 32 + 2 * (c + k))) : w;
                     }
                     const uint32_t hi4 = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
-                    pk[ch][c >> 1] = hi4;
+                    pk[c >> 1] = hi4;
                     if (RESID) {
-                        pl[ch][c >> 1] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
+                        pl[c >> 1] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
                     }
+                }
+                // the packed weights of a chunk land in S columns of chunk 0 of this half, which has been read by then
+                TmemStN<8>(tLane + colBase + ch * 8, pk);
+                if (RESID) {
+                    TmemStN<8>(tLane + colBase + 16 + ch * 8, pl);
                 }
             };
             auto zeroChunk = [&](int ch) {
+                uint32_t z[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    pk[ch][k] = 0;
-                    pl[ch][k] = 0;
+                    z[k] = 0;
                 }
+                TmemStN<8>(tLane + colBase + ch * 8, z);
+                TmemStN<8>(tLane + colBase + 16 + ch * 8, z);
             };
             if (warpMasked) {
                 // masked tiles always carry the residual (tileMasked is true whenever any warp is masked)
@@ -477,17 +486,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                     zeroChunk(1);
                 }
             } else if (tileMasked) {
-                chunkWeights(std::false_type(), std::true_type(), 0);
-                chunkWeights(std::false_type(), std::true_type(), 1);
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    chunkWeights(std::false_type(), std::true_type(), ch);
+                }
             } else {
-                chunkWeights(std::false_type(), std::false_type(), 0);
-                chunkWeights(std::false_type(), std::false_type(), 1);
-            }
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                TmemStN<8>(tLane + colBase + ch * 8, pk[ch]);
-                if (tileMasked) {
-                    TmemStN<8>(tLane + colBase + 16 + ch * 8, pl[ch]);
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    chunkWeights(std::false_type(), std::false_type(), ch);
                 }
             }
             TmemWaitSt();
