@@ -407,7 +407,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             const float rowOff = -p.Slope * (float)(row - c0);
             const float rowConst = MODE_DKV ? -rowOff : rowOff - rowLse;
             const float2 rowConst2 = make_float2(rowConst, rowConst);
-#pragma unroll
+#pragma unroll 1
             for (int sc = 0; sc < 2; ++sc) {
                 const int cb = quarter * 32 + sc * 16; // first tile column of this step
                 // span clipped to this step, step-local: (unsigned)(c - lsQ) <= spanW  <=>  inside the span
