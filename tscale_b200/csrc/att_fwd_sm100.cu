@@ -40,6 +40,15 @@ constexpr int TILE_N = 128;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O_COL = 128;
 
+// Phase trace for profiling builds (-DTSA_FWD_TRACE): thread 0 of a few CTAs records clock64() at the phases of
+// a CTA's life; tsa_debug_trace copies the buffer out.
+#ifdef TSA_FWD_TRACE
+__device__ long long g_trace[4096];
+#define TRC(e) do { if (traceOn) g_trace[traceSlot * 16 + (e)] = clock64(); } while (0)
+#else
+#define TRC(e) do { } while (0)
+#endif
+
 struct TFwdParams {
     int HeadCount;
     int OutRows;      // rows of out that may be written
@@ -111,6 +120,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     const int tid = threadIdx.x, warp = tid >> 5;
     const int head = blockIdx.y;
     const int qTile = gridDim.x - 1 - blockIdx.x; // late (long) rows first
+#ifdef TSA_FWD_TRACE
+    const bool traceOn = tid == 0 && blockIdx.y == 5 && (blockIdx.x % 37) == 3 && blockIdx.x / 37 < 12;
+    const int traceSlot = blockIdx.x / 37;
+#endif
+    TRC(0);
 
     if ((SmemAddr(smem) & 1023u) != 0) {
         // the launch did not honour the alignment: report instead of computing on mis-swizzled tiles
@@ -119,6 +133,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
         }
         return;
     }
+    // the span groups of the tile are fetched first: two dependent global loads that overlap with the set-up below
+    TTileIter cur;
+    cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, qTile, p.KeyRows);
+    TRC(1);
     if (tid == 0) {
         MbarInit(&misc.BarQ, 1);
         for (int s = 0; s < STAGES; ++s) {
@@ -141,8 +159,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     TcFenceAfter();
     const uint32_t tmem = misc.TmemBase;
 
-    TTileIter cur;
-    cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, qTile, p.KeyRows);
+    TRC(2);
 
     if (warp == CTRL_WARP) {
         // ---------------------------------------------------------------- control warp
@@ -346,6 +363,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                 }
             }
             TcFenceAfter();
+            if (it < 4) {
+                TRC(3 + 2 * it);
+            }
 
             // The scores are read from tensor memory twice, 32 columns at a time (first for the row maximum, then for
             // the weights), which keeps the live registers of a thread at one chunk instead of its whole half row.
@@ -502,11 +522,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
                 misc.TileMasked[it & 1] = tileMasked ? 1 : 0;
             }
             MbarArrive(&misc.BarP);
+            if (it < 4) {
+                TRC(4 + 2 * it);
+            }
             cur = nxt;
             ++it;
         }
 
         const int tiles = it;
+        TRC(11);
         if (tiles > 0 && !failed) {
             if (!WaitBar(&misc.BarMma, tiles & 1)) {
                 failed = true;
@@ -519,9 +543,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
         if (failed) {
             *(volatile int *)&misc.Abort = 1;
         }
+        TRC(14);
         // total weight of the row: both halves
         misc.RowX[half][r] = lacc2.x + lacc2.y;
         BarSync(BAR_STAGE, SOFTMAX_THREADS);
+        TRC(15);
         failed = failed || (*(volatile int *)&misc.Abort != 0);
         if (!failed) {
             const float lTot = (lacc2.x + lacc2.y + misc.RowX[half ^ 1][r]) * (1.0f / 128.0f) + exp2f(-m);
@@ -573,11 +599,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
             }
         }
     }
+    TRC(12);
     TcFenceBefore();
     __syncthreads();
     if (warp == CTRL_WARP) {
         TmemDealloc(tmem, TMEM_COLS);
     }
+    TRC(13);
 }
 
 // per head maximum of the V scale plane (normalises the weights' e4m3 range).  Scales are non-negative, so
@@ -809,3 +837,10 @@ int LaunchScoresI8(tsa_ptr2d qk, tsa_ptr2d qv, int headCount, int headDim, int l
 }
 
 } // namespace tsa
+
+#ifdef TSA_FWD_TRACE
+extern "C" __attribute__((visibility("default"))) int tsa_debug_trace(long long *dst, int n)
+{
+    return (int)cudaMemcpyFromSymbol(dst, tsa::g_trace, n * sizeof(long long));
+}
+#endif
