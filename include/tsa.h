@@ -144,6 +144,18 @@ enum tsa_quant_kind { TSA_QUANT_RMS = 0, TSA_QUANT_ABSMAX = 1 };
 int tsa_quant_rows(int kind, int srcDtype, int dstDtype, float vecScale, tsa_ptr2d src, tsa_ptr2d dst,
     tsa_ptr2d scale, int len, int tile, tsa_stream_t stream);
 
+/* ---- producer of the attention inputs ("next" scope row: the step on the input side of the path) ------------
+ * Replaces the TStoreRowTileNormalizeRope epilogue of the QKV projection used stand-alone (code/gpt/compute/
+ * gpt_rope.cuh:4-66: normalise, rope, store, write the scale) and, with rope absent, TStoreRowTileNormalize
+ * (lib/cuda/cuda_matmul.cuh:147-204).  Per row and head: scale = sqrt(mean(x^2)) * vecScale, y = x / scale, then
+ * the rope rotation as the CPU model defines it (code/gpt/att/rope.cpp:28-46: inside every 64-element block elements
+ * k and k + 32 rotate by the angle whose cosine is rope[row][block + k] and sine rope[row][block + k + 32] * ropeDir;
+ * ropeDir = -1 rotates back), then dst = sat_rne(y) as i8 or e4m3 and scale plane f32 [H][len].  rope: table
+ * [>= len][headDim] of f32 or f16 (the reference's TRopeFloat), absent = no rotation.  Rows in [len, dst.ysize) are
+ * zeroed.  srcDtype: TSA_F32, TSA_F16 or TSA_BF16; headDim 64, 128, 256 or 512. */
+int tsa_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, tsa_ptr2d src, tsa_ptr2d rope, int ropeDtype,
+    float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, tsa_stream_t stream);
+
 /* ---- KV-cache decode -------------------------------------------------------------------------
  * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
  * batched over sequences.  Per sequence the cache is caller-owned device memory:

@@ -133,6 +133,50 @@ def quant_rows(kind, dst, vec_scale, src, tile):
 
 
 # ------------------------------------------------------------------------------------------------
+# producer of the attention inputs: normalise per head, rope, quantise
+def fill_rope(width, max_len, use_ref=False):
+    """Rope table [max_len][width] (rope.cpp:4-24): per 64-element block 32 cosines then 32 sines."""
+    out = np.zeros((max_len, width), dtype=np.float32)
+    (ref() if use_ref else lib()).__getattr__("ref_fill_rope" if use_ref else "oracle_fill_rope")(
+        width, max_len, out.ctypes.data_as(_fp))
+    return out
+
+
+def apply_rope(rope, data, direction=1.0, use_ref=False):
+    """Rotates a copy of data [len][dim] with rope [len][headDim] (rope.cpp:28-61)."""
+    rope, rp = _f(rope)
+    data = np.array(data, dtype=np.float32, order="C", copy=True)
+    ln, dim = data.shape
+    fn = ref().ref_apply_rope if use_ref else lib().oracle_apply_rope
+    fn(rope.shape[1], ln, dim, c_float(direction), rp, data.ctypes.data_as(_fp))
+    return data
+
+
+def normalize_state_ref(src, heads):
+    """The reference's fp32 NormalizeState (gpt_cpu.cpp:297-324): every head scaled to unit RMS."""
+    src, sp = _f(src)
+    out = np.zeros_like(src)
+    ref().ref_normalize_state_f32(src.shape[0], src.shape[1], heads, sp, out.ctypes.data_as(_fp))
+    return out
+
+
+def norm_rope_quant(dst, vec_scale, src, rope, head_dim, direction=1.0):
+    """Per-head RMS normalise, rope (None: no rotation), quantise.
+    Returns (bytes [len][dim] int8, scale [dim/head_dim][len] f32, roped fp32 [len][dim])."""
+    src, sp = _f(src)
+    ln, dim = src.shape
+    out = np.zeros((ln, dim), dtype=np.int8)
+    scale = np.zeros((dim // head_dim, ln), dtype=np.float32)
+    roped = np.zeros((ln, dim), dtype=np.float32)
+    rp = None
+    if rope is not None:
+        rope, rp = _f(rope)
+    lib().oracle_norm_rope_quant({"i8": 0, "e4m3": 1}[dst], c_float(vec_scale), ln, dim, head_dim, c_float(direction), sp, rp,
+                                 out.ctypes.data_as(_bp), scale.ctypes.data_as(_fp), roped.ctypes.data_as(_fp))
+    return out, scale, roped
+
+
+# ------------------------------------------------------------------------------------------------
 # spans
 def window_spans(frag_lens, window):
     """Causal window spans of TScale (att/sliding_window.cpp:80-87,211-222): row i of a fragment

@@ -152,6 +152,33 @@ int ref_group_attention_64_128(int len, const int *spans, const int *spanPtr, in
     return n;
 }
 
+// FillRopeBuf / ApplyRope (code/gpt/att/rope.cpp:4-61) and NormalizeState (gpt_cpu.cpp:297-324): the producer of the
+// attention inputs on the CPU path (gpt_cpu.cpp:625-630: normalise per head, then rope on the query / key vectors)
+void ref_fill_rope(int width, int maxLen, float *rope)
+{
+    TArray2D<float> buf;
+    FillRopeBuf(&buf, width, maxLen);
+    StoreArr(buf, rope);
+}
+
+// data [len][dim] in place; rope [len][width]
+void ref_apply_rope(int width, int len, int dim, float dir, const float *rope, float *data)
+{
+    TArray2D<float> buf, arr;
+    FillArr(&buf, rope, width, len);
+    FillArr(&arr, data, dim, len);
+    ApplyRope(buf, dir, &arr);
+    StoreArr(arr, data);
+}
+
+void ref_normalize_state_f32(int len, int dim, int headCount, const float *src, float *dst)
+{
+    TArray2D<float> arr;
+    FillArr(&arr, src, dim, len);
+    TArray2D<float> res = NormalizeState(arr, headCount);
+    StoreArr(res, dst);
+}
+
 int ref_float2i8(float x)
 {
     return Float2I8(x);

@@ -552,3 +552,84 @@ int oracle_group_attention_64_128(int len, const int *spans, const int *spanPtr,
 }
 
 }
+
+///////////////////////////////////////////////////////////////////////////////////////////////////
+// producer of the attention inputs: per-head RMS normalise, rope, quantise
+// FillRopeBuf (code/gpt/att/rope.cpp:4-24): theta = 500000; per 64-element block the first 32 entries hold cos, the
+// next 32 sin of angle t * theta^(-(2k)/width), k = block/2 + index
+extern "C" void oracle_fill_rope(int width, int maxLen, float *rope)
+{
+    float theta = 500000;
+    std::vector<float> freq;
+    for (int k = 0; k < width / 2; ++k) {
+        freq.push_back((float)exp(-logf(theta) * (k * 2. / width))); // float log, double product and exp, as the reference's overloads resolve
+    }
+    for (int t = 0; t < maxLen; ++t) {
+        for (int base = 0; base < width; base += 64) {
+            for (int k = 0; k < 32; ++k) {
+                float angle = t * freq[base / 2 + k];
+                rope[(size_t)t * width + base + k] = cosf(angle);
+                rope[(size_t)t * width + base + k + 32] = sinf(angle);
+            }
+        }
+    }
+}
+
+// ReferenceApplyRope (rope.cpp:28-46): inside every head, elements k and k + 32 of a 64-element block rotate by the
+// block's angle; dir = -1 rotates back.  data [len][dim] in place, rope [len][headDim]
+extern "C" void oracle_apply_rope(int headDim, int len, int dim, float dir, const float *rope, float *data)
+{
+    for (int t = 0; t < len; ++t) {
+        float *row = data + (size_t)t * dim;
+        const float *rp = rope + (size_t)t * headDim;
+        for (int offset = 0; offset < dim; offset += headDim) {
+            for (int blk = 0; blk < headDim; blk += 64) {
+                for (int k = 0; k < 32; ++k) {
+                    float v0 = row[offset + blk + k], v1 = row[offset + blk + k + 32];
+                    float cosValue = rp[blk + k];
+                    float sinValue = rp[blk + k + 32] * dir;
+                    row[offset + blk + k] = v0 * cosValue - v1 * sinValue;
+                    row[offset + blk + k + 32] = v0 * sinValue + v1 * cosValue;
+                }
+            }
+        }
+    }
+}
+
+// normalise (row_tile_scale.cuh:11-34 / cuda_matmul.cuh:147-204: discr = sqrt(sum2 / D) * vecScale, x / discr), rope
+// (gpt_rope.cuh:37-51 applies it to the normalised vector), quantise; roped [len][dim] (may be null) receives the
+// fp32 vectors before quantisation.  dstType 0 = i8, 1 = e4m3; scale [dim/headDim][len]
+extern "C" void oracle_norm_rope_quant(int dstType, float vecScale, int len, int dim, int headDim, float dir,
+    const float *src, const float *rope, int8_t *dst, float *scale, float *roped)
+{
+    int heads = dim / headDim;
+    std::vector<float> rowBuf(dim);
+    for (int t = 0; t < len; ++t) {
+        for (int h = 0; h < heads; ++h) {
+            const float *s = src + (size_t)t * dim + h * headDim;
+            float sum2 = 0;
+            for (int x = 0; x < headDim; ++x) {
+                sum2 += s[x] * s[x];
+            }
+            float discr = 0;
+            if (sum2 > 0) {
+                discr = sqrtf(sum2 / headDim) * vecScale;
+            }
+            float mult = (discr > 0) ? 1 / discr : 0;
+            for (int x = 0; x < headDim; ++x) {
+                rowBuf[h * headDim + x] = s[x] * mult;
+            }
+            scale[(size_t)h * len + t] = discr;
+        }
+        if (rope) {
+            oracle_apply_rope(headDim, 1, dim, dir, rope + (size_t)t * headDim, rowBuf.data());
+        }
+        for (int x = 0; x < dim; ++x) {
+            float y = rowBuf[x];
+            if (roped) {
+                roped[(size_t)t * dim + x] = y;
+            }
+            dst[(size_t)t * dim + x] = (int8_t)(dstType == 0 ? oracle_f32_to_i8(y) : oracle_f32_to_e4m3(y));
+        }
+    }
+}

@@ -63,6 +63,19 @@ def decode_case(name, seed, ctx, heads, d, width, slope):
     print(name, "ctx", ctx)
 
 
+def producer_case(name, seed, rows, heads, d):
+    """NormalizeState + ApplyRope of the reference (gpt_cpu.cpp:297-324, 625-630; att/rope.cpp) on seeded projections."""
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal((rows, heads * d)) * 2.0).astype(np.float32)
+    x[3] = 0
+    table = O.fill_rope(d, rows, use_ref=True)
+    norm = O.normalize_state_ref(x, heads)
+    fwd = O.apply_rope(table, norm, 1.0, use_ref=True)
+    back = O.apply_rope(table, fwd, -1.0, use_ref=True)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), heads=heads, d=d, src=x, rope=table, roped=fwd, unroped=back)
+    print(name, rows, heads, d)
+
+
 def main():
     assert O.ref() is not None, "build oracle/_ref first (make -C oracle ref)"
     # window-64 layers of the reference use ALiBi slope 0.5, wide layers slope 0 (model_dim.cpp:83-90)
@@ -77,6 +90,8 @@ def main():
     decode_case("decode_wide", 11, 333, 3, 64, 1024, 0.0)
     decode_case("decode_w0", 12, 17, 2, 128, 0, 0.0)
     decode_case("decode_first", 13, 1, 2, 64, 64, 0.5)
+    producer_case("producer_d64", 20, 150, 3, 64)
+    producer_case("producer_d128", 21, 90, 2, 128)
     # 8-bit code points: ConvertE4toFloat for all bytes, Float2I8 on a grid
     e4 = np.array([O.ref().ref_e4m3_to_float(i) for i in range(256)], dtype=np.float32)
     grid = np.concatenate([np.linspace(-130, 130, 2081), np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5])]).astype(np.float32)

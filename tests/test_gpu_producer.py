@@ -1,0 +1,79 @@
+"""GPU parity of tsa_norm_rope_quant (per-head RMS normalise, rope, quantise) against the CPU oracle, and the chain
+producer -> attention forward against the oracle chain."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _codes_close(got, want, dst):
+    """Bytes equal except where the value sat on a rounding boundary: there the neighbouring code is accepted."""
+    got = got.astype(np.int8)
+    want = want.astype(np.int8)
+    diff = got != want
+    frac = diff.mean()
+    if dst == "i8":
+        step = np.abs(got.astype(np.int32) - want.astype(np.int32))
+    else:
+        step = np.abs(O.dequant(got, "e4m3") - O.dequant(want, "e4m3")) / np.maximum(np.abs(O.dequant(want, "e4m3")), 2.0 ** -6)
+        step = np.where(diff, np.ceil(step * 8 - 1e-6), 0)  # in units of the e4m3 spacing (1/8 relative)
+    return frac, float(step.max()) if step.size else 0.0
+
+
+@pytest.mark.parametrize("d,heads", [(64, 12), (128, 5)])
+@pytest.mark.parametrize("dst", ["i8", "e4m3"])
+@pytest.mark.parametrize("src_dtype,rope_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float16), (torch.float16, None)])
+@pytest.mark.parametrize("direction", [1.0, -1.0])
+def test_norm_rope_quant(d, heads, dst, src_dtype, rope_dtype, direction):
+    from tscale_b200 import ops
+    rng = np.random.default_rng(31)
+    rows = 777
+    src_t = torch.from_numpy(rng.standard_normal((rows, heads * d)).astype(np.float32) * 3.0).to(src_dtype)
+    src_t[5] = 0  # an all-zero row: scale 0, zeros out
+    rope_np = O.fill_rope(d, rows)
+    rope_t = None if rope_dtype is None else torch.from_numpy(rope_np).to(rope_dtype)
+    vec_scale = 1 / 24.0 if dst == "i8" else 1 / 4.0
+    want_b, want_s, _ = O.norm_rope_quant(dst, vec_scale, src_t.float().numpy(), None if rope_t is None else rope_t.float().numpy(), d, direction)
+    got_b, got_s = ops.norm_rope_quant(src_t.to(DEV), None if rope_t is None else rope_t.to(DEV), dst, heads, d, vec_scale, direction)
+    torch.cuda.synchronize()
+    got_s = got_s.cpu().numpy()
+    assert np.allclose(got_s, want_s, rtol=2e-6, atol=0), float(np.abs(got_s - want_s).max())
+    assert got_s[:, 5].max() == 0
+    frac, step = _codes_close(got_b.cpu().numpy().view(np.int8), want_b, dst)
+    assert frac < 2e-3 and step <= 1, (frac, step)
+
+
+def test_producer_feeds_attention():
+    """fp32 projections -> tsa_norm_rope_quant -> tsa_att_fwd against the oracle chain on the same inputs."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(32)
+    frag_lens, heads, d, window, slope = [300, 212], 4, 64, 64, 0.5
+    rows = sum(frag_lens)
+    rope_np = O.fill_rope(d, rows)
+    proj = {n: (rng.standard_normal((rows, heads * d)) * 2.0).astype(np.float32) for n in ("q", "k", "v")}
+    vec = 1 / 4.0
+    dev_in, deq = {}, {}
+    for n in ("q", "k", "v"):
+        rope = rope_np if n != "v" else None
+        b, s, _ = O.norm_rope_quant("e4m3", vec, proj[n], rope, d)
+        deq[n] = (O.dequant(b, "e4m3").reshape(rows, heads, d) * s.T[:, :, None]).reshape(rows, heads * d).astype(np.float32)
+        dev_in[n] = ops.norm_rope_quant(torch.from_numpy(proj[n]).to(DEV), None if rope is None else torch.from_numpy(rope).to(DEV),
+                                        "e4m3", heads, d, vec)
+    spans, ptr = O.window_spans(frag_lens, window)
+    ref = O.att_fwd(deq["q"], deq["k"], deq["v"], spans, ptr, heads, slope)
+    cfg = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.float32)
+    mask = ops.Mask.window(frag_lens, window)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out, lse = ops.att_fwd(cfg, dev_in["q"][0], dev_in["k"][0], dev_in["v"][0], dev_in["k"][1], mask, slope, heads,
+                           qk_scale=dev_in["q"][1], v_scale=dev_in["v"][1], status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    vmax = float(np.abs(deq["v"]).max())
+    mx, mean = util.err_stats(util.to_np(out), ref["out"])
+    # a handful of bytes may sit one code off a rounding boundary: tolerance relative to the value range as elsewhere
+    assert mx < max(util.OUT_MAX_ABS, 0.06 * vmax) and mean < max(util.OUT_MEAN_ABS, 0.01 * vmax), util.describe(util.to_np(out), ref["out"])

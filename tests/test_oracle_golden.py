@@ -90,3 +90,17 @@ def test_quantisers_small():
     b, s = O.quant_rows("rms", "i8", 1 / 24.0, x, 32)
     rms = np.sqrt(np.mean(x[0] ** 2))
     assert np.isclose(s[0, 0], rms / 24.0, rtol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["producer_d64", "producer_d128"])
+def test_producer_against_reference_fixture(golden_dir, name):
+    """Rope table and rotation bit for bit; the normalised vectors to a few ulp (the reference multiplies by
+    sqrt(D / sum2), the quantising path divides by sqrt(sum2 / D) like the GPU store op)."""
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    heads, d = int(z["heads"]), int(z["d"])
+    rows = z["src"].shape[0]
+    assert np.array_equal(O.fill_rope(d, rows), z["rope"])
+    assert np.array_equal(O.apply_rope(z["rope"], z["roped"], -1.0), z["unroped"])
+    _, scale, roped = O.norm_rope_quant("i8", 1.0, z["src"], z["rope"], d)
+    assert np.abs(roped - z["roped"]).max() < 4e-6 * np.abs(z["roped"]).max()
+    assert scale[:, 3].max() == 0 and np.abs(roped[3]).max() == 0

@@ -63,3 +63,33 @@ def test_decode(ctx, heads, d, width, slope):
     a = O.decode_step(kc, ks, vc, vs, q8, qs, heads, width, slope, exp_mode="poly")
     b = O.decode_step(kc, ks, vc, None, q8, None, heads, width, slope, use_ref=True)
     assert np.array_equal(a, b)
+
+
+def test_rope_table_and_rotation_bit_exact():
+    """FillRopeBuf / ApplyRope (code/gpt/att/rope.cpp) restated in the oracle: bit for bit, both directions."""
+
+    rng = np.random.default_rng(41)
+    for d, heads in ((64, 3), (128, 4)):
+        table = O.fill_rope(d, 333)
+        assert np.array_equal(table, O.fill_rope(d, 333, use_ref=True))
+        x = rng.standard_normal((333, heads * d)).astype(np.float32)
+        for direction in (1.0, -1.0):
+            assert np.array_equal(O.apply_rope(table, x, direction), O.apply_rope(table, x, direction, use_ref=True))
+        # rotating there and back is the identity up to rounding
+        back = O.apply_rope(table, O.apply_rope(table, x, 1.0), -1.0)
+        assert np.abs(back - x).max() < 1e-5
+
+
+def test_normalise_rope_against_reference_chain():
+    """oracle_norm_rope_quant's fp32 stage against NormalizeState + ApplyRope of the reference (gpt_cpu.cpp:297-324, 625-630).
+    The reference multiplies by sqrt(D / sum2), the GPU store op divides by sqrt(sum2 / D): equal to a few ulp."""
+
+    rng = np.random.default_rng(42)
+    d, heads = 128, 4
+    x = (rng.standard_normal((200, heads * d)) * 2.5).astype(np.float32)
+    table = O.fill_rope(d, 200)
+    _, scale, roped = O.norm_rope_quant("i8", 1.0, x, table, d)
+    want = O.apply_rope(table, O.normalize_state_ref(x, heads), use_ref=True)
+    assert np.abs(roped - want).max() < 1e-6 * np.abs(want).max() * 4
+    rms = np.sqrt((x.reshape(200, heads, d) ** 2).mean(axis=2)).T
+    assert np.allclose(scale, rms, rtol=1e-6)

@@ -45,6 +45,35 @@ __device__ __forceinline__ void LoadVec<TagBF16, 4>(const __nv_bfloat16 *p, floa
     dst[0] = a.x, dst[1] = a.y, dst[2] = b.x, dst[3] = b.y;
 }
 
+template <>
+__device__ __forceinline__ void LoadVec<TagF32, 8>(const float *p, float *dst)
+{
+    LoadVec<TagF32, 4>(p, dst);
+    LoadVec<TagF32, 4>(p + 4, dst + 4);
+}
+template <>
+__device__ __forceinline__ void LoadVec<TagF16, 8>(const __half *p, float *dst)
+{
+    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        dst[2 * i] = a.x, dst[2 * i + 1] = a.y;
+    }
+}
+template <>
+__device__ __forceinline__ void LoadVec<TagBF16, 8>(const __nv_bfloat16 *p, float *dst)
+{
+    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i]));
+        dst[2 * i] = a.x, dst[2 * i + 1] = a.y;
+    }
+}
+
 // grid: x = ceil(rows * tiles / warpsPerBlock); rows = dst rows (>= len, padding rows are zeroed)
 template <class TSrc, bool DST_E4M3, int VEC>
 __global__ void __launch_bounds__(256) QuantRowsKernel(int kind, float vecScale, int len, int rows, int tileCount, int tile,
@@ -143,6 +172,165 @@ static int LaunchQuant(int kind, float vecScale, tsa_ptr2d src, tsa_ptr2d dst, t
         QuantRowsKernel<TSrc, DST_E4M3, 1><<<blocks, 256, 0, stream>>>(kind, vecScale, len, rows, tileCount, tile, s, d, sc);
     }
     return CheckCuda(cudaGetLastError(), "tsa_quant_rows launch");
+}
+
+// ---- producer of the attention inputs: per-head RMS normalise, rope, quantise ---------------------------------
+// A lane holds both rope partners: EPL consecutive elements from k and EPL from k + 32 of one 64-element block
+// (code/gpt/att/rope.cpp:28-46 rotates k with k + 32), so the rotation needs no exchange between lanes.  EPL = 4 for
+// f32 sources, 8 for 16-bit ones (16-byte loads either way): 32 / EPL lanes cover a block, a warp item = 64 * EPL
+// consecutive elements of a row; heads wider than an item take several steps.  A warp works on ITEMS items at once
+// (all their loads are issued before the first reduction) so that enough bytes are in flight per SM.
+template <class TSrc, class TRope, bool DST_E4M3, int EPL, int ITEMS, int STEPS>
+__global__ void __launch_bounds__(256) NormRopeQuantKernel(float vecScale, float ropeDir, int len, int rows, int headCount, int headShift,
+    P2D<typename TSrc::T> src, P2D<typename TRope::T> rope, P2D<uint8_t> dst, P2D<float> scale)
+{
+    constexpr int LPB = 32 / EPL;                                   // lanes per 64-element block
+    constexpr int STEP_ELEMS = 64 * EPL;                            // elements of a warp step
+    const int headDim = 1 << headShift;
+    const int span = STEP_ELEMS * STEPS;                            // elements of one item
+    const int width = headCount << headShift;
+    const int groups = (width + span - 1) / span;                   // items per row
+    const long long items = (long long)rows * groups;
+    const long long first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * ITEMS;
+    const int lane = threadIdx.x & 31;
+    if (first >= items) {
+        return;
+    }
+    const int laneOff = (lane / LPB) * 64 + (lane % LPB) * EPL;     // first element of the lane inside a step
+    float lo[ITEMS][STEPS][EPL], hi[ITEMS][STEPS][EPL];
+    int row[ITEMS], base[ITEMS];
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+        const long long it = first + j;
+        row[j] = it < items ? (int)(it / groups) : rows;             // rows: nothing to do
+        base[j] = it < items ? (int)(it - (long long)row[j] * groups) * span : 0;
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) {
+            const int e = base[j] + st * STEP_ELEMS + laneOff;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                lo[j][st][i] = 0;
+                hi[j][st][i] = 0;
+            }
+            if (row[j] < len && e < width) {
+                LoadVec<TSrc, EPL>(src.Row(row[j]) + e, lo[j][st]);
+                LoadVec<TSrc, EPL>(src.Row(row[j]) + e + 32, hi[j][st]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+        const int t = row[j];
+        float sum2 = 0;
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                sum2 += lo[j][st][i] * lo[j][st][i] + hi[j][st][i] * hi[j][st][i];
+            }
+        }
+        // sum over the head: LPB lanes per 64 elements
+        const int headLanes = min(32, (headDim / 64) * LPB);
+        for (int o = 1; o < headLanes; o <<= 1) {
+            sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+        }
+        float discr = 0;
+        if (sum2 > 0) {
+            discr = __fmul_rn(__fsqrt_rn(__fdiv_rn(sum2, (float)headDim)), vecScale);
+        }
+        const float mult = (discr > 0) ? __fdiv_rn(1.0f, discr) : 0.0f;
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) {
+            const int e = base[j] + st * STEP_ELEMS + laneOff;
+            const bool live = t < len && e < width;
+            float y0[EPL], y1[EPL];
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                y0[i] = __fmul_rn(lo[j][st][i], mult);
+                y1[i] = __fmul_rn(hi[j][st][i], mult);
+            }
+            if (rope.Valid() && live) {
+                float cs[EPL], sn[EPL];
+                const int k = e & (headDim - 1);
+                LoadVec<TRope, EPL>(rope.Row(t) + k, cs);
+                LoadVec<TRope, EPL>(rope.Row(t) + k + 32, sn);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    const float sinValue = __fmul_rn(sn[i], ropeDir);
+                    const float r0 = __fsub_rn(__fmul_rn(y0[i], cs[i]), __fmul_rn(y1[i], sinValue));
+                    const float r1 = __fadd_rn(__fmul_rn(y0[i], sinValue), __fmul_rn(y1[i], cs[i]));
+                    y0[i] = r0;
+                    y1[i] = r1;
+                }
+            }
+            if (t < rows && e < width) {
+                uint32_t p0[EPL / 4], p1[EPL / 4];
+#pragma unroll
+                for (int q = 0; q < EPL / 4; ++q) {
+                    p0[q] = 0;
+                    p1[q] = 0;
+                    if (live) {
+                        if (DST_E4M3) {
+                            p0[q] = PackE4M3x4(y0[4 * q], y0[4 * q + 1], y0[4 * q + 2], y0[4 * q + 3]);
+                            p1[q] = PackE4M3x4(y1[4 * q], y1[4 * q + 1], y1[4 * q + 2], y1[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                p0[q] |= (uint32_t)(FloatToI8Sat(y0[4 * q + i]) & 0xff) << (8 * i);
+                                p1[q] |= (uint32_t)(FloatToI8Sat(y1[4 * q + i]) & 0xff) << (8 * i);
+                            }
+                        }
+                    }
+                }
+                if (EPL == 8) {
+                    *reinterpret_cast<uint2 *>(dst.Row(t) + e) = make_uint2(p0[0], p0[EPL / 4 - 1]);
+                    *reinterpret_cast<uint2 *>(dst.Row(t) + e + 32) = make_uint2(p1[0], p1[EPL / 4 - 1]);
+                } else {
+                    *reinterpret_cast<uint32_t *>(dst.Row(t) + e) = p0[0];
+                    *reinterpret_cast<uint32_t *>(dst.Row(t) + e + 32) = p1[0];
+                }
+                // one lane per head writes the scale: the lane that holds the head's first element
+                if (scale.Valid() && st == 0 && (e & (headDim - 1)) == 0) {
+                    scale.Row(e >> headShift)[t] = (t < len) ? discr : 0.0f;
+                }
+            }
+        }
+    }
+}
+
+template <class TSrc, class TRope>
+static int LaunchNormRope(bool e4, float vecScale, float ropeDir, tsa_ptr2d src, tsa_ptr2d rope, tsa_ptr2d dst, tsa_ptr2d scale,
+    int headCount, int headDim, int len, cudaStream_t stream)
+{
+    constexpr int EPL = sizeof(typename TSrc::T) == 4 ? 4 : 8;
+    const int rows = dst.ysize;
+    const int stepElems = 64 * EPL;
+    const int steps = headDim > stepElems ? headDim / stepElems : 1;
+    int headShift = 6;
+    while ((1 << headShift) < headDim) {
+        ++headShift;
+    }
+    const long long items = (long long)rows * ((headCount * headDim + stepElems * steps - 1) / (stepElems * steps));
+    if (items == 0) {
+        return TSA_OK;
+    }
+    P2D<typename TSrc::T> s(src);
+    P2D<typename TRope::T> r(rope);
+    P2D<uint8_t> d(dst);
+    P2D<float> sc(scale);
+#define TSA_NRQ_LAUNCH(E4, ITEMS, STEPS)                                                                                         \
+    {                                                                                                                           \
+        const long long warps = (items + ITEMS - 1) / ITEMS;                                                                    \
+        const int blocks = (int)((warps * 32 + 255) / 256);                                                                     \
+        NormRopeQuantKernel<TSrc, TRope, E4, EPL, ITEMS, STEPS><<<blocks, 256, 0, stream>>>(vecScale, ropeDir, len, rows, headCount, headShift, s, r, d, sc); \
+    }
+    if (steps == 1) {
+        if (e4) TSA_NRQ_LAUNCH(true, 2, 1) else TSA_NRQ_LAUNCH(false, 2, 1)
+    } else {
+        if (e4) TSA_NRQ_LAUNCH(true, 1, 2) else TSA_NRQ_LAUNCH(false, 1, 2)
+    }
+#undef TSA_NRQ_LAUNCH
+    return CheckCuda(cudaGetLastError(), "tsa_norm_rope_quant launch");
 }
 
 // dScale: one warp per (row, head)
@@ -263,6 +451,42 @@ extern "C" __attribute__((visibility("default"))) int tsa_quant_rows(int kind, i
         return e4 ? LaunchQuant<TagBF16, true>(kind, vecScale, src, dst, scale, len, tile, s) : LaunchQuant<TagBF16, false>(kind, vecScale, src, dst, scale, len, tile, s);
     }
     return Fail(TSA_BAD_ARG, "tsa_quant_rows: src dtype must be f32, f16 or bf16");
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, tsa_ptr2d src,
+    tsa_ptr2d rope, int ropeDtype, float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, tsa_stream_t stream)
+{
+    TSA_REQUIRE(dstDtype == TSA_I8 || dstDtype == TSA_E4M3, "tsa_norm_rope_quant: dst dtype must be i8 or e4m3");
+    TSA_REQUIRE(src.data && dst.data, "tsa_norm_rope_quant: null src/dst");
+    TSA_REQUIRE(headCount > 0 && (headDim == 64 || headDim == 128 || headDim == 256 || headDim == 512), "tsa_norm_rope_quant: head size %d must be 64, 128, 256 or 512", headDim);
+    TSA_REQUIRE(dst.xsize >= headCount * headDim && src.xsize >= headCount * headDim, "tsa_norm_rope_quant: rows narrower than H*D");
+    TSA_REQUIRE(len >= 0 && len <= src.ysize && len <= dst.ysize, "tsa_norm_rope_quant: len %d exceeds buffers (%d, %d rows)", len, src.ysize, dst.ysize);
+    TSA_REQUIRE((uintptr_t)src.data % 16 == 0 && src.stride_bytes % 16 == 0 && (uintptr_t)dst.data % 8 == 0 && dst.stride_bytes % 8 == 0,
+        "tsa_norm_rope_quant: src must be 16-byte aligned, dst 8-byte aligned");
+    if (scale.data) {
+        TSA_REQUIRE(scale.ysize >= headCount && scale.xsize >= dst.ysize, "tsa_norm_rope_quant: scale plane too small");
+    }
+    if (rope.data) {
+        TSA_REQUIRE(ropeDtype == TSA_F32 || ropeDtype == TSA_F16, "tsa_norm_rope_quant: rope dtype must be f32 or f16");
+        TSA_REQUIRE(rope.xsize >= headDim && rope.ysize >= len, "tsa_norm_rope_quant: rope table smaller than [len][headDim]");
+        TSA_REQUIRE((uintptr_t)rope.data % 16 == 0 && rope.stride_bytes % 16 == 0, "tsa_norm_rope_quant: rope table must be 16-byte aligned");
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool e4 = dstDtype == TSA_E4M3;
+    const bool ropeF16 = rope.data && ropeDtype == TSA_F16;
+#define TSA_NRQ(TS)                                                                                                            \
+    return ropeF16 ? LaunchNormRope<TS, TagF16>(e4, vecScale, ropeDir, src, rope, dst, scale, headCount, headDim, len, s)     \
+                   : LaunchNormRope<TS, TagF32>(e4, vecScale, ropeDir, src, rope, dst, scale, headCount, headDim, len, s);
+    switch (srcDtype) {
+    case TSA_F32:
+        TSA_NRQ(TagF32)
+    case TSA_F16:
+        TSA_NRQ(TagF16)
+    case TSA_BF16:
+        TSA_NRQ(TagBF16)
+    }
+#undef TSA_NRQ
+    return Fail(TSA_BAD_ARG, "tsa_norm_rope_quant: src dtype must be f32, f16 or bf16");
 }
 
 extern "C" __attribute__((visibility("default"))) int tsa_calc_dscale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa_ptr2d dScale,

@@ -120,6 +120,18 @@ def quant_rows(src, kind, dst, tile, vec_scale=0.0, length=None):
     return out, scale
 
 
+def norm_rope_quant(src, rope, dst, heads, head_dim, vec_scale=1.0, direction=1.0, length=None):
+    """Per-head RMS normalise, rope (None: no rotation), quantise.  Returns (bytes uint8 [rows][H*D], scale f32 [H][rows])."""
+    rows = src.shape[0]
+    length = rows if length is None else length
+    out = torch.empty((rows, heads * head_dim), dtype=torch.uint8, device=src.device)
+    scale = torch.empty((heads, rows), dtype=torch.float32, device=src.device)
+    check(abi.lib().tsa_norm_rope_quant(_DT[src.dtype], _DT[dst], vec_scale, p2d(src), p2d(rope),
+                                        _DT[rope.dtype] if rope is not None else abi.TSA_F32, direction, p2d(out), p2d(scale),
+                                        heads, head_dim, length, _stream()))
+    return out, scale
+
+
 def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat16, grad_dtype=torch.bfloat16,
              qk_vec_scale=1.0, v_vec_scale=1.0, force_generic=False):
     return abi.AttCfg(_DT[qk_dtype], _DT[v_dtype], _DT[out_dtype], _DT[grad_dtype], head_dim_qk, head_dim_v,
