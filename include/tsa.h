@@ -156,6 +156,16 @@ int tsa_quant_rows(int kind, int srcDtype, int dstDtype, float vecScale, tsa_ptr
 int tsa_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, tsa_ptr2d src, tsa_ptr2d rope, int ropeDtype,
     float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, tsa_stream_t stream);
 
+/* Back-propagation through tsa_norm_rope_quant's fp32 stage.  Replaces the inverse rope and the RMS-normalise
+ * gradient folded into the epilogues of the reference's backward kernels (gpt_att_fp8.cuh:527-566, 917-981) and
+ * ApplyRope(-1) + NormalizeStateBackward of the CPU model (gpt_cpu.cpp:329-360, 759-764).  grad [len][H*D]: gradient
+ * with respect to the roped unit-RMS vector (what tsa_att_bwd returns, divided by the vector scale); src: the raw
+ * projection the producer normalised; out (dtype of grad) = sqrt(D / sum2) * (g - src * dot(src, g) / sum2) per head,
+ * g = grad rotated by -ropeDir; all-zero heads give zeros.  Supported (src, grad) dtypes: (f32, f32), (bf16, bf16),
+ * (f16, f16), (f32, bf16), (bf16, f32). */
+int tsa_rope_norm_bwd(int srcDtype, int gradDtype, tsa_ptr2d src, tsa_ptr2d grad, tsa_ptr2d rope, int ropeDtype,
+    float ropeDir, tsa_ptr2d out, int headCount, int headDim, int len, tsa_stream_t stream);
+
 /* ---- KV-cache decode -------------------------------------------------------------------------
  * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
  * batched over sequences.  Per sequence the cache is caller-owned device memory:

@@ -176,6 +176,27 @@ def norm_rope_quant(dst, vec_scale, src, rope, head_dim, direction=1.0):
     return out, scale, roped
 
 
+def normalize_state_backward_ref(src, d_norm, heads):
+    """The reference's NormalizeStateBackward (gpt_cpu.cpp:329-360)."""
+    src, sp = _f(src)
+    d_norm, dp = _f(d_norm)
+    out = np.zeros_like(src)
+    ref().ref_normalize_state_backward_f32(src.shape[0], src.shape[1], heads, sp, dp, out.ctypes.data_as(_fp))
+    return out
+
+
+def rope_norm_bwd(src, d_roped, rope, head_dim, direction=1.0):
+    """Gradient with respect to the raw projections, given the gradient with respect to the roped unit-RMS vectors."""
+    src, sp = _f(src)
+    d_roped, dp = _f(d_roped)
+    ln, dim = src.shape
+    out = np.zeros((ln, dim), dtype=np.float32)
+    rp = None
+    if rope is not None:
+        rope, rp = _f(rope)
+    lib().oracle_rope_norm_bwd(ln, dim, head_dim, c_float(direction), sp, dp, rp, out.ctypes.data_as(_fp))
+    return out
+
 # ------------------------------------------------------------------------------------------------
 # spans
 def window_spans(frag_lens, window):

@@ -179,6 +179,15 @@ void ref_normalize_state_f32(int len, int dim, int headCount, const float *src, 
     StoreArr(res, dst);
 }
 
+void ref_normalize_state_backward_f32(int len, int dim, int headCount, const float *src, const float *dNorm, float *grad)
+{
+    TArray2D<float> arr, dn, res;
+    FillArr(&arr, src, dim, len);
+    FillArr(&dn, dNorm, dim, len);
+    NormalizeStateBackward(arr, headCount, dn, &res);
+    StoreArr(res, grad);
+}
+
 int ref_float2i8(float x)
 {
     return Float2I8(x);

@@ -633,3 +633,40 @@ extern "C" void oracle_norm_rope_quant(int dstType, float vecScale, int len, int
         }
     }
 }
+
+// back-propagation through the producer's fp32 stage: inverse rope (ApplyRope with the opposite direction, gpt_cpu.cpp:
+// 759-760), then NormalizeStateBackward (gpt_cpu.cpp:329-360): grad = sqrt(D / sum2) * (g - src * dot(src, g) / sum2).
+// src: raw projections [len][dim]; dRoped: gradient with respect to the roped unit-RMS vectors; rope may be null
+extern "C" void oracle_rope_norm_bwd(int len, int dim, int headDim, float dir, const float *src, const float *dRoped,
+    const float *rope, float *grad)
+{
+    std::vector<float> g(dim);
+    for (int t = 0; t < len; ++t) {
+        for (int x = 0; x < dim; ++x) {
+            g[x] = dRoped[(size_t)t * dim + x];
+        }
+        if (rope) {
+            oracle_apply_rope(headDim, 1, dim, -dir, rope + (size_t)t * headDim, g.data());
+        }
+        for (int offset = 0; offset < dim; offset += headDim) {
+            const float *sp = src + (size_t)t * dim + offset;
+            float sum2 = 0, dp = 0;
+            for (int x = 0; x < headDim; ++x) {
+                sum2 += sp[x] * sp[x];
+                dp += sp[x] * g[offset + x];
+            }
+            float *dst = grad + (size_t)t * dim + offset;
+            if (sum2 == 0) {
+                for (int x = 0; x < headDim; ++x) {
+                    dst[x] = 0;
+                }
+            } else {
+                float sigma = dp / sum2;
+                float scale = sqrtf(headDim / sum2);
+                for (int x = 0; x < headDim; ++x) {
+                    dst[x] = scale * (g[offset + x] - sp[x] * sigma);
+                }
+            }
+        }
+    }
+}

@@ -77,3 +77,24 @@ def test_producer_feeds_attention():
     mx, mean = util.err_stats(util.to_np(out), ref["out"])
     # a handful of bytes may sit one code off a rounding boundary: tolerance relative to the value range as elsewhere
     assert mx < max(util.OUT_MAX_ABS, 0.06 * vmax) and mean < max(util.OUT_MEAN_ABS, 0.01 * vmax), util.describe(util.to_np(out), ref["out"])
+
+
+@pytest.mark.parametrize("d,heads", [(64, 12), (128, 5), (256, 2)])
+@pytest.mark.parametrize("src_dtype,grad_dtype,rope_dtype", [(torch.float32, torch.float32, torch.float32),
+                                                             (torch.bfloat16, torch.bfloat16, torch.float16),
+                                                             (torch.float32, torch.bfloat16, None)])
+def test_rope_norm_bwd(d, heads, src_dtype, grad_dtype, rope_dtype):
+    from tscale_b200 import ops
+    rng = np.random.default_rng(33)
+    rows = 555
+    src_t = torch.from_numpy((rng.standard_normal((rows, heads * d)) * 2.0).astype(np.float32)).to(src_dtype)
+    src_t[9] = 0
+    grad_t = torch.from_numpy(rng.standard_normal((rows, heads * d)).astype(np.float32)).to(grad_dtype)
+    rope_t = None if rope_dtype is None else torch.from_numpy(O.fill_rope(d, rows)).to(rope_dtype)
+    want = O.rope_norm_bwd(src_t.float().numpy(), grad_t.float().numpy(), None if rope_t is None else rope_t.float().numpy(), d)
+    got = ops.rope_norm_bwd(src_t.to(DEV), grad_t.to(DEV), None if rope_t is None else rope_t.to(DEV), heads, d)
+    torch.cuda.synchronize()
+    got = util.to_np(got)
+    assert np.abs(got[9]).max() == 0
+    tol = 1e-5 if grad_dtype == torch.float32 else 1e-2  # bf16 results carry their own rounding
+    assert util.rel_l2(got, want) < tol, util.rel_l2(got, want)

@@ -93,3 +93,16 @@ def test_normalise_rope_against_reference_chain():
     assert np.abs(roped - want).max() < 1e-6 * np.abs(want).max() * 4
     rms = np.sqrt((x.reshape(200, heads, d) ** 2).mean(axis=2)).T
     assert np.allclose(scale, rms, rtol=1e-6)
+
+
+def test_producer_backward_bit_exact():
+    """Inverse rope + NormalizeStateBackward of the reference (gpt_cpu.cpp:329-360, 759-764) restated in the oracle."""
+    rng = np.random.default_rng(43)
+    for d, heads in ((64, 3), (128, 4)):
+        x = (rng.standard_normal((120, heads * d)) * 2).astype(np.float32)
+        x[7] = 0
+        g = rng.standard_normal((120, heads * d)).astype(np.float32)
+        table = O.fill_rope(d, 120)
+        a = O.rope_norm_bwd(x, g, table, d)
+        b = O.normalize_state_backward_ref(x, O.apply_rope(table, g, -1.0, use_ref=True), heads)
+        assert np.array_equal(a, b)

@@ -333,6 +333,145 @@ static int LaunchNormRope(bool e4, float vecScale, float ropeDir, tsa_ptr2d src,
     return CheckCuda(cudaGetLastError(), "tsa_norm_rope_quant launch");
 }
 
+// N (4 or 8) consecutive results as one or two 8 / 16-byte stores
+template <class TDst, int N>
+__device__ __forceinline__ void StoreVec(typename TDst::T *p, const float *v)
+{
+    if (sizeof(typename TDst::T) == 4) {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) {
+            *reinterpret_cast<float4 *>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+    } else {
+        uint32_t w[N / 2];
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            if (std::is_same<TDst, TagF16>::value) {
+                __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&h);
+            } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t *>(&h);
+            }
+        }
+        if (N == 8) {
+            *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[N / 2 - 2], w[N / 2 - 1]);
+        } else {
+            *reinterpret_cast<uint2 *>(p) = make_uint2(w[0], w[1]);
+        }
+    }
+}
+
+// ---- back-propagation through the producer: inverse rope, then the RMS-normalise gradient ----------------------
+// Same lane layout as NormRopeQuantKernel.  grad (gradient with respect to the roped unit-RMS vector) and src (the raw
+// projection) are read once; out = sqrt(D / sum2) * (g - src * dot(src, g) / sum2) with g = grad rotated back
+// (code/gpt/compute/gpt_cpu.cpp:329-360, 759-764).
+template <class TSrc, class TGrad, class TRope, int EPL, int STEPS>
+__global__ void __launch_bounds__(256) RopeNormBwdKernel(float ropeDir, int len, int headCount, int headShift,
+    P2D<typename TSrc::T> src, P2D<typename TGrad::T> grad, P2D<typename TRope::T> rope, P2D<typename TGrad::T> out)
+{
+    constexpr int LPB = 32 / EPL;
+    constexpr int STEP_ELEMS = 64 * EPL;
+    const int headDim = 1 << headShift;
+    const int span = STEP_ELEMS * STEPS;
+    const int width = headCount << headShift;
+    const int groups = (width + span - 1) / span;
+    const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (item >= (long long)len * groups) {
+        return;
+    }
+    const int t = (int)(item / groups);
+    const int base = (int)(item - (long long)t * groups) * span;
+    const int laneOff = (lane / LPB) * 64 + (lane % LPB) * EPL;
+    float s0[STEPS][EPL], s1[STEPS][EPL], g0[STEPS][EPL], g1[STEPS][EPL];
+    float sum2 = 0, dp = 0;
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) {
+        const int e = base + st * STEP_ELEMS + laneOff;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            s0[st][i] = s1[st][i] = g0[st][i] = g1[st][i] = 0;
+        }
+        if (e < width) {
+            LoadVec<TSrc, EPL>(src.Row(t) + e, s0[st]);
+            LoadVec<TSrc, EPL>(src.Row(t) + e + 32, s1[st]);
+            LoadVec<TGrad, EPL>(grad.Row(t) + e, g0[st]);
+            LoadVec<TGrad, EPL>(grad.Row(t) + e + 32, g1[st]);
+            if (rope.Valid()) {
+                float cs[EPL], sn[EPL];
+                const int k = e & (headDim - 1);
+                LoadVec<TRope, EPL>(rope.Row(t) + k, cs);
+                LoadVec<TRope, EPL>(rope.Row(t) + k + 32, sn);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    const float sinValue = __fmul_rn(sn[i], -ropeDir); // rotate back
+                    const float r0 = __fsub_rn(__fmul_rn(g0[st][i], cs[i]), __fmul_rn(g1[st][i], sinValue));
+                    const float r1 = __fadd_rn(__fmul_rn(g0[st][i], sinValue), __fmul_rn(g1[st][i], cs[i]));
+                    g0[st][i] = r0;
+                    g1[st][i] = r1;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            sum2 += s0[st][i] * s0[st][i] + s1[st][i] * s1[st][i];
+            dp += s0[st][i] * g0[st][i] + s1[st][i] * g1[st][i];
+        }
+    }
+    const int headLanes = min(32, (headDim / 64) * LPB);
+    for (int o = 1; o < headLanes; o <<= 1) {
+        sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+        dp += __shfl_xor_sync(0xffffffffu, dp, o);
+    }
+    float sigma = 0, scale = 0;
+    if (sum2 > 0) {
+        sigma = __fdiv_rn(dp, sum2);
+        scale = __fsqrt_rn(__fdiv_rn((float)headDim, sum2));
+    }
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) {
+        const int e = base + st * STEP_ELEMS + laneOff;
+        if (e < width) {
+            float r0[EPL], r1[EPL];
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                r0[i] = __fmul_rn(scale, __fsub_rn(g0[st][i], __fmul_rn(s0[st][i], sigma)));
+                r1[i] = __fmul_rn(scale, __fsub_rn(g1[st][i], __fmul_rn(s1[st][i], sigma)));
+            }
+            StoreVec<TGrad, EPL>(out.Row(t) + e, r0);
+            StoreVec<TGrad, EPL>(out.Row(t) + e + 32, r1);
+        }
+    }
+}
+
+template <class TSrc, class TGrad, class TRope>
+static int LaunchRopeNormBwd(float ropeDir, tsa_ptr2d src, tsa_ptr2d grad, tsa_ptr2d rope, tsa_ptr2d out, int headCount, int headDim, int len,
+    cudaStream_t stream)
+{
+    constexpr int EPL = (sizeof(typename TSrc::T) == 4 || sizeof(typename TGrad::T) == 4) ? 4 : 8;
+    const int stepElems = 64 * EPL;
+    const int steps = headDim > stepElems ? headDim / stepElems : 1;
+    int headShift = 6;
+    while ((1 << headShift) < headDim) {
+        ++headShift;
+    }
+    const long long items = (long long)len * ((headCount * headDim + stepElems * steps - 1) / (stepElems * steps));
+    if (items == 0) {
+        return TSA_OK;
+    }
+    const int blocks = (int)((items * 32 + 255) / 256);
+    P2D<typename TSrc::T> s(src);
+    P2D<typename TGrad::T> g(grad), o(out);
+    P2D<typename TRope::T> r(rope);
+    if (steps == 1) {
+        RopeNormBwdKernel<TSrc, TGrad, TRope, EPL, 1><<<blocks, 256, 0, stream>>>(ropeDir, len, headCount, headShift, s, g, r, o);
+    } else {
+        RopeNormBwdKernel<TSrc, TGrad, TRope, EPL, 2><<<blocks, 256, 0, stream>>>(ropeDir, len, headCount, headShift, s, g, r, o);
+    }
+    return CheckCuda(cudaGetLastError(), "tsa_rope_norm_bwd launch");
+}
+
 // dScale: one warp per (row, head)
 __global__ void __launch_bounds__(256) DScaleKernel(int outDt, int gradDt, int len, int headCount, int headDim,
     P2D<char> out, P2D<char> dOut, P2D<float> dScale)
@@ -487,6 +626,45 @@ extern "C" __attribute__((visibility("default"))) int tsa_norm_rope_quant(int sr
     }
 #undef TSA_NRQ
     return Fail(TSA_BAD_ARG, "tsa_norm_rope_quant: src dtype must be f32, f16 or bf16");
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_rope_norm_bwd(int srcDtype, int gradDtype, tsa_ptr2d src, tsa_ptr2d grad,
+    tsa_ptr2d rope, int ropeDtype, float ropeDir, tsa_ptr2d out, int headCount, int headDim, int len, tsa_stream_t stream)
+{
+    TSA_REQUIRE(src.data && grad.data && out.data, "tsa_rope_norm_bwd: null buffer");
+    TSA_REQUIRE(headCount > 0 && (headDim == 64 || headDim == 128 || headDim == 256 || headDim == 512), "tsa_rope_norm_bwd: head size %d must be 64, 128, 256 or 512", headDim);
+    const int width = headCount * headDim;
+    TSA_REQUIRE(src.xsize >= width && grad.xsize >= width && out.xsize >= width, "tsa_rope_norm_bwd: rows narrower than H*D");
+    TSA_REQUIRE(len >= 0 && len <= src.ysize && len <= grad.ysize && len <= out.ysize, "tsa_rope_norm_bwd: len %d exceeds buffers", len);
+    TSA_REQUIRE((uintptr_t)src.data % 16 == 0 && src.stride_bytes % 16 == 0 && (uintptr_t)grad.data % 16 == 0 && grad.stride_bytes % 16 == 0 &&
+                    (uintptr_t)out.data % 16 == 0 && out.stride_bytes % 16 == 0, "tsa_rope_norm_bwd: buffers must be 16-byte aligned");
+    if (rope.data) {
+        TSA_REQUIRE(ropeDtype == TSA_F32 || ropeDtype == TSA_F16, "tsa_rope_norm_bwd: rope dtype must be f32 or f16");
+        TSA_REQUIRE(rope.xsize >= headDim && rope.ysize >= len, "tsa_rope_norm_bwd: rope table smaller than [len][headDim]");
+        TSA_REQUIRE((uintptr_t)rope.data % 16 == 0 && rope.stride_bytes % 16 == 0, "tsa_rope_norm_bwd: rope table must be 16-byte aligned");
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool ropeF16 = rope.data && ropeDtype == TSA_F16;
+#define TSA_RNB(TS, TG)                                                                                                   \
+    return ropeF16 ? LaunchRopeNormBwd<TS, TG, TagF16>(ropeDir, src, grad, rope, out, headCount, headDim, len, s)        \
+                   : LaunchRopeNormBwd<TS, TG, TagF32>(ropeDir, src, grad, rope, out, headCount, headDim, len, s);
+    if (srcDtype == TSA_F32 && gradDtype == TSA_F32) {
+        TSA_RNB(TagF32, TagF32)
+    }
+    if (srcDtype == TSA_BF16 && gradDtype == TSA_BF16) {
+        TSA_RNB(TagBF16, TagBF16)
+    }
+    if (srcDtype == TSA_F16 && gradDtype == TSA_F16) {
+        TSA_RNB(TagF16, TagF16)
+    }
+    if (srcDtype == TSA_F32 && gradDtype == TSA_BF16) {
+        TSA_RNB(TagF32, TagBF16)
+    }
+    if (srcDtype == TSA_BF16 && gradDtype == TSA_F32) {
+        TSA_RNB(TagBF16, TagF32)
+    }
+#undef TSA_RNB
+    return Fail(TSA_UNSUPPORTED, "tsa_rope_norm_bwd: src / grad dtypes must be (f32, f32), (bf16, bf16), (f16, f16), (f32, bf16) or (bf16, f32)");
 }
 
 extern "C" __attribute__((visibility("default"))) int tsa_calc_dscale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa_ptr2d dScale,

@@ -132,6 +132,15 @@ def norm_rope_quant(src, rope, dst, heads, head_dim, vec_scale=1.0, direction=1.
     return out, scale
 
 
+def rope_norm_bwd(src, grad, rope, heads, head_dim, direction=1.0):
+    """Gradient with respect to the raw projections given the gradient with respect to the roped unit-RMS vectors."""
+    out = torch.empty_like(grad)
+    check(abi.lib().tsa_rope_norm_bwd(_DT[src.dtype], _DT[grad.dtype], p2d(src), p2d(grad), p2d(rope),
+                                      _DT[rope.dtype] if rope is not None else abi.TSA_F32, direction, p2d(out), heads, head_dim,
+                                      src.shape[0], _stream()))
+    return out
+
+
 def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat16, grad_dtype=torch.bfloat16,
              qk_vec_scale=1.0, v_vec_scale=1.0, force_generic=False):
     return abi.AttCfg(_DT[qk_dtype], _DT[v_dtype], _DT[out_dtype], _DT[grad_dtype], head_dim_qk, head_dim_v,
