@@ -38,6 +38,12 @@ def test_bad_arguments_return_status_not_abort():
     null = abi.Ptr2D(None, 0, 0, 0)
     assert lib.tsa_quant_rows(7, abi.TSA_F32, abi.TSA_I8, 0.0, null, null, null, 0, 128, None) == abi.TSA_BAD_ARG
     assert b"kind" in lib.tsa_last_error()
+    fake = abi.Ptr2D(4096, 96 * 4, 96, 8)  # never dereferenced: validation comes first
+    assert lib.tsa_norm_rope_quant(abi.TSA_F32, abi.TSA_I8, 1.0, fake, null, abi.TSA_F32, 1.0, fake, null, 1, 96, 8, None) == abi.TSA_BAD_ARG
+    assert b"head size" in lib.tsa_last_error()
+    assert lib.tsa_norm_rope_quant(abi.TSA_F32, abi.TSA_F16, 1.0, fake, null, abi.TSA_F32, 1.0, fake, null, 1, 64, 8, None) == abi.TSA_BAD_ARG
+    assert lib.tsa_rope_norm_bwd(abi.TSA_F32, abi.TSA_F32, null, fake, null, abi.TSA_F32, 1.0, fake, 1, 64, 8, None) == abi.TSA_BAD_ARG
+    assert lib.tsa_rope_norm_bwd(abi.TSA_F16, abi.TSA_F32, fake, fake, null, abi.TSA_F32, 1.0, fake, 1, 64, 8, None) == abi.TSA_UNSUPPORTED
     assert lib.tsa_quant_rows(0, abi.TSA_F32, abi.TSA_F16, 0.0, null, null, null, 0, 128, None) == abi.TSA_BAD_ARG
     cfg = ops.make_cfg("e4m3", "e4m3", 64, 64)
     rc = lib.tsa_att_fwd(ctypes.byref(cfg), None, null, null, null, null, null, null, None, None, 0.0, null, null, 2, 1,
