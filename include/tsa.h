@@ -230,6 +230,15 @@ int tsa_group_attention(int len, const int *spans, const int *spanPtr, int maxGr
 int tsa_group_window_spans(int fragCount, const int *fragLens, int window, int transposed, int maxGroups,
     tsa_span_group *groups, int *groupPtr);
 
+/* ---- device-side span generation ("next" scope row: the mask preparation on the input side of the path) -------
+ * The same records as tsa_group_window_spans, written by a kernel into device memory: no host work and no copy of the
+ * mask per step (the reference prepares the spans on the CPU and uploads them, gpt_cuda.cu:1346-1353).
+ * fragStarts: device array of fragCount + 1 ascending row offsets (fragStarts[0] = 0, fragStarts[fragCount] = len).
+ * groups needs room for ceil(len / 64) records (maxGroups), groupPtr for ceil(len / 64) + 1 ints; the number of
+ * groups ends up in groupPtr[ceil(len / 64)]. */
+int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len, int window, int transposed,
+    int maxGroups, tsa_span_group *groups, int *groupPtr, tsa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -148,3 +148,20 @@ def test_decode_matches_reference_fixture(golden_dir):
     out = cache.decode(torch.from_numpy(q8[None]).to(DEV), None, width, slope).cpu().numpy()[0]
     # the reference's polynomial 2^x is accurate to ~1e-4 relative; exact exp2 on the GPU
     assert np.abs(out - z["out"]).max() < 1e-3 * max(1.0, np.abs(z["out"]).max())
+
+
+@pytest.mark.parametrize("frag_lens", [[4096] * 4, [1, 1, 1, 300, 1, 64, 63, 65, 129], [70], [5000, 3, 2049]])
+@pytest.mark.parametrize("window", [0, 1, 64, 256])
+def test_device_span_generation_equals_host(frag_lens, window):
+    """tsa_group_window_spans_device writes the records the host helper computes, bit for bit, for the mask and its transpose."""
+    from tscale_b200 import ops
+    host = ops.Mask.window(frag_lens, window)
+    length = sum(frag_lens)
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(frag_lens)]), dtype=torch.int32, device=DEV)
+    dev = ops.Mask.window_on_device(starts, length, window, DEV)
+    torch.cuda.synchronize()
+    g, gp, rg, rgp = (x.cpu().numpy() for x in dev.dev(DEV))
+    for got_g, got_p, want_g, want_p in ((g, gp, host.groups, host.group_ptr), (rg, rgp, host.rev_groups, host.rev_group_ptr)):
+        assert np.array_equal(got_p, want_p)
+        n = int(want_p[-1])
+        assert np.array_equal(got_g[:n], want_g[:n])

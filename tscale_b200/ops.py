@@ -73,6 +73,23 @@ class Mask:
         return cls(length, *res)
 
     @classmethod
+    def window_on_device(cls, frag_starts, length, window, device):
+        """The same mask built by tsa_group_window_spans_device: frag_starts is an int32 CUDA tensor of fragment offsets
+        (first 0, last = length); nothing is computed or copied on the host."""
+        L = abi.lib()
+        tiles = (length + abi.ATT_GROUP - 1) // abi.ATT_GROUP
+        bufs = []
+        for transposed in (0, 1):
+            groups = torch.empty((max(tiles, 1), 130), dtype=torch.int32, device=device)
+            gptr = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+            check(L.tsa_group_window_spans_device(_ptr(frag_starts), frag_starts.numel() - 1, length, int(window or 0), transposed,
+                                                  max(tiles, 1), _ptr(groups), _ptr(gptr), _stream()))
+            bufs += [groups, gptr]
+        m = cls(length, None, None, None, None)
+        m._dev[str(device)] = tuple(bufs)
+        return m
+
+    @classmethod
     def from_spans(cls, spans, span_ptr):
         """General mask from per-row inclusive spans in CSR form."""
         L = abi.lib()
