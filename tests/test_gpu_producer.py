@@ -98,3 +98,18 @@ def test_rope_norm_bwd(d, heads, src_dtype, grad_dtype, rope_dtype):
     assert np.abs(got[9]).max() == 0
     tol = 1e-5 if grad_dtype == torch.float32 else 1e-2  # bf16 results carry their own rounding
     assert util.rel_l2(got, want) < tol, util.rel_l2(got, want)
+
+
+def test_norm_rope_quant_pads_with_zeros():
+    """Rows in [len, rows) of the destination are written with zeros and scale 0, like the reference's padding rows."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(34)
+    heads, d, rows, length = 3, 64, 128, 100
+    src = torch.from_numpy(rng.standard_normal((rows, heads * d)).astype(np.float32)).to(DEV)
+    rope = torch.from_numpy(O.fill_rope(d, rows)).to(DEV)
+    b, s = ops.norm_rope_quant(src, rope, "i8", heads, d, 1 / 24.0, length=length)
+    torch.cuda.synchronize()
+    assert int(b[length:].abs().max().item()) == 0 and float(s[:, length:].abs().max().item()) == 0
+    want_b, want_s, _ = O.norm_rope_quant("i8", 1 / 24.0, src[:length].cpu().numpy(), rope[:length].cpu().numpy(), d)
+    frac, step = _codes_close(b[:length].cpu().numpy().view(np.int8), want_b, "i8")
+    assert frac < 2e-3 and step <= 1
