@@ -166,6 +166,20 @@ int tsa_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, tsa_ptr2d sr
 int tsa_rope_norm_bwd(int srcDtype, int gradDtype, tsa_ptr2d src, tsa_ptr2d grad, tsa_ptr2d rope, int ropeDtype,
     float ropeDir, tsa_ptr2d out, int headCount, int headDim, int len, tsa_stream_t stream);
 
+/* ---- consumer of the attention output ("next" scope row: the step on the output side of the path) -------------
+ * Replaces KVProduct and KVProductBackprop (code/gpt/compute/gpt_combiner.cuh:12-39, 85-217; CPU form
+ * gpt_cpu.cpp:191-262): the input of the combiner matrix
+ *   kv[t][head * 4 D + blk * D + z] = k[t][head * D + (z ^ blk)] * valLookup[t][head * D + z] * kvMult,  blk = 0 .. 3,
+ * and its back-propagation dK[z] = sum_blk dkv[blk][z ^ blk] * val[z ^ blk], dValLookup[z] = sum_blk dkv[blk][z] *
+ * k[z ^ blk], plus dScale[head][t] = sum_z dValLookup[z] * valLookup[z] (f32 plane [H][len], may be absent), which is
+ * the dScale argument of tsa_att_bwd (the reference's KVProductBackpropE4fused computes it in the same pass).
+ * Dtypes (in, out): (f32, f32), (bf16, bf16), (f16, f16), (bf16, f32), (f16, f32); backward (in, grad): the first
+ * three and (bf16, f32).  Head size 64, 128 or 256; all buffers 16-byte aligned. */
+int tsa_kv_product(int inDtype, int outDtype, tsa_ptr2d k, tsa_ptr2d valLookup, float kvMult, tsa_ptr2d kv,
+    int headCount, int headDim, int len, tsa_stream_t stream);
+int tsa_kv_product_bwd(int inDtype, int gradDtype, tsa_ptr2d k, tsa_ptr2d valLookup, tsa_ptr2d dkv, tsa_ptr2d dK,
+    tsa_ptr2d dValLookup, tsa_ptr2d dScale, int headCount, int headDim, int len, tsa_stream_t stream);
+
 /* ---- KV-cache decode -------------------------------------------------------------------------
  * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
  * batched over sequences.  Per sequence the cache is caller-owned device memory:

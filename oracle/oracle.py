@@ -197,6 +197,30 @@ def rope_norm_bwd(src, d_roped, rope, head_dim, direction=1.0):
     lib().oracle_rope_norm_bwd(ln, dim, head_dim, c_float(direction), sp, dp, rp, out.ctypes.data_as(_fp))
     return out
 
+def kv_product(k, val, heads, use_ref=False):
+    """Combiner input (gpt_cpu.cpp:191-216): [len][H*D*4]."""
+    k, kp = _f(k)
+    val, vp = _f(val)
+    ln, dim = k.shape
+    out = np.zeros((ln, dim * 4), dtype=np.float32)
+    fn = ref().ref_kv_product if use_ref else lib().oracle_kv_product
+    fn(ln, heads, dim // heads, kp, vp, out.ctypes.data_as(_fp))
+    return out
+
+
+def kv_product_bwd(k, val, dkv, heads, use_ref=False):
+    """Back-propagation of kv_product: returns (dK, dVal [len][H*D], dScale [H][len])."""
+    k, kp = _f(k)
+    val, vp = _f(val)
+    dkv, dp = _f(dkv)
+    ln, dim = k.shape
+    dk = np.zeros((ln, dim), dtype=np.float32)
+    dv = np.zeros((ln, dim), dtype=np.float32)
+    ds = np.zeros((heads, ln), dtype=np.float32)
+    fn = ref().ref_kv_product_backprop if use_ref else lib().oracle_kv_product_bwd
+    fn(ln, heads, dim // heads, kp, vp, dp, dk.ctypes.data_as(_fp), dv.ctypes.data_as(_fp), ds.ctypes.data_as(_fp))
+    return dk, dv, ds
+
 # ------------------------------------------------------------------------------------------------
 # spans
 def window_spans(frag_lens, window):

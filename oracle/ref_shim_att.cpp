@@ -188,6 +188,38 @@ void ref_normalize_state_backward_f32(int len, int dim, int headCount, const flo
     StoreArr(res, grad);
 }
 
+// KVProduct / KVProductBackprop (gpt_cpu.cpp:191-262): the consumer of the attention output on the CPU path
+static TModelDims CombinerDims(int headCount, int ttDim)
+{
+    TModelDims dims;
+    dims.TTDim = ttDim;
+    dims.HeadCount = headCount;
+    return dims;
+}
+
+void ref_kv_product(int len, int headCount, int ttDim, const float *k, const float *valLookup, float *kv)
+{
+    TArray2D<float> ka, va, res;
+    FillArr(&ka, k, headCount * ttDim, len);
+    FillArr(&va, valLookup, headCount * ttDim, len);
+    KVProduct(CombinerDims(headCount, ttDim), ka, va, &res);
+    StoreArr(res, kv);
+}
+
+// dScale [headCount][len]
+void ref_kv_product_backprop(int len, int headCount, int ttDim, const float *k, const float *valLookup, const float *dkv,
+    float *dK, float *dValLookup, float *dScale)
+{
+    TArray2D<float> ka, va, da, dk, dv, ds;
+    FillArr(&ka, k, headCount * ttDim, len);
+    FillArr(&va, valLookup, headCount * ttDim, len);
+    FillArr(&da, dkv, headCount * ttDim * COMBINER_REP, len);
+    KVProductBackprop(CombinerDims(headCount, ttDim), ka, va, da, &dk, &dv, &ds);
+    StoreArr(dk, dK);
+    StoreArr(dv, dValLookup);
+    StoreArr(ds, dScale);
+}
+
 int ref_float2i8(float x)
 {
     return Float2I8(x);

@@ -670,3 +670,55 @@ extern "C" void oracle_rope_norm_bwd(int len, int dim, int headDim, float dir, c
         }
     }
 }
+
+///////////////////////////////////////////////////////////////////////////////////////////////////
+// consumer of the attention output: the combiner input (gpt_cpu.cpp:191-216) and its back-propagation (219-262).
+// kv[t][head * D * 4 + blk * D + z] = k[t][head * D + (z ^ blk)] * val[t][head * D + z],  blk = 0 .. 3 (COMBINER_REP)
+extern "C" void oracle_kv_product(int len, int H, int D, const float *k, const float *val, float *kv)
+{
+    const int REP = 4;
+    for (int t = 0; t < len; ++t) {
+        for (int head = 0; head < H; ++head) {
+            const float *kp = k + ((size_t)t * H + head) * D;
+            const float *vp = val + ((size_t)t * H + head) * D;
+            for (int blk = 0; blk < REP; ++blk) {
+                float *dst = kv + (size_t)t * H * D * REP + (size_t)head * D * REP + blk * D;
+                for (int z = 0; z < D; ++z) {
+                    dst[z] = kp[z ^ blk] * vp[z];
+                }
+            }
+        }
+    }
+}
+
+// dK[z] = sum_blk dkv[blk][z ^ blk] * val[z ^ blk];  dVal[z] = sum_blk dkv[blk][z] * k[z ^ blk];  dScale[head][t] =
+// sum_z dVal[z] * val[z] (the quantity the attention backward calls dScale)
+extern "C" void oracle_kv_product_bwd(int len, int H, int D, const float *k, const float *val, const float *dkv,
+    float *dK, float *dVal, float *dScale)
+{
+    const int REP = 4;
+    for (int t = 0; t < len; ++t) {
+        for (int head = 0; head < H; ++head) {
+            const float *kp = k + ((size_t)t * H + head) * D;
+            const float *vp = val + ((size_t)t * H + head) * D;
+            float *dk = dK + ((size_t)t * H + head) * D;
+            float *dv = dVal + ((size_t)t * H + head) * D;
+            for (int z = 0; z < D; ++z) {
+                dk[z] = 0;
+                dv[z] = 0;
+            }
+            for (int blk = 0; blk < REP; ++blk) {
+                const float *g = dkv + (size_t)t * H * D * REP + (size_t)head * D * REP + blk * D;
+                for (int z = 0; z < D; ++z) {
+                    dk[z] += g[z ^ blk] * vp[z ^ blk];
+                    dv[z] += g[z] * kp[z ^ blk];
+                }
+            }
+            float sum = 0;
+            for (int z = 0; z < D; ++z) {
+                sum += dv[z] * vp[z];
+            }
+            dScale[(size_t)head * len + t] = sum;
+        }
+    }
+}

@@ -76,6 +76,18 @@ def producer_case(name, seed, rows, heads, d):
     print(name, rows, heads, d)
 
 
+def consumer_case(name, seed, rows, heads, d):
+    """KVProduct / KVProductBackprop of the reference (gpt_cpu.cpp:191-262)."""
+    rng = np.random.default_rng(seed)
+    k = rng.standard_normal((rows, heads * d)).astype(np.float32)
+    v = rng.standard_normal((rows, heads * d)).astype(np.float32)
+    g = rng.standard_normal((rows, heads * d * 4)).astype(np.float32)
+    kv = O.kv_product(k, v, heads, use_ref=True)
+    dk, dv, ds = O.kv_product_bwd(k, v, g, heads, use_ref=True)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), heads=heads, d=d, k=k, val=v, dkv=g, kv=kv, dk=dk, dval=dv, dscale=ds)
+    print(name, rows, heads, d)
+
+
 def main():
     assert O.ref() is not None, "build oracle/_ref first (make -C oracle ref)"
     # window-64 layers of the reference use ALiBi slope 0.5, wide layers slope 0 (model_dim.cpp:83-90)
@@ -92,6 +104,7 @@ def main():
     decode_case("decode_first", 13, 1, 2, 64, 64, 0.5)
     producer_case("producer_d64", 20, 150, 3, 64)
     producer_case("producer_d128", 21, 90, 2, 128)
+    consumer_case("consumer_d64", 30, 40, 3, 64)
     # 8-bit code points: ConvertE4toFloat for all bytes, Float2I8 on a grid
     e4 = np.array([O.ref().ref_e4m3_to_float(i) for i in range(256)], dtype=np.float32)
     grid = np.concatenate([np.linspace(-130, 130, 2081), np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5])]).astype(np.float32)

@@ -104,3 +104,11 @@ def test_producer_against_reference_fixture(golden_dir, name):
     _, scale, roped = O.norm_rope_quant("i8", 1.0, z["src"], z["rope"], d)
     assert np.abs(roped - z["roped"]).max() < 4e-6 * np.abs(z["roped"]).max()
     assert scale[:, 3].max() == 0 and np.abs(roped[3]).max() == 0
+
+
+def test_consumer_against_reference_fixture(golden_dir):
+    z = np.load(os.path.join(golden_dir, "consumer_d64.npz"))
+    heads = int(z["heads"])
+    assert np.array_equal(O.kv_product(z["k"], z["val"], heads), z["kv"])
+    dk, dv, ds = O.kv_product_bwd(z["k"], z["val"], z["dkv"], heads)
+    assert np.array_equal(dk, z["dk"]) and np.array_equal(dv, z["dval"]) and np.array_equal(ds, z["dscale"])

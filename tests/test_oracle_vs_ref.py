@@ -106,3 +106,15 @@ def test_producer_backward_bit_exact():
         a = O.rope_norm_bwd(x, g, table, d)
         b = O.normalize_state_backward_ref(x, O.apply_rope(table, g, -1.0, use_ref=True), heads)
         assert np.array_equal(a, b)
+
+
+def test_combiner_product_bit_exact():
+    """KVProduct / KVProductBackprop (gpt_cpu.cpp:191-262) restated in the oracle."""
+    rng = np.random.default_rng(44)
+    for d, heads in ((64, 3), (128, 2)):
+        k = rng.standard_normal((50, heads * d)).astype(np.float32)
+        v = rng.standard_normal((50, heads * d)).astype(np.float32)
+        g = rng.standard_normal((50, heads * d * 4)).astype(np.float32)
+        assert np.array_equal(O.kv_product(k, v, heads), O.kv_product(k, v, heads, use_ref=True))
+        for a, b in zip(O.kv_product_bwd(k, v, g, heads), O.kv_product_bwd(k, v, g, heads, use_ref=True)):
+            assert np.array_equal(a, b)

@@ -53,7 +53,7 @@ EXPORTS = [
     "tsa_att_bwd_workspace_bytes", "tsa_calc_dscale", "tsa_qk_scores_i32", "tsa_quant_rows", "tsa_kv_append",
     "tsa_att_decode", "tsa_att_decode_workspace_bytes", "tsa_make_window_spans", "tsa_transpose_attention",
     "tsa_group_attention", "tsa_group_window_spans", "tsa_att_decode_static", "tsa_att_decode_static_capacity_bytes",
-    "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device",
+    "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device", "tsa_kv_product", "tsa_kv_product_bwd",
 ]
 
 
@@ -76,6 +76,8 @@ def _declare(lib):
     lib.tsa_norm_rope_quant.argtypes = [c_int, c_int, c_float, P, P, c_int, c_float, P, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_rope_norm_bwd.argtypes = [c_int, c_int, P, P, P, c_int, c_float, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_group_window_spans_device.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.tsa_kv_product.argtypes = [c_int, c_int, P, P, c_float, P, c_int, c_int, c_int, c_void_p]
+    lib.tsa_kv_product_bwd.argtypes = [c_int, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_kv_append.argtypes = [ctypes.POINTER(DecodeCfg), c_void_p, c_void_p, c_int, c_int, P, P, P, P, c_int,
                                   c_void_p, c_void_p]
     lib.tsa_att_decode.argtypes = [ctypes.POINTER(DecodeCfg), c_void_p, c_void_p, c_int, c_int, P, P, c_int, c_float,

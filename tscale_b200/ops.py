@@ -158,6 +158,25 @@ def rope_norm_bwd(src, grad, rope, heads, head_dim, direction=1.0):
     return out
 
 
+def kv_product(k, val, heads, head_dim, kv_mult=1.0, out_dtype=None):
+    """Combiner input [rows][H*D*4] from k and the attention output."""
+    out_dtype = k.dtype if out_dtype is None else out_dtype
+    out = torch.empty((k.shape[0], heads * head_dim * 4), dtype=out_dtype, device=k.device)
+    check(abi.lib().tsa_kv_product(_DT[k.dtype], _DT[out_dtype], p2d(k), p2d(val), kv_mult, p2d(out), heads, head_dim, k.shape[0], _stream()))
+    return out
+
+
+def kv_product_bwd(k, val, dkv, heads, head_dim):
+    """Returns (dK, dVal [rows][H*D] of dkv's dtype, dScale f32 [H][rows])."""
+    rows = k.shape[0]
+    dk = torch.empty((rows, heads * head_dim), dtype=dkv.dtype, device=k.device)
+    dv = torch.empty_like(dk)
+    ds = torch.empty((heads, rows), dtype=torch.float32, device=k.device)
+    check(abi.lib().tsa_kv_product_bwd(_DT[k.dtype], _DT[dkv.dtype], p2d(k), p2d(val), p2d(dkv), p2d(dk), p2d(dv), p2d(ds),
+                                       heads, head_dim, rows, _stream()))
+    return dk, dv, ds
+
+
 def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat16, grad_dtype=torch.bfloat16,
              qk_vec_scale=1.0, v_vec_scale=1.0, force_generic=False):
     return abi.AttCfg(_DT[qk_dtype], _DT[v_dtype], _DT[out_dtype], _DT[grad_dtype], head_dim_qk, head_dim_v,
