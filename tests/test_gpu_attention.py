@@ -189,6 +189,48 @@ def test_bwd_against_oracle(window, slope, d):
 
 
 @pytest.mark.parametrize("d", [64, 128])
+def test_bwd_ragged_and_multispan(d):
+    """Backward on a ragged length with empty rows and rows of two spans: the tensor-core path (transposed spans from
+    the library's own transpose) and the SIMT path against the oracle."""
+    from tscale_b200 import ops
+    length = 300
+    rows = []
+    for i in range(length):
+        if i % 7 == 0:
+            rows.append([])
+        elif i > 140 and i % 5 == 0:
+            rows.append([(3, 40), (i - 20, i - 1)])
+        else:
+            rows.append([(max(0, i - 90), i - 1)] if i > 0 else [])
+    spans, ptr = [], [0]
+    for r in rows:
+        spans.extend(r)
+        ptr.append(len(spans))
+    custom = (np.array(spans, dtype=np.int32).reshape(-1, 2), np.array(ptr, dtype=np.int32))
+    heads, slope = 2, 0.25
+    out, lse, ref, (g, mask, cfg, spans_np, ptr_np, (qd, kd, vd)) = _run_fwd(
+        7, [length], None, slope, heads, d, "i8", "e4m3", out_dtype=torch.float32, scale=0.5, custom=custom)
+    rng = np.random.default_rng(8)
+    d_out = (rng.standard_normal(out.shape) * 1e-2).astype(np.float32)
+    gref = O.att_bwd(qd, kd, vd, d_out, spans_np, ptr_np, heads, slope, fwd=ref)
+    cfg.grad_dtype = 4  # f32
+    out_t = torch.from_numpy(ref["out"]).to(_dev())
+    lse_t = torch.from_numpy(ref["lse"]).to(_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    for flags in (0, 1):
+        cfg.flags = flags
+        dq, dk, dv = ops.att_bwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], torch.from_numpy(d_out).to(_dev()), out_t, lse_t,
+                                 mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+            r = util.rel_l2(util.to_np(got), gref[name])
+            assert r < util.GRAD_REL_L2, (flags, name, r)
+        empty = [i for i, r in enumerate(rows) if not r]
+        assert float(dq[empty].abs().max().item()) == 0
+
+
+@pytest.mark.parametrize("d", [64, 128])
 def test_int8_scores_bit_exact(d):
     from tscale_b200 import ops
     rng = np.random.default_rng(6)
