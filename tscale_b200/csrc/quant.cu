@@ -243,24 +243,31 @@ __global__ void __launch_bounds__(256) NormRopeQuantKernel(float vecScale, float
         for (int st = 0; st < STEPS; ++st) {
             const int e = base[j] + st * STEP_ELEMS + laneOff;
             const bool live = t < len && e < width;
+            // packed f32x2 arithmetic (two elements per instruction, each product and sum rounded on its own like the
+            // scalar form: no fused multiply-add)
             float y0[EPL], y1[EPL];
+            const float2 mult2 = make_float2(mult, mult);
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) {
-                y0[i] = __fmul_rn(lo[j][st][i], mult);
-                y1[i] = __fmul_rn(hi[j][st][i], mult);
+            for (int i = 0; i < EPL; i += 2) {
+                const float2 a = __fmul2_rn(make_float2(lo[j][st][i], lo[j][st][i + 1]), mult2);
+                const float2 b = __fmul2_rn(make_float2(hi[j][st][i], hi[j][st][i + 1]), mult2);
+                y0[i] = a.x, y0[i + 1] = a.y, y1[i] = b.x, y1[i + 1] = b.y;
             }
             if (rope.Valid() && live) {
                 float cs[EPL], sn[EPL];
                 const int k = e & (headDim - 1);
                 LoadVec<TRope, EPL>(rope.Row(t) + k, cs);
                 LoadVec<TRope, EPL>(rope.Row(t) + k + 32, sn);
+                const float2 dir2 = make_float2(ropeDir, ropeDir), ndir2 = make_float2(-ropeDir, -ropeDir);
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) {
-                    const float sinValue = __fmul_rn(sn[i], ropeDir);
-                    const float r0 = __fsub_rn(__fmul_rn(y0[i], cs[i]), __fmul_rn(y1[i], sinValue));
-                    const float r1 = __fadd_rn(__fmul_rn(y0[i], sinValue), __fmul_rn(y1[i], cs[i]));
-                    y0[i] = r0;
-                    y1[i] = r1;
+                for (int i = 0; i < EPL; i += 2) {
+                    const float2 c2 = make_float2(cs[i], cs[i + 1]), s2 = make_float2(sn[i], sn[i + 1]);
+                    const float2 sp = __fmul2_rn(s2, dir2), sm = __fmul2_rn(s2, ndir2); // sin * dir and its negative (exact)
+                    const float2 v0 = make_float2(y0[i], y0[i + 1]), v1 = make_float2(y1[i], y1[i + 1]);
+                    // r0 = v0 cos - v1 sin,  r1 = v0 sin + v1 cos
+                    const float2 r0 = __fadd2_rn(__fmul2_rn(v0, c2), __fmul2_rn(v1, sm));
+                    const float2 r1 = __fadd2_rn(__fmul2_rn(v0, sp), __fmul2_rn(v1, c2));
+                    y0[i] = r0.x, y0[i + 1] = r0.y, y1[i] = r1.x, y1[i + 1] = r1.y;
                 }
             }
             if (t < rows && e < width) {
