@@ -105,6 +105,40 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
     }
     int chunk = (total + p.TargetCtas - 1) / p.TargetCtas;
     chunk = max((chunk + 7) & ~7, DEC_MIN_CHUNK);
+    // A sequence's last chunk is a partial one, so that chunk size can give up to NSeq chunks more than CTAs are
+    // resident, and those would run as a second, nearly empty wave.  Take the smallest chunk size (a multiple of 8)
+    // whose chunks all fit the one wave instead: the count of chunks falls as the size grows, and
+    // total / (TargetCtas - NSeq) is always enough, so a bisection between the two finds it.
+    if (p.NSeq < p.TargetCtas) {
+        int lo = chunk / 8;
+        int hi = max(((total + (p.TargetCtas - p.NSeq) - 1) / (p.TargetCtas - p.NSeq) + 7) / 8, lo);
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            int cnt = 0;
+            for (int s = tid; s < p.NSeq; s += nThreads) {
+                cnt += (SeqKeys(p.CtxLens, s, p.Window) + mid * 8 - 1) / (mid * 8);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+            }
+            PlanSync(); // the previous round's sums have been read
+            if ((tid & 31) == 0) {
+                red[tid >> 5] = cnt;
+            }
+            PlanSync();
+            cnt = 0;
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                cnt += red[w];
+            }
+            if (cnt <= p.TargetCtas) {
+                hi = mid;
+            } else {
+                lo = mid + 1;
+            }
+        }
+        chunk = lo * 8;
+    }
     // chunk slots per contiguous slice of sequences, then an exclusive scan over the slices
     const int per = (p.NSeq + nThreads - 1) / nThreads;
     const int s0 = tid * per, s1 = min(s0 + per, p.NSeq);
@@ -170,6 +204,20 @@ __device__ __forceinline__ int Dp4aUS(uint32_t a, uint32_t b, int c)
 {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// two 16-bit x 8-bit products added to c: a = (w0 | w1 << 16) unsigned, b bytes signed; lo takes bytes 0 and 1 of b, hi bytes 2 and 3
+__device__ __forceinline__ int Dp2aLoUS(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp2a.lo.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int Dp2aHiUS(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp2a.hi.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
 
@@ -257,20 +305,44 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
                     acc[i] *= corr;
                 }
             }
+            // weights times value scales of the batch as 16-bit integers relative to the batch maximum (relative error of a
+            // weight at most 2^-17 of the largest one), so that the 8 x 16 byte products run as two-token integer dot
+            // products (dp2a) instead of a convert and a multiply-add per byte; one float update per batch
+            float wv[DEC_UNROLL];
+            float bmax = 0;
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
                 const float w = exp2f(z[u] - m);
                 l += w;
-                const float wv = w * vs[u];
-                const int words[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+                wv[u] = w * vs[u];
+                bmax = fmaxf(bmax, wv[u]);
+            }
+            const float qScale = bmax > 0 ? 65535.0f / bmax : 0.0f;
+            int iacc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                iacc[i] = 0;
+            }
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; u += 2) {
+                const uint32_t wp = __float2uint_rn(wv[u] * qScale) | (__float2uint_rn(wv[u + 1] * qScale) << 16);
+                const uint32_t w0[4] = {(uint32_t)vv[u].x, (uint32_t)vv[u].y, (uint32_t)vv[u].z, (uint32_t)vv[u].w};
+                const uint32_t w1[4] = {(uint32_t)vv[u + 1].x, (uint32_t)vv[u + 1].y, (uint32_t)vv[u + 1].z, (uint32_t)vv[u + 1].w};
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) {
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        const int s8 = (int)(int8_t)(words[wi] >> (8 * b));
-                        acc[wi * 4 + b] = fmaf(wv, (float)s8, acc[wi * 4 + b]);
-                    }
+                    // bytes (t0 b0, t1 b0, t0 b1, t1 b1) and (t0 b2, t1 b2, t0 b3, t1 b3)
+                    const uint32_t lo = __byte_perm(w0[wi], w1[wi], 0x5140);
+                    const uint32_t hi = __byte_perm(w0[wi], w1[wi], 0x7362);
+                    iacc[wi * 4 + 0] = Dp2aLoUS(wp, lo, iacc[wi * 4 + 0]);
+                    iacc[wi * 4 + 1] = Dp2aHiUS(wp, lo, iacc[wi * 4 + 1]);
+                    iacc[wi * 4 + 2] = Dp2aLoUS(wp, hi, iacc[wi * 4 + 2]);
+                    iacc[wi * 4 + 3] = Dp2aHiUS(wp, hi, iacc[wi * 4 + 3]);
                 }
+            }
+            const float deq = bmax * (1.0f / 65535.0f);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                acc[i] = fmaf((float)iacc[i], deq, acc[i]);
             }
         }
         if (headOk) {
