@@ -373,3 +373,74 @@ def decode_step(k_cache, k_scale, v_cache, v_scale, q8, q_scale, heads, width, s
     lib().oracle_decode_step(ctx, heads, d, width, c_float(slope), 0 if exp_mode == "poly" else 1,
                              kp, ksp, vp, vsp, qp, qsp, out.ctypes.data_as(_fp))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# one-token inference through the int8 model (cpu_infer.cpp:466-560)
+def make_infer_model(seed, dim, head_dim, heads, relu_mult, vocab, label_count, widths_slopes):
+    """Seeded random int8 model in the form of TCPUModelParams (cpu_infer.cpp:59-84): a dict of numpy arrays.
+    widths_slopes: one (attention width, ALiBi slope) pair per layer."""
+    rng = np.random.default_rng(seed)
+    hs, relu_dim = heads * head_dim, heads * 128 * relu_mult
+
+    def mat(rows, cols):
+        return np.clip(np.rint(rng.standard_normal((rows, cols)) * 32), -127, 127).astype(np.int8)
+
+    def scale():
+        return np.float32(rng.uniform(0.5, 1.5) / 32)
+
+    layers = []
+    for width, slope in widths_slopes:
+        layers.append(dict(qk=mat(hs, dim), qv=mat(hs, dim), k=mat(hs, dim), v=mat(hs, dim), combiner=mat(dim, hs * 4),
+                           expand=mat(relu_dim, dim), contract=mat(dim, relu_dim), qv_scale=scale(), combiner_scale=scale(),
+                           contract_scale=scale(), width=int(width), slope=float(slope)))
+    return dict(dim=dim, head_dim=head_dim, heads=heads, relu_mult=relu_mult, vocab=vocab, label_count=label_count, layers=layers,
+                label_embed=mat(label_count, dim), label_embed_scale=scale(), final_layer=mat(vocab, dim), final_layer_scale=scale(),
+                bias=(rng.standard_normal(vocab) * 0.5).astype(np.float32))
+
+
+class InferOracle:
+    """One sequence stepping through the model: the restated oracle (use_ref=False) or the reference's own
+    NCPUInfer::ComputePrediction (use_ref=True).  rope_len bounds the number of steps."""
+
+    def __init__(self, model, rope_len, use_ref=False, exp_mode="exact"):
+        self.model = model          # keeps the weight arrays alive: the C side holds pointers into them
+        self.use_ref = use_ref
+        self.vocab = model["vocab"]
+        self._l = ref() if use_ref else lib()
+        pre = "ref_infer_" if use_ref else "oracle_infer_"
+        create = getattr(self._l, pre + "create")
+        create.restype = ctypes.c_void_p
+        self._step = getattr(self._l, pre + "step")
+        self._free = getattr(self._l, pre + "free")
+        names = ("qk", "qv", "k", "v", "combiner", "expand", "contract")
+        n = len(model["layers"])
+        mats = (ctypes.c_void_p * (7 * n))()
+        for i, layer in enumerate(model["layers"]):
+            for j, nm in enumerate(names):
+                assert layer[nm].dtype == np.int8 and layer[nm].flags["C_CONTIGUOUS"]
+                mats[i * 7 + j] = layer[nm].ctypes.data
+        self._scalars = np.array([[l["qv_scale"], l["combiner_scale"], l["contract_scale"], l["width"], l["slope"]] for l in model["layers"]],
+                                 dtype=np.float32)
+        self._mats = mats
+        self._h = ctypes.c_void_p(create(
+            model["dim"], model["head_dim"], model["heads"], model["relu_mult"], model["vocab"], model["label_count"], n, int(rope_len),
+            mats, self._scalars.ctypes.data_as(_fp), model["label_embed"].ctypes.data_as(_bp), c_float(model["label_embed_scale"]),
+            model["final_layer"].ctypes.data_as(_bp), c_float(model["final_layer_scale"]), model["bias"].ctypes.data_as(_fp)))
+        if not use_ref:
+            self._l.oracle_infer_set_exp(self._h, 0 if exp_mode == "poly" else 1)
+
+    def step(self, labels, want_logits=False):
+        labels, lp = _i(labels)
+        pred = np.zeros(self.vocab, dtype=np.float32)
+        if self.use_ref:
+            self._step(self._h, lp, len(labels), pred.ctypes.data_as(_fp))
+            return pred
+        logits = np.zeros(self.vocab, dtype=np.float32)
+        self._step(self._h, lp, len(labels), pred.ctypes.data_as(_fp), logits.ctypes.data_as(_fp))
+        return (pred, logits) if want_logits else pred
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._free(self._h)
+            self._h = None

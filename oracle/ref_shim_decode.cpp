@@ -93,4 +93,91 @@ float ref_e4m3_to_float(int x)
     return ConvertE4toFloat((i8)x);
 }
 
+// ---- the whole one-token inference step (NCPUInfer::ComputePrediction, cpu_infer.cpp:530-560) ------------------
+// The model is handed over already in the reference's int8 form (TCPUModelParams, cpu_infer.cpp:59-84):
+//   layerMats  : 7 matrices per layer, row-major int8: QK, QV [H*D][dim], K, V [H*D][dim], Combiner [dim][4*H*D],
+//                Expand [reluDim][dim], Contract [dim][reluDim]
+//   layerScalars : 5 floats per layer: QVScale, CombinerScale, ContractScale, attention width, ALiBi slope
+// ropeLen is the number of positions the context can take (the reference sizes its rope table by the widest window).
+struct TRefInfer
+{
+    NCPUInfer::TCPUModelParams Params;
+    NCPUInfer::TCPUInferContext Ctx;
+};
+
+static void FillMatrix(TArray2D<i8> *p, const signed char *src, yint xSize, yint ySize)
+{
+    p->SetSizes(xSize, ySize);
+    for (yint y = 0; y < ySize; ++y) {
+        memcpy(&(*p)[y][0], src + y * xSize, xSize);
+    }
+}
+
+void *ref_infer_create(int dim, int headDim, int headCount, int reluMult, int vocab, int labelCount, int layerCount, int ropeLen,
+    const signed char *const *layerMats, const float *layerScalars, const signed char *labelEmbed, float labelEmbedScale,
+    const signed char *finalLayer, float finalLayerScale, const float *bias)
+{
+    using namespace NCPUInfer;
+    TRefInfer *h = new TRefInfer;
+    TCPUModelParams &p = h->Params;
+    p.ModelDescr.Dims.Dim = dim;
+    p.ModelDescr.Dims.QDim = headDim;
+    p.ModelDescr.Dims.TTDim = headDim;
+    p.ModelDescr.Dims.HeadCount = headCount;
+    p.ModelDescr.Dims.ReluMult = reluMult;
+    p.ModelDescr.VocabSize = vocab;
+    p.ModelDescr.LabelCount = labelCount;
+    p.ModelDescr.AttentionWidthArr.push_back(ropeLen);
+    yint hs = (yint)headDim * headCount;
+    yint reluDim = p.ModelDescr.Dims.GetReluDim();
+    p.LayerArr.resize(layerCount);
+    for (int d = 0; d < layerCount; ++d) {
+        TCPUModelParams::TAttentionMatrices &att = p.LayerArr[d];
+        const signed char *const *m = layerMats + d * 7;
+        FillMatrix(&att.QK, m[0], dim, hs);
+        FillMatrix(&att.QV, m[1], dim, hs);
+        FillMatrix(&att.K, m[2], dim, hs);
+        FillMatrix(&att.V, m[3], dim, hs);
+        FillMatrix(&att.Combiner, m[4], hs * COMBINER_REP, dim);
+        FillMatrix(&att.Expand, m[5], dim, reluDim);
+        FillMatrix(&att.Contract, m[6], reluDim, dim);
+        const float *s = layerScalars + d * 5;
+        att.QVScale = s[0];
+        att.CombinerScale = s[1];
+        att.ContractScale = s[2];
+        att.AttentionWidth = (int)s[3];
+        att.AlibiSlope = s[4];
+        p.ModelDescr.Layers.push_back(TModelDescr::TAttentionPosParams(s[4], 0));
+    }
+    FillMatrix(&p.LabelEmbed, labelEmbed, dim, labelCount);
+    p.LabelEmbedScale = labelEmbedScale;
+    FillMatrix(&p.FinalLayer, finalLayer, dim, vocab);
+    p.FinalLayerScale = finalLayerScale;
+    p.Bias.resize(vocab);
+    memcpy(p.Bias.data(), bias, sizeof(float) * vocab);
+    h->Ctx.Init(p);
+    return h;
+}
+
+// one step: the labels of the new token in, the distribution over the vocabulary out (prediction may be null)
+void ref_infer_step(void *handle, const int *labels, int labelCount, float *prediction)
+{
+    using namespace NCPUInfer;
+    TRefInfer *h = (TRefInfer *)handle;
+    TVector<TLabelIndex> labelArr;
+    for (int i = 0; i < labelCount; ++i) {
+        labelArr.push_back(labels[i]);
+    }
+    TVector<float> distr;
+    ComputePrediction(h->Params, labelArr, &h->Ctx, prediction ? &distr : nullptr);
+    if (prediction) {
+        memcpy(prediction, distr.data(), sizeof(float) * YSize(distr));
+    }
+}
+
+void ref_infer_free(void *handle)
+{
+    delete (TRefInfer *)handle;
+}
+
 }

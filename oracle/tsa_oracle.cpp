@@ -722,3 +722,219 @@ extern "C" void oracle_kv_product_bwd(int len, int H, int D, const float *k, con
         }
     }
 }
+
+///////////////////////////////////////////////////////////////////////////////////////////////////
+// one-token inference step through the int8 model with per-layer KV caches
+// (NCPUInfer::ComputePrediction / AddLookupProduct, code/gpt/train/cpu_infer.cpp:466-560).
+// Matrices are row-major int8 [rows][cols]; same argument layout as ref_infer_create of the reference shim.
+namespace {
+const float kVecScale = 1.0f / 24; // VEC_SCALE, cpu_infer.cpp:16
+
+struct TInferLayer
+{
+    const int8_t *QK, *QV, *K, *V, *Combiner, *Expand, *Contract;
+    float QVScale, CombinerScale, ContractScale, Slope;
+    int Width;
+    std::vector<int8_t> KeyCache, ValCache; // [t][H*D]
+    std::vector<float> KeyScale, ValScale;  // [t][H]
+};
+
+struct TInferOracle
+{
+    int Dim, HeadDim, HeadCount, ReluDim, Vocab, LabelCount, RopeLen, T = 0, ExpMode = 1;
+    std::vector<TInferLayer> Layers;
+    const int8_t *LabelEmbed, *FinalLayer;
+    float LabelEmbedScale, FinalLayerScale;
+    const float *Bias;
+    std::vector<float> Rope;
+    std::vector<float> Logits;
+};
+
+// ConvertToInt8 (cpu_infer.cpp:88-92): round to nearest even, clamp to +-127
+int8_t InferToInt8(float x)
+{
+    float r = nearbyintf(x);
+    r = r > 127.0f ? 127.0f : (r < -127.0f ? -127.0f : r);
+    return (int8_t)r;
+}
+
+// NormalizeState (cpu_infer.cpp:357-391): groups of dim / groups elements, sequential float sum of squares
+void InferNormalize(const float *src, int dim, int groups, int8_t *dst, float *groupScale)
+{
+    int gd = dim / groups;
+    for (int h = 0; h < groups; ++h) {
+        const float *s = src + h * gd;
+        float sum2 = 0;
+        for (int x = 0; x < gd; ++x) {
+            sum2 += s[x] * s[x];
+        }
+        if (sum2 == 0) {
+            for (int x = 0; x < gd; ++x) {
+                dst[h * gd + x] = 0;
+            }
+            if (groupScale) {
+                groupScale[h] = 0;
+            }
+        } else {
+            float sko = sqrtf(sum2 / gd);
+            float discrScale = sko * kVecScale;
+            float mult = 1 / discrScale;
+            for (int x = 0; x < gd; ++x) {
+                dst[h * gd + x] = InferToInt8(s[x] * mult);
+            }
+            if (groupScale) {
+                groupScale[h] = discrScale;
+            }
+        }
+    }
+}
+
+// MulForward (cpu_infer.cpp:282-293): exact int32 dot products of the vector with every matrix row, as floats
+void InferMul(const int8_t *vec, const int8_t *mat, int rows, int cols, float *res)
+{
+    for (int k = 0; k < rows; ++k) {
+        int32_t dot = 0;
+        for (int x = 0; x < cols; ++x) {
+            dot += (int32_t)vec[x] * (int32_t)mat[(size_t)k * cols + x];
+        }
+        res[k] = (float)dot;
+    }
+}
+} // namespace
+
+extern "C" void *oracle_infer_create(int dim, int headDim, int headCount, int reluMult, int vocab, int labelCount, int layerCount, int ropeLen,
+    const int8_t *const *layerMats, const float *layerScalars, const int8_t *labelEmbed, float labelEmbedScale,
+    const int8_t *finalLayer, float finalLayerScale, const float *bias)
+{
+    TInferOracle *h = new TInferOracle;
+    h->Dim = dim;
+    h->HeadDim = headDim;
+    h->HeadCount = headCount;
+    h->ReluDim = headCount * 128 * reluMult; // TModelDims::GetReluDim, model_dim.h:66
+    h->Vocab = vocab;
+    h->LabelCount = labelCount;
+    h->RopeLen = ropeLen;
+    h->Layers.resize(layerCount);
+    for (int d = 0; d < layerCount; ++d) {
+        TInferLayer &l = h->Layers[d];
+        const int8_t *const *m = layerMats + d * 7;
+        l.QK = m[0], l.QV = m[1], l.K = m[2], l.V = m[3], l.Combiner = m[4], l.Expand = m[5], l.Contract = m[6];
+        const float *s = layerScalars + d * 5;
+        l.QVScale = s[0], l.CombinerScale = s[1], l.ContractScale = s[2], l.Width = (int)s[3], l.Slope = s[4];
+    }
+    h->LabelEmbed = labelEmbed;
+    h->LabelEmbedScale = labelEmbedScale;
+    h->FinalLayer = finalLayer;
+    h->FinalLayerScale = finalLayerScale;
+    h->Bias = bias;
+    h->Rope.resize((size_t)ropeLen * headDim);
+    oracle_fill_rope(headDim, ropeLen, h->Rope.data());
+    return h;
+}
+
+// expMode 0: the reference's polynomial 2^x, 1: exact exp2f
+extern "C" void oracle_infer_set_exp(void *handle, int expMode)
+{
+    ((TInferOracle *)handle)->ExpMode = expMode;
+}
+
+// prediction [vocab] (may be null); logits [vocab] (may be null) receives the int32 products of the final layer as floats
+extern "C" void oracle_infer_step(void *handle, const int *labels, int labelCount, float *prediction, float *logits)
+{
+    TInferOracle &m = *(TInferOracle *)handle;
+    const int dim = m.Dim, H = m.HeadCount, D = m.HeadDim, hs = H * D, reluDim = m.ReluDim;
+    std::vector<float> state(dim, 0.0f);
+    for (int i = 0; i < labelCount; ++i) {
+        for (int x = 0; x < dim; ++x) {
+            state[x] += m.LabelEmbed[(size_t)labels[i] * dim + x] * m.LabelEmbedScale;
+        }
+    }
+    std::vector<int8_t> norm(std::max(dim, reluDim)), qk(hs), qv(hs), k(hs), v(hs), kv((size_t)hs * 4), relu(reluDim);
+    std::vector<float> qkSrc(hs), qvSrc(hs), kSrc(hs), vSrc(hs), qvScale(H), vScale(H, kVecScale), qScale(H, kVecScale), val(hs), delta(dim),
+        reluSrc(reluDim);
+    const float *rope = m.Rope.data() + (size_t)m.T * D;
+    for (TInferLayer &l : m.Layers) {
+        InferNormalize(state.data(), dim, dim / 128, norm.data(), nullptr); // STATE_NORM_TILE = 128
+        InferMul(norm.data(), l.QK, hs, dim, qkSrc.data());
+        InferMul(norm.data(), l.QV, hs, dim, qvSrc.data());
+        InferMul(norm.data(), l.K, hs, dim, kSrc.data());
+        InferMul(norm.data(), l.V, hs, dim, vSrc.data());
+        oracle_apply_rope(D, 1, hs, 1.0f, rope, qkSrc.data());
+        oracle_apply_rope(D, 1, hs, 1.0f, rope, qvSrc.data());
+        InferNormalize(qkSrc.data(), hs, H, qk.data(), nullptr);
+        InferNormalize(qvSrc.data(), hs, H, qv.data(), qvScale.data());
+        InferNormalize(kSrc.data(), hs, H, k.data(), nullptr);
+        InferNormalize(vSrc.data(), hs, H, v.data(), nullptr);
+        const float qvMult = l.QVScale * kVecScale * sqrtf(1.0f / dim);
+        for (float &x : qvScale) {
+            x *= qvMult;
+        }
+        l.KeyCache.insert(l.KeyCache.end(), qv.begin(), qv.end());
+        l.ValCache.insert(l.ValCache.end(), v.begin(), v.end());
+        l.KeyScale.insert(l.KeyScale.end(), qvScale.begin(), qvScale.end());
+        l.ValScale.insert(l.ValScale.end(), vScale.begin(), vScale.end());
+        int ctxLen = (int)(l.KeyCache.size() / hs);
+        oracle_decode_step(ctxLen, H, D, l.Width, l.Slope, m.ExpMode, l.KeyCache.data(), l.KeyScale.data(), l.ValCache.data(), l.ValScale.data(),
+            qk.data(), qScale.data(), val.data());
+        // KVProduct (cpu_infer.cpp:318-337)
+        for (int head = 0; head < H; ++head) {
+            for (int blk = 0; blk < 4; ++blk) {
+                for (int z = 0; z < D; ++z) {
+                    kv[(size_t)head * D * 4 + blk * D + z] = InferToInt8(k[head * D + (z ^ blk)] * val[head * D + z]);
+                }
+            }
+        }
+        InferMul(kv.data(), l.Combiner, dim, hs * 4, delta.data());
+        const float combScale = l.CombinerScale * kVecScale * sqrtf(1.0f / (hs * 4));
+        for (int x = 0; x < dim; ++x) {
+            state[x] += delta[x] * combScale;
+        }
+        InferNormalize(state.data(), dim, dim / 128, norm.data(), nullptr);
+        InferMul(norm.data(), l.Expand, reluDim, dim, reluSrc.data());
+        InferNormalize(reluSrc.data(), reluDim, H, relu.data(), nullptr);
+        for (int8_t &x : relu) {
+            x = std::max<int8_t>(0, x);
+        }
+        InferMul(relu.data(), l.Contract, dim, reluDim, delta.data());
+        const float contractScale = l.ContractScale * kVecScale * sqrtf(1.0f / reluDim);
+        for (int x = 0; x < dim; ++x) {
+            state[x] += delta[x] * contractScale;
+        }
+    }
+    if (prediction || logits) {
+        InferNormalize(state.data(), dim, dim / 128, norm.data(), nullptr);
+        m.Logits.resize(m.Vocab);
+        InferMul(norm.data(), m.FinalLayer, m.Vocab, dim, m.Logits.data());
+        if (logits) {
+            memcpy(logits, m.Logits.data(), sizeof(float) * m.Vocab);
+        }
+        if (prediction) {
+            // SoftMax (cpu_infer.cpp:340-354) over TSoftMaxBuf (cpu_infer.cpp:216-268): the maximum starts at 0
+            const float finalScale = sqrtf(1.0f / dim) * (1.0f / 0.693147f) * m.FinalLayerScale * kVecScale;
+            int padded = (m.Vocab + 7) / 8 * 8;
+            std::vector<float> buf(std::max(padded, 8), -1e38f);
+            float maxValue = 0;
+            for (int x = 0; x < m.Vocab; ++x) {
+                buf[x] = m.Logits[x] * finalScale + m.Bias[x];
+                maxValue = std::max(maxValue, buf[x]);
+            }
+            float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int i = 0; i < padded; ++i) {
+                float e = (m.ExpMode == 0) ? RefPolyExp2(buf[i] - maxValue) : exp2f(fmaxf(buf[i] - maxValue, -127.0f));
+                buf[i] = e;
+                lanes[i & 7] += e;
+            }
+            float total = ((lanes[0] + lanes[4]) + (lanes[2] + lanes[6])) + ((lanes[1] + lanes[5]) + (lanes[3] + lanes[7]));
+            float scale = 1 / total;
+            for (int x = 0; x < m.Vocab; ++x) {
+                prediction[x] = buf[x] * scale;
+            }
+        }
+    }
+    m.T += 1;
+}
+
+extern "C" void oracle_infer_free(void *handle)
+{
+    delete (TInferOracle *)handle;
+}
