@@ -253,6 +253,58 @@ int tsa_group_window_spans(int fragCount, const int *fragLens, int window, int t
 int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len, int window, int transposed,
     int maxGroups, tsa_span_group *groups, int *groupPtr, tsa_stream_t stream);
 
+/* ---- one-token inference step with KV caches ("next" scope row: the caller of the decode kernel) ---------------
+ * Replaces NCPUInfer::ComputePrediction / AddLookupProduct (code/gpt/train/cpu_infer.cpp:466-560), which steps one
+ * sequence on the CPU, for a batch of up to 64 sequences on the GPU.  The model is in the reference's int8 form
+ * (TCPUModelParams, cpu_infer.cpp:59-84, made by ConvertModel, cpu_infer.cpp:139-158): all matrices row-major int8
+ * [rows][cols] in device memory, 16-byte aligned:
+ *   qk, qv, k, v [head_count * head_dim][dim];  combiner [dim][4 * head_count * head_dim];
+ *   expand [relu_dim][dim];  contract [dim][relu_dim];  label_embed [label_count][dim];  final_layer [vocab_size][dim]
+ * bias f32 [vocab_size]; rope f32 [rope_len][head_dim] as FillRopeBuf writes it (code/gpt/att/rope.cpp:4-24).
+ * Query and value heads have one size (QDim == TTDim == head_dim, 64 or 128); relu_dim = head_count * 128 * ReluMult
+ * (TModelDims::GetReluDim, model_dim.h:66).  `layers` is a host array.
+ * State per layer: one KV cache per sequence (tsa_kv_seq with f32 scale planes, capacity rows) and its token count;
+ * layerSeqs[l] is a device array of nSeq tsa_kv_seq, ctxLens a device array [layer_count][nSeq] that the step
+ * increments (all layers of a sequence hold the same count).  maxCtx: host-side upper bound of the counts before the
+ * step.  labels: device int [nSeq][labelsPerSeq], the embedding rows summed for each sequence's new token.
+ * prediction f32 [nSeq][vocab_size] (may be NULL) receives the distribution over the vocabulary, logits (may be NULL)
+ * the exact int32 products of the final layer as floats.  Asynchronous on `stream`; allocates nothing. */
+typedef struct {
+    int dim;
+    int head_dim;
+    int head_count;
+    int relu_dim;
+    int vocab_size;
+    int label_count;
+    int layer_count;
+} tsa_infer_dims;
+
+typedef struct {
+    const signed char *qk, *qv, *k, *v, *combiner, *expand, *contract;
+    float qv_scale;       /* TAttentionMatrices::QVScale */
+    float combiner_scale; /* CombinerScale */
+    float contract_scale; /* ContractScale */
+    int attention_width;  /* keys [cur - width, cur - 1]; 0: the new token itself (cpu_infer.cpp:424-432) */
+    float alibi_slope;
+} tsa_infer_layer;
+
+typedef struct {
+    tsa_infer_dims dims;
+    const tsa_infer_layer *layers;
+    const signed char *label_embed;
+    float label_embed_scale;
+    const signed char *final_layer;
+    float final_layer_scale;
+    const float *bias;
+    const float *rope;
+    int rope_len;
+} tsa_infer_model;
+
+size_t tsa_infer_workspace_bytes(const tsa_infer_model *model, int nSeq, int maxCtx);
+int tsa_infer_step(const tsa_infer_model *model, const tsa_kv_seq *const *layerSeqs, int *ctxLens, int capacity,
+    const int *labels, int labelsPerSeq, int nSeq, int maxCtx, float *prediction, float *logits,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

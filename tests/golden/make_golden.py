@@ -12,6 +12,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
 from oracle import oracle as O  # noqa: E402
+from tests.util import INFER_CASES  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -88,6 +89,20 @@ def consumer_case(name, seed, rows, heads, d):
     print(name, rows, heads, d)
 
 
+def infer_case(name, steps, n_seq):
+    """Predictions of the reference's own ComputePrediction (cpu_infer.cpp:530-560) for n_seq label streams."""
+    model = O.make_infer_model(**INFER_CASES[name])
+    rng = np.random.default_rng(INFER_CASES[name]["seed"] + 1000)
+    labels = rng.integers(0, model["label_count"], (n_seq, steps, 1)).astype(np.int32)
+    pred = np.zeros((n_seq, steps, model["vocab"]), dtype=np.float32)
+    for s in range(n_seq):
+        ref = O.InferOracle(model, steps, use_ref=True)
+        for t in range(steps):
+            pred[s, t] = ref.step(labels[s, t])
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), labels=labels, prediction=pred)
+    print(name, steps, n_seq)
+
+
 def main():
     assert O.ref() is not None, "build oracle/_ref first (make -C oracle ref)"
     # window-64 layers of the reference use ALiBi slope 0.5, wide layers slope 0 (model_dim.cpp:83-90)
@@ -105,6 +120,8 @@ def main():
     producer_case("producer_d64", 20, 150, 3, 64)
     producer_case("producer_d128", 21, 90, 2, 128)
     consumer_case("consumer_d64", 30, 40, 3, 64)
+    infer_case("infer_d64", 24, 3)
+    infer_case("infer_d128", 12, 2)
     # 8-bit code points: ConvertE4toFloat for all bytes, Float2I8 on a grid
     e4 = np.array([O.ref().ref_e4m3_to_float(i) for i in range(256)], dtype=np.float32)
     grid = np.concatenate([np.linspace(-130, 130, 2081), np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5])]).astype(np.float32)

@@ -56,6 +56,17 @@ def test_bad_arguments_return_status_not_abort():
     dcfg = abi.DecodeCfg(96, abi.TSA_F16, abi.TSA_F32, 1.0)
     assert lib.tsa_att_decode(ctypes.byref(dcfg), None, None, 1, 1, null, null, 0, 0.0, null, 1, None, 0, None, None) == abi.TSA_BAD_ARG
     assert lib.tsa_att_decode_workspace_bytes(ctypes.byref(abi.DecodeCfg(128, abi.TSA_F16, abi.TSA_F32, 1.0)), 64, 16, 8192) > 0
+    # inference step: sizes are checked before anything is dereferenced or launched
+    im = abi.InferModel()
+    im.dims = abi.InferDims(768, 64, 12, 1536, 50000, 50100, 0)
+    assert lib.tsa_infer_workspace_bytes(ctypes.byref(im), 64, 8192) > 64 * 50000 * 4
+    assert lib.tsa_infer_workspace_bytes(ctypes.byref(im), 65, 8192) == 0          # at most 64 sequences per step
+    assert lib.tsa_infer_step(ctypes.byref(im), None, None, 16, None, 1, 4, 8, None, None, None, 0, None, None) == abi.TSA_BAD_ARG
+    im.dims.head_dim = 96
+    assert lib.tsa_infer_workspace_bytes(ctypes.byref(im), 4, 16) == 0
+    assert lib.tsa_infer_step(ctypes.byref(im), None, None, 16, None, 1, 4, 8, None, None, None, 0, None, None) == abi.TSA_BAD_ARG
+    assert b"head_dim" in lib.tsa_last_error()
+    assert ctypes.sizeof(abi.InferLayer) == 80 and ctypes.sizeof(abi.InferDims) == 28
 
 
 @pytest.mark.parametrize("name", ["att_w64_slope05", "att_full_slope0", "att_w1_d32", "att_handmade"])

@@ -118,3 +118,14 @@ def test_combiner_product_bit_exact():
         assert np.array_equal(O.kv_product(k, v, heads), O.kv_product(k, v, heads, use_ref=True))
         for a, b in zip(O.kv_product_bwd(k, v, g, heads), O.kv_product_bwd(k, v, g, heads, use_ref=True)):
             assert np.array_equal(a, b)
+
+
+def test_inference_step_bit_exact():
+    """NCPUInfer::ComputePrediction (cpu_infer.cpp:530-560) restated in the oracle: a fresh model, 16 steps."""
+    model = O.make_infer_model(77, 256, 64, 4, 1, 200, 30, [(4, 0.25), (0, 0.0), (32, 0.0)])
+    a = O.InferOracle(model, 16, exp_mode="poly")
+    b = O.InferOracle(model, 16, use_ref=True)
+    rng = np.random.default_rng(78)
+    for t in range(16):
+        labels = rng.integers(0, 30, 2)   # two labels summed per token
+        assert np.array_equal(a.step(labels), b.step(labels)), t

@@ -8,6 +8,14 @@ OUT_MAX_ABS = 2e-2
 OUT_MEAN_ABS = 2e-3
 GRAD_REL_L2 = 1e-2
 
+# arguments of oracle.make_infer_model for the inference fixtures tests/golden/infer_*.npz (the models are rebuilt
+# from their seeds; the fixtures hold the label streams and the reference's predictions)
+INFER_CASES = {
+    "infer_d64": dict(seed=40, dim=256, head_dim=64, heads=2, relu_mult=1, vocab=300, label_count=40,
+                      widths_slopes=[(8, 0.5), (0, 0.0), (64, 0.0)]),
+    "infer_d128": dict(seed=41, dim=384, head_dim=128, heads=3, relu_mult=2, vocab=150, label_count=20, widths_slopes=[(16, 0.0), (4, 0.5)]),
+}
+
 
 def make_qkv(seed, length, heads, dq, dv, scale=1.0):
     rng = np.random.default_rng(seed)

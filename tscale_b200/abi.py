@@ -48,12 +48,33 @@ class DecodeCfg(ctypes.Structure):
     _fields_ = [("head_dim", c_int), ("scale_dtype", c_int), ("out_dtype", c_int), ("qk_vec_scale", c_float)]
 
 
+class InferDims(ctypes.Structure):
+    """tsa_infer_dims"""
+    _fields_ = [("dim", c_int), ("head_dim", c_int), ("head_count", c_int), ("relu_dim", c_int), ("vocab_size", c_int),
+                ("label_count", c_int), ("layer_count", c_int)]
+
+
+class InferLayer(ctypes.Structure):
+    """tsa_infer_layer"""
+    _fields_ = [("qk", c_void_p), ("qv", c_void_p), ("k", c_void_p), ("v", c_void_p), ("combiner", c_void_p),
+                ("expand", c_void_p), ("contract", c_void_p), ("qv_scale", c_float), ("combiner_scale", c_float),
+                ("contract_scale", c_float), ("attention_width", c_int), ("alibi_slope", c_float)]
+
+
+class InferModel(ctypes.Structure):
+    """tsa_infer_model"""
+    _fields_ = [("dims", InferDims), ("layers", ctypes.POINTER(InferLayer)), ("label_embed", c_void_p),
+                ("label_embed_scale", c_float), ("final_layer", c_void_p), ("final_layer_scale", c_float),
+                ("bias", c_void_p), ("rope", c_void_p), ("rope_len", c_int)]
+
+
 EXPORTS = [
     "tsa_version", "tsa_last_error", "tsa_att_fwd", "tsa_att_fwd_workspace_bytes", "tsa_att_bwd",
     "tsa_att_bwd_workspace_bytes", "tsa_calc_dscale", "tsa_qk_scores_i32", "tsa_quant_rows", "tsa_kv_append",
     "tsa_att_decode", "tsa_att_decode_workspace_bytes", "tsa_make_window_spans", "tsa_transpose_attention",
     "tsa_group_attention", "tsa_group_window_spans", "tsa_att_decode_static", "tsa_att_decode_static_capacity_bytes",
     "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device", "tsa_kv_product", "tsa_kv_product_bwd",
+    "tsa_infer_workspace_bytes", "tsa_infer_step",
 ]
 
 
@@ -88,6 +109,10 @@ def _declare(lib):
                                           P, c_int, c_void_p, c_void_p]
     lib.tsa_att_decode_static_capacity_bytes.restype = c_size_t
     lib.tsa_att_decode_static_capacity_bytes.argtypes = []
+    lib.tsa_infer_workspace_bytes.restype = c_size_t
+    lib.tsa_infer_workspace_bytes.argtypes = [ctypes.POINTER(InferModel), c_int, c_int]
+    lib.tsa_infer_step.argtypes = [ctypes.POINTER(InferModel), ctypes.POINTER(c_void_p), c_void_p, c_int, c_void_p, c_int, c_int,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]
     lib.tsa_make_window_spans.argtypes = [c_int, c_int_p, c_int, c_int, c_int_p, c_int_p]
     lib.tsa_transpose_attention.argtypes = [c_int, c_int_p, c_int_p, c_int, c_int_p, c_int_p]
     lib.tsa_group_attention.argtypes = [c_int, c_int_p, c_int_p, c_int, c_void_p, c_int_p]
