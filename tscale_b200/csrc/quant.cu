@@ -190,20 +190,27 @@ __global__ void __launch_bounds__(256) NormRopeQuantKernel(float vecScale, float
     const int span = STEP_ELEMS * STEPS;                            // elements of one item
     const int width = headCount << headShift;
     const int groups = (width + span - 1) / span;                   // items per row
-    const long long items = (long long)rows * groups;
-    const long long first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * ITEMS;
+    const unsigned items = (unsigned)rows * (unsigned)groups;      // the launcher checks that this fits 31 bits
+    const unsigned first = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ITEMS;
     const int lane = threadIdx.x & 31;
     if (first >= items) {
         return;
     }
+    const int firstRow = (int)(first / (unsigned)groups), firstGroup = (int)(first - (unsigned)firstRow * (unsigned)groups);
+    const float invHeadDim = 1.0f / (float)headDim;                 // a power of two: multiplying by it is the exact division
     const int laneOff = (lane / LPB) * 64 + (lane % LPB) * EPL;     // first element of the lane inside a step
     float lo[ITEMS][STEPS][EPL], hi[ITEMS][STEPS][EPL];
     int row[ITEMS], base[ITEMS];
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-        const long long it = first + j;
-        row[j] = it < items ? (int)(it / groups) : rows;             // rows: nothing to do
-        base[j] = it < items ? (int)(it - (long long)row[j] * groups) * span : 0;
+        // item first + j: ITEMS <= groups or groups == 1, so one wrap at most
+        int g = firstGroup + j, r = firstRow;
+        if (g >= groups) {
+            r += g / groups;
+            g = g % groups;
+        }
+        row[j] = first + j < items ? r : rows;                       // rows: nothing to do
+        base[j] = first + j < items ? g * span : 0;
 #pragma unroll
         for (int st = 0; st < STEPS; ++st) {
             const int e = base[j] + st * STEP_ELEMS + laneOff;
@@ -236,7 +243,7 @@ __global__ void __launch_bounds__(256) NormRopeQuantKernel(float vecScale, float
         }
         float discr = 0;
         if (sum2 > 0) {
-            discr = __fmul_rn(__fsqrt_rn(__fdiv_rn(sum2, (float)headDim)), vecScale);
+            discr = __fmul_rn(__fsqrt_rn(__fmul_rn(sum2, invHeadDim)), vecScale);
         }
         const float mult = (discr > 0) ? __fdiv_rn(1.0f, discr) : 0.0f;
 #pragma unroll
@@ -321,6 +328,7 @@ static int LaunchNormRope(bool e4, float vecScale, float ropeDir, tsa_ptr2d src,
     if (items == 0) {
         return TSA_OK;
     }
+    TSA_REQUIRE(items < (1ll << 31) - 64, "tsa_norm_rope_quant: %lld warp items, fewer than 2^31 supported", items);
     P2D<typename TSrc::T> s(src);
     P2D<typename TRope::T> r(rope);
     P2D<uint8_t> d(dst);
