@@ -154,7 +154,7 @@ def run(args, rank, world, local_rank):
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
-            ctx.compute_prediction(labels, prediction=pred)
+            ctx.compute_prediction(labels, prediction=pred, max_ctx_bound=cap - 1)
     torch.cuda.synchronize()
     lens = [n + 1 for n in ctx0]   # the captured step has not run yet
 

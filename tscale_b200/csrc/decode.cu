@@ -38,6 +38,7 @@ struct TDecodeParams {
     int TargetCtas;  // chunk slots the keys of all sequences are spread over
     int *Status;     // device status word (may be null)
     int MaxSlots;    // TargetCtas + nSeq
+    int MaxCtx;      // the caller's upper bound of CtxLens: sizes the grid, checked on the device
 };
 
 __device__ __forceinline__ float LoadScale(const void *base, size_t idx, int dt)
@@ -90,6 +91,9 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
     int sum = 0;
     for (int s = tid; s < p.NSeq; s += nThreads) {
         sum += SeqKeys(p.CtxLens, s, p.Window);
+        if (p.CtxLens[s] > p.MaxCtx && blockIdx.x == 0 && p.Status) {
+            atomicOr(p.Status, kDevBadSpan); // the grid was sized for shorter sequences
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -430,7 +434,6 @@ size_t DecodeWorkspaceBytes(int headDim, int nSeq, int headCount, int maxCtx)
 
 int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStream_t stream)
 {
-    (void)maxCtx;
     int dev = 0, sms = 0;
     int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (rc == TSA_OK) {
@@ -455,9 +458,13 @@ int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStr
     perSm = perSm < 1 ? 1 : perSm;
     p.TargetCtas = sms * perSm < DEC_MAX_TARGET_CTAS ? sms * perSm : DEC_MAX_TARGET_CTAS;
     p.MaxSlots = p.TargetCtas + p.NSeq;
+    p.MaxCtx = maxCtx;
     p.Plan = (int *)p.Partial;
     p.Partial = (float *)((char *)p.Partial + DecodeHeaderBytes(p.NSeq));
-    dim3 grid(p.MaxSlots);
+    // chunks hold at least DEC_MIN_CHUNK keys, so short windows or contexts need fewer CTAs than the full wave
+    const long long keysMax = p.Window > 0 ? (p.Window < maxCtx ? p.Window : maxCtx) : 1;
+    const long long slotBound = (long long)p.NSeq * (keysMax / DEC_MIN_CHUNK + 1);
+    dim3 grid((unsigned)(slotBound < p.MaxSlots ? slotBound : p.MaxSlots));
     dim3 gridC(p.HeadCount, p.NSeq);
     void *args[] = {&p};
     rc = CheckCuda(cudaLaunchKernel(kern, grid, dim3(DEC_WARPS * 32), args, 0, stream), "decode launch");

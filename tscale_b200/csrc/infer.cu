@@ -25,8 +25,8 @@ constexpr float INF_VEC_SCALE = 1.0f / 24; // VEC_SCALE, cpu_infer.cpp:16
 constexpr int INF_NORM_TILE = 128;         // STATE_NORM_TILE, model_dim.h:23
 constexpr int INF_GEMV_ROWS = 4;           // matrix rows per warp
 constexpr int INF_GEMV_WARPS = 4;
-constexpr int INF_MAX_SEQ = 64;            // sequences per step (two lanes-per-sequence groups of a warp)
-constexpr int INF_TILE_BYTES = 200 * 1024; // shared memory for the batch's vectors in a matrix product
+constexpr int INF_MAX_SEQ = 64;            // sequences per step
+constexpr int INF_TILE_BYTES = 200 * 1024; // shared memory of a matrix product block: 32 vectors and its matrix rows, a chunk of columns
 
 // ConvertToInt8 (cpu_infer.cpp:88-92): round to nearest even, clamp to +-127
 __device__ __forceinline__ int ToInt8Clamp127(float x)
@@ -80,16 +80,26 @@ __device__ __forceinline__ void NormScales(float sum2, int n, float *discr, floa
     }
 }
 
-// NormalizeState over groups of groupSize elements: warp per (sequence, group); relu clamps negatives to 0 afterwards
+// NormalizeState over groups of groupSize elements: warp per (sequence, group); relu clamps negatives to 0 afterwards.
+// The group is staged in shared memory (coalesced loads) when it fits, so that the sequential sum reads broadcasts.
+constexpr int INF_NORM_STAGE = 512; // floats per warp
 __global__ void __launch_bounds__(256) InferNormKernel(const float *src, int n, int groupSize, int nSeq, int8_t *dst, int relu)
 {
+    __shared__ float stage[8][INF_NORM_STAGE];
     const int groups = n / groupSize;
-    const int task = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int task = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (task >= nSeq * groups) {
         return;
     }
     const int b = task / groups, g = task - b * groups;
     const float *s = src + (size_t)b * n + g * groupSize;
+    if (groupSize <= INF_NORM_STAGE) {
+        for (int x = lane; x < groupSize; x += 32) {
+            stage[warp][x] = s[x];
+        }
+        __syncwarp();
+        s = stage[warp];
+    }
     float discr, mult;
     NormScales(SequentialSum2(s, groupSize), groupSize, &discr, &mult);
     int8_t *d = dst + (size_t)b * n + g * groupSize;
@@ -180,82 +190,85 @@ struct TGemvParams {
     float Scale;
 };
 
+__device__ __forceinline__ void InferCpAsync16(void *smemDst, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smemDst)), "l"(src) : "memory");
+}
+
 // out[b][r] = (float)(int32 dot of vec[b] and W[r])            (MulForward, cpu_infer.cpp:282-293)
 // ADD: out[b][r] += (float)dot * scale                          (AddScaled, cpu_infer.cpp:296-303)
-// The batch's vectors are staged in shared memory a chunk of columns at a time (row pitch an odd number of 16-byte
-// words, so the 16-byte reads of a warp's lanes fall into different banks); a lane owns one sequence (two with more
-// than 32 sequences), a warp INF_GEMV_ROWS matrix rows whose 16-byte words every lane loads from the same address.
-template <bool ADD, int GROUPS>
+// A block owns INF_GEMV_WARPS * INF_GEMV_ROWS matrix rows (blockIdx.x), one matrix (blockIdx.y) and 32 sequences
+// (blockIdx.z).  Both operands go through shared memory a chunk of columns at a time, fetched with cp.async so that
+// all of a block's loads are in flight at once: the matrix rows as they lie (every lane reads the same 16-byte word,
+// a broadcast), the 32 vectors with a row pitch of an odd number of 16-byte words (the lanes' reads fall into
+// different banks).  A lane owns one sequence, a warp INF_GEMV_ROWS rows.
+template <bool ADD>
 __global__ void __launch_bounds__(INF_GEMV_WARPS * 32) InferGemvKernel(TGemvParams p)
 {
-    extern __shared__ int4 vecTile[];
-    const TGemvJob job = p.Jobs[blockIdx.y];
+    extern __shared__ int4 gemvSmem[];
+    constexpr int TILE_ROWS = INF_GEMV_WARPS * INF_GEMV_ROWS;
+    const TGemvJob job = blockIdx.y == 0 ? p.Jobs[0] : blockIdx.y == 1 ? p.Jobs[1] : blockIdx.y == 2 ? p.Jobs[2] : p.Jobs[3];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r0 = (blockIdx.x * INF_GEMV_WARPS + warp) * INF_GEMV_ROWS;
-    if (blockIdx.x * INF_GEMV_WARPS * INF_GEMV_ROWS >= job.Rows) {
+    const int rowBase = blockIdx.x * TILE_ROWS;
+    if (rowBase >= job.Rows) {
         return; // whole block past this matrix
     }
+    const int seqBase = blockIdx.z * 32;
+    const int nb = min(32, p.NSeq - seqBase);
     const int c16 = p.Cols / 16, chunk16 = p.ChunkCols / 16;
     const int ld16 = chunk16 | 1; // odd pitch
-    int acc[GROUPS][INF_GEMV_ROWS];
-#pragma unroll
-    for (int g = 0; g < GROUPS; ++g) {
-#pragma unroll
-        for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-            acc[g][r] = 0;
-        }
-    }
-    const int4 *wRow[INF_GEMV_ROWS];
+    int4 *vecTile = gemvSmem;                  // [32][ld16]
+    int4 *wTile = gemvSmem + 32 * ld16;        // [TILE_ROWS][chunk16]
+    int acc[INF_GEMV_ROWS];
 #pragma unroll
     for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-        wRow[r] = reinterpret_cast<const int4 *>(job.W + (size_t)min(r0 + r, job.Rows - 1) * p.Cols);
+        acc[r] = 0;
     }
+    const int b = min(lane, nb - 1);
     for (int x0 = 0; x0 < c16; x0 += chunk16) {
         const int n16 = min(chunk16, c16 - x0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < p.NSeq * n16; i += blockDim.x) {
-            const int b = i / n16, x = i - b * n16;
-            vecTile[b * ld16 + x] = *reinterpret_cast<const int4 *>(p.Vec + (size_t)b * p.Cols + (size_t)(x0 + x) * 16);
+        __syncthreads(); // the previous chunk has been read
+        for (int s = warp; s < nb; s += INF_GEMV_WARPS) {
+            const int4 *src = reinterpret_cast<const int4 *>(p.Vec + (size_t)(seqBase + s) * p.Cols) + x0;
+            for (int x = lane; x < n16; x += 32) {
+                InferCpAsync16(vecTile + s * ld16 + x, src + x);
+            }
         }
+        for (int r = warp; r < TILE_ROWS; r += INF_GEMV_WARPS) {
+            const int4 *src = reinterpret_cast<const int4 *>(job.W + (size_t)min(rowBase + r, job.Rows - 1) * p.Cols) + x0;
+            for (int x = lane; x < n16; x += 32) {
+                InferCpAsync16(wTile + r * chunk16 + x, src + x);
+            }
+        }
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        if (r0 < job.Rows) {
+        const int4 *vrow = vecTile + b * ld16;
+        const int4 *wrow = wTile + warp * INF_GEMV_ROWS * chunk16;
 #pragma unroll 4
-            for (int x = 0; x < n16; ++x) {
-                int4 w[INF_GEMV_ROWS];
+        for (int x = 0; x < n16; ++x) {
+            const int4 v = vrow[x];
 #pragma unroll
-                for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-                    w[r] = __ldg(wRow[r] + x0 + x);
-                }
-#pragma unroll
-                for (int g = 0; g < GROUPS; ++g) {
-                    const int b = min(g * 32 + lane, p.NSeq - 1);
-                    const int4 v = vecTile[b * ld16 + x];
-#pragma unroll
-                    for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-                        int a = acc[g][r];
-                        a = __dp4a(w[r].x, v.x, a);
-                        a = __dp4a(w[r].y, v.y, a);
-                        a = __dp4a(w[r].z, v.z, a);
-                        a = __dp4a(w[r].w, v.w, a);
-                        acc[g][r] = a;
-                    }
-                }
+            for (int r = 0; r < INF_GEMV_ROWS; ++r) {
+                const int4 w = wrow[r * chunk16 + x];
+                int a = acc[r];
+                a = __dp4a(w.x, v.x, a);
+                a = __dp4a(w.y, v.y, a);
+                a = __dp4a(w.z, v.z, a);
+                a = __dp4a(w.w, v.w, a);
+                acc[r] = a;
             }
         }
     }
+    if (lane < nb) {
 #pragma unroll
-    for (int g = 0; g < GROUPS; ++g) {
-        const int b = g * 32 + lane;
-        if (b < p.NSeq) {
-#pragma unroll
-            for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-                if (r0 + r < job.Rows) {
-                    float *o = job.Out + (size_t)b * p.OutStride + r0 + r;
-                    if (ADD) {
-                        *o = __fadd_rn(*o, __fmul_rn((float)acc[g][r], p.Scale));
-                    } else {
-                        *o = (float)acc[g][r];
-                    }
+        for (int r = 0; r < INF_GEMV_ROWS; ++r) {
+            const int row = rowBase + warp * INF_GEMV_ROWS + r;
+            if (row < job.Rows) {
+                float *o = job.Out + (size_t)(seqBase + lane) * p.OutStride + row;
+                if (ADD) {
+                    *o = __fadd_rn(*o, __fmul_rn((float)acc[r], p.Scale));
+                } else {
+                    *o = (float)acc[r];
                 }
             }
         }
@@ -327,19 +340,18 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     p.NSeq = nSeq;
     p.OutStride = outStride;
     p.Scale = scale;
-    // columns per shared-memory pass: all of them if the batch's vectors fit
-    int chunk16 = INF_TILE_BYTES / 16 / nSeq - 1;
+    // columns per shared-memory pass: all of them if 32 vectors and the block's matrix rows fit
+    constexpr int TILE_ROWS = INF_GEMV_WARPS * INF_GEMV_ROWS;
+    int chunk16 = (INF_TILE_BYTES / 16 - 32) / (32 + TILE_ROWS);
     chunk16 = chunk16 < cols / 16 ? chunk16 : cols / 16;
     p.ChunkCols = chunk16 * 16;
-    const size_t smem = (size_t)nSeq * (chunk16 | 1) * 16;
-    const void *kern = nSeq > 32 ? (add ? (const void *)InferGemvKernel<true, 2> : (const void *)InferGemvKernel<false, 2>)
-                                 : (add ? (const void *)InferGemvKernel<true, 1> : (const void *)InferGemvKernel<false, 1>);
-    int rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, INF_TILE_BYTES + 1024), "cudaFuncSetAttribute");
+    const size_t smem = ((size_t)32 * (chunk16 | 1) + (size_t)TILE_ROWS * chunk16) * 16;
+    const void *kern = add ? (const void *)InferGemvKernel<true> : (const void *)InferGemvKernel<false>;
+    int rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, INF_TILE_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {
         return rc;
     }
-    const int rowsPerBlock = INF_GEMV_WARPS * INF_GEMV_ROWS;
-    dim3 grid((maxRows + rowsPerBlock - 1) / rowsPerBlock, jobCount);
+    dim3 grid((maxRows + TILE_ROWS - 1) / TILE_ROWS, jobCount, (nSeq + 31) / 32);
     void *args[] = {&p};
     return CheckCuda(cudaLaunchKernel(kern, grid, dim3(INF_GEMV_WARPS * 32), args, smem, stream), "inference matrix product launch");
 }

@@ -80,15 +80,17 @@ class InferContext:
         self.ctx_lens.copy_(t.unsqueeze(0).expand_as(self.ctx_lens))
         self.max_ctx = int(max(lens))
 
-    def compute_prediction(self, labels, prediction=None, logits=None, want_prediction=True):
+    def compute_prediction(self, labels, prediction=None, logits=None, want_prediction=True, max_ctx_bound=None):
         """One token per sequence.  labels: int32 device tensor [n_seq][labels per token].  Returns the distribution
-        over the vocabulary [n_seq][vocab] (None with want_prediction=False: the caches advance all the same)."""
+        over the vocabulary [n_seq][vocab] (None with want_prediction=False: the caches advance all the same).
+        max_ctx_bound: upper bound of the token counts to size the launches for instead of the tracked maximum; a
+        step captured into a CUDA graph and replayed many times needs the bound of its last replay."""
         m = self.model
         assert labels.dtype == torch.int32 and labels.dim() == 2 and labels.shape[0] == self.n_seq and labels.is_contiguous()
         if want_prediction and prediction is None:
             prediction = torch.empty((self.n_seq, m.vocab), dtype=torch.float32, device=m.device)
         check(abi.lib().tsa_infer_step(ctypes.byref(m.c), self.layer_seqs, _ptr(self.ctx_lens), self.capacity, _ptr(labels), labels.shape[1],
-                                       self.n_seq, self.max_ctx, _ptr(prediction), _ptr(logits), _ptr(self.workspace), self.workspace.numel(),
+                                       self.n_seq, self.max_ctx if max_ctx_bound is None else int(max_ctx_bound), _ptr(prediction), _ptr(logits), _ptr(self.workspace), self.workspace.numel(),
                                        _ptr(self.status), _stream()))
         self.max_ctx += 1
         return prediction
