@@ -58,7 +58,7 @@ __device__ __forceinline__ void KeyRange(int ctxLen, int window, int *j0, int *j
     }
 }
 
-constexpr int DEC_MIN_CHUNK = 64;
+constexpr int DEC_MIN_CHUNK = 16; // keys: short windows are spread over several CTAs of two batches rather than one CTA of eight
 
 __device__ __forceinline__ int SeqKeys(const int *ctxLens, int s, int window)
 {

@@ -14,19 +14,15 @@
 // Everything but the attention weights and the last softmax is integer or single-rounded float arithmetic in the
 // reference's order (sums of squares are accumulated sequentially like the scalar loops there), so those stages are
 // bit-identical to the CPU code; the attention (tsa_att_decode) and the softmax use exp2 instead of the CPU's
-// polynomial.  The matrix products read every int8 weight once per step for the whole batch (dp4a, the batch's
-// vectors staged in shared memory, a lane per sequence); at realistic context lengths the step is dominated by the
-// KV-cache stream of the decode kernel.
-#include "tsa_common.cuh"
+// polynomial.  The matrix products read every int8 weight once per step for the whole batch (tcgen05 kind::i8, exact
+// int32 accumulators); at realistic context lengths the step is dominated by the KV-cache stream of the decode kernel.
+#include "att_sm100_common.cuh"
 
 namespace tsa {
 
 constexpr float INF_VEC_SCALE = 1.0f / 24; // VEC_SCALE, cpu_infer.cpp:16
 constexpr int INF_NORM_TILE = 128;         // STATE_NORM_TILE, model_dim.h:23
-constexpr int INF_GEMV_ROWS = 4;           // matrix rows per warp
-constexpr int INF_GEMV_WARPS = 4;
 constexpr int INF_MAX_SEQ = 64;            // sequences per step
-constexpr int INF_TILE_BYTES = 200 * 1024; // shared memory of a matrix product block: 32 vectors and its matrix rows, a chunk of columns
 
 // ConvertToInt8 (cpu_infer.cpp:88-92): round to nearest even, clamp to +-127
 __device__ __forceinline__ int ToInt8Clamp127(float x)
@@ -183,95 +179,145 @@ struct TGemvJob {
     float *Out;      // element (b, r) at Out[b * OutStride + r]
     int Rows;
 };
-struct TGemvParams {
-    TGemvJob Jobs[4]; // matrices that share the input vectors, blockIdx.y picks one
-    const int8_t *Vec; // [nSeq][cols] int8
-    int Cols, ChunkCols, NSeq, OutStride;
+
+// ---- int8 matrix products on the tensor cores --------------------------------------------------------------------
+// out[b][r] = (float)(int32 dot of vec[b] and W[r])            (MulForward, cpu_infer.cpp:282-293)
+// ADD: out[b][r] += (float)dot * scale                          (AddScaled, cpu_infer.cpp:296-303)
+// One CTA = 128 rows of one matrix (blockIdx.x, blockIdx.y) times all sequences (at most 64): tcgen05.mma kind::i8,
+// M = 128 matrix rows, N = 64 sequences, exact int32 accumulators in 64 tensor-memory columns.  Thread 0 streams the
+// row slab and the batch's vectors through a ring of GEMM_STAGES shared-memory stages of 128 columns (TMA, 128-byte
+// swizzle; rows past the matrix and sequences past the batch read as zeros) and issues the MMAs; afterwards thread t
+// holds row t of the tile and writes its 64 products, coalesced over the rows of a warp.  Every wait is bounded.
+constexpr int GEMM_STAGES = 8;
+constexpr int GEMM_M = 128, GEMM_N = 64, GEMM_KB = 128;
+constexpr int GEMM_STAGE_BYTES = (GEMM_M + GEMM_N) * GEMM_KB;
+constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * GEMM_STAGE_BYTES + 1024 /* barriers */ + 1024 /* alignment */;
+
+struct TGemmMisc {
+    uint64_t Full[GEMM_STAGES], Empty[GEMM_STAGES], Done;
+    uint32_t TmemBase;
+};
+struct TGemmArgs {
+    float *Out[4];
+    int Rows[4];
+    int OutStride, NSeq, Chunks;
     float Scale;
 };
 
-__device__ __forceinline__ void InferCpAsync16(void *smemDst, const void *src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smemDst)), "l"(src) : "memory");
-}
-
-// out[b][r] = (float)(int32 dot of vec[b] and W[r])            (MulForward, cpu_infer.cpp:282-293)
-// ADD: out[b][r] += (float)dot * scale                          (AddScaled, cpu_infer.cpp:296-303)
-// A block owns INF_GEMV_WARPS * INF_GEMV_ROWS matrix rows (blockIdx.x), one matrix (blockIdx.y) and 32 sequences
-// (blockIdx.z).  Both operands go through shared memory a chunk of columns at a time, fetched with cp.async so that
-// all of a block's loads are in flight at once: the matrix rows as they lie (every lane reads the same 16-byte word,
-// a broadcast), the 32 vectors with a row pitch of an odd number of 16-byte words (the lanes' reads fall into
-// different banks).  A lane owns one sequence, a warp INF_GEMV_ROWS rows.
 template <bool ADD>
-__global__ void __launch_bounds__(INF_GEMV_WARPS * 32) InferGemvKernel(TGemvParams p)
+__global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+    const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW3, const __grid_constant__ CUtensorMap tmVec, TGemmArgs a,
+    int *status)
 {
-    extern __shared__ int4 gemvSmem[];
-    constexpr int TILE_ROWS = INF_GEMV_WARPS * INF_GEMV_ROWS;
-    const TGemvJob job = blockIdx.y == 0 ? p.Jobs[0] : blockIdx.y == 1 ? p.Jobs[1] : blockIdx.y == 2 ? p.Jobs[2] : p.Jobs[3];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rowBase = blockIdx.x * TILE_ROWS;
-    if (rowBase >= job.Rows) {
-        return; // whole block past this matrix
+    constexpr uint32_t IDESC = MakeInstrDesc(2, 1, 1, 0, 0, GEMM_M, GEMM_N); // s32 accumulators, s8 x s8, both K-major
+    extern __shared__ uint8_t gemmSmemRaw[];
+    const int job = blockIdx.y;
+    const int rows = job == 0 ? a.Rows[0] : job == 1 ? a.Rows[1] : job == 2 ? a.Rows[2] : a.Rows[3];
+    float *out = job == 0 ? a.Out[0] : job == 1 ? a.Out[1] : job == 2 ? a.Out[2] : a.Out[3];
+    const CUtensorMap *tmW = job == 0 ? &tmW0 : job == 1 ? &tmW1 : job == 2 ? &tmW2 : &tmW3;
+    const int rowBase = blockIdx.x * GEMM_M;
+    if (rowBase >= rows) {
+        return; // the grid is sized for the tallest matrix of the launch
     }
-    const int seqBase = blockIdx.z * 32;
-    const int nb = min(32, p.NSeq - seqBase);
-    const int c16 = p.Cols / 16, chunk16 = p.ChunkCols / 16;
-    const int ld16 = chunk16 | 1; // odd pitch
-    int4 *vecTile = gemvSmem;                  // [32][ld16]
-    int4 *wTile = gemvSmem + 32 * ld16;        // [TILE_ROWS][chunk16]
-    int acc[INF_GEMV_ROWS];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)gemmSmemRaw + 1023) & ~(uintptr_t)1023);
+    TGemmMisc &misc = *reinterpret_cast<TGemmMisc *>(smem + GEMM_STAGES * GEMM_STAGE_BYTES);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
 #pragma unroll
-    for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-        acc[r] = 0;
+        for (int s = 0; s < GEMM_STAGES; ++s) {
+            MbarInit(&misc.Full[s], 1);
+            MbarInit(&misc.Empty[s], 1);
+        }
+        MbarInit(&misc.Done, 1);
+        FenceBarrierInit();
     }
-    const int b = min(lane, nb - 1);
-    for (int x0 = 0; x0 < c16; x0 += chunk16) {
-        const int n16 = min(chunk16, c16 - x0);
-        __syncthreads(); // the previous chunk has been read
-        for (int s = warp; s < nb; s += INF_GEMV_WARPS) {
-            const int4 *src = reinterpret_cast<const int4 *>(p.Vec + (size_t)(seqBase + s) * p.Cols) + x0;
-            for (int x = lane; x < n16; x += 32) {
-                InferCpAsync16(vecTile + s * ld16 + x, src + x);
-            }
+    if (warp == 0) {
+        TmemAlloc(&misc.TmemBase, GEMM_N);
+        TmemRelinquish();
+    }
+    TcFenceBefore();
+    __syncthreads();
+    TcFenceAfter();
+    const uint32_t tmem = misc.TmemBase;
+    bool failed = false;
+    if (tid == 0) {
+        PrefetchTensorMap(tmW);
+        PrefetchTensorMap(&tmVec);
+        auto load = [&](int chunk) {
+            const int s = chunk % GEMM_STAGES;
+            uint8_t *sA = smem + s * GEMM_STAGE_BYTES, *sB = sA + GEMM_M * GEMM_KB;
+            MbarExpectTx(&misc.Full[s], GEMM_STAGE_BYTES);
+            TmaLoad2D(sA, tmW, chunk * GEMM_KB, rowBase, &misc.Full[s]);
+            TmaLoad2D(sB, &tmVec, chunk * GEMM_KB, 0, &misc.Full[s]);
+        };
+        const int chunks = a.Chunks;
+        for (int c = 0; c < GEMM_STAGES - 1 && c < chunks; ++c) {
+            load(c);
         }
-        for (int r = warp; r < TILE_ROWS; r += INF_GEMV_WARPS) {
-            const int4 *src = reinterpret_cast<const int4 *>(job.W + (size_t)min(rowBase + r, job.Rows - 1) * p.Cols) + x0;
-            for (int x = lane; x < n16; x += 32) {
-                InferCpAsync16(wTile + r * chunk16 + x, src + x);
+        for (int c = 0; c < chunks && !failed; ++c) {
+            const int ahead = c + GEMM_STAGES - 1;
+            if (ahead < chunks) {
+                if (ahead >= GEMM_STAGES && !WaitBar(&misc.Empty[ahead % GEMM_STAGES], (uint32_t)((ahead / GEMM_STAGES - 1) & 1))) {
+                    failed = true; // the MMAs that read this stage never finished
+                    if (status) {
+                        atomicOr(status, kDevTimeoutMma);
+                    }
+                    break;
+                }
+                load(ahead);
             }
-        }
-        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        const int4 *vrow = vecTile + b * ld16;
-        const int4 *wrow = wTile + warp * INF_GEMV_ROWS * chunk16;
-#pragma unroll 4
-        for (int x = 0; x < n16; ++x) {
-            const int4 v = vrow[x];
+            const int s = c % GEMM_STAGES;
+            if (!WaitBar(&misc.Full[s], (uint32_t)((c / GEMM_STAGES) & 1))) {
+                failed = true;
+                if (status) {
+                    atomicOr(status, kDevTimeoutTma);
+                }
+                break;
+            }
+            TcFenceAfter();
+            const uint32_t sA = SmemAddr(smem + s * GEMM_STAGE_BYTES), sB = sA + GEMM_M * GEMM_KB;
 #pragma unroll
-            for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-                const int4 w = wrow[r * chunk16 + x];
-                int a = acc[r];
-                a = __dp4a(w.x, v.x, a);
-                a = __dp4a(w.y, v.y, a);
-                a = __dp4a(w.z, v.z, a);
-                a = __dp4a(w.w, v.w, a);
-                acc[r] = a;
+            for (int ks = 0; ks < GEMM_KB / 32; ++ks) {
+                const uint64_t aDesc = MakeSmemDesc(sA + ks * 32, 16, 8 * GEMM_KB, 128);
+                const uint64_t bDesc = MakeSmemDesc(sB + ks * 32, 16, 8 * GEMM_KB, 128);
+                MmaI8SS(tmem, aDesc, bDesc, IDESC, (c > 0 || ks > 0) ? 1u : 0u);
             }
+            MmaCommit(&misc.Empty[s]);
+        }
+        MmaCommit(&misc.Done);
+    }
+    if (!WaitBar(&misc.Done, 0)) {
+        failed = true;
+        if (status) {
+            atomicOr(status, kDevTimeoutMma);
         }
     }
-    if (lane < nb) {
+    TcFenceAfter();
+    failed = __syncthreads_or(failed ? 1 : 0) != 0;
+    const int row = rowBase + tid;
+    if (!failed) {
+        const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
-        for (int r = 0; r < INF_GEMV_ROWS; ++r) {
-            const int row = rowBase + warp * INF_GEMV_ROWS + r;
-            if (row < job.Rows) {
-                float *o = job.Out + (size_t)(seqBase + lane) * p.OutStride + row;
-                if (ADD) {
-                    *o = __fadd_rn(*o, __fmul_rn((float)acc[r], p.Scale));
-                } else {
-                    *o = (float)acc[r];
+        for (int c0 = 0; c0 < GEMM_N; c0 += 32) {
+            uint32_t r[32];
+            TmemLd32(tLane + c0, r);
+            TmemWaitLd();
+            if (row < rows) {
+#pragma unroll
+                for (int cc = 0; cc < 32; ++cc) {
+                    if (c0 + cc < a.NSeq) {
+                        float *o = out + (size_t)(c0 + cc) * a.OutStride + row;
+                        const float v = (float)(int32_t)r[cc];
+                        *o = ADD ? __fadd_rn(*o, __fmul_rn(v, a.Scale)) : v;
+                    }
                 }
             }
         }
+    }
+    TcFenceBefore();
+    __syncthreads();
+    if (warp == 0) {
+        TmemDealloc(tmem, GEMM_N);
     }
 }
 
@@ -327,33 +373,45 @@ __global__ void __launch_bounds__(1024) InferSoftmaxKernel(const float *logits, 
     }
 }
 
-static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t *vec, int cols, int nSeq, int outStride, float scale, cudaStream_t stream)
+static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t *vec, int cols, int nSeq, int outStride, float scale, int *statusWord,
+    cudaStream_t stream)
 {
-    TGemvParams p;
+    CUtensorMap mw[4], mv;
+    TGemmArgs a;
     int maxRows = 0;
     for (int j = 0; j < 4; ++j) {
-        p.Jobs[j] = jobs[j < jobCount ? j : 0];
-        maxRows = p.Jobs[j].Rows > maxRows ? p.Jobs[j].Rows : maxRows;
+        const TGemvJob &job = jobs[j < jobCount ? j : 0];
+        tsa_ptr2d w = {(void *)job.W, cols, cols, job.Rows};
+        int rc = MakeTileMapEx(&mw[j], w, 1, GEMM_KB, GEMM_M, "inference matrix");
+        if (rc != TSA_OK) {
+            return rc;
+        }
+        a.Out[j] = job.Out;
+        a.Rows[j] = job.Rows;
+        maxRows = job.Rows > maxRows ? job.Rows : maxRows;
     }
-    p.Vec = vec;
-    p.Cols = cols;
-    p.NSeq = nSeq;
-    p.OutStride = outStride;
-    p.Scale = scale;
-    // columns per shared-memory pass: all of them if 32 vectors and the block's matrix rows fit
-    constexpr int TILE_ROWS = INF_GEMV_WARPS * INF_GEMV_ROWS;
-    int chunk16 = (INF_TILE_BYTES / 16 - 32) / (32 + TILE_ROWS);
-    chunk16 = chunk16 < cols / 16 ? chunk16 : cols / 16;
-    p.ChunkCols = chunk16 * 16;
-    const size_t smem = ((size_t)32 * (chunk16 | 1) + (size_t)TILE_ROWS * chunk16) * 16;
-    const void *kern = add ? (const void *)InferGemvKernel<true> : (const void *)InferGemvKernel<false>;
-    int rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, INF_TILE_BYTES), "cudaFuncSetAttribute");
+    tsa_ptr2d v = {(void *)vec, cols, cols, nSeq};
+    int rc = MakeTileMapEx(&mv, v, 1, GEMM_KB, GEMM_N, "inference vectors");
     if (rc != TSA_OK) {
         return rc;
     }
-    dim3 grid((maxRows + TILE_ROWS - 1) / TILE_ROWS, jobCount, (nSeq + 31) / 32);
-    void *args[] = {&p};
-    return CheckCuda(cudaLaunchKernel(kern, grid, dim3(INF_GEMV_WARPS * 32), args, smem, stream), "inference matrix product launch");
+    a.OutStride = outStride;
+    a.NSeq = nSeq;
+    a.Chunks = cols / GEMM_KB;
+    a.Scale = scale;
+    dim3 grid((maxRows + GEMM_M - 1) / GEMM_M, jobCount);
+    if (add) {
+        rc = CheckCuda(cudaFuncSetAttribute(InferGemmI8Kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
+        if (rc == TSA_OK) {
+            InferGemmI8Kernel<true><<<grid, 128, GEMM_SMEM_BYTES, stream>>>(mw[0], mw[1], mw[2], mw[3], mv, a, statusWord);
+        }
+    } else {
+        rc = CheckCuda(cudaFuncSetAttribute(InferGemmI8Kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
+        if (rc == TSA_OK) {
+            InferGemmI8Kernel<false><<<grid, 128, GEMM_SMEM_BYTES, stream>>>(mw[0], mw[1], mw[2], mw[3], mv, a, statusWord);
+        }
+    }
+    return rc != TSA_OK ? rc : CheckCuda(cudaGetLastError(), "inference matrix product launch");
 }
 
 static size_t Align256(size_t x)
@@ -406,8 +464,8 @@ static int CheckInferModel(const tsa_infer_model *m, int nSeq, const char *fn)
     const tsa_infer_dims &d = m->dims;
     TSA_REQUIRE(d.head_dim == 64 || d.head_dim == 128, "%s: head_dim %d must be 64 or 128 (query and value heads have one size here)", fn, d.head_dim);
     TSA_REQUIRE(d.dim > 0 && d.dim % INF_NORM_TILE == 0, "%s: dim %d must be a multiple of %d", fn, d.dim, INF_NORM_TILE);
-    TSA_REQUIRE(d.head_count > 0 && d.relu_dim > 0 && d.relu_dim % d.head_count == 0 && d.relu_dim % 16 == 0,
-        "%s: relu_dim %d must be a multiple of head_count %d and of 16", fn, d.relu_dim, d.head_count);
+    TSA_REQUIRE(d.head_count > 0 && d.relu_dim > 0 && d.relu_dim % d.head_count == 0 && d.relu_dim % GEMM_KB == 0,
+        "%s: relu_dim %d must be a multiple of head_count %d and of %d", fn, d.relu_dim, d.head_count, GEMM_KB);
     TSA_REQUIRE(d.vocab_size > 0 && d.label_count > 0 && d.layer_count >= 0, "%s: vocab_size, label_count must be positive", fn);
     TSA_REQUIRE(nSeq >= 0 && nSeq <= INF_MAX_SEQ, "%s: %d sequences per step, at most %d", fn, nSeq, INF_MAX_SEQ);
     return TSA_OK;
@@ -471,7 +529,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
             break;
         }
         TGemvJob proj[4] = {{layer.qk, b.Proj, hs}, {layer.qv, b.Proj + hs, hs}, {layer.k, b.Proj + 2 * hs, hs}, {layer.v, b.Proj + 3 * hs, hs}};
-        rc = LaunchGemv(false, proj, 4, b.Norm, dim, nSeq, 4 * hs, 0.0f, stream);
+        rc = LaunchGemv(false, proj, 4, b.Norm, dim, nSeq, 4 * hs, 0.0f, statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
@@ -506,7 +564,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
             break;
         }
         TGemvJob comb[1] = {{layer.combiner, b.State, dim}};
-        rc = LaunchGemv(true, comb, 1, b.Kv8, hs * 4, nSeq, dim, layer.combiner_scale * INF_VEC_SCALE * sqrtf(1.0f / (hs * 4)), stream);
+        rc = LaunchGemv(true, comb, 1, b.Kv8, hs * 4, nSeq, dim, layer.combiner_scale * INF_VEC_SCALE * sqrtf(1.0f / (hs * 4)), statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
@@ -515,7 +573,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
             break;
         }
         TGemvJob expand[1] = {{layer.expand, b.Relu, d.relu_dim}};
-        rc = LaunchGemv(false, expand, 1, b.Norm, dim, nSeq, d.relu_dim, 0.0f, stream);
+        rc = LaunchGemv(false, expand, 1, b.Norm, dim, nSeq, d.relu_dim, 0.0f, statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
@@ -524,7 +582,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
             break;
         }
         TGemvJob contract[1] = {{layer.contract, b.State, dim}};
-        rc = LaunchGemv(true, contract, 1, b.Norm, d.relu_dim, nSeq, dim, layer.contract_scale * INF_VEC_SCALE * sqrtf(1.0f / d.relu_dim), stream);
+        rc = LaunchGemv(true, contract, 1, b.Norm, d.relu_dim, nSeq, dim, layer.contract_scale * INF_VEC_SCALE * sqrtf(1.0f / d.relu_dim), statusWord, stream);
     }
     if (rc != TSA_OK) {
         return rc;
@@ -536,7 +594,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
         }
         float *lg = logits ? logits : b.Logits;
         TGemvJob fin[1] = {{model->final_layer, lg, d.vocab_size}};
-        rc = LaunchGemv(false, fin, 1, b.Norm, dim, nSeq, d.vocab_size, 0.0f, stream);
+        rc = LaunchGemv(false, fin, 1, b.Norm, dim, nSeq, d.vocab_size, 0.0f, statusWord, stream);
         if (rc != TSA_OK) {
             return rc;
         }
