@@ -303,12 +303,19 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             TmemLd32(tLane + c0, r);
             TmemWaitLd();
             if (row < rows) {
+                float *o = out + (size_t)c0 * a.OutStride + row;
+                float old[32];
+                if (ADD) { // all loads before the first store: they are independent, a store in between would serialise them
+#pragma unroll
+                    for (int cc = 0; cc < 32; ++cc) {
+                        old[cc] = (c0 + cc < a.NSeq) ? o[(size_t)cc * a.OutStride] : 0.0f;
+                    }
+                }
 #pragma unroll
                 for (int cc = 0; cc < 32; ++cc) {
                     if (c0 + cc < a.NSeq) {
-                        float *o = out + (size_t)(c0 + cc) * a.OutStride + row;
                         const float v = (float)(int32_t)r[cc];
-                        *o = ADD ? __fadd_rn(*o, __fmul_rn(v, a.Scale)) : v;
+                        o[(size_t)cc * a.OutStride] = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
                     }
                 }
             }
