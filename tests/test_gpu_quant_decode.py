@@ -119,7 +119,7 @@ def _decode_case(seed, ctx_lens, heads, d, window, slope, steps=2, scale_dtype=t
             assert np.abs(out[s] - ref).max() < 2e-4 * scale, (step, s, np.abs(out[s] - ref).max(), scale)
 
 
-@pytest.mark.parametrize("d,heads", [(128, 16), (64, 12), (128, 3)])
+@pytest.mark.parametrize("d,heads", [(128, 16), (64, 12), (128, 3), (64, 4), (128, 8)])
 def test_decode_wide(d, heads):
     _decode_case(3, [700, 1, 255, 256, 257, 1024], heads, d, 100000, 0.0)
 

@@ -247,7 +247,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
     typedef typename TScaleOf<SCALE_F16>::T TScale;
 
     const int headGroups = (H + HPW - 1) / HPW;
-    for (int hg = warp; hg < headGroups; hg += DEC_WARPS) {
+    // With fewer head groups than warps (12 heads x 64: two groups) the spare warps would idle: the warps that share a
+    // head group split the chunk's tokens between them instead and merge their partial sums through shared memory.
+    __shared__ float mergeBuf[DEC_WARPS][32][18];
+    const int split = headGroups == 1 ? 4 : headGroups == 2 ? 2 : 1;
+    const int tokenPart = split > 1 ? warp / headGroups : 0;
+    const int perPart = (((cEnd - cBeg) + split - 1) / split + 7) & ~7;
+    const int tBeg = cBeg + tokenPart * perPart, tEnd = min(tBeg + perPart, cEnd);
+    for (int hg = split > 1 ? warp % headGroups : warp; hg < headGroups; hg += DEC_WARPS) {
         const int head = hg * HPW + lane / LPH;
         const bool headOk = head < H;
         const int headC = headOk ? head : H - 1;
@@ -256,10 +263,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
         const float qs = p.QScale.Valid() ? p.QScale.Row(seq)[headC] : p.QVecScale;
         const float logitMult = p.DotScale * qs;
         // running pointers: one add per token instead of a 64-bit multiply
-        const int4 *kp = reinterpret_cast<const int4 *>((const int8_t *)sq.k + (size_t)cBeg * H * D + colOff);
-        const int4 *vp = reinterpret_cast<const int4 *>((const int8_t *)sq.v + (size_t)cBeg * H * D + colOff);
-        const TScale *ksp = (const TScale *)sq.kScale + (size_t)cBeg * H + headC;
-        const TScale *vsp = (const TScale *)sq.vScale + (size_t)cBeg * H + headC;
+        const int4 *kp = reinterpret_cast<const int4 *>((const int8_t *)sq.k + (size_t)tBeg * H * D + colOff);
+        const int4 *vp = reinterpret_cast<const int4 *>((const int8_t *)sq.v + (size_t)tBeg * H * D + colOff);
+        const TScale *ksp = (const TScale *)sq.kScale + (size_t)tBeg * H + headC;
+        const TScale *vsp = (const TScale *)sq.vScale + (size_t)tBeg * H + headC;
 
         float m = -1e30f, l = 0;
         float acc[16];
@@ -267,10 +274,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
         for (int i = 0; i < 16; ++i) {
             acc[i] = 0;
         }
-        for (int tBase = cBeg; tBase < cEnd; tBase += DEC_UNROLL) {
+        for (int tBase = tBeg; tBase < tEnd; tBase += DEC_UNROLL) {
             int4 kv[DEC_UNROLL], vv[DEC_UNROLL];
             float ks[DEC_UNROLL], vs[DEC_UNROLL];
-            const int cnt = cEnd - tBase; // tokens left, >= 1
+            const int cnt = tEnd - tBase; // tokens left, >= 1
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
                 const int tt = u < cnt ? u : cnt - 1;
@@ -349,7 +356,30 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
                 acc[i] = fmaf((float)iacc[i], deq, acc[i]);
             }
         }
-        if (headOk) {
+        if (split > 1) {
+            float *mine = mergeBuf[warp][lane];
+            mine[0] = m;
+            mine[1] = l;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                mine[2 + i] = acc[i];
+            }
+            PlanSync(); // every warp passes here exactly once when the tokens are split
+            if (tokenPart == 0) {
+                for (int s = 1; s < split; ++s) {
+                    const float *other = mergeBuf[warp + s * headGroups][lane];
+                    const float mAll = fmaxf(m, other[0]);
+                    const float c1 = exp2f(m - mAll), c2 = exp2f(other[0] - mAll);
+                    l = l * c1 + other[1] * c2;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        acc[i] = acc[i] * c1 + other[2 + i] * c2;
+                    }
+                    m = mAll;
+                }
+            }
+        }
+        if (headOk && tokenPart == 0) {
             float *dst = p.Partial + ((size_t)chunk * H + head) * (D + 4);
             if (sub == 0) {
                 dst[D] = m;
