@@ -39,7 +39,17 @@ struct TDecodeParams {
     int *Status;     // device status word (may be null)
     int MaxSlots;    // TargetCtas + nSeq
     int MaxCtx;      // the caller's upper bound of CtxLens: sizes the grid, checked on the device
+    // inference step only (null otherwise): the merge kernel also writes the combiner input
+    // kv[seq][head][blk][z] = int8(KvKey[seq][head][z ^ blk] * out[seq][head][z]), blk = 0..3 (KVProduct, cpu_infer.cpp:318-337)
+    const int8_t *KvKey;
+    int8_t *KvOut;
+    int CtxBias;     // added to every CtxLens entry: 1 when the caller has written the new token but not yet counted it
 };
+
+__device__ __forceinline__ int CtxLenOf(const TDecodeParams &p, int s)
+{
+    return p.CtxLens[s] + p.CtxBias;
+}
 
 __device__ __forceinline__ float LoadScale(const void *base, size_t idx, int dt)
 {
@@ -60,9 +70,9 @@ __device__ __forceinline__ void KeyRange(int ctxLen, int window, int *j0, int *j
 
 constexpr int DEC_MIN_CHUNK = 16; // keys: short windows are spread over several CTAs of two batches rather than one CTA of eight
 
-__device__ __forceinline__ int SeqKeys(const int *ctxLens, int s, int window)
+__device__ __forceinline__ int SeqKeys(const int *ctxLens, int ctxBias, int s, int window)
 {
-    int ctxLen = ctxLens[s];
+    int ctxLen = ctxLens[s] + ctxBias;
     if (ctxLen <= 0) {
         return 0;
     }
@@ -90,8 +100,8 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
     // total number of keys
     int sum = 0;
     for (int s = tid; s < p.NSeq; s += nThreads) {
-        sum += SeqKeys(p.CtxLens, s, p.Window);
-        if (p.CtxLens[s] > p.MaxCtx && blockIdx.x == 0 && p.Status) {
+        sum += SeqKeys(p.CtxLens, p.CtxBias, s, p.Window);
+        if (CtxLenOf(p, s) > p.MaxCtx && blockIdx.x == 0 && p.Status) {
             atomicOr(p.Status, kDevBadSpan); // the grid was sized for shorter sequences
         }
     }
@@ -120,7 +130,7 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
             const int mid = (lo + hi) >> 1;
             int cnt = 0;
             for (int s = tid; s < p.NSeq; s += nThreads) {
-                cnt += (SeqKeys(p.CtxLens, s, p.Window) + mid * 8 - 1) / (mid * 8);
+                cnt += (SeqKeys(p.CtxLens, p.CtxBias, s, p.Window) + mid * 8 - 1) / (mid * 8);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -148,7 +158,7 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
     const int s0 = tid * per, s1 = min(s0 + per, p.NSeq);
     int mine = 0;
     for (int s = s0; s < s1; ++s) {
-        mine += (SeqKeys(p.CtxLens, s, p.Window) + chunk - 1) / chunk;
+        mine += (SeqKeys(p.CtxLens, p.CtxBias, s, p.Window) + chunk - 1) / chunk;
     }
     sliceBase[tid + 1] = mine;
     if (tid == 0) {
@@ -168,13 +178,13 @@ __device__ bool DecodePlan(const TDecodeParams &p, int slot, int *pSeq, int *pBe
         p.Plan[0] = chunk;
     }
     for (int s = s0; s < s1; ++s) {
-        int keys = SeqKeys(p.CtxLens, s, p.Window);
+        int keys = SeqKeys(p.CtxLens, p.CtxBias, s, p.Window);
         int n = (keys + chunk - 1) / chunk;
         if (writePlan) {
             p.Plan[1 + s] = base;
         }
         if (slot >= base && slot < base + n) {
-            int ctxLen = p.CtxLens[s];
+            int ctxLen = CtxLenOf(p, s);
             int j0, j1;
             KeyRange(ctxLen, p.Window, &j0, &j1);
             found[0] = s;
@@ -237,7 +247,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
     if (!DecodePlan(p, chunk, &seq, &cBeg, &cEnd)) {
         return;
     }
-    const int ctxLen = p.CtxLens[seq];
+    const int ctxLen = CtxLenOf(p, seq);
     const int cur = ctxLen - 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPH;             // 16-byte slice inside the head
@@ -399,7 +409,7 @@ template <int D>
 __global__ void __launch_bounds__(D) DecodeCombineKernel(TDecodeParams p)
 {
     int seq = blockIdx.y, head = blockIdx.x, x = threadIdx.x;
-    int ctxLen = p.CtxLens[seq];
+    int ctxLen = CtxLenOf(p, seq);
     float res = 0;
     if (ctxLen > 0) {
         const int first = p.Plan[1 + seq];
@@ -420,6 +430,16 @@ __global__ void __launch_bounds__(D) DecodeCombineKernel(TDecodeParams p)
         res = acc / l;
     }
     StoreFromFloat(p.Out.Row(seq), head * D + x, p.OutDtype, res);
+    if (p.KvOut) {
+        const size_t rowSize = (size_t)p.HeadCount * D;
+        const int8_t *key = p.KvKey + seq * rowSize + head * D;
+        int8_t *kv = p.KvOut + (seq * rowSize + head * D) * 4;
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+            // ConvertToInt8 (cpu_infer.cpp:88-92): round to nearest even, clamp to +-127
+            kv[blk * D + x] = (int8_t)max(-127, min(127, __float2int_rn(__fmul_rn((float)key[x ^ blk], res))));
+        }
+    }
 }
 
 __global__ void KvAppendKernel(const tsa_kv_seq *seqs, int *ctxLens, int nSeq, int capacity, int rowBytes, int headCount, int scaleBytes,
@@ -462,8 +482,12 @@ size_t DecodeWorkspaceBytes(int headDim, int nSeq, int headCount, int maxCtx)
     return DecodeHeaderBytes(nSeq) + (size_t)(DEC_MAX_TARGET_CTAS + nSeq) * headCount * (headDim + 4) * sizeof(float);
 }
 
-int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStream_t stream)
+int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStream_t stream, const int8_t *kvKey = nullptr, int8_t *kvOut = nullptr,
+    int ctxBias = 0)
 {
+    p.KvKey = kvKey;
+    p.KvOut = kvOut;
+    p.CtxBias = ctxBias;
     int dev = 0, sms = 0;
     int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (rc == TSA_OK) {
@@ -530,9 +554,12 @@ extern "C" __attribute__((visibility("default"))) size_t tsa_att_decode_workspac
     return DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
 }
 
-extern "C" __attribute__((visibility("default"))) int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+namespace tsa {
+// tsa_att_decode plus the inference step's combiner input written by the merge kernel (kvKey int8 [nSeq][H*D] packed,
+// kvOut int8 [nSeq][4*H*D] packed; both null for the plain entry point); ctxBias is added to every ctxLens entry
+int DecodeWithKvProduct(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
     tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
-    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream, const int8_t *kvKey, int8_t *kvOut, int ctxBias)
 {
     int rc = CheckDecodeCfg(cfg, "tsa_att_decode");
     if (rc != TSA_OK) {
@@ -568,7 +595,16 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_decode(const tsa_d
     p.QScale = P2D<float>(qScale);
     p.Out = P2D<char>(out);
     p.Partial = (float *)workspace;
-    return LaunchDecode(cfg, p, maxCtx, (cudaStream_t)stream);
+    return LaunchDecode(cfg, p, maxCtx, (cudaStream_t)stream, kvKey, kvOut, ctxBias);
+}
+} // namespace tsa
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
+    tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+{
+    return DecodeWithKvProduct(cfg, seqs, ctxLens, nSeq, maxCtx, q, qScale, window, alibiSlope, out, headCount, workspace, workspaceBytes, statusWord, stream,
+        nullptr, nullptr, 0);
 }
 
 extern "C" __attribute__((visibility("default"))) int tsa_kv_append(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, int *ctxLens, int nSeq, int capacity,

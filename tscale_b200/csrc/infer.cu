@@ -6,8 +6,8 @@
 //   per layer (cpu_infer.cpp:466-527):
 //     norm   = NormalizeState(state, tiles of 128)            -> int8
 //     qk, qv, k, v = int8 matrix * norm (exact int32), rope on qk and qv, NormalizeState per head -> int8
-//     cache.append(qv, qvScale * QVScale * VEC_SCALE * dotScale(dim), v);  val = decode attention(qk, cache)
-//     kv     = int8(k[z ^ blk] * val[z]), 4 blocks per head; state += Combiner * kv * scale
+//     cache.append(qv, qvScale * QVScale * VEC_SCALE * dotScale(dim), v)  (written by the rope kernel);  val = decode attention(qk, cache)
+//     kv     = int8(k[z ^ blk] * val[z]), 4 blocks per head (written by the decode merge kernel); state += Combiner * kv * scale
 //     norm   = NormalizeState(state);  relu = max(0, NormalizeState(Expand * norm, per head));  state += Contract * relu * scale
 //   prediction = softmax2(FinalLayer * NormalizeState(state) * scale + bias)    (cpu_infer.cpp:549-558)
 //
@@ -19,6 +19,11 @@
 #include "att_sm100_common.cuh"
 
 namespace tsa {
+
+// decode.cu: tsa_att_decode whose merge kernel also writes the combiner input
+int DecodeWithKvProduct(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx, tsa_ptr2d q, tsa_ptr2d qScale, int window,
+    float alibiSlope, tsa_ptr2d out, int headCount, void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream, const int8_t *kvKey,
+    int8_t *kvOut, int ctxBias);
 
 constexpr float INF_VEC_SCALE = 1.0f / 24; // VEC_SCALE, cpu_infer.cpp:16
 constexpr int INF_NORM_TILE = 128;         // STATE_NORM_TILE, model_dim.h:23
@@ -107,10 +112,13 @@ __global__ void __launch_bounds__(256) InferNormKernel(const float *src, int n, 
 
 // The four projections of a token: rope on qk and qv (ReferenceApplyRope, code/gpt/att/rope.cpp:28-46, position =
 // tokens already in the cache), then NormalizeState per head.  proj f32 [nSeq][4 * hs] = qk | qv | k | v.
-// Warp per (sequence, matrix, head).  qvScale = discrScale * qvMult (cpu_infer.cpp:503-505); vScale = VEC_SCALE.
+// Warp per (sequence, matrix, head).  qv and v go straight into the sequence's KV cache at row ctxLens[b]
+// (AddVectors, cpu_infer.cpp:403-408) with the key scale discrScale * qvMult (cpu_infer.cpp:503-505) and the value
+// scale VEC_SCALE; the token is counted by InferCountKernel at the end of the step, the attention in between is told
+// to add one to every count.
 template <int D>
 __global__ void __launch_bounds__(128) InferRopeNormKernel(const float *proj, const float *rope, int ropeLen, const int *ctxLens, int nSeq, int headCount,
-    float qvMult, int8_t *qk8, int8_t *qv8, int8_t *k8, int8_t *v8, float *qvScale, float *vScale, int *statusWord)
+    float qvMult, int8_t *qk8, int8_t *k8, const tsa_kv_seq *seqs, int capacity, int *statusWord)
 {
     __shared__ float buf[4][D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,14 +131,14 @@ __global__ void __launch_bounds__(128) InferRopeNormKernel(const float *proj, co
     const int hs = headCount * D;
     const float *s = proj + (size_t)b * 4 * hs + (size_t)m * hs + head * D;
     float *w = buf[warp];
-    if (m < 2) {
-        int pos = ctxLens[b];
-        if (pos < 0 || pos >= ropeLen) {
-            if (lane == 0 && statusWord) {
-                atomicOr(statusWord, kDevBadSpan);
-            }
-            pos = 0;
+    int pos = ctxLens[b];
+    if (pos < 0 || pos >= ropeLen || pos >= capacity) {
+        if (lane == 0 && statusWord) {
+            atomicOr(statusWord, kDevBadSpan); // the cache or the rope table is full
         }
+        return;
+    }
+    if (m < 2) {
         const float *rp = rope + (size_t)pos * D;
 #pragma unroll
         for (int blk = 0; blk < D; blk += 64) {
@@ -147,31 +155,29 @@ __global__ void __launch_bounds__(128) InferRopeNormKernel(const float *proj, co
     __syncwarp();
     float discr, mult;
     NormScales(SequentialSum2(w, D), D, &discr, &mult);
-    int8_t *dst = (m == 0 ? qk8 : m == 1 ? qv8 : m == 2 ? k8 : v8) + (size_t)b * hs + head * D;
+    int8_t *dst;
+    if (m == 0 || m == 2) {
+        dst = (m == 0 ? qk8 : k8) + (size_t)b * hs + head * D;
+    } else {
+        const tsa_kv_seq sq = seqs[b];
+        dst = (int8_t *)(m == 1 ? sq.k : sq.v) + (size_t)pos * hs + head * D;
+        if (lane == 0) {
+            float *scale = (float *)(m == 1 ? sq.kScale : sq.vScale) + (size_t)pos * headCount + head;
+            *scale = m == 1 ? __fmul_rn(discr, qvMult) : INF_VEC_SCALE;
+        }
+    }
     for (int x = lane; x < D; x += 32) {
         dst[x] = (int8_t)ToInt8Clamp127(__fmul_rn(w[x], mult));
     }
-    if (lane == 0) {
-        if (m == 1) {
-            qvScale[b * headCount + head] = __fmul_rn(discr, qvMult);
-        } else if (m == 3) {
-            vScale[b * headCount + head] = INF_VEC_SCALE;
-        }
-    }
 }
 
-// KVProduct of the inference path (cpu_infer.cpp:318-337): kv[head][blk][z] = int8(k[head][z ^ blk] * val[head][z])
-__global__ void __launch_bounds__(256) InferKvProductKernel(const int8_t *k8, const float *val, int hs, int headDim, int nSeq, int8_t *kv)
+// counts the step's token in every layer's cache
+__global__ void InferCountKernel(int *ctxLens, int n)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= nSeq * hs * 4) {
-        return;
+    if (i < n) {
+        ctxLens[i] += 1;
     }
-    const int b = i / (hs * 4), r = i - b * hs * 4;
-    const int head = r / (headDim * 4), r2 = r - head * headDim * 4;
-    const int blk = r2 / headDim, z = r2 - blk * headDim;
-    const float key = (float)k8[(size_t)b * hs + head * headDim + (z ^ blk)];
-    kv[i] = (int8_t)ToInt8Clamp127(__fmul_rn(key, val[(size_t)b * hs + head * headDim + z]));
 }
 
 struct TGemvJob {
@@ -202,6 +208,7 @@ struct TGemmArgs {
     int Rows[4];
     int OutStride, NSeq, Chunks;
     float Scale;
+    int8_t *NormOut; // ADD only, may be null: NormalizeState of the updated rows, [NSeq][OutStride] int8
 };
 
 template <bool ADD>
@@ -250,12 +257,16 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             TmaLoad2D(sA, tmW, chunk * GEMM_KB, rowBase, &misc.Full[s]);
             TmaLoad2D(sB, &tmVec, chunk * GEMM_KB, 0, &misc.Full[s]);
         };
+        // GEMM_AHEAD chunks are in flight; the stage a new load overwrites was read by the MMAs of two iterations ago,
+        // whose completion has long arrived (waiting for the previous iteration's would stall every step on the
+        // commit round trip)
+        constexpr int GEMM_AHEAD = GEMM_STAGES - 2;
         const int chunks = a.Chunks;
-        for (int c = 0; c < GEMM_STAGES - 1 && c < chunks; ++c) {
+        for (int c = 0; c < GEMM_AHEAD && c < chunks; ++c) {
             load(c);
         }
         for (int c = 0; c < chunks && !failed; ++c) {
-            const int ahead = c + GEMM_STAGES - 1;
+            const int ahead = c + GEMM_AHEAD;
             if (ahead < chunks) {
                 if (ahead >= GEMM_STAGES && !WaitBar(&misc.Empty[ahead % GEMM_STAGES], (uint32_t)((ahead / GEMM_STAGES - 1) & 1))) {
                     failed = true; // the MMAs that read this stage never finished
@@ -295,6 +306,13 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     TcFenceAfter();
     failed = __syncthreads_or(failed ? 1 : 0) != 0;
     const int row = rowBase + tid;
+    // ADD with NormOut: the tile's 128 rows are one normalisation tile of the state (STATE_NORM_TILE = 128), so the
+    // int8 input of the next matrix product is made here, from the values just stored: they go through shared memory
+    // (the ring is idle by now), one thread per sequence adds the squares in row order like the scalar loop of
+    // NormalizeState, then every thread converts its row.
+    float *normTile = reinterpret_cast<float *>(smem);            // [GEMM_N][GEMM_M + 1]
+    float *normMult = normTile + GEMM_N * (GEMM_M + 1);           // [GEMM_N]
+    const bool withNorm = ADD && a.NormOut != nullptr;
     if (!failed) {
         const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
@@ -315,8 +333,26 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
                 for (int cc = 0; cc < 32; ++cc) {
                     if (c0 + cc < a.NSeq) {
                         const float v = (float)(int32_t)r[cc];
-                        o[(size_t)cc * a.OutStride] = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
+                        const float res = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
+                        o[(size_t)cc * a.OutStride] = res;
+                        if (withNorm) {
+                            normTile[(c0 + cc) * (GEMM_M + 1) + tid] = res;
+                        }
                     }
+                }
+            }
+        }
+        if (withNorm) {
+            __syncthreads();
+            if (tid < a.NSeq) {
+                float discr, mult;
+                NormScales(SequentialSum2(normTile + tid * (GEMM_M + 1), GEMM_M), GEMM_M, &discr, &mult);
+                normMult[tid] = mult;
+            }
+            __syncthreads();
+            if (row < rows) {
+                for (int s = 0; s < a.NSeq; ++s) {
+                    a.NormOut[(size_t)s * a.OutStride + row] = (int8_t)ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
                 }
             }
         }
@@ -328,60 +364,76 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     }
 }
 
-// SoftMax of the final layer (cpu_infer.cpp:340-354): base 2, the maximum starts at 0 (TSoftMaxBuf::Clear)
-__global__ void __launch_bounds__(1024) InferSoftmaxKernel(const float *logits, const float *bias, float finalScale, int vocab, float *prediction)
+// SoftMax of the final layer (cpu_infer.cpp:340-354): base 2, the maximum starts at 0 (TSoftMaxBuf::Clear).
+// Two kernels over (sequence, slice of the vocabulary) so that a batch of 64 sequences fills the GPU: the first leaves
+// each slice's maximum and sum of 2^(w - max), the second merges the slices' pairs and writes the probabilities.
+constexpr int INF_SOFTMAX_SLICES = 8;
+
+__device__ __forceinline__ float BlockReduce(float v, bool isMax, float *red)
 {
-    __shared__ float red[32];
-    __shared__ float bcast;
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    v = isMax ? WarpMax(v) : WarpSum(v);
+    __syncthreads(); // red may still be read from the previous reduction
+    if (lane == 0) {
+        red[warp] = v;
+    }
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < warps; ++w) {
+        r = isMax ? fmaxf(r, red[w]) : r + red[w];
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(256) InferSoftmaxPartKernel(const float *logits, const float *bias, float finalScale, int vocab, float *part)
+{
+    __shared__ float red[8];
+    const int b = blockIdx.y, slice = blockIdx.x;
+    const int per = (vocab + INF_SOFTMAX_SLICES - 1) / INF_SOFTMAX_SLICES;
+    const int x0 = slice * per, x1 = min(x0 + per, vocab);
     const float *l = logits + (size_t)b * vocab;
-    float *out = prediction + (size_t)b * vocab;
     float mx = 0;
-    for (int x = tid; x < vocab; x += blockDim.x) {
+    for (int x = x0 + threadIdx.x; x < x1; x += blockDim.x) {
         mx = fmaxf(mx, __fadd_rn(__fmul_rn(l[x], finalScale), bias[x]));
     }
-    mx = WarpMax(mx);
-    if (lane == 0) {
-        red[warp] = mx;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        float v = lane < (int)(blockDim.x >> 5) ? red[lane] : 0.0f;
-        v = WarpMax(v);
-        if (lane == 0) {
-            bcast = v;
-        }
-    }
-    __syncthreads();
-    mx = bcast;
+    mx = BlockReduce(mx, true, red);
     float sum = 0;
-    for (int x = tid; x < vocab; x += blockDim.x) {
-        const float e = exp2f(__fadd_rn(__fmul_rn(l[x], finalScale), bias[x]) - mx);
-        out[x] = e;
-        sum += e;
+    for (int x = x0 + threadIdx.x; x < x1; x += blockDim.x) {
+        sum += exp2f(__fadd_rn(__fmul_rn(l[x], finalScale), bias[x]) - mx);
     }
-    sum = WarpSum(sum);
-    __syncthreads();
-    if (lane == 0) {
-        red[warp] = sum;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        float v = lane < (int)(blockDim.x >> 5) ? red[lane] : 0.0f;
-        v = WarpSum(v);
-        if (lane == 0) {
-            bcast = 1.0f / v;
-        }
-    }
-    __syncthreads();
-    const float inv = bcast;
-    for (int x = tid; x < vocab; x += blockDim.x) {
-        out[x] *= inv;
+    sum = BlockReduce(sum, false, red);
+    if (threadIdx.x == 0) {
+        part[(b * INF_SOFTMAX_SLICES + slice) * 2] = mx;
+        part[(b * INF_SOFTMAX_SLICES + slice) * 2 + 1] = sum;
     }
 }
 
-static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t *vec, int cols, int nSeq, int outStride, float scale, int *statusWord,
-    cudaStream_t stream)
+__global__ void __launch_bounds__(256) InferSoftmaxKernel(const float *logits, const float *bias, float finalScale, int vocab, const float *part,
+    float *prediction)
+{
+    const int b = blockIdx.y, slice = blockIdx.x;
+    const int per = (vocab + INF_SOFTMAX_SLICES - 1) / INF_SOFTMAX_SLICES;
+    const int x0 = slice * per, x1 = min(x0 + per, vocab);
+    float mx = 0;
+#pragma unroll
+    for (int s = 0; s < INF_SOFTMAX_SLICES; ++s) {
+        mx = fmaxf(mx, part[(b * INF_SOFTMAX_SLICES + s) * 2]);
+    }
+    float sum = 0;
+#pragma unroll
+    for (int s = 0; s < INF_SOFTMAX_SLICES; ++s) {
+        sum += part[(b * INF_SOFTMAX_SLICES + s) * 2 + 1] * exp2f(part[(b * INF_SOFTMAX_SLICES + s) * 2] - mx);
+    }
+    const float inv = 1.0f / sum;
+    const float *l = logits + (size_t)b * vocab;
+    float *out = prediction + (size_t)b * vocab;
+    for (int x = x0 + threadIdx.x; x < x1; x += blockDim.x) {
+        out[x] = exp2f(__fadd_rn(__fmul_rn(l[x], finalScale), bias[x]) - mx) * inv;
+    }
+}
+
+static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t *vec, int cols, int nSeq, int outStride, float scale, int8_t *normOut,
+    int *statusWord, cudaStream_t stream)
 {
     CUtensorMap mw[4], mv;
     TGemmArgs a;
@@ -406,6 +458,7 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     a.NSeq = nSeq;
     a.Chunks = cols / GEMM_KB;
     a.Scale = scale;
+    a.NormOut = normOut;
     dim3 grid((maxRows + GEMM_M - 1) / GEMM_M, jobCount);
     if (add) {
         rc = CheckCuda(cudaFuncSetAttribute(InferGemmI8Kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
@@ -427,8 +480,8 @@ static size_t Align256(size_t x)
 }
 
 struct TInferBuffers {
-    float *State, *Proj, *QvScale, *VScale, *Val, *Relu, *Logits;
-    int8_t *Norm, *Qk8, *Qv8, *K8, *V8, *Kv8;
+    float *State, *Proj, *Val, *Relu, *Logits, *SoftmaxPart;
+    int8_t *NormState, *NormRelu, *Qk8, *K8, *Kv8;
     void *DecodeWs;
     size_t DecodeWsBytes, Total;
 };
@@ -437,7 +490,6 @@ static TInferBuffers CarveInferBuffers(const tsa_infer_model *m, int nSeq, int m
 {
     const tsa_infer_dims &d = m->dims;
     const size_t hs = (size_t)d.head_count * d.head_dim;
-    const size_t widest = (size_t)(d.dim > d.relu_dim ? d.dim : d.relu_dim);
     tsa_decode_cfg cfg = {d.head_dim, TSA_F32, TSA_F32, INF_VEC_SCALE};
     TInferBuffers b;
     size_t off = 0;
@@ -448,16 +500,14 @@ static TInferBuffers CarveInferBuffers(const tsa_infer_model *m, int nSeq, int m
     };
     b.State = (float *)take(sizeof(float) * nSeq * d.dim);
     b.Proj = (float *)take(sizeof(float) * nSeq * 4 * hs);
-    b.QvScale = (float *)take(sizeof(float) * nSeq * d.head_count);
-    b.VScale = (float *)take(sizeof(float) * nSeq * d.head_count);
     b.Val = (float *)take(sizeof(float) * nSeq * hs);
     b.Relu = (float *)take(sizeof(float) * nSeq * d.relu_dim);
     b.Logits = (float *)take(sizeof(float) * nSeq * d.vocab_size);
-    b.Norm = (int8_t *)take((size_t)nSeq * widest);
+    b.SoftmaxPart = (float *)take(sizeof(float) * nSeq * INF_SOFTMAX_SLICES * 2);
+    b.NormState = (int8_t *)take((size_t)nSeq * d.dim);
+    b.NormRelu = (int8_t *)take((size_t)nSeq * d.relu_dim);
     b.Qk8 = (int8_t *)take((size_t)nSeq * hs);
-    b.Qv8 = (int8_t *)take((size_t)nSeq * hs);
     b.K8 = (int8_t *)take((size_t)nSeq * hs);
-    b.V8 = (int8_t *)take((size_t)nSeq * hs);
     b.Kv8 = (int8_t *)take((size_t)nSeq * hs * 4);
     b.DecodeWsBytes = tsa_att_decode_workspace_bytes(&cfg, nSeq, d.head_count, maxCtx + 1);
     b.DecodeWs = take(b.DecodeWsBytes);
@@ -514,9 +564,9 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
     const int H = d.head_count, D = d.head_dim, hs = H * D, dim = d.dim;
     tsa_decode_cfg cfg = {D, TSA_F32, TSA_F32, INF_VEC_SCALE};
 
-    auto norm = [&](const float *src, int n, int groupSize, bool relu) {
+    auto norm = [&](const float *src, int n, int groupSize, int8_t *dst, bool relu) {
         const int warps = nSeq * (n / groupSize);
-        InferNormKernel<<<(warps * 32 + 255) / 256, 256, 0, stream>>>(src, n, groupSize, nSeq, b.Norm, relu ? 1 : 0);
+        InferNormKernel<<<(warps * 32 + 255) / 256, 256, 0, stream>>>(src, n, groupSize, nSeq, dst, relu ? 1 : 0);
         return CheckCuda(cudaGetLastError(), "inference normalise launch");
     };
     auto ptr2d = [](void *data, int strideBytes, int xs, int ys) {
@@ -526,17 +576,17 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
 
     InferEmbedKernel<<<nSeq, 256, 0, stream>>>(labels, labelsPerSeq, d.label_count, model->label_embed, model->label_embed_scale, dim, b.State, statusWord);
     rc = CheckCuda(cudaGetLastError(), "inference embedding launch");
+    if (rc == TSA_OK) {
+        // the state's int8 form; afterwards the matrix products that update the state renew it in their epilogues
+        rc = norm(b.State, dim, INF_NORM_TILE, b.NormState, false);
+    }
     for (int l = 0; l < d.layer_count && rc == TSA_OK; ++l) {
         const tsa_infer_layer &layer = model->layers[l];
         TSA_REQUIRE(layer.qk && layer.qv && layer.k && layer.v && layer.combiner && layer.expand && layer.contract && layerSeqs[l],
             "tsa_infer_step: layer %d has a null matrix or cache", l);
         int *lens = ctxLens + (size_t)l * nSeq;
-        rc = norm(b.State, dim, INF_NORM_TILE, false);
-        if (rc != TSA_OK) {
-            break;
-        }
         TGemvJob proj[4] = {{layer.qk, b.Proj, hs}, {layer.qv, b.Proj + hs, hs}, {layer.k, b.Proj + 2 * hs, hs}, {layer.v, b.Proj + 3 * hs, hs}};
-        rc = LaunchGemv(false, proj, 4, b.Norm, dim, nSeq, 4 * hs, 0.0f, statusWord, stream);
+        rc = LaunchGemv(false, proj, 4, b.NormState, dim, nSeq, 4 * hs, 0.0f, nullptr, statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
@@ -544,71 +594,65 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
         const float qvMult = layer.qv_scale * INF_VEC_SCALE * sqrtf(1.0f / dim);
         dim3 gridR((4 * H + 3) / 4, nSeq);
         if (D == 64) {
-            InferRopeNormKernel<64><<<gridR, 128, 0, stream>>>(b.Proj, model->rope, model->rope_len, lens, nSeq, H, qvMult, b.Qk8, b.Qv8, b.K8, b.V8, b.QvScale,
-                b.VScale, statusWord);
+            InferRopeNormKernel<64><<<gridR, 128, 0, stream>>>(b.Proj, model->rope, model->rope_len, lens, nSeq, H, qvMult, b.Qk8, b.K8, layerSeqs[l], capacity,
+                statusWord);
         } else {
-            InferRopeNormKernel<128><<<gridR, 128, 0, stream>>>(b.Proj, model->rope, model->rope_len, lens, nSeq, H, qvMult, b.Qk8, b.Qv8, b.K8, b.V8, b.QvScale,
-                b.VScale, statusWord);
+            InferRopeNormKernel<128><<<gridR, 128, 0, stream>>>(b.Proj, model->rope, model->rope_len, lens, nSeq, H, qvMult, b.Qk8, b.K8, layerSeqs[l], capacity,
+                statusWord);
         }
         rc = CheckCuda(cudaGetLastError(), "inference rope launch");
         if (rc != TSA_OK) {
             break;
         }
-        rc = tsa_kv_append(&cfg, layerSeqs[l], lens, nSeq, capacity, ptr2d(b.Qv8, hs, hs, nSeq), ptr2d(b.QvScale, H * 4, H, nSeq), ptr2d(b.V8, hs, hs, nSeq),
-            ptr2d(b.VScale, H * 4, H, nSeq), H, statusWord, streamArg);
-        if (rc != TSA_OK) {
-            break;
-        }
         tsa_ptr2d none = {nullptr, 0, 0, 0};
-        rc = tsa_att_decode(&cfg, layerSeqs[l], lens, nSeq, maxCtx + 1, ptr2d(b.Qk8, hs, hs, nSeq), none, layer.attention_width, layer.alibi_slope,
-            ptr2d(b.Val, hs * 4, hs, nSeq), H, b.DecodeWs, b.DecodeWsBytes, statusWord, streamArg);
-        if (rc != TSA_OK) {
-            break;
-        }
-        InferKvProductKernel<<<(nSeq * hs * 4 + 255) / 256, 256, 0, stream>>>(b.K8, b.Val, hs, D, nSeq, b.Kv8);
-        rc = CheckCuda(cudaGetLastError(), "inference kv product launch");
+        // attention; its merge kernel also forms the combiner input kv = int8(k[z ^ blk] * val[z])
+        rc = DecodeWithKvProduct(&cfg, layerSeqs[l], lens, nSeq, maxCtx + 1, ptr2d(b.Qk8, hs, hs, nSeq), none, layer.attention_width, layer.alibi_slope,
+            ptr2d(b.Val, hs * 4, hs, nSeq), H, b.DecodeWs, b.DecodeWsBytes, statusWord, streamArg, b.K8, b.Kv8, 1);
         if (rc != TSA_OK) {
             break;
         }
         TGemvJob comb[1] = {{layer.combiner, b.State, dim}};
-        rc = LaunchGemv(true, comb, 1, b.Kv8, hs * 4, nSeq, dim, layer.combiner_scale * INF_VEC_SCALE * sqrtf(1.0f / (hs * 4)), statusWord, stream);
-        if (rc != TSA_OK) {
-            break;
-        }
-        rc = norm(b.State, dim, INF_NORM_TILE, false);
+        rc = LaunchGemv(true, comb, 1, b.Kv8, hs * 4, nSeq, dim, layer.combiner_scale * INF_VEC_SCALE * sqrtf(1.0f / (hs * 4)), b.NormState,
+            statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
         TGemvJob expand[1] = {{layer.expand, b.Relu, d.relu_dim}};
-        rc = LaunchGemv(false, expand, 1, b.Norm, dim, nSeq, d.relu_dim, 0.0f, statusWord, stream);
+        rc = LaunchGemv(false, expand, 1, b.NormState, dim, nSeq, d.relu_dim, 0.0f, nullptr, statusWord, stream);
         if (rc != TSA_OK) {
             break;
         }
-        rc = norm(b.Relu, d.relu_dim, d.relu_dim / H, true);
+        rc = norm(b.Relu, d.relu_dim, d.relu_dim / H, b.NormRelu, true);
         if (rc != TSA_OK) {
             break;
         }
         TGemvJob contract[1] = {{layer.contract, b.State, dim}};
-        rc = LaunchGemv(true, contract, 1, b.Norm, d.relu_dim, nSeq, dim, layer.contract_scale * INF_VEC_SCALE * sqrtf(1.0f / d.relu_dim), statusWord, stream);
+        rc = LaunchGemv(true, contract, 1, b.NormRelu, d.relu_dim, nSeq, dim, layer.contract_scale * INF_VEC_SCALE * sqrtf(1.0f / d.relu_dim), b.NormState,
+            statusWord, stream);
     }
     if (rc != TSA_OK) {
         return rc;
     }
-    if (prediction || logits) {
-        rc = norm(b.State, dim, INF_NORM_TILE, false);
+    if (d.layer_count > 0) {
+        InferCountKernel<<<(d.layer_count * nSeq + 255) / 256, 256, 0, stream>>>(ctxLens, d.layer_count * nSeq);
+        rc = CheckCuda(cudaGetLastError(), "inference count launch");
         if (rc != TSA_OK) {
             return rc;
         }
+    }
+    if (prediction || logits) {
         float *lg = logits ? logits : b.Logits;
         TGemvJob fin[1] = {{model->final_layer, lg, d.vocab_size}};
-        rc = LaunchGemv(false, fin, 1, b.Norm, dim, nSeq, d.vocab_size, 0.0f, statusWord, stream);
+        rc = LaunchGemv(false, fin, 1, b.NormState, dim, nSeq, d.vocab_size, 0.0f, nullptr, statusWord, stream);
         if (rc != TSA_OK) {
             return rc;
         }
         if (prediction) {
             // CalcDotScale(dim) * CalcFinalLayerMult() * FinalLayerScale * VEC_SCALE (cpu_infer.cpp:555)
             const float finalScale = sqrtf(1.0f / dim) * (1.0f / 0.693147f) * model->final_layer_scale * INF_VEC_SCALE;
-            InferSoftmaxKernel<<<nSeq, 1024, 0, stream>>>(lg, model->bias, finalScale, d.vocab_size, prediction);
+            dim3 gridS(INF_SOFTMAX_SLICES, nSeq);
+            InferSoftmaxPartKernel<<<gridS, 256, 0, stream>>>(lg, model->bias, finalScale, d.vocab_size, b.SoftmaxPart);
+            InferSoftmaxKernel<<<gridS, 256, 0, stream>>>(lg, model->bias, finalScale, d.vocab_size, b.SoftmaxPart, prediction);
             rc = CheckCuda(cudaGetLastError(), "inference softmax launch");
         }
     }
