@@ -206,7 +206,9 @@ int tsa_kv_append(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, int *ctxLen
     tsa_ptr2d kNew, tsa_ptr2d kScaleNew, tsa_ptr2d vNew, tsa_ptr2d vScaleNew, int headCount,
     int *statusWord, tsa_stream_t stream);
 /* q int8 [nSeq][H*D]; qScale f32 [nSeq][H] (may be absent); out [nSeq][H*D].  maxCtx: host-side upper
- * bound of ctxLens, only used to size the launch.  seqs and ctxLens are device arrays. */
+ * bound of ctxLens; it sizes the launch (short windows and contexts get a smaller grid), and a sequence that
+ * turns out longer sets a bit in the status word instead of being attended in part.  seqs and ctxLens are
+ * device arrays. */
 int tsa_att_decode(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
     tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);

@@ -17,6 +17,7 @@
 // polynomial.  The matrix products read every int8 weight once per step for the whole batch (tcgen05 kind::i8, exact
 // int32 accumulators); at realistic context lengths the step is dominated by the KV-cache stream of the decode kernel.
 #include "att_sm100_common.cuh"
+#include <cooperative_groups.h>
 
 namespace tsa {
 
@@ -194,6 +195,10 @@ struct TGemvJob {
 // row slab and the batch's vectors through a ring of GEMM_STAGES shared-memory stages of 128 columns (TMA, 128-byte
 // swizzle; rows past the matrix and sequences past the batch read as zeros) and issues the MMAs; afterwards thread t
 // holds row t of the tile and writes its 64 products, coalesced over the rows of a warp.  Every wait is bounded.
+// A matrix with few rows and many columns (the combiner: 768 x 3072) would leave a handful of CTAs each waiting on
+// two dozen dependent-latency chunk loads, so its columns are split over the KSplit CTAs of a thread-block cluster:
+// every CTA accumulates its share, ranks above 0 park their int32 tile in their own shared memory and rank 0 adds
+// them through distributed shared memory (exact, order does not matter) before the epilogue.
 constexpr int GEMM_STAGES = 8;
 constexpr int GEMM_M = 128, GEMM_N = 64, GEMM_KB = 128;
 constexpr int GEMM_STAGE_BYTES = (GEMM_M + GEMM_N) * GEMM_KB;
@@ -209,6 +214,7 @@ struct TGemmArgs {
     int OutStride, NSeq, Chunks;
     float Scale;
     int8_t *NormOut; // ADD only, may be null: NormalizeState of the updated rows, [NSeq][OutStride] int8
+    int KSplit;      // CTAs of a cluster that share a row tile, each with Chunks / KSplit of the columns
 };
 
 template <bool ADD>
@@ -222,9 +228,10 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     const int rows = job == 0 ? a.Rows[0] : job == 1 ? a.Rows[1] : job == 2 ? a.Rows[2] : a.Rows[3];
     float *out = job == 0 ? a.Out[0] : job == 1 ? a.Out[1] : job == 2 ? a.Out[2] : a.Out[3];
     const CUtensorMap *tmW = job == 0 ? &tmW0 : job == 1 ? &tmW1 : job == 2 ? &tmW2 : &tmW3;
-    const int rowBase = blockIdx.x * GEMM_M;
+    const int kSplit = a.KSplit, kRank = blockIdx.x % kSplit;
+    const int rowBase = (blockIdx.x / kSplit) * GEMM_M;
     if (rowBase >= rows) {
-        return; // the grid is sized for the tallest matrix of the launch
+        return; // the grid is sized for the tallest matrix of the launch; a cluster leaves as a whole
     }
     uint8_t *smem = (uint8_t *)(((uintptr_t)gemmSmemRaw + 1023) & ~(uintptr_t)1023);
     TGemmMisc &misc = *reinterpret_cast<TGemmMisc *>(smem + GEMM_STAGES * GEMM_STAGE_BYTES);
@@ -254,14 +261,15 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             const int s = chunk % GEMM_STAGES;
             uint8_t *sA = smem + s * GEMM_STAGE_BYTES, *sB = sA + GEMM_M * GEMM_KB;
             MbarExpectTx(&misc.Full[s], GEMM_STAGE_BYTES);
-            TmaLoad2D(sA, tmW, chunk * GEMM_KB, rowBase, &misc.Full[s]);
-            TmaLoad2D(sB, &tmVec, chunk * GEMM_KB, 0, &misc.Full[s]);
+            const int col = (kRank * (a.Chunks / kSplit) + chunk) * GEMM_KB;
+            TmaLoad2D(sA, tmW, col, rowBase, &misc.Full[s]);
+            TmaLoad2D(sB, &tmVec, col, 0, &misc.Full[s]);
         };
         // GEMM_AHEAD chunks are in flight; the stage a new load overwrites was read by the MMAs of two iterations ago,
         // whose completion has long arrived (waiting for the previous iteration's would stall every step on the
         // commit round trip)
         constexpr int GEMM_AHEAD = GEMM_STAGES - 2;
-        const int chunks = a.Chunks;
+        const int chunks = a.Chunks / kSplit;
         for (int c = 0; c < GEMM_AHEAD && c < chunks; ++c) {
             load(c);
         }
@@ -313,13 +321,40 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     float *normTile = reinterpret_cast<float *>(smem);            // [GEMM_N][GEMM_M + 1]
     float *normMult = normTile + GEMM_N * (GEMM_M + 1);           // [GEMM_N]
     const bool withNorm = ADD && a.NormOut != nullptr;
-    if (!failed) {
+    uint32_t accum[GEMM_N];
+    {
         const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
+        TmemLd32(tLane, accum);
+        TmemLd32(tLane + 32, accum + 32);
+        TmemWaitLd();
+    }
+    if (kSplit > 1) {
+        // both cluster barriers are passed by every CTA whatever happened before, so that none waits alone
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        int *part = reinterpret_cast<int *>(smem); // [GEMM_N][GEMM_M], the ring is idle by now
+        if (kRank > 0) {
+#pragma unroll
+            for (int cc = 0; cc < GEMM_N; ++cc) {
+                part[cc * GEMM_M + tid] = (int)accum[cc];
+            }
+        }
+        cluster.sync();
+        if (kRank == 0) {
+            for (int other = 1; other < kSplit; ++other) {
+                const int *remote = cluster.map_shared_rank(part, other);
+#pragma unroll
+                for (int cc = 0; cc < GEMM_N; ++cc) {
+                    accum[cc] += (uint32_t)remote[cc * GEMM_M + tid];
+                }
+            }
+        }
+        cluster.sync(); // the other CTAs' shared memory has been read
+    }
+    if (!failed && kRank == 0) {
 #pragma unroll
         for (int c0 = 0; c0 < GEMM_N; c0 += 32) {
-            uint32_t r[32];
-            TmemLd32(tLane + c0, r);
-            TmemWaitLd();
+            const uint32_t *r = accum + c0;
             if (row < rows) {
                 float *o = out + (size_t)c0 * a.OutStride + row;
                 float old[32];
@@ -459,19 +494,27 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     a.Chunks = cols / GEMM_KB;
     a.Scale = scale;
     a.NormOut = normOut;
-    dim3 grid((maxRows + GEMM_M - 1) / GEMM_M, jobCount);
-    if (add) {
-        rc = CheckCuda(cudaFuncSetAttribute(InferGemmI8Kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
-        if (rc == TSA_OK) {
-            InferGemmI8Kernel<true><<<grid, 128, GEMM_SMEM_BYTES, stream>>>(mw[0], mw[1], mw[2], mw[3], mv, a, statusWord);
-        }
-    } else {
-        rc = CheckCuda(cudaFuncSetAttribute(InferGemmI8Kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
-        if (rc == TSA_OK) {
-            InferGemmI8Kernel<false><<<grid, 128, GEMM_SMEM_BYTES, stream>>>(mw[0], mw[1], mw[2], mw[3], mv, a, statusWord);
-        }
+    // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix
+    a.KSplit = (a.Chunks >= 24 && a.Chunks % 4 == 0) ? 4 : (a.Chunks >= 12 && a.Chunks % 2 == 0) ? 2 : 1;
+    const void *kern = add ? (const void *)InferGemmI8Kernel<true> : (const void *)InferGemmI8Kernel<false>;
+    rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
+    if (rc != TSA_OK) {
+        return rc;
     }
-    return rc != TSA_OK ? rc : CheckCuda(cudaGetLastError(), "inference matrix product launch");
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = a.KSplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((maxRows + GEMM_M - 1) / GEMM_M * a.KSplit, jobCount);
+    lc.blockDim = dim3(128);
+    lc.dynamicSmemBytes = GEMM_SMEM_BYTES;
+    lc.stream = stream;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    void *args[] = {&mw[0], &mw[1], &mw[2], &mw[3], &mv, &a, &statusWord};
+    return CheckCuda(cudaLaunchKernelExC(&lc, kern, args), "inference matrix product launch");
 }
 
 static size_t Align256(size_t x)
