@@ -386,6 +386,7 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             }
             __syncthreads();
             if (row < rows) {
+#pragma unroll 8
                 for (int s = 0; s < a.NSeq; ++s) {
                     a.NormOut[(size_t)s * a.OutStride + row] = (int8_t)ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
                 }
