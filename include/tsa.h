@@ -255,6 +255,18 @@ int tsa_group_window_spans(int fragCount, const int *fragLens, int window, int t
 int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len, int window, int transposed,
     int maxGroups, tsa_span_group *groups, int *groupPtr, tsa_stream_t stream);
 
+/* ---- projection fused with the producer ("next" scope row: the GEMM epilogue in front of the path) ------------
+ * Replaces MulForwardInt8<TStoreRowTileNormalizeRope> and <TStoreRowTileNormalize> (code/gpt/compute/gpt_cuda.cu:
+ * 493-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204; rope code/gpt/compute/gpt_rope.cuh:4-66):
+ *   y[t][n] = (float)(int32 dot of x[t] and w[n]) * srcScale,   x int8 [len][dim], w int8 [H*D][dim] (dim % 64 == 0)
+ *   per head: discr = sqrt(sum y^2 / D) * vecScale; dst = quantise(rope(y / discr)); scale[head][t] = discr
+ * i.e. tsa_norm_rope_quant applied to the projection without the projection ever going to memory.  rope: f32
+ * [len][D] table or absent (the K and V projections are stored without rotation).  dst int8 or e4m3 [rows][H*D],
+ * rows in [len, dst.ysize) are zeroed with scale 0; scale f32 [H][rows] may be absent.  D = 64 or 128. */
+int tsa_matmul_norm_rope_quant(int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w, tsa_ptr2d rope,
+    float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, int *statusWord,
+    tsa_stream_t stream);
+
 /* ---- one-token inference step with KV caches ("next" scope row: the caller of the decode kernel) ---------------
  * Replaces NCPUInfer::ComputePrediction / AddLookupProduct (code/gpt/train/cpu_infer.cpp:466-560), which steps one
  * sequence on the CPU, for a batch of up to 64 sequences on the GPU.  The model is in the reference's int8 form

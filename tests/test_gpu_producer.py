@@ -113,3 +113,34 @@ def test_norm_rope_quant_pads_with_zeros():
     want_b, want_s, _ = O.norm_rope_quant("i8", 1 / 24.0, src[:length].cpu().numpy(), rope[:length].cpu().numpy(), d)
     frac, step = _codes_close(b[:length].cpu().numpy().view(np.int8), want_b, "i8")
     assert frac < 2e-3 and step <= 1
+
+
+@pytest.mark.parametrize("dst", ["i8", "e4m3"])
+@pytest.mark.parametrize("rows,length,dim,heads,d,with_rope", [
+    (300, 300, 256, 3, 64, True), (257, 200, 768, 12, 64, True), (130, 130, 384, 2, 128, True), (512, 512, 512, 5, 128, False),
+])
+def test_matmul_norm_rope_quant_bit_exact(dst, rows, length, dim, heads, d, with_rope):
+    """The projection fused with the producer: int32 products are exact and the epilogue follows the oracle's rounding
+    order (sequential sum of squares, separate roundings), so bytes and scales equal the oracle's
+    norm_rope_quant of the same projection bit for bit; padding rows are zero."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(rows + dim + heads)
+    x = rng.integers(-127, 128, (rows, dim)).astype(np.int8)
+    x[7] = 0                                                 # a row of zeros: scale 0, bytes 0
+    w = rng.integers(-127, 128, (heads * d, dim)).astype(np.int8)
+    src_scale = np.float32(1.0 / 4096)
+    y = (x[:length].astype(np.int32) @ w.T.astype(np.int32)).astype(np.float32) * src_scale
+    table = O.fill_rope(d, rows) if with_rope else None
+    want_b, want_s, _ = O.norm_rope_quant(dst, 1 / 24.0, y, None if table is None else table[:length], d)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got_b, got_s = ops.matmul_norm_rope_quant(torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV),
+                                              None if table is None else torch.from_numpy(table).to(DEV), dst, heads, d,
+                                              vec_scale=1 / 24.0, src_scale=float(src_scale), length=length, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got_b = got_b.cpu().numpy().view(np.int8)
+    got_s = got_s.cpu().numpy()
+    assert np.array_equal(got_s[:, :length], want_s)
+    assert np.array_equal(got_b[:length], want_b)
+    assert np.abs(got_b[length:]).max(initial=0) == 0 and np.abs(got_s[:, length:]).max(initial=0) == 0
+    assert got_s[:, 7].max() == 0
