@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized attention path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--workload prefill125m|train15b|decode|longctx|infer] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload prefill125m|train15b|decode|longctx|infer|neighbours] [--impl reference]
 
 Default workload `prefill125m` is the 125M-style prefill forward: 16 fragments x 4096 tokens, 12 heads x 64,
 e4m3 Q/K/V with per-row f32 scales, bf16 output; one step = 3 window-64 layers (ALiBi slope 0.5) + 1 full
@@ -157,7 +157,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill125m", choices=sorted(WORKLOADS) + ["decode", "infer"])
+    ap.add_argument("--workload", default="prefill125m", choices=sorted(WORKLOADS) + ["decode", "infer", "neighbours"])
     ap.add_argument("--gather", action="store_true", help="all-gather the bf16 outputs over NCCL inside the timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -175,6 +175,9 @@ def main():
     if args.workload == "infer":
         from tscale_b200 import bench_infer
         return bench_infer.run(args, rank, world, local_rank)
+    if args.workload == "neighbours":
+        from tscale_b200 import bench_neighbours
+        return bench_neighbours.run(args, rank, world, local_rank)
 
     w = dict(WORKLOADS[args.workload])
     if args.frags > 0:
