@@ -256,14 +256,15 @@ int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len,
     int maxGroups, tsa_span_group *groups, int *groupPtr, tsa_stream_t stream);
 
 /* ---- projection fused with the producer ("next" scope row: the GEMM epilogue in front of the path) ------------
- * Replaces MulForwardInt8<TStoreRowTileNormalizeRope> and <TStoreRowTileNormalize> (code/gpt/compute/gpt_cuda.cu:
- * 493-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204; rope code/gpt/compute/gpt_rope.cuh:4-66):
- *   y[t][n] = (float)(int32 dot of x[t] and w[n]) * srcScale,   x int8 [len][dim], w int8 [H*D][dim] (dim % 64 == 0)
+ * Replaces MulForwardInt8 / MulForwardFp8 <TStoreRowTileNormalizeRope> and <TStoreRowTileNormalize>
+ * (code/gpt/compute/gpt_cuda.cu:488-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204; rope code/gpt/compute/gpt_rope.cuh:4-66):
+ *   y[t][n] = (float)(int32 dot of x[t] and w[n]) * srcScale,   x int8 [len][dim], w int8 [H*D][dim] (dim % 64 == 0);
+ *   srcDtype TSA_E4M3: x and w hold e4m3 bytes and the dot is accumulated in f32 by the tensor cores
  *   per head: discr = sqrt(sum y^2 / D) * vecScale; dst = quantise(rope(y / discr)); scale[head][t] = discr
  * i.e. tsa_norm_rope_quant applied to the projection without the projection ever going to memory.  rope: f32
  * [len][D] table or absent (the K and V projections are stored without rotation).  dst int8 or e4m3 [rows][H*D],
  * rows in [len, dst.ysize) are zeroed with scale 0; scale f32 [H][rows] may be absent.  D = 64 or 128. */
-int tsa_matmul_norm_rope_quant(int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w, tsa_ptr2d rope,
+int tsa_matmul_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w, tsa_ptr2d rope,
     float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, int *statusWord,
     tsa_stream_t stream);
 

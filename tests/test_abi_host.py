@@ -58,9 +58,9 @@ def test_bad_arguments_return_status_not_abort():
     assert lib.tsa_att_decode_workspace_bytes(ctypes.byref(abi.DecodeCfg(128, abi.TSA_F16, abi.TSA_F32, 1.0)), 64, 16, 8192) > 0
     # fused projection: validation before any tensor map is made
     fx = abi.Ptr2D(4096, 200, 200, 8)
-    assert lib.tsa_matmul_norm_rope_quant(abi.TSA_I8, 1.0, 1.0, fx, fx, null, 1.0, fake, null, 1, 64, 8, None, None) == abi.TSA_BAD_ARG
+    assert lib.tsa_matmul_norm_rope_quant(abi.TSA_I8, abi.TSA_I8, 1.0, 1.0, fx, fx, null, 1.0, fake, null, 1, 64, 8, None, None) == abi.TSA_BAD_ARG
     assert b"multiples of 64" in lib.tsa_last_error()
-    assert lib.tsa_matmul_norm_rope_quant(abi.TSA_F32, 1.0, 1.0, fx, fx, null, 1.0, fake, null, 1, 64, 8, None, None) == abi.TSA_BAD_ARG
+    assert lib.tsa_matmul_norm_rope_quant(abi.TSA_I8, abi.TSA_F32, 1.0, 1.0, fx, fx, null, 1.0, fake, null, 1, 64, 8, None, None) == abi.TSA_BAD_ARG
     # inference step: sizes are checked before anything is dereferenced or launched
     im = abi.InferModel()
     im.dims = abi.InferDims(768, 64, 12, 1536, 50000, 50100, 0)

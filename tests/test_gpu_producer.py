@@ -144,3 +144,26 @@ def test_matmul_norm_rope_quant_bit_exact(dst, rows, length, dim, heads, d, with
     assert np.array_equal(got_b[:length], want_b)
     assert np.abs(got_b[length:]).max(initial=0) == 0 and np.abs(got_s[:, length:]).max(initial=0) == 0
     assert got_s[:, 7].max() == 0
+
+
+@pytest.mark.parametrize("rows,dim,heads,d", [(300, 256, 3, 64), (200, 512, 2, 128)])
+def test_matmul_norm_rope_quant_e4m3_operands(rows, dim, heads, d):
+    """e4m3 x e4m3 projection: the tensor cores add the products in f32 in their own order, so the projection matches
+    the float64 product to f32 rounding and the output codes differ from the oracle's at rounding boundaries only."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(rows + dim)
+    xf = (rng.standard_normal((rows, dim)) * 0.7).astype(np.float32)
+    wf = (rng.standard_normal((heads * d, dim)) * 0.7).astype(np.float32)
+    x8 = np.array([O.lib().oracle_f32_to_e4m3(float(v)) for v in xf.ravel()], dtype=np.uint8).reshape(xf.shape)
+    w8 = np.array([O.lib().oracle_f32_to_e4m3(float(v)) for v in wf.ravel()], dtype=np.uint8).reshape(wf.shape)
+    y = (O.e4m3_to_f32(x8).astype(np.float64) @ O.e4m3_to_f32(w8).astype(np.float64).T).astype(np.float32)
+    table = O.fill_rope(d, rows)
+    want_b, want_s, _ = O.norm_rope_quant("i8", 1 / 24.0, y, table, d)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got_b, got_s = ops.matmul_norm_rope_quant(torch.from_numpy(x8).to(DEV), torch.from_numpy(w8).to(DEV), torch.from_numpy(table).to(DEV), "i8",
+                                              heads, d, vec_scale=1 / 24.0, status=status, src="e4m3")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.allclose(got_s.cpu().numpy(), want_s, rtol=2e-6, atol=0)
+    frac, step = _codes_close(got_b.cpu().numpy().view(np.int8), want_b, "i8")
+    assert frac < 2e-3 and step <= 1, (frac, step)

@@ -109,7 +109,7 @@ def _declare(lib):
                                           P, c_int, c_void_p, c_void_p]
     lib.tsa_att_decode_static_capacity_bytes.restype = c_size_t
     lib.tsa_att_decode_static_capacity_bytes.argtypes = []
-    lib.tsa_matmul_norm_rope_quant.argtypes = [c_int, c_float, c_float, P, P, P, c_float, P, P, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.tsa_matmul_norm_rope_quant.argtypes = [c_int, c_int, c_float, c_float, P, P, P, c_float, P, P, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.tsa_infer_workspace_bytes.restype = c_size_t
     lib.tsa_infer_workspace_bytes.argtypes = [ctypes.POINTER(InferModel), c_int, c_int]
     lib.tsa_infer_step.argtypes = [ctypes.POINTER(InferModel), ctypes.POINTER(c_void_p), c_void_p, c_int, c_void_p, c_int, c_int,

@@ -1,10 +1,10 @@
 // The projection that feeds the attention fused with its store op: int8 activations x int8 matrix on the tensor cores,
 // then per-head RMS normalise, rope and quantise in the epilogue, straight from the accumulators.
-// Replaces MulForwardInt8<TStoreRowTileNormalizeRope> / <TStoreRowTileNormalize> of the reference
-// (code/gpt/compute/gpt_cuda.cu:493-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204, rope
+// Replaces MulForwardInt8 / MulForwardFp8 <TStoreRowTileNormalizeRope> / <TStoreRowTileNormalize> of the reference
+// (code/gpt/compute/gpt_cuda.cu:488-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204, rope
 // code/gpt/compute/gpt_rope.cuh:4-66): the fp32 projection never goes to memory.
 //
-//   y[t][n]  = (float)(int32 dot of x[t] and w[n]) * srcScale
+//   y[t][n]  = (float)(int32 dot of x[t] and w[n]) * srcScale      (e4m3 operands: f32 dot on the tensor cores)
 //   per head: discr = sqrt(sum y^2 / D) * vecScale;  z = y / discr;  rope (elements k and k + 32 of a 64-block);
 //             dst = quantise(z) (int8 or e4m3);  scale[head][t] = discr
 //
@@ -52,10 +52,14 @@ struct TProjArgs {
     int Len, Rows, HeadCount, Chunks;
 };
 
-template <int D, bool DST_E4M3>
+// X_E4M3: both operands are e4m3 bytes (MulForwardFp8, gpt_cuda.cu:488-491), products accumulate in f32 on the tensor
+// cores (kind::f8f6f4); otherwise int8 x int8 with exact int32 accumulators (kind::i8).
+template <int D, bool DST_E4M3, bool X_E4M3>
 __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, TProjArgs a, int *status)
 {
-    constexpr uint32_t IDESC = MakeInstrDesc(2, 1, 1, 0, 0, PROJ_M, PROJ_N); // s32 accumulators, s8 x s8, both K-major
+    // s32 accumulators, s8 x s8 -- or f32 accumulators, e4m3 x e4m3; both operands K-major
+    constexpr uint32_t IDESC = X_E4M3 ? MakeInstrDesc(1, 0, 0, 0, 0, PROJ_M, PROJ_N) : MakeInstrDesc(2, 1, 1, 0, 0, PROJ_M, PROJ_N);
+    auto accValue = [](uint32_t bits) { return X_E4M3 ? __uint_as_float(bits) : (float)(int32_t)bits; };
     constexpr int HPC = PROJ_N / D;                                          // heads per CTA
     extern __shared__ uint8_t projSmemRaw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)projSmemRaw + 1023) & ~(uintptr_t)1023);
@@ -122,7 +126,11 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
             for (int ks = 0; ks < PROJ_KB / 32; ++ks) {
                 const uint64_t aDesc = MakeSmemDesc(sA + ks * 32, 16, 8 * PROJ_KB, PROJ_KB);
                 const uint64_t bDesc = MakeSmemDesc(sB + ks * 32, 16, 8 * PROJ_KB, PROJ_KB);
-                MmaI8SS(tmem, aDesc, bDesc, IDESC, (c > 0 || ks > 0) ? 1u : 0u);
+                if (X_E4M3) {
+                    MmaF8SS(tmem, aDesc, bDesc, IDESC, (c > 0 || ks > 0) ? 1u : 0u);
+                } else {
+                    MmaI8SS(tmem, aDesc, bDesc, IDESC, (c > 0 || ks > 0) ? 1u : 0u);
+                }
             }
             MmaCommit(&misc.Empty[s]);
         }
@@ -175,7 +183,7 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
                 TmemWaitLd();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float y = __fmul_rn((float)(int32_t)r[i], a.SrcScale);
+                    const float y = __fmul_rn(accValue(r[i]), a.SrcScale);
                     sum2 = __fadd_rn(sum2, __fmul_rn(y, y));
                 }
             }
@@ -198,8 +206,8 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int k = q * 4 + i;
-                        float y0 = __fmul_rn(__fmul_rn((float)(int32_t)lo[k], a.SrcScale), mult);
-                        float y1 = __fmul_rn(__fmul_rn((float)(int32_t)hi[k], a.SrcScale), mult);
+                        float y0 = __fmul_rn(__fmul_rn(accValue(lo[k]), a.SrcScale), mult);
+                        float y1 = __fmul_rn(__fmul_rn(accValue(hi[k]), a.SrcScale), mult);
                         if (withRope && live) {
                             const float cs = ropeTile[tid * (D + 1) + blk + k];
                             const float sn = __fmul_rn(ropeTile[tid * (D + 1) + blk + k + 32], a.RopeDir);
@@ -248,9 +256,10 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
 
 using namespace tsa;
 
-extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant(int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w,
+extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w,
     tsa_ptr2d rope, float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, int *statusWord, tsa_stream_t stream)
 {
+    TSA_REQUIRE(srcDtype == TSA_I8 || srcDtype == TSA_E4M3, "tsa_matmul_norm_rope_quant: x and w must both be i8 or both e4m3");
     TSA_REQUIRE(dstDtype == TSA_I8 || dstDtype == TSA_E4M3, "tsa_matmul_norm_rope_quant: dst dtype must be i8 or e4m3");
     TSA_REQUIRE(x.data && w.data && dst.data, "tsa_matmul_norm_rope_quant: null x / w / dst");
     TSA_REQUIRE(headCount > 0 && (headDim == 64 || headDim == 128), "tsa_matmul_norm_rope_quant: head size %d must be 64 or 128", headDim);
@@ -296,9 +305,21 @@ extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant
     a.HeadCount = headCount;
     a.Chunks = dim / PROJ_KB;
     dim3 grid((dst.ysize + PROJ_M - 1) / PROJ_M, (outCols + PROJ_N - 1) / PROJ_N);
-    const bool e4 = dstDtype == TSA_E4M3;
-    const void *kern = headDim == 64 ? (e4 ? (const void *)ProjNormRopeKernel<64, true> : (const void *)ProjNormRopeKernel<64, false>)
-                                     : (e4 ? (const void *)ProjNormRopeKernel<128, true> : (const void *)ProjNormRopeKernel<128, false>);
+    const bool e4 = dstDtype == TSA_E4M3, x8 = srcDtype == TSA_E4M3;
+    const void *kern = nullptr;
+#define TSA_PROJ_CASE(DD, E4, X8)                                       \
+    if (headDim == DD && e4 == E4 && x8 == X8) {                        \
+        kern = (const void *)ProjNormRopeKernel<DD, E4, X8>;            \
+    }
+    TSA_PROJ_CASE(64, false, false)
+    TSA_PROJ_CASE(64, true, false)
+    TSA_PROJ_CASE(64, false, true)
+    TSA_PROJ_CASE(64, true, true)
+    TSA_PROJ_CASE(128, false, false)
+    TSA_PROJ_CASE(128, true, false)
+    TSA_PROJ_CASE(128, false, true)
+    TSA_PROJ_CASE(128, true, true)
+#undef TSA_PROJ_CASE
     rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {
         return rc;
