@@ -113,3 +113,33 @@ def test_span_helpers_report_needed_capacity():
 def test_empty_mask():
     m = ops.Mask.from_spans(np.zeros((0, 2), dtype=np.int32), np.zeros(65, dtype=np.int32))
     assert m.groups.shape[0] == 0 and np.all(m.group_ptr == 0) and m.len_att_tiles == 1
+
+
+def test_header_is_plain_c_and_links(tmp_path):
+    """include/tsa.h compiles as C11 without warnings, and a C program bound against the shared library the way a host
+    in another language would (plain pointers and sizes) resolves every declared entry point and runs the host-side ones."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "tsa.h")).read(), flags=re.S)
+    names = sorted(set(re.findall(r"\b(tsa_[a-z0-9_]+)\s*\(", text)))
+    src = tmp_path / "bind.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <string.h>\n#include "tsa.h"\n'
+        "typedef void (*fn_t)(void);\n"
+        "int main(void) {\n"
+        "    fn_t table[] = {" + ", ".join("(fn_t)%s" % n for n in names) + "};\n"
+        "    int lens[2] = {5, 3}, spans[64], ptr[9];\n"
+        "    int n = tsa_make_window_spans(2, lens, 2, 32, spans, ptr);\n"
+        "    if (n != ptr[8] || strstr(tsa_version(), \"sm_100a\") == NULL) return 1;\n"
+        "    printf(\"%d %d\\n\", (int)(sizeof(table) / sizeof(table[0])), n);\n"
+        "    return 0;\n}\n")
+    exe = tmp_path / "bind"
+    lib_dir = os.path.dirname(abi.LIB_PATH)
+    subprocess.run([cc, "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", lib_dir, "-ltsa_b200", "-Wl,-rpath," + lib_dir], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == len(names) == len(abi.EXPORTS)
+    assert int(out[1]) == 4 + 2      # one span per row that has keys: rows 1..4 of the first fragment, rows 1..2 of the second
