@@ -313,6 +313,7 @@ def main():
 
     peaks = load_peaks()
     fp8_peak = measure_fp8_peak(torch, dev)
+    int8_peak = measure_int8_peak(torch, dev)
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": "FwdSm100Kernel (full-causal layer, %s QK^T, e4m3 PV)" % w["qk"],
@@ -320,6 +321,7 @@ def main():
         "peak_source": "MEASURED_PEAKS.json bf16 burst (%s)" % peaks["_source"],
         "peak_fp8_measured": fp8_peak, "frac_fp8_measured": (achieved / fp8_peak) if fp8_peak else None,
         "peak_fp8_nominal": 4500.0, "frac_fp8_nominal": achieved / 4500.0,
+        "peak_int8_measured": int8_peak, "frac_int8_measured": (achieved / int8_peak) if int8_peak else None,
         "ms_per_launch": dom_ms, "algorithmic_flops_per_launch": dom_flops, "traffic": None,
         "timed": "CUDA events around the layer's tsa_att_fwd call (V-scale maximum kernel of a few microseconds + the attention kernel)",
     }
@@ -368,6 +370,29 @@ def measure_fp8_peak(torch, dev):
             e1 = torch.cuda.Event(enable_timing=True)
             e0.record()
             torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:  # noqa: BLE001  (a peak probe must not break the benchmark)
+        return None
+
+
+def measure_int8_peak(torch, dev):
+    """Dense int8 x int8 -> int32 GEMM rate of this GPU (cuBLASLt through torch._int_mm), in TOP/s; None if the library
+    has no such kernel here."""
+    try:
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8).t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = 1e9
+        for _ in range(8):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
             e1.record()
             torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1))
