@@ -167,3 +167,47 @@ def test_matmul_norm_rope_quant_e4m3_operands(rows, dim, heads, d):
     assert np.allclose(got_s.cpu().numpy(), want_s, rtol=2e-6, atol=0)
     frac, step = _codes_close(got_b.cpu().numpy().view(np.int8), want_b, "i8")
     assert frac < 2e-3 and step <= 1, (frac, step)
+
+
+def test_block_chain_projection_attention_consumer():
+    """The whole block front to back: int8 state x int8 matrices -> fused projection + producer (bit-exact, so the
+    attention sees the oracle's own bytes and scale planes, in the layout it takes them) -> tsa_att_fwd -> tsa_kv_product,
+    against the oracle chain."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(52)
+    frag_lens, heads, d, dim, window, slope = [260, 124], 4, 64, 256, 64, 0.5
+    rows = sum(frag_lens)
+    x = rng.integers(-127, 128, (rows, dim)).astype(np.int8)
+    rope_np = O.fill_rope(d, rows)
+    vec, src_scale = 1 / 4.0, np.float32(1 / 2048.0)
+    xd = torch.from_numpy(x).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dev_in, deq = {}, {}
+    for n in ("q", "k", "v"):
+        w = rng.integers(-127, 128, (heads * d, dim)).astype(np.int8)
+        rope = rope_np if n != "v" else None
+        y = (x.astype(np.int32) @ w.T.astype(np.int32)).astype(np.float32) * src_scale
+        b, s, _ = O.norm_rope_quant("e4m3", vec, y, rope, d)
+        deq[n] = (O.dequant(b, "e4m3").reshape(rows, heads, d) * s.T[:, :, None]).reshape(rows, heads * d).astype(np.float32)
+        dev_in[n] = ops.matmul_norm_rope_quant(xd, torch.from_numpy(w).to(DEV), None if rope is None else torch.from_numpy(rope).to(DEV), "e4m3",
+                                               heads, d, vec_scale=vec, src_scale=float(src_scale), status=status)
+        assert np.array_equal(dev_in[n][0].cpu().numpy().view(np.int8), b) and np.array_equal(dev_in[n][1].cpu().numpy(), s), n
+    spans, ptr = O.window_spans(frag_lens, window)
+    ref = O.att_fwd(deq["q"], deq["k"], deq["v"], spans, ptr, heads, slope)
+    cfg = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.float32)
+    mask = ops.Mask.window(frag_lens, window)
+    out, _ = ops.att_fwd(cfg, dev_in["q"][0], dev_in["k"][0], dev_in["v"][0], dev_in["k"][1], mask, slope, heads,
+                         qk_scale=dev_in["q"][1], v_scale=dev_in["v"][1], status=status)
+    comb_key = rng.standard_normal((rows, heads * d)).astype(np.float32)
+    kv = ops.kv_product(torch.from_numpy(comb_key).to(DEV), out, heads, d)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # the values here are the projections themselves (tens in magnitude): the tolerances scale with their range
+    vmax = float(np.abs(deq["v"]).max())
+    mx, mean = util.err_stats(util.to_np(out), ref["out"])
+    assert mx < util.OUT_MAX_ABS * vmax and mean < util.OUT_MEAN_ABS * vmax, util.describe(util.to_np(out), ref["out"])
+    want_kv = O.kv_product(comb_key, ref["out"], heads)
+    scale = float(np.abs(comb_key).max())
+    assert np.abs(util.to_np(kv) - want_kv).max() < util.OUT_MAX_ABS * vmax * scale
+    # the consumer itself is exact on the attention output it was given
+    assert np.array_equal(util.to_np(kv), O.kv_product(comb_key, util.to_np(out), heads))
