@@ -213,7 +213,8 @@ struct TGemmArgs {
     int Rows[4];
     int OutStride, NSeq, Chunks;
     float Scale;
-    int8_t *NormOut; // ADD only, may be null: NormalizeState of the updated rows, [NSeq][OutStride] int8
+    int8_t *NormOut; // may be null: NormalizeState of the tile's 128 result rows, [NSeq][OutStride] int8
+    int NormRelu;    // clamp the normalised values at 0 (the relu block's input)
     int KSplit;      // CTAs of a cluster that share a row tile, each with Chunks / KSplit of the columns
 };
 
@@ -314,13 +315,14 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     TcFenceAfter();
     failed = __syncthreads_or(failed ? 1 : 0) != 0;
     const int row = rowBase + tid;
-    // ADD with NormOut: the tile's 128 rows are one normalisation tile of the state (STATE_NORM_TILE = 128), so the
+    // With NormOut: the tile's 128 rows are one normalisation group (a STATE_NORM_TILE of the state, or a head of the
+    // relu block when its heads are 128 wide), so the
     // int8 input of the next matrix product is made here, from the values just stored: they go through shared memory
     // (the ring is idle by now), one thread per sequence adds the squares in row order like the scalar loop of
     // NormalizeState, then every thread converts its row.
     float *normTile = reinterpret_cast<float *>(smem);            // [GEMM_N][GEMM_M + 1]
     float *normMult = normTile + GEMM_N * (GEMM_M + 1);           // [GEMM_N]
-    const bool withNorm = ADD && a.NormOut != nullptr;
+    const bool withNorm = a.NormOut != nullptr;
     uint32_t accum[GEMM_N];
     {
         const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
@@ -369,7 +371,9 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
                     if (c0 + cc < a.NSeq) {
                         const float v = (float)(int32_t)r[cc];
                         const float res = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
-                        o[(size_t)cc * a.OutStride] = res;
+                        if (ADD || !withNorm) { // a product that is only normalised does not need its fp32 form in memory
+                            o[(size_t)cc * a.OutStride] = res;
+                        }
                         if (withNorm) {
                             normTile[(c0 + cc) * (GEMM_M + 1) + tid] = res;
                         }
@@ -388,7 +392,8 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             if (row < rows) {
 #pragma unroll 8
                 for (int s = 0; s < a.NSeq; ++s) {
-                    a.NormOut[(size_t)s * a.OutStride + row] = (int8_t)ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
+                    const int q = ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
+                    a.NormOut[(size_t)s * a.OutStride + row] = (int8_t)(a.NormRelu ? max(q, 0) : q);
                 }
             }
         }
@@ -469,7 +474,7 @@ __global__ void __launch_bounds__(256) InferSoftmaxKernel(const float *logits, c
 }
 
 static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t *vec, int cols, int nSeq, int outStride, float scale, int8_t *normOut,
-    int *statusWord, cudaStream_t stream)
+    int *statusWord, cudaStream_t stream, bool normRelu = false)
 {
     CUtensorMap mw[4], mv;
     TGemmArgs a;
@@ -495,6 +500,7 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     a.Chunks = cols / GEMM_KB;
     a.Scale = scale;
     a.NormOut = normOut;
+    a.NormRelu = normRelu ? 1 : 0;
     // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix
     a.KSplit = (a.Chunks >= 24 && a.Chunks % 4 == 0) ? 4 : (a.Chunks >= 12 && a.Chunks % 2 == 0) ? 2 : 1;
     const void *kern = add ? (const void *)InferGemmI8Kernel<true> : (const void *)InferGemmI8Kernel<false>;
@@ -662,11 +668,15 @@ extern "C" __attribute__((visibility("default"))) int tsa_infer_step(const tsa_i
             break;
         }
         TGemvJob expand[1] = {{layer.expand, b.Relu, d.relu_dim}};
-        rc = LaunchGemv(false, expand, 1, b.NormState, dim, nSeq, d.relu_dim, 0.0f, nullptr, statusWord, stream);
-        if (rc != TSA_OK) {
-            break;
+        if (d.relu_dim / H == GEMM_M) {
+            // 128-wide relu heads coincide with the product's row tiles: normalise + relu in its epilogue
+            rc = LaunchGemv(false, expand, 1, b.NormState, dim, nSeq, d.relu_dim, 0.0f, b.NormRelu, statusWord, stream, true);
+        } else {
+            rc = LaunchGemv(false, expand, 1, b.NormState, dim, nSeq, d.relu_dim, 0.0f, nullptr, statusWord, stream);
+            if (rc == TSA_OK) {
+                rc = norm(b.Relu, d.relu_dim, d.relu_dim / H, b.NormRelu, true);
+            }
         }
-        rc = norm(b.Relu, d.relu_dim, d.relu_dim / H, b.NormRelu, true);
         if (rc != TSA_OK) {
             break;
         }
