@@ -218,8 +218,8 @@ struct TGemmArgs {
     int KSplit;      // CTAs of a cluster that share a row tile, each with Chunks / KSplit of the columns
 };
 
-template <bool ADD>
-__global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+template <bool ADD, int KS>
+__global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
     const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW3, const __grid_constant__ CUtensorMap tmVec, TGemmArgs a,
     int *status)
 {
@@ -229,7 +229,9 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
     const int rows = job == 0 ? a.Rows[0] : job == 1 ? a.Rows[1] : job == 2 ? a.Rows[2] : a.Rows[3];
     float *out = job == 0 ? a.Out[0] : job == 1 ? a.Out[1] : job == 2 ? a.Out[2] : a.Out[3];
     const CUtensorMap *tmW = job == 0 ? &tmW0 : job == 1 ? &tmW1 : job == 2 ? &tmW2 : &tmW3;
-    const int kSplit = a.KSplit, kRank = blockIdx.x % kSplit;
+    constexpr int kSplit = KS;                 // CTAs of the cluster that share this row tile
+    constexpr int CPR = GEMM_N / KS;           // sequences (accumulator columns) a CTA finishes
+    const int kRank = blockIdx.x % kSplit;
     const int rowBase = (blockIdx.x / kSplit) * GEMM_M;
     if (rowBase >= rows) {
         return; // the grid is sized for the tallest matrix of the launch; a cluster leaves as a whole
@@ -330,46 +332,51 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
         TmemLd32(tLane + 32, accum + 32);
         TmemWaitLd();
     }
-    if (kSplit > 1) {
+    // Reduce-scatter over the cluster: every CTA parks its int32 tile in its own shared memory, then finishes CPR of the
+    // 64 sequences: it adds the other CTAs' partial sums of those columns through distributed shared memory (exact, the
+    // order does not matter) and runs the epilogue for them, so the epilogue's work is split as well.
+    int sum[KS > 1 ? CPR : 1];
+    if (KS > 1) {
         // both cluster barriers are passed by every CTA whatever happened before, so that none waits alone
         namespace cg = cooperative_groups;
         cg::cluster_group cluster = cg::this_cluster();
         int *part = reinterpret_cast<int *>(smem); // [GEMM_N][GEMM_M], the ring is idle by now
-        if (kRank > 0) {
 #pragma unroll
-            for (int cc = 0; cc < GEMM_N; ++cc) {
-                part[cc * GEMM_M + tid] = (int)accum[cc];
-            }
+        for (int cc = 0; cc < GEMM_N; ++cc) {
+            part[cc * GEMM_M + tid] = (int)accum[cc];
         }
         cluster.sync();
-        if (kRank == 0) {
-            for (int other = 1; other < kSplit; ++other) {
-                const int *remote = cluster.map_shared_rank(part, other);
 #pragma unroll
-                for (int cc = 0; cc < GEMM_N; ++cc) {
-                    accum[cc] += (uint32_t)remote[cc * GEMM_M + tid];
-                }
+        for (int j = 0; j < CPR; ++j) {
+            sum[j] = part[(kRank * CPR + j) * GEMM_M + tid];
+        }
+        for (int step = 1; step < KS; ++step) {
+            const int *remote = cluster.map_shared_rank(part, (kRank + step) % KS);
+#pragma unroll
+            for (int j = 0; j < CPR; ++j) {
+                sum[j] += remote[(kRank * CPR + j) * GEMM_M + tid];
             }
         }
-        cluster.sync(); // the other CTAs' shared memory has been read
+        cluster.sync(); // every CTA's shared memory has been read: it may be reused and the CTA may leave
     }
-    if (!failed && kRank == 0) {
+    const int colBase = kRank * CPR;
+    if (!failed) {
+        constexpr int BLK = CPR < 32 ? CPR : 32;
 #pragma unroll
-        for (int c0 = 0; c0 < GEMM_N; c0 += 32) {
-            const uint32_t *r = accum + c0;
+        for (int c0 = 0; c0 < CPR; c0 += BLK) {
             if (row < rows) {
-                float *o = out + (size_t)c0 * a.OutStride + row;
-                float old[32];
+                float *o = out + (size_t)(colBase + c0) * a.OutStride + row;
+                float old[BLK];
                 if (ADD) { // all loads before the first store: they are independent, a store in between would serialise them
 #pragma unroll
-                    for (int cc = 0; cc < 32; ++cc) {
-                        old[cc] = (c0 + cc < a.NSeq) ? o[(size_t)cc * a.OutStride] : 0.0f;
+                    for (int cc = 0; cc < BLK; ++cc) {
+                        old[cc] = (colBase + c0 + cc < a.NSeq) ? o[(size_t)cc * a.OutStride] : 0.0f;
                     }
                 }
 #pragma unroll
-                for (int cc = 0; cc < 32; ++cc) {
-                    if (c0 + cc < a.NSeq) {
-                        const float v = (float)(int32_t)r[cc];
+                for (int cc = 0; cc < BLK; ++cc) {
+                    if (colBase + c0 + cc < a.NSeq) {
+                        const float v = (float)(KS > 1 ? sum[(c0 + cc) % (KS > 1 ? CPR : 1)] : (int)accum[c0 + cc]);
                         const float res = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
                         if (ADD || !withNorm) { // a product that is only normalised does not need its fp32 form in memory
                             o[(size_t)cc * a.OutStride] = res;
@@ -383,7 +390,7 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
         }
         if (withNorm) {
             __syncthreads();
-            if (tid < a.NSeq) {
+            if (tid < CPR && colBase + tid < a.NSeq) {
                 float discr, mult;
                 NormScales(SequentialSum2(normTile + tid * (GEMM_M + 1), GEMM_M), GEMM_M, &discr, &mult);
                 normMult[tid] = mult;
@@ -391,9 +398,11 @@ __global__ void __launch_bounds__(128) InferGemmI8Kernel(const __grid_constant__
             __syncthreads();
             if (row < rows) {
 #pragma unroll 8
-                for (int s = 0; s < a.NSeq; ++s) {
-                    const int q = ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
-                    a.NormOut[(size_t)s * a.OutStride + row] = (int8_t)(a.NormRelu ? max(q, 0) : q);
+                for (int s = 0; s < CPR; ++s) {
+                    if (colBase + s < a.NSeq) {
+                        const int q = ToInt8Clamp127(__fmul_rn(normTile[s * (GEMM_M + 1) + tid], normMult[s]));
+                        a.NormOut[(size_t)(colBase + s) * a.OutStride + row] = (int8_t)(a.NormRelu ? max(q, 0) : q);
+                    }
                 }
             }
         }
@@ -503,7 +512,14 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     a.NormRelu = normRelu ? 1 : 0;
     // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix
     a.KSplit = (a.Chunks >= 24 && a.Chunks % 4 == 0) ? 4 : (a.Chunks >= 12 && a.Chunks % 2 == 0) ? 2 : 1;
-    const void *kern = add ? (const void *)InferGemmI8Kernel<true> : (const void *)InferGemmI8Kernel<false>;
+    const void *kern = nullptr;
+    if (a.KSplit == 4) {
+        kern = add ? (const void *)InferGemmI8Kernel<true, 4> : (const void *)InferGemmI8Kernel<false, 4>;
+    } else if (a.KSplit == 2) {
+        kern = add ? (const void *)InferGemmI8Kernel<true, 2> : (const void *)InferGemmI8Kernel<false, 2>;
+    } else {
+        kern = add ? (const void *)InferGemmI8Kernel<true, 1> : (const void *)InferGemmI8Kernel<false, 1>;
+    }
     rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {
         return rc;
