@@ -120,3 +120,19 @@ def test_bad_arguments():
     ctx2.compute_prediction(bad)
     torch.cuda.synchronize()
     assert int(ctx2.status.item()) != 0
+
+
+def test_batch_of_twenty_sequences():
+    """17 to 32 sequences take the matrix products' two-way sequence split: exact first-step logits, identical slots."""
+    model = O.make_infer_model(95, 256, 64, 2, 1, 96, 16, [(8, 0.0), (32, 0.5)])
+    rng = np.random.default_rng(96)
+    steps = 4
+    streams = rng.integers(0, 16, (2, steps, 1)).astype(np.int32)
+    labels = np.concatenate([streams] * 10, axis=0)   # 20 sequences
+    pred, logits = _run_gpu(model, labels, want_logits=True)
+    for s in range(2):
+        orc = O.InferOracle(model, steps, exp_mode="exact")
+        _, want_logits = orc.step(streams[s, 0], want_logits=True)
+        assert np.array_equal(logits[s, 0], want_logits), s
+    for s in range(2, 20):
+        assert np.array_equal(logits[s], logits[s % 2]) and np.array_equal(pred[s], pred[s % 2]), s

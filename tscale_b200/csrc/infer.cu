@@ -218,19 +218,26 @@ struct TGemmArgs {
     int KSplit;      // CTAs of a cluster that share a row tile, each with Chunks / KSplit of the columns
 };
 
-template <bool ADD, int KS>
+// KS > 1: the matrix columns (the inner dimension) are split over a cluster of KS CTAs (wide matrices).
+// NS > 1: the sequences are split over NS independent CTAs, each with its own MMA of GEMM_N / NS accumulator columns
+// (narrow matrices with few row tiles: more CTAs, and each runs a quarter of the epilogue).  Never both.
+template <bool ADD, int KS, int NS>
 __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
     const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW3, const __grid_constant__ CUtensorMap tmVec, TGemmArgs a,
     int *status)
 {
-    constexpr uint32_t IDESC = MakeInstrDesc(2, 1, 1, 0, 0, GEMM_M, GEMM_N); // s32 accumulators, s8 x s8, both K-major
+    static_assert(KS == 1 || NS == 1, "split the inner dimension or the sequences, not both");
+    constexpr int NT = GEMM_N / NS;                                       // accumulator columns (sequences) of this CTA's MMA
+    constexpr int TMEM_COLS = NT < 32 ? 32 : NT;
+    constexpr uint32_t STAGE_TX = (GEMM_M + NT) * GEMM_KB;                // bytes a stage receives
+    constexpr uint32_t IDESC = MakeInstrDesc(2, 1, 1, 0, 0, GEMM_M, NT); // s32 accumulators, s8 x s8, both K-major
     extern __shared__ uint8_t gemmSmemRaw[];
     const int job = blockIdx.y;
     const int rows = job == 0 ? a.Rows[0] : job == 1 ? a.Rows[1] : job == 2 ? a.Rows[2] : a.Rows[3];
     float *out = job == 0 ? a.Out[0] : job == 1 ? a.Out[1] : job == 2 ? a.Out[2] : a.Out[3];
     const CUtensorMap *tmW = job == 0 ? &tmW0 : job == 1 ? &tmW1 : job == 2 ? &tmW2 : &tmW3;
-    constexpr int kSplit = KS;                 // CTAs of the cluster that share this row tile
-    constexpr int CPR = GEMM_N / KS;           // sequences (accumulator columns) a CTA finishes
+    constexpr int kSplit = KS * NS;            // CTAs that share this row tile
+    constexpr int CPR = GEMM_N / kSplit;       // sequences (accumulator columns) a CTA finishes
     const int kRank = blockIdx.x % kSplit;
     const int rowBase = (blockIdx.x / kSplit) * GEMM_M;
     if (rowBase >= rows) {
@@ -249,7 +256,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
         FenceBarrierInit();
     }
     if (warp == 0) {
-        TmemAlloc(&misc.TmemBase, GEMM_N);
+        TmemAlloc(&misc.TmemBase, TMEM_COLS);
         TmemRelinquish();
     }
     TcFenceBefore();
@@ -263,16 +270,16 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
         auto load = [&](int chunk) {
             const int s = chunk % GEMM_STAGES;
             uint8_t *sA = smem + s * GEMM_STAGE_BYTES, *sB = sA + GEMM_M * GEMM_KB;
-            MbarExpectTx(&misc.Full[s], GEMM_STAGE_BYTES);
-            const int col = (kRank * (a.Chunks / kSplit) + chunk) * GEMM_KB;
+            MbarExpectTx(&misc.Full[s], STAGE_TX);
+            const int col = ((KS > 1 ? kRank * (a.Chunks / KS) : 0) + chunk) * GEMM_KB;
             TmaLoad2D(sA, tmW, col, rowBase, &misc.Full[s]);
-            TmaLoad2D(sB, &tmVec, col, 0, &misc.Full[s]);
+            TmaLoad2D(sB, &tmVec, col, NS > 1 ? kRank * NT : 0, &misc.Full[s]);
         };
         // GEMM_AHEAD chunks are in flight; the stage a new load overwrites was read by the MMAs of two iterations ago,
         // whose completion has long arrived (waiting for the previous iteration's would stall every step on the
         // commit round trip)
         constexpr int GEMM_AHEAD = GEMM_STAGES - 2;
-        const int chunks = a.Chunks / kSplit;
+        const int chunks = a.Chunks / KS;
         for (int c = 0; c < GEMM_AHEAD && c < chunks; ++c) {
             load(c);
         }
@@ -325,11 +332,17 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
     float *normTile = reinterpret_cast<float *>(smem);            // [GEMM_N][GEMM_M + 1]
     float *normMult = normTile + GEMM_N * (GEMM_M + 1);           // [GEMM_N]
     const bool withNorm = a.NormOut != nullptr;
-    uint32_t accum[GEMM_N];
+    uint32_t accum[NT];
     {
         const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
-        TmemLd32(tLane, accum);
-        TmemLd32(tLane + 32, accum + 32);
+        if (NT == 16) {
+            TmemLd16(tLane, accum);
+        } else {
+            TmemLd32(tLane, accum);
+            if (NT == 64) {
+                TmemLd32(tLane + 32, accum + (NT == 64 ? 32 : 0));
+            }
+        }
         TmemWaitLd();
     }
     // Reduce-scatter over the cluster: every CTA parks its int32 tile in its own shared memory, then finishes CPR of the
@@ -410,7 +423,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
     TcFenceBefore();
     __syncthreads();
     if (warp == 0) {
-        TmemDealloc(tmem, GEMM_N);
+        TmemDealloc(tmem, TMEM_COLS);
     }
 }
 
@@ -499,8 +512,14 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
         a.Rows[j] = job.Rows;
         maxRows = job.Rows > maxRows ? job.Rows : maxRows;
     }
+    const int rowTiles = (maxRows + GEMM_M - 1) / GEMM_M;
+    const int chunkCount = cols / GEMM_KB;
+    // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix; a narrow matrix
+    // with few row tiles spreads the sequences over 2 or 4 CTAs per row tile instead
+    const int kSplit = (chunkCount >= 24 && chunkCount % 4 == 0) ? 4 : (chunkCount >= 12 && chunkCount % 2 == 0) ? 2 : 1;
+    const int nSplit = (kSplit > 1 || rowTiles * jobCount > 48 || nSeq <= 16) ? 1 : (nSeq <= 32 ? 2 : 4);
     tsa_ptr2d v = {(void *)vec, cols, cols, nSeq};
-    int rc = MakeTileMapEx(&mv, v, 1, GEMM_KB, GEMM_N, "inference vectors");
+    int rc = MakeTileMapEx(&mv, v, 1, GEMM_KB, GEMM_N / nSplit, "inference vectors");
     if (rc != TSA_OK) {
         return rc;
     }
@@ -510,16 +529,18 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     a.Scale = scale;
     a.NormOut = normOut;
     a.NormRelu = normRelu ? 1 : 0;
-    // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix
-    a.KSplit = (a.Chunks >= 24 && a.Chunks % 4 == 0) ? 4 : (a.Chunks >= 12 && a.Chunks % 2 == 0) ? 2 : 1;
+    a.KSplit = kSplit;
     const void *kern = nullptr;
-    if (a.KSplit == 4) {
-        kern = add ? (const void *)InferGemmI8Kernel<true, 4> : (const void *)InferGemmI8Kernel<false, 4>;
-    } else if (a.KSplit == 2) {
-        kern = add ? (const void *)InferGemmI8Kernel<true, 2> : (const void *)InferGemmI8Kernel<false, 2>;
-    } else {
-        kern = add ? (const void *)InferGemmI8Kernel<true, 1> : (const void *)InferGemmI8Kernel<false, 1>;
+#define TSA_GEMM_CASE(KS, NS)                                                                                              \
+    if (kSplit == KS && nSplit == NS) {                                                                                    \
+        kern = add ? (const void *)InferGemmI8Kernel<true, KS, NS> : (const void *)InferGemmI8Kernel<false, KS, NS>;       \
     }
+    TSA_GEMM_CASE(1, 1)
+    TSA_GEMM_CASE(2, 1)
+    TSA_GEMM_CASE(4, 1)
+    TSA_GEMM_CASE(1, 2)
+    TSA_GEMM_CASE(1, 4)
+#undef TSA_GEMM_CASE
     rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {
         return rc;
@@ -530,7 +551,7 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3((maxRows + GEMM_M - 1) / GEMM_M * a.KSplit, jobCount);
+    lc.gridDim = dim3(rowTiles * kSplit * nSplit, jobCount);
     lc.blockDim = dim3(128);
     lc.dynamicSmemBytes = GEMM_SMEM_BYTES;
     lc.stream = stream;
