@@ -220,13 +220,12 @@ struct TGemmArgs {
 
 // KS > 1: the matrix columns (the inner dimension) are split over a cluster of KS CTAs (wide matrices).
 // NS > 1: the sequences are split over NS independent CTAs, each with its own MMA of GEMM_N / NS accumulator columns
-// (narrow matrices with few row tiles: more CTAs, and each runs a quarter of the epilogue).  Never both.
+// (matrices with few row tiles: more CTAs, and each runs a share of the epilogue).
 template <bool ADD, int KS, int NS>
 __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
     const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmW3, const __grid_constant__ CUtensorMap tmVec, TGemmArgs a,
     int *status)
 {
-    static_assert(KS == 1 || NS == 1, "split the inner dimension or the sequences, not both");
     constexpr int NT = GEMM_N / NS;                                       // accumulator columns (sequences) of this CTA's MMA
     constexpr int TMEM_COLS = NT < 32 ? 32 : NT;
     constexpr uint32_t STAGE_TX = (GEMM_M + NT) * GEMM_KB;                // bytes a stage receives
@@ -238,7 +237,8 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
     const CUtensorMap *tmW = job == 0 ? &tmW0 : job == 1 ? &tmW1 : job == 2 ? &tmW2 : &tmW3;
     constexpr int kSplit = KS * NS;            // CTAs that share this row tile
     constexpr int CPR = GEMM_N / kSplit;       // sequences (accumulator columns) a CTA finishes
-    const int kRank = blockIdx.x % kSplit;
+    const int kRank = blockIdx.x % KS;         // rank in the cluster (share of the inner dimension)
+    const int nRank = (blockIdx.x / KS) % NS;  // share of the sequences
     const int rowBase = (blockIdx.x / kSplit) * GEMM_M;
     if (rowBase >= rows) {
         return; // the grid is sized for the tallest matrix of the launch; a cluster leaves as a whole
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
             MbarExpectTx(&misc.Full[s], STAGE_TX);
             const int col = ((KS > 1 ? kRank * (a.Chunks / KS) : 0) + chunk) * GEMM_KB;
             TmaLoad2D(sA, tmW, col, rowBase, &misc.Full[s]);
-            TmaLoad2D(sB, &tmVec, col, NS > 1 ? kRank * NT : 0, &misc.Full[s]);
+            TmaLoad2D(sB, &tmVec, col, nRank * NT, &misc.Full[s]);
         };
         // GEMM_AHEAD chunks are in flight; the stage a new load overwrites was read by the MMAs of two iterations ago,
         // whose completion has long arrived (waiting for the previous iteration's would stall every step on the
@@ -353,9 +353,9 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
         // both cluster barriers are passed by every CTA whatever happened before, so that none waits alone
         namespace cg = cooperative_groups;
         cg::cluster_group cluster = cg::this_cluster();
-        int *part = reinterpret_cast<int *>(smem); // [GEMM_N][GEMM_M], the ring is idle by now
+        int *part = reinterpret_cast<int *>(smem); // [NT][GEMM_M], the ring is idle by now
 #pragma unroll
-        for (int cc = 0; cc < GEMM_N; ++cc) {
+        for (int cc = 0; cc < NT; ++cc) {
             part[cc * GEMM_M + tid] = (int)accum[cc];
         }
         cluster.sync();
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
         }
         cluster.sync(); // every CTA's shared memory has been read: it may be reused and the CTA may leave
     }
-    const int colBase = kRank * CPR;
+    const int colBase = nRank * NT + kRank * CPR;
     if (!failed) {
         constexpr int BLK = CPR < 32 ? CPR : 32;
 #pragma unroll
@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
 #pragma unroll
                 for (int cc = 0; cc < BLK; ++cc) {
                     if (colBase + c0 + cc < a.NSeq) {
-                        const float v = (float)(KS > 1 ? sum[(c0 + cc) % (KS > 1 ? CPR : 1)] : (int)accum[c0 + cc]);
+                        const float v = (float)(KS > 1 ? sum[(c0 + cc) % (KS > 1 ? CPR : 1)] : (int)accum[(c0 + cc) % NT]);
                         const float res = ADD ? __fadd_rn(old[cc], __fmul_rn(v, a.Scale)) : v;
                         if (ADD || !withNorm) { // a product that is only normalised does not need its fp32 form in memory
                             o[(size_t)cc * a.OutStride] = res;
@@ -517,7 +517,10 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     // about six 128-column chunks per CTA: a cluster of 2 or 4 CTAs shares a row tile of a wide matrix; a narrow matrix
     // with few row tiles spreads the sequences over 2 or 4 CTAs per row tile instead
     const int kSplit = (chunkCount >= 24 && chunkCount % 4 == 0) ? 4 : (chunkCount >= 12 && chunkCount % 2 == 0) ? 2 : 1;
-    const int nSplit = (kSplit > 1 || rowTiles * jobCount > 48 || nSeq <= 16) ? 1 : (nSeq <= 32 ? 2 : 4);
+    int nSplit = (rowTiles * jobCount * kSplit > 48 || nSeq <= 16) ? 1 : (nSeq <= 32 ? 2 : 4);
+    if (kSplit * nSplit > 4) {
+        nSplit = 4 / kSplit; // a CTA finishes at least 16 sequences
+    }
     tsa_ptr2d v = {(void *)vec, cols, cols, nSeq};
     int rc = MakeTileMapEx(&mv, v, 1, GEMM_KB, GEMM_N / nSplit, "inference vectors");
     if (rc != TSA_OK) {
@@ -540,6 +543,7 @@ static int LaunchGemv(bool add, const TGemvJob *jobs, int jobCount, const int8_t
     TSA_GEMM_CASE(4, 1)
     TSA_GEMM_CASE(1, 2)
     TSA_GEMM_CASE(1, 4)
+    TSA_GEMM_CASE(2, 2)
 #undef TSA_GEMM_CASE
     rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {
