@@ -237,14 +237,28 @@ __device__ __forceinline__ int Dp2aHiUS(uint32_t a, uint32_t b, int c)
 
 // One CTA = one chunk slot of the balanced plan, four warps, all heads.  Each lane keeps DEC_UNROLL tokens of K and
 // V (16 bytes each) in flight; four such CTAs are resident per SM.
-template <int D, int DEC_UNROLL, bool SCALE_F16>
+// FINAL: every sequence attends so few keys (a short window or short contexts, decided on the host from its bound) that
+// one CTA takes a whole sequence: no plan, no partials and no merge kernel -- the CTA adds the sink and writes the
+// result (and the inference step's combiner input) itself.
+template <int D, int DEC_UNROLL, bool SCALE_F16, bool FINAL>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecodeParams p)
 {
     constexpr int LPH = D / 16;       // lanes per head
     constexpr int HPW = 32 / LPH;     // heads per warp-wide load
-    const int chunk = blockIdx.x;     // chunk slot
+    const int chunk = blockIdx.x;     // chunk slot (FINAL: the sequence)
     int seq, cBeg, cEnd;
-    if (!DecodePlan(p, chunk, &seq, &cBeg, &cEnd)) {
+    if (FINAL) {
+        seq = blockIdx.x;
+        const int len = CtxLenOf(p, seq);
+        if (len > p.MaxCtx && threadIdx.x == 0 && p.Status) {
+            atomicOr(p.Status, kDevBadSpan); // the launch was sized for shorter sequences
+        }
+        if (len > 0) {
+            KeyRange(len, p.Window, &cBeg, &cEnd);
+        } else {
+            cBeg = cEnd = 0; // no token yet: zeros
+        }
+    } else if (!DecodePlan(p, chunk, &seq, &cBeg, &cEnd)) {
         return;
     }
     const int ctxLen = CtxLenOf(p, seq);
@@ -389,7 +403,34 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 4) DecodePartialKernel(TDecode
                 }
             }
         }
-        if (headOk && tokenPart == 0) {
+        if (FINAL) {
+            if (headOk && tokenPart == 0) {
+                // the sink has logit 0 (softMax.Add(0), cpu_infer.cpp:444); same arithmetic as the merge kernel with one chunk
+                const float mAll = fmaxf(m, 0.0f);
+                const float f = exp2f(m - mAll);
+                const float lAll = exp2f(-mAll) + f * l;
+                const size_t rowSize = (size_t)H * D;
+                int4 keyWords = make_int4(0, 0, 0, 0);
+                if (p.KvOut) {
+                    keyWords = *reinterpret_cast<const int4 *>(p.KvKey + seq * rowSize + head * D + sub * 16);
+                }
+                const int8_t *key = reinterpret_cast<const int8_t *>(&keyWords);
+                int8_t *kv = p.KvOut ? p.KvOut + (seq * rowSize + head * D) * 4 : nullptr;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float res = ctxLen > 0 ? (f * acc[i]) / lAll : 0.0f;
+                    const int x = sub * 16 + i;
+                    StoreFromFloat(p.Out.Row(seq), head * D + x, p.OutDtype, res);
+                    if (kv) {
+#pragma unroll
+                        for (int blk = 0; blk < 4; ++blk) {
+                            // ConvertToInt8 (cpu_infer.cpp:88-92): round to nearest even, clamp to +-127
+                            kv[blk * D + x] = (int8_t)max(-127, min(127, __float2int_rn(__fmul_rn((float)key[i ^ blk], res))));
+                        }
+                    }
+                }
+            }
+        } else if (headOk && tokenPart == 0) {
             float *dst = p.Partial + ((size_t)chunk * H + head) * (D + 4);
             if (sub == 0) {
                 dst[D] = m;
@@ -469,6 +510,7 @@ __global__ void KvAppendKernel(const tsa_kv_seq *seqs, int *ctxLens, int nSeq, i
     }
 }
 
+constexpr int DEC_SINGLE_KEYS = 16;       // up to this many keys per sequence (one batch per warp) one CTA takes the whole sequence; with 64 keys four CTAs and the merge kernel are faster (0.80 against 0.81 ms per inference step)
 constexpr int DEC_MAX_TARGET_CTAS = 1024; // workspace is sized for this many chunk slots plus one per sequence
 
 static size_t DecodeHeaderBytes(int nSeq)
@@ -497,11 +539,16 @@ int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStr
         return rc;
     }
     const bool f16 = cfg->scale_dtype == TSA_F16;
+    // at most DEC_SINGLE_KEYS keys per sequence: one CTA per sequence finishes it, no merge kernel
+    const long long keysBound = p.Window > 0 ? (p.Window < maxCtx ? p.Window : maxCtx) : 1;
+    const bool single = keysBound <= DEC_SINGLE_KEYS;
     const void *kern = nullptr;
     if (cfg->head_dim == 128) {
-        kern = f16 ? (const void *)DecodePartialKernel<128, 8, true> : (const void *)DecodePartialKernel<128, 8, false>;
+        kern = single ? (f16 ? (const void *)DecodePartialKernel<128, 8, true, true> : (const void *)DecodePartialKernel<128, 8, false, true>)
+                      : (f16 ? (const void *)DecodePartialKernel<128, 8, true, false> : (const void *)DecodePartialKernel<128, 8, false, false>);
     } else {
-        kern = f16 ? (const void *)DecodePartialKernel<64, 8, true> : (const void *)DecodePartialKernel<64, 8, false>;
+        kern = single ? (f16 ? (const void *)DecodePartialKernel<64, 8, true, true> : (const void *)DecodePartialKernel<64, 8, false, true>)
+                      : (f16 ? (const void *)DecodePartialKernel<64, 8, true, false> : (const void *)DecodePartialKernel<64, 8, false, false>);
     }
     // one full wave of equal chunks: as many chunk slots as CTAs are resident at once
     int perSm = 0;
@@ -518,11 +565,11 @@ int LaunchDecode(const tsa_decode_cfg *cfg, TDecodeParams p, int maxCtx, cudaStr
     // chunks hold at least DEC_MIN_CHUNK keys, so short windows or contexts need fewer CTAs than the full wave
     const long long keysMax = p.Window > 0 ? (p.Window < maxCtx ? p.Window : maxCtx) : 1;
     const long long slotBound = (long long)p.NSeq * (keysMax / DEC_MIN_CHUNK + 1);
-    dim3 grid((unsigned)(slotBound < p.MaxSlots ? slotBound : p.MaxSlots));
+    dim3 grid(single ? (unsigned)p.NSeq : (unsigned)(slotBound < p.MaxSlots ? slotBound : p.MaxSlots));
     dim3 gridC(p.HeadCount, p.NSeq);
     void *args[] = {&p};
     rc = CheckCuda(cudaLaunchKernel(kern, grid, dim3(DEC_WARPS * 32), args, 0, stream), "decode launch");
-    if (rc != TSA_OK) {
+    if (rc != TSA_OK || single) {
         return rc;
     }
     if (cfg->head_dim == 128) {
