@@ -10,7 +10,8 @@
 //
 // One CTA = 128 rows of x times 256 output columns (4 heads of 64 or 2 of 128): tcgen05.mma kind::i8, M = 128, N = 256,
 // exact int32 accumulators in 256 tensor-memory columns; thread 0 streams both operands through a TMA ring of 64-column
-// chunks and issues the MMAs.  In the epilogue thread t owns row t, so a head's sum of squares, the rotation partners
+// chunks and issues the MMAs.  In the epilogue a row belongs to two threads (256 per CTA), each with half of the tile's
+// heads, so a head's sum of squares, the rotation partners
 // and the 64 output bytes of a block are all in one thread: no exchange between threads, sums in the scalar loop's
 // order (bit-identical to the stand-alone normalise + rope + quantise of the CPU code on the same projection).
 #include "att_sm100_common.cuh"
@@ -55,7 +56,7 @@ struct TProjArgs {
 // X_E4M3: both operands are e4m3 bytes (MulForwardFp8, gpt_cuda.cu:488-491), products accumulate in f32 on the tensor
 // cores (kind::f8f6f4); otherwise int8 x int8 with exact int32 accumulators (kind::i8).
 template <int D, bool DST_E4M3, bool X_E4M3>
-__global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, TProjArgs a, int *status)
+__global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, TProjArgs a, int *status)
 {
     // s32 accumulators, s8 x s8 -- or f32 accumulators, e4m3 x e4m3; both operands K-major
     constexpr uint32_t IDESC = X_E4M3 ? MakeInstrDesc(1, 0, 0, 0, 0, PROJ_M, PROJ_N) : MakeInstrDesc(2, 1, 1, 0, 0, PROJ_M, PROJ_N);
@@ -147,14 +148,15 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
 
     // every thread of a warp takes part in the tensor-memory loads (they are warp-wide instructions): rows past the
     // buffer only skip their global loads and stores
-    const int t = rowBase + tid;
+    const int rowInTile = tid & (PROJ_M - 1), colHalf = tid >> 7; // two threads per row: each takes half of the tile's heads
+    const int t = rowBase + rowInTile;
     const bool inBuf = t < a.Rows;
     // the tile's rows of the rope table through shared memory (the ring is idle now): coalesced loads, and a row pitch
     // of D + 1 words lets every thread walk its own row without bank conflicts
     float *ropeTile = reinterpret_cast<float *>(smem);
     const bool withRope = a.Rope.Valid();
     if (!failed && withRope) {
-        for (int idx = tid; idx < PROJ_M * (D / 4); idx += 128) {
+        for (int idx = tid; idx < PROJ_M * (D / 4); idx += 256) {
             const int row = idx / (D / 4), c4 = idx - row * (D / 4);
             float4 v = make_float4(0, 0, 0, 0);
             if (rowBase + row < a.Len) {
@@ -166,10 +168,10 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
         __syncthreads();
     }
     if (!failed) {
-        const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const bool live = t < a.Len;
 #pragma unroll 1
-        for (int hh = 0; hh < HPC; ++hh) {
+        for (int hh = colHalf * (HPC / 2); hh < (colHalf + 1) * (HPC / 2); ++hh) {
             const int head = blockIdx.y * HPC + hh;
             if (head >= a.HeadCount) {
                 break;
@@ -209,8 +211,8 @@ __global__ void __launch_bounds__(128, 2) ProjNormRopeKernel(const __grid_consta
                         float y0 = __fmul_rn(__fmul_rn(accValue(lo[k]), a.SrcScale), mult);
                         float y1 = __fmul_rn(__fmul_rn(accValue(hi[k]), a.SrcScale), mult);
                         if (withRope && live) {
-                            const float cs = ropeTile[tid * (D + 1) + blk + k];
-                            const float sn = __fmul_rn(ropeTile[tid * (D + 1) + blk + k + 32], a.RopeDir);
+                            const float cs = ropeTile[rowInTile * (D + 1) + blk + k];
+                            const float sn = __fmul_rn(ropeTile[rowInTile * (D + 1) + blk + k + 32], a.RopeDir);
                             const float r0 = __fsub_rn(__fmul_rn(y0, cs), __fmul_rn(y1, sn));
                             const float r1 = __fadd_rn(__fmul_rn(y0, sn), __fmul_rn(y1, cs));
                             y0 = r0;
@@ -325,5 +327,5 @@ extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant
         return rc;
     }
     void *args[] = {&mx, &mw, &a, &statusWord};
-    return CheckCuda(cudaLaunchKernel(kern, grid, dim3(128), args, PROJ_SMEM_BYTES, (cudaStream_t)stream), "tsa_matmul_norm_rope_quant launch");
+    return CheckCuda(cudaLaunchKernel(kern, grid, dim3(256), args, PROJ_SMEM_BYTES, (cudaStream_t)stream), "tsa_matmul_norm_rope_quant launch");
 }
