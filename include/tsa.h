@@ -263,6 +263,7 @@ int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len,
  *   per head: discr = sqrt(sum y^2 / D) * vecScale; dst = quantise(rope(y / discr)); scale[head][t] = discr
  * i.e. tsa_norm_rope_quant applied to the projection without the projection ever going to memory.  rope: f32
  * [len][D] table or absent (the K and V projections are stored without rotation).  dst int8 or e4m3 [rows][H*D],
+ * or f16 / bf16 (dstDtype TSA_F16 / TSA_BF16: the normalised, rotated values unquantised, the reference's K16),
  * rows in [len, dst.ysize) are zeroed with scale 0; scale f32 [H][rows] may be absent.  D = 64 or 128. */
 int tsa_matmul_norm_rope_quant(int srcDtype, int dstDtype, float vecScale, float srcScale, tsa_ptr2d x, tsa_ptr2d w, tsa_ptr2d rope,
     float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, int *statusWord,

@@ -211,3 +211,26 @@ def test_block_chain_projection_attention_consumer():
     assert np.abs(util.to_np(kv) - want_kv).max() < util.OUT_MAX_ABS * vmax * scale
     # the consumer itself is exact on the attention output it was given
     assert np.array_equal(util.to_np(kv), O.kv_product(comb_key, util.to_np(out), heads))
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim,heads,d,with_rope", [(200, 256, 3, 64, False), (150, 384, 2, 128, True)])
+def test_matmul_norm_rope_16bit_output(dt, rows, dim, heads, d, with_rope):
+    """16-bit output of the fused projection (the reference's K16): the oracle's normalised, rotated fp32 values rounded to
+    the output type, bit for bit."""
+    from tscale_b200 import ops
+    rng = np.random.default_rng(rows + heads)
+    x = rng.integers(-127, 128, (rows, dim)).astype(np.int8)
+    w = rng.integers(-127, 128, (heads * d, dim)).astype(np.int8)
+    src_scale = np.float32(1.0 / 1024)
+    y = (x.astype(np.int32) @ w.T.astype(np.int32)).astype(np.float32) * src_scale
+    table = O.fill_rope(d, rows) if with_rope else None
+    _, want_s, roped = O.norm_rope_quant("i8", 0.5, y, table, d)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got, got_s = ops.matmul_norm_rope_quant(torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV),
+                                            None if table is None else torch.from_numpy(table).to(DEV), dt, heads, d,
+                                            vec_scale=0.5, src_scale=float(src_scale), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(got.cpu(), torch.from_numpy(roped).to(dt))
+    assert np.array_equal(got_s.cpu().numpy(), want_s)

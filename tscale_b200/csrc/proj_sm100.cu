@@ -55,7 +55,8 @@ struct TProjArgs {
 
 // X_E4M3: both operands are e4m3 bytes (MulForwardFp8, gpt_cuda.cu:488-491), products accumulate in f32 on the tensor
 // cores (kind::f8f6f4); otherwise int8 x int8 with exact int32 accumulators (kind::i8).
-template <int D, bool DST_E4M3, bool X_E4M3>
+// DST: TSA_I8, TSA_E4M3 (quantised) or TSA_F16 / TSA_BF16 (the normalised, rotated values themselves: the reference's K16).
+template <int D, int DST, bool X_E4M3>
 __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, TProjArgs a, int *status)
 {
     // s32 accumulators, s8 x s8 -- or f32 accumulators, e4m3 x e4m3; both operands K-major
@@ -194,7 +195,8 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                 discr = __fmul_rn(__fsqrt_rn(__fdiv_rn(sum2, (float)D)), a.VecScale);
             }
             const float mult = discr > 0 ? __fdiv_rn(1.0f, discr) : 0.0f;
-            uint8_t *dstRow = a.Dst.Row(inBuf ? t : 0) + head * D;
+            constexpr int ES = (DST == TSA_F16 || DST == TSA_BF16) ? 2 : 1; // bytes per output element
+            uint8_t *dstRow = a.Dst.Row(inBuf ? t : 0) + head * D * ES;
 #pragma unroll 1
             for (int blk = 0; blk < D; blk += 64) {
                 uint32_t lo[32], hi[32];
@@ -221,7 +223,24 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                         z0[i] = y0;
                         z1[i] = y1;
                     }
-                    if (DST_E4M3) {
+                    if (ES == 2) {
+                        uint2 w0, w1;
+                        if (DST == TSA_F16) {
+                            const __half2 a0 = __floats2half2_rn(z0[0], z0[1]), a1 = __floats2half2_rn(z0[2], z0[3]);
+                            const __half2 b0 = __floats2half2_rn(z1[0], z1[1]), b1 = __floats2half2_rn(z1[2], z1[3]);
+                            w0 = make_uint2(*reinterpret_cast<const uint32_t *>(&a0), *reinterpret_cast<const uint32_t *>(&a1));
+                            w1 = make_uint2(*reinterpret_cast<const uint32_t *>(&b0), *reinterpret_cast<const uint32_t *>(&b1));
+                        } else {
+                            const __nv_bfloat162 a0 = __floats2bfloat162_rn(z0[0], z0[1]), a1 = __floats2bfloat162_rn(z0[2], z0[3]);
+                            const __nv_bfloat162 b0 = __floats2bfloat162_rn(z1[0], z1[1]), b1 = __floats2bfloat162_rn(z1[2], z1[3]);
+                            w0 = make_uint2(*reinterpret_cast<const uint32_t *>(&a0), *reinterpret_cast<const uint32_t *>(&a1));
+                            w1 = make_uint2(*reinterpret_cast<const uint32_t *>(&b0), *reinterpret_cast<const uint32_t *>(&b1));
+                        }
+                        if (inBuf) {
+                            *reinterpret_cast<uint2 *>(dstRow + (blk + q * 4) * 2) = w0;
+                            *reinterpret_cast<uint2 *>(dstRow + (blk + 32 + q * 4) * 2) = w1;
+                        }
+                    } else if (DST == TSA_E4M3) {
                         outLo[q] = PackE4M3x4(z0[0], z0[1], z0[2], z0[3]);
                         outHi[q] = PackE4M3x4(z1[0], z1[1], z1[2], z1[3]);
                     } else {
@@ -234,7 +253,7 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                         }
                     }
                 }
-                if (inBuf) {
+                if (inBuf && ES == 1) {
                     uint4 *d4 = reinterpret_cast<uint4 *>(dstRow + blk);
                     d4[0] = make_uint4(outLo[0], outLo[1], outLo[2], outLo[3]);
                     d4[1] = make_uint4(outLo[4], outLo[5], outLo[6], outLo[7]);
@@ -262,7 +281,8 @@ extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant
     tsa_ptr2d rope, float ropeDir, tsa_ptr2d dst, tsa_ptr2d scale, int headCount, int headDim, int len, int *statusWord, tsa_stream_t stream)
 {
     TSA_REQUIRE(srcDtype == TSA_I8 || srcDtype == TSA_E4M3, "tsa_matmul_norm_rope_quant: x and w must both be i8 or both e4m3");
-    TSA_REQUIRE(dstDtype == TSA_I8 || dstDtype == TSA_E4M3, "tsa_matmul_norm_rope_quant: dst dtype must be i8 or e4m3");
+    TSA_REQUIRE(dstDtype == TSA_I8 || dstDtype == TSA_E4M3 || dstDtype == TSA_F16 || dstDtype == TSA_BF16,
+        "tsa_matmul_norm_rope_quant: dst dtype must be i8, e4m3, f16 or bf16");
     TSA_REQUIRE(x.data && w.data && dst.data, "tsa_matmul_norm_rope_quant: null x / w / dst");
     TSA_REQUIRE(headCount > 0 && (headDim == 64 || headDim == 128), "tsa_matmul_norm_rope_quant: head size %d must be 64 or 128", headDim);
     const int dim = x.xsize, outCols = headCount * headDim;
@@ -307,20 +327,18 @@ extern "C" __attribute__((visibility("default"))) int tsa_matmul_norm_rope_quant
     a.HeadCount = headCount;
     a.Chunks = dim / PROJ_KB;
     dim3 grid((dst.ysize + PROJ_M - 1) / PROJ_M, (outCols + PROJ_N - 1) / PROJ_N);
-    const bool e4 = dstDtype == TSA_E4M3, x8 = srcDtype == TSA_E4M3;
+    const bool x8 = srcDtype == TSA_E4M3;
     const void *kern = nullptr;
-#define TSA_PROJ_CASE(DD, E4, X8)                                       \
-    if (headDim == DD && e4 == E4 && x8 == X8) {                        \
-        kern = (const void *)ProjNormRopeKernel<DD, E4, X8>;            \
+#define TSA_PROJ_CASE(DD, DT, X8)                                       \
+    if (headDim == DD && dstDtype == DT && x8 == X8) {                  \
+        kern = (const void *)ProjNormRopeKernel<DD, DT, X8>;            \
     }
-    TSA_PROJ_CASE(64, false, false)
-    TSA_PROJ_CASE(64, true, false)
-    TSA_PROJ_CASE(64, false, true)
-    TSA_PROJ_CASE(64, true, true)
-    TSA_PROJ_CASE(128, false, false)
-    TSA_PROJ_CASE(128, true, false)
-    TSA_PROJ_CASE(128, false, true)
-    TSA_PROJ_CASE(128, true, true)
+#define TSA_PROJ_CASES(DD, X8) TSA_PROJ_CASE(DD, TSA_I8, X8) TSA_PROJ_CASE(DD, TSA_E4M3, X8) TSA_PROJ_CASE(DD, TSA_F16, X8) TSA_PROJ_CASE(DD, TSA_BF16, X8)
+    TSA_PROJ_CASES(64, false)
+    TSA_PROJ_CASES(64, true)
+    TSA_PROJ_CASES(128, false)
+    TSA_PROJ_CASES(128, true)
+#undef TSA_PROJ_CASES
 #undef TSA_PROJ_CASE
     rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM_BYTES), "cudaFuncSetAttribute");
     if (rc != TSA_OK) {

@@ -151,10 +151,11 @@ def norm_rope_quant(src, rope, dst, heads, head_dim, vec_scale=1.0, direction=1.
 
 def matmul_norm_rope_quant(x, w, rope, dst, heads, head_dim, vec_scale=1.0, src_scale=1.0, direction=1.0, length=None, status=None, src="i8"):
     """The projection x @ w^T fused with norm_rope_quant: x [rows][dim], w [H*D][dim] both int8 (exact int32 products) or both
-    e4m3 bytes (src="e4m3", f32 accumulation), rope f32 [rows][D] or None.  Returns (bytes uint8 [rows][H*D], scale f32 [H][rows])."""
+    e4m3 bytes (src="e4m3", f32 accumulation), rope f32 [rows][D] or None; dst "i8" / "e4m3" (quantised bytes) or torch.float16 /
+    torch.bfloat16 (the normalised, rotated values).  Returns (out [rows][H*D], scale f32 [H][rows])."""
     rows = x.shape[0]
     length = rows if length is None else length
-    out = torch.empty((rows, heads * head_dim), dtype=torch.uint8, device=x.device)
+    out = torch.empty((rows, heads * head_dim), dtype=torch.uint8 if isinstance(dst, str) else dst, device=x.device)
     scale = torch.empty((heads, rows), dtype=torch.float32, device=x.device)
     check(abi.lib().tsa_matmul_norm_rope_quant(_DT[src], _DT[dst], vec_scale, src_scale, p2d(x), p2d(w), p2d(rope), direction, p2d(out), p2d(scale),
                                                heads, head_dim, length, _ptr(status), _stream()))
