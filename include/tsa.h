@@ -100,6 +100,8 @@ int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
     const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
     tsa_ptr2d out, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+/* workspace: tsa_att_fwd_workspace_bytes(...) bytes of 16-byte aligned device memory (per-head maxima of the vScale
+ * plane and the work-item counter of the persistent kernel); the call clears what it uses. */
 size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len);
 
 /* ---- backward --------------------------------------------------------------------------------
@@ -132,6 +134,14 @@ int tsa_calc_dscale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, 
  * for the exactness of the integer QK^T accumulators (s8 -> s32 tiles of gpt_att_fp16.cuh:76-101). */
 int tsa_qk_scores_i32(tsa_ptr2d qk, tsa_ptr2d qv, int headCount, int headDim, int lenQ, int lenK,
     int32_t *scores, int *statusWord, tsa_stream_t stream);
+
+/* Parity hook of the int8 forward itself: the next tsa_att_fwd calls with qk_dtype TSA_I8 on the tensor-core path
+ * also store, for query tile `queryTile` (128 rows) of head `head`, the raw s32 accumulators of its `keyTile`-th
+ * key tile exactly as the softmax threads read them from tensor memory, into dst (device memory, int32 [128][128],
+ * row = query row inside the tile).  dst == NULL switches the dump off.  Process-wide setting, meant for tests; it
+ * checks the bit-exactness of the s8 x s8 -> s32 products (gpt_att_fp16.cuh:76-101) inside the forward's own pipeline
+ * (ring slots, barrier phases) rather than in tsa_qk_scores_i32's separate kernel. */
+int tsa_att_fwd_set_score_dump(int32_t *dst, int head, int queryTile, int keyTile);
 
 /* ---- per-row quantisers ----------------------------------------------------------------------
  * Replaces NormalizeVecsRowTile / NormalizeVecsRowTileMax (code/gpt/compute/row_tile_scale.cuh:11-34,

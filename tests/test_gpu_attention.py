@@ -243,3 +243,29 @@ def test_int8_scores_bit_exact(d):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert np.array_equal(got.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_fwd_int8_accumulators_bit_exact_inside_forward(d):
+    """The s32 tile the forward itself read from tensor memory (a key tile late enough that the K/V ring has wrapped
+    and every barrier has changed phase), against the integer oracle."""
+    import ctypes
+    from tscale_b200 import abi, ops
+    heads, seq = 2, 1024
+    g, (qd, kd, vd) = _setup(11, [seq], heads, d, "i8", "e4m3", 0.5)
+    mask = ops.Mask.window([seq], 0)
+    cfg = ops.make_cfg("i8", "e4m3", d, d, out_dtype=torch.float32)
+    head, q_tile, k_tile = 1, 7, 5
+    dump = torch.full((128, 128), -7, dtype=torch.int32, device=_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    abi.check(abi.lib().tsa_att_fwd_set_score_dump(ctypes.c_void_p(dump.data_ptr()), head, q_tile, k_tile))
+    try:
+        ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, 0.0, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status)
+        torch.cuda.synchronize()
+    finally:
+        abi.check(abi.lib().tsa_att_fwd_set_score_dump(None, 0, 0, 0))
+    assert int(status.item()) == 0
+    q8 = g["q8"].cpu().numpy().view(np.int8)[q_tile * 128:(q_tile + 1) * 128]
+    k8 = g["k8"].cpu().numpy().view(np.int8)[k_tile * 128:(k_tile + 1) * 128]
+    ref = O.qk_int32(np.ascontiguousarray(q8), np.ascontiguousarray(k8), heads)[head]
+    assert np.array_equal(dump.cpu().numpy(), ref)

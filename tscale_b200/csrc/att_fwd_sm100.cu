@@ -1,29 +1,39 @@
-// Quantized attention forward for sm_100a: tcgen05 MMA with accumulators in tensor memory, TMA-staged
-// Q/K/V tiles, online base-2 softmax in registers.
+// Quantized attention forward for sm_100a: persistent, warp-specialised CTAs around tcgen05 MMA with accumulators in
+// tensor memory, a TMA loader warp that runs ahead across work items, and a one-thread-per-row base-2 softmax.
 //
 // Replaces Fp8Att (code/gpt/compute/gpt_att_fp8.cuh:43-248) and the int8 QK^T variant of Fp16Att
 // (gpt_att_fp16.cuh:121-318) of the reference:
 //   S = Q K^T          kind::f8f6f4 (e4m3 x e4m3 -> f32) or kind::i8 (s8 x s8 -> s32, exact), 128 x 128 x D
 //   z = S * sq_i * sk_j * c - slope * (i - j), masked by the row's span            (gpt_att_fp8.cuh:137-147)
-//   m = running floor(max) so that rescale factors are powers of two                 (gpt_att_fp8.cuh:163-164)
+//   m = integer-valued running reference of the row maximum, so that rescale factors are powers of two
+//                                                                                    (gpt_att_fp8.cuh:163-164)
 //   P = e4m3(2^(z - m) * 128 * sv_j / svRef); O += P V   kind::f8f6f4, A = P from tensor memory,
 //                                                         B = V tile as an MN-major operand (no transposed copy)
 //   out = O * (svRef / 128) / (2^-m + sum 2^(z - m));  sumWeightLog = m + log2(...)   (gpt_att_fp8.cuh:225-245)
-// On tiles where the span mask is active (the only tiles a row with few keys ever sees) P is split into
-// e4m3(P) + e4m3(P - e4m3(P)) and multiplied in two MMAs, which removes the 3-bit-mantissa rounding of the
-// weights where it is not averaged out over many keys.
 //
-// One CTA = one head x 128 query rows (two 64-row span blocks).  Eight softmax warps, two threads per row
-// (each owns 64 of the row's 128 score columns; a row is one tensor-memory lane), plus a control warp whose
-// lane 0 issues every TMA copy and every MMA.  Tensor memory: columns [0,128) S (f32 / s32); each half writes its
-// packed e4m3 weights (16 columns, plus 16 for the residual) back over its own S columns; columns [128, 128 + D)
-// hold O (f32).  256 columns are allocated so two CTAs share an SM and one CTA's softmax overlaps the other's
-// MMAs.  Shared memory: Q tile, STAGES x (K tile, V tile) filled by TMA with the 128 B (D = 128) or 64 B (D = 64)
-// swizzle the MMA descriptors expect.  Softmax arithmetic uses packed f32x2 multiply-adds and 3-input max.
-// Key tiles follow the reference's grouped spans: for round r the tiles [Start, Finish] of the two blocks'
-// r-th groups; 32-column chunks no row of a warp attends cost no exponentials (window layers).
-// Every barrier wait is bounded; when one runs out the kernel records a code in *statusWord, drains its
-// outstanding copies, frees its tensor memory and returns.
+// Work item = one head x 128 query rows (two 64-row span blocks).  A CTA takes items from a counter (late rows
+// first, as they are the long ones under a causal mask) until none is left; two CTAs share an SM (256 of the 512
+// tensor-memory columns each), so one CTA's softmax runs under the other's MMAs.
+//
+// Warp roles (192 threads):
+//   warps 0-3  softmax: thread t owns query row t of the item = tensor-memory lane t.  It reads the 128 scores of a
+//              key tile 16 columns at a time (the next chunk's tcgen05.ld is in flight while the current one is being
+//              worked on), scales them and exponentiates once against the reference m it already holds.  Only when
+//              a score exceeds m by more than the e4m3 headroom (weights up to 2^8.75 < 448) does the warp take the
+//              slow path: raise m and shrink O, the sum and the tile's weights written so far.
+//              Tiles the span mask cuts through add a second e4m3 residual term (P split into
+//              e4m3(P) + e4m3(P - e4m3(P)), two MMAs), which removes the 3-bit-mantissa rounding where it is not
+//              averaged out over many keys (rows with few keys see only such tiles).
+//   warp 4     lane 0 issues every MMA: S = Q K^T, then, once the softmax threads have written P over S, O += P V.
+//   warp 5     loader: reads the item's span groups and query scales, publishes one "round" record per span round
+//              in shared memory (per-row spans, tile range), and streams Q, K, V tiles (TMA) and the key / value scale
+//              rows (bulk copies) through shared-memory rings, up to a full ring ahead of the consumers and across
+//              item boundaries, so DRAM latency of short items (window layers) is hidden.
+// Tensor memory: columns [0,128) S (f32 / s32); the e4m3 weights of each 32-key block overwrite the first 8 (16 with
+// the residual) of the block's own 32 score columns;
+// columns [128, 128 + D) O (f32).
+// Every barrier wait is bounded; when one runs out the kernel records a code in *statusWord, all roles stop at their
+// next wait, outstanding copies are drained, tensor memory is freed and the kernel returns.
 #include "att_internal.cuh"
 #include "att_sm100_common.cuh"
 
@@ -31,33 +41,34 @@ namespace tsa {
 
 using namespace sm100;
 
-constexpr int SOFTMAX_THREADS = 256;
-constexpr int CTRL_WARP = SOFTMAX_THREADS / 32;
-constexpr int FWD_THREADS = SOFTMAX_THREADS + 32;
-constexpr int SCORE_THREADS = 128;
+constexpr int FW_SOFTMAX_THREADS = 128;
+constexpr int FW_MMA_WARP = 4;
+constexpr int FW_LOAD_WARP = 5;
+constexpr int FW_THREADS = 192;
 constexpr int TILE_M = 128;
 constexpr int TILE_N = 128;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O_COL = 128;
+constexpr int ROUND_SLOTS = 4;
+constexpr int Q_SLOTS = 2;
+// a weight is 2^t with t = z - m + 7; e4m3 holds up to 448 = 2^8.8, so t may reach 8.75 before m has to move
+constexpr float P_HEADROOM = 8.75f;
 
-// Phase trace for profiling builds (-DTSA_FWD_TRACE): thread 0 of a few CTAs records clock64() at the phases of
-// a CTA's life; tsa_debug_trace copies the buffer out.
-#ifdef TSA_FWD_TRACE
-__device__ long long g_trace[4096];
-#define TRC(e) do { if (traceOn) g_trace[traceSlot * 16 + (e)] = clock64(); } while (0)
-#else
-#define TRC(e) do { } while (0)
-#endif
+enum { RF_FIRST = 1, RF_LAST = 2, RF_END = 4 };
 
 struct TFwdParams {
     int HeadCount;
     int OutRows;      // rows of out that may be written
     int KeyRows;      // rows of K / V
     int LenAttTiles;  // number of 64-row span blocks
+    int QTiles;       // number of 128-row query tiles
+    int TotalItems;   // QTiles * HeadCount
+    int *Counter;     // work-item counter, zero at launch
     const tsa_span_group *Spans;
     const int *SpanPtr;
     P2D<float> QScale, KScale, VScale;
     const float *VRef; // per head max of VScale (workspace), null without VScale
+    int ScaleBulk;     // key / value scale rows may be fetched with 16-byte bulk copies
     P2D<char> Out;
     P2D<float> Lse;
     const float *GlobalScale;
@@ -66,38 +77,163 @@ struct TFwdParams {
     float Slope;
     int OutDtype;
     int *Status;
+    // parity hook: raw s32 scores of one tile as this kernel read them from tensor memory (null in production)
+    int32_t *DumpScores;
+    int DumpHead, DumpQTile, DumpTile;
+};
+
+// one span round of a work item, published by the loader
+struct TFwdRound {
+    int SpanS[TILE_M];   // inclusive key span of each row in this round, clipped to the key range (empty: 1, 0)
+    int SpanF[TILE_M];
+    float Sq[TILE_M];    // query scale of each row (0 for rows past the end)
+    int J0;              // first key tile of the round (multiple of 128)
+    int NTiles;
+    int Flags;           // RF_*
+    int QTile, Head, QSlot;
+    int FullLo, FullHi;  // key tiles inside [FullLo, FullHi] are attended in full by every row
+};
+
+struct TFwdAux {
+    float Sk[TILE_N];    // key scale of each column of the tile
+    float Sv[TILE_N];    // value scale times the head's power-of-two normaliser
+};
+
+struct TFwdMisc {
+    uint64_t QFull[Q_SLOTS], QEmpty[Q_SLOTS];
+    uint64_t KvFull[4], KvEmpty[4];
+    uint64_t RFull[ROUND_SLOTS], REmpty[ROUND_SLOTS];
+    // a key tile is handed back and forth in two halves of 64 keys, so that the MMAs of one half (O += P V, then the next
+    // tile's S = Q K^T into the columns just freed) run while the softmax threads work on the other half
+    uint64_t BarS[2];    // MMA -> softmax: this half of S is ready
+    uint64_t BarP[2];    // softmax -> MMA: this half of P is written, 128 arrivals
+    uint64_t BarOFull;   // MMA -> softmax: the item's last PV has retired, O is final (its own barrier: the S barrier
+                         // could otherwise run two phases ahead of the softmax threads across an item boundary)
+    uint32_t TmemBase;
+    int Abort;           // a bounded wait ran out somewhere in the CTA
+    float Al[TILE_N];    // ALiBi term slope * column
 };
 
 template <int D>
 struct TFwdSmem {
-    static constexpr int STAGES = (D == 64) ? 3 : 2;
+    static constexpr int STAGES = (D == 64) ? 4 : 2;
     static constexpr int TILE_BYTES = 128 * D;
     static constexpr int Q_OFF = 0;
-    static constexpr int K_OFF = TILE_BYTES;
+    static constexpr int K_OFF = Q_SLOTS * TILE_BYTES;
     static constexpr int V_OFF = K_OFF + STAGES * TILE_BYTES;
-    static constexpr int MISC_OFF = V_OFF + STAGES * TILE_BYTES;
-    static constexpr int TOTAL = MISC_OFF + 4096 + 1024; // misc + alignment slack
+    static constexpr int AUX_OFF = V_OFF + STAGES * TILE_BYTES;
+    static constexpr int ROUND_OFF = AUX_OFF + STAGES * (int)sizeof(TFwdAux);
+    static constexpr int MISC_OFF = ROUND_OFF + ROUND_SLOTS * (int)sizeof(TFwdRound);
+    static constexpr int TOTAL = MISC_OFF + (int)sizeof(TFwdMisc) + 1024; // + alignment slack
 };
 
-struct TFwdMisc {
-    float Sk[2][TILE_N];     // key scale of each column of the tile, double buffered by tile parity: fast warps
-    float Sv[2][TILE_N];     // stage the next tile's scales while slower warps still read the current ones
-    float Al[TILE_N];        // ALiBi term slope * column (tile invariant)
-    float RowX[2][TILE_M];   // exchange between the two threads of a row (tile max, final sum)
-    int TileMasked[2];       // softmax -> control warp: P has a residual part for this tile
-    int Abort;               // a bounded wait ran out somewhere in the CTA
-    uint64_t BarQ;
-    uint64_t BarFull[4];
-    uint64_t BarMma;         // control -> softmax: S(it) ready (and PV(it-1) retired)
-    uint64_t BarP;           // softmax -> control: P(it) written, 256 arrivals
-    uint32_t TmemBase;
-};
+// tcgen05.wait::ld that names the registers an earlier tcgen05.ld fills, so that no use of them moves above the wait
+__device__ __forceinline__ void TmemWaitLdRegs(uint32_t *r)
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
 
-// Thread layout: warps 0-7 are softmax warps, two threads per query row: thread (half, row) with half = tid / 128
-// owns columns [64 * half, 64 * half + 64) of the row's scores and columns [half * D/2, (half + 1) * D/2) of its
-// output.  Warp 8 is the control warp: lane 0 issues every TMA copy and every MMA.
+__device__ __forceinline__ void TmemWaitLdRegs16(uint32_t *r)
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
+
+// 2^x for a pair on the FMA / ALU pipes instead of the special-function unit: x = n + r with n = round(x),
+// |r| <= 0.5, 2^r by a cubic (relative error 7.5e-5, far below the e4m3 rounding of the weights), n added to the
+// exponent field.  x is clamped at -120 so the exponent cannot wrap; such weights are zero after the e4m3 pack.
+__device__ __forceinline__ float2 PolyExp2Pair(float2 x)
+{
+    const float kMagic = 12582912.0f; // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+    x.x = fmaxf(x.x, -120.0f);
+    x.y = fmaxf(x.y, -120.0f);
+    const float2 magic2 = make_float2(kMagic, kMagic);
+    float2 y = __fadd2_rn(x, magic2);
+    float2 r = __fadd2_rn(x, __fadd2_rn(make_float2(kMagic, kMagic), make_float2(-y.x, -y.y)));
+    float2 p = __ffma2_rn(r, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.242611125f, 0.242611125f));
+    p = __ffma2_rn(p, r, make_float2(0.693260968f, 0.693260968f));
+    p = __ffma2_rn(p, r, make_float2(0.999928057f, 0.999928057f));
+    // the low 9 bits of the magic constant's pattern are zero, so (bits(y) << 23) is round(x) << 23
+    return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(y.x) << 23)),
+        __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(y.y) << 23)));
+}
+
+// Slow path of the softmax: the row's reference moves up by d whole units, so what has been accumulated shrinks by
+// alpha = 2^-d: the O accumulator (D columns) and this tile's e4m3 weights that are already in tensor memory.  The
+// weights of the 32-key block b sit in columns [32b, 32b + 8) and their residuals in [32b + 8, 32b + 16);
+// quads [firstQuad, firstQuad + nQuads) are the 4-column (16-key) groups written and not yet handed to the MMA.  All lanes of the warp execute the
+// tensor-memory accesses; a lane whose row needs no change passes alpha = 1.  Kept out of line and in small pieces:
+// it is rare, and inlined it costs the common path registers.
+template <int D>
+__device__ __noinline__ void ShrinkAccumulated(uint32_t tLane, float alpha, int hasO, int firstQuad, int nQuads, int withResidual)
+{
+    TmemWaitSt(); // the weights stored so far have landed
+    if (hasO) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 8) {
+            uint32_t o[8];
+            TmemLd8(tLane + TMEM_O_COL + c0, o);
+            TmemWaitLd();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            }
+            TmemStN<8>(tLane + TMEM_O_COL + c0, o);
+        }
+    }
+    const __half2 ah = __float2half2_rn(alpha);
+    const uint32_t ah2 = *reinterpret_cast<const uint32_t *>(&ah);
+#pragma unroll 1
+    for (int q = firstQuad; q < firstQuad + nQuads; ++q) {
+#pragma unroll 1
+        for (int part = 0; part < (withResidual ? 2 : 1); ++part) {
+            const uint32_t col = 32 * (q >> 1) + 4 * (q & 1) + 8 * part;
+#pragma unroll 1
+            for (int k = 0; k < 4; k += 2) {
+                uint32_t w0, w1;
+                TmemLd2(tLane + col + k, w0, w1);
+                TmemWaitLd();
+                w0 = ScaleE4M3x4(w0, ah2);
+                w1 = ScaleE4M3x4(w1, ah2);
+                TmemSt2(tLane + col + k, w0, w1);
+            }
+        }
+    }
+    TmemWaitSt();
+}
+
+// e with 2^(e-1) < x <= 2^e for a positive float (clamped below so that 2^-e stays finite)
+__device__ __forceinline__ int ValueScaleExponent(float x)
+{
+    const int bits = __float_as_int(x);
+    const int e = ((bits >> 23) & 0xff) - 127 + ((bits & 0x7fffff) ? 1 : 0);
+    return max(e, -100);
+}
+
+// pause between barrier polls, in nanoseconds, of the MMA-issuing thread and of the softmax threads
+#ifndef TSA_FWD_SLEEP_MMA
+#define TSA_FWD_SLEEP_MMA 20
+#endif
+#ifndef TSA_FWD_SLEEP_SOFTMAX
+#define TSA_FWD_SLEEP_SOFTMAX 40
+#endif
+
+// number of register pairs out of every 8 whose exponentials go to the polynomial (0 = all on the SFU)
+#ifndef TSA_FWD_POLY_PAIRS
+#define TSA_FWD_POLY_PAIRS 0
+#endif
+
 template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
-__global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TFwdParams p)
 {
     using SM = TFwdSmem<D>;
@@ -106,25 +242,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     constexpr uint32_t GROUP_BYTES = 8 * D; // 8 rows of a tile
     constexpr uint32_t IDESC_QK = QK_I8 ? MakeInstrDesc(2, 1, 1, 0, 0, TILE_M, TILE_N) : MakeInstrDesc(1, 0, 0, 0, 0, TILE_M, TILE_N);
     constexpr uint32_t IDESC_PV = MakeInstrDesc(1, 0, 0, 0, 1, TILE_M, D);
-    constexpr int BAR_STAGE = 1;     // named barrier of the 256 softmax threads
-    constexpr int BAR_PAIR0 = 2;     // + (warp & 3): the two warps that share 32 rows
-    constexpr int HALF_N = TILE_N / 2;
-    constexpr int HALF_D = D / 2;
 
     extern __shared__ __align__(1024) uint8_t smem[]; // tiles need 1024-byte alignment for the 128 B swizzle
     uint8_t *sQ = smem + SM::Q_OFF;
     uint8_t *sK = smem + SM::K_OFF;
     uint8_t *sV = smem + SM::V_OFF;
+    TFwdAux *aux = reinterpret_cast<TFwdAux *>(smem + SM::AUX_OFF);
+    TFwdRound *rounds = reinterpret_cast<TFwdRound *>(smem + SM::ROUND_OFF);
     TFwdMisc &misc = *reinterpret_cast<TFwdMisc *>(smem + SM::MISC_OFF);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int head = blockIdx.y;
-    const int qTile = gridDim.x - 1 - blockIdx.x; // late (long) rows first
-#ifdef TSA_FWD_TRACE
-    const bool traceOn = tid == 0 && blockIdx.y == 5 && (blockIdx.x % 37) == 3 && blockIdx.x / 37 < 12;
-    const int traceSlot = blockIdx.x / 37;
-#endif
-    TRC(0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if ((SmemAddr(smem) & 1023u) != 0) {
         // the launch did not honour the alignment: report instead of computing on mis-swizzled tiles
@@ -133,21 +260,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
         }
         return;
     }
-    // the span groups of the tile are fetched first: two dependent global loads that overlap with the set-up below
-    TTileIter cur;
-    cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, qTile, p.KeyRows);
-    TRC(1);
     if (tid == 0) {
-        MbarInit(&misc.BarQ, 1);
-        for (int s = 0; s < STAGES; ++s) {
-            MbarInit(&misc.BarFull[s], 1);
+        for (int s = 0; s < Q_SLOTS; ++s) {
+            MbarInit(&misc.QFull[s], 1);
+            MbarInit(&misc.QEmpty[s], 1);
         }
-        MbarInit(&misc.BarMma, 1);
-        MbarInit(&misc.BarP, SOFTMAX_THREADS);
+        for (int s = 0; s < STAGES; ++s) {
+            MbarInit(&misc.KvFull[s], 2); // the TMA issue (with the byte count) and the loader's own staging of the scales
+            MbarInit(&misc.KvEmpty[s], 1);
+        }
+        for (int s = 0; s < ROUND_SLOTS; ++s) {
+            MbarInit(&misc.RFull[s], 1);
+            MbarInit(&misc.REmpty[s], FW_SOFTMAX_THREADS + 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            MbarInit(&misc.BarS[h], 1);
+            MbarInit(&misc.BarP[h], FW_SOFTMAX_THREADS);
+        }
+        MbarInit(&misc.BarOFull, 1);
         misc.Abort = 0;
         FenceBarrierInit();
     }
-    if (warp == CTRL_WARP) {
+    if (warp == FW_MMA_WARP) {
         TmemAlloc(&misc.TmemBase, TMEM_COLS);
         TmemRelinquish();
     }
@@ -158,454 +292,811 @@ __global__ void __launch_bounds__(FWD_THREADS, 2) FwdSm100Kernel(const __grid_co
     __syncthreads();
     TcFenceAfter();
     const uint32_t tmem = misc.TmemBase;
+    const int *abortFlag = &misc.Abort;
+    auto fail = [&](int code) {
+        *(volatile int *)&misc.Abort = 1;
+        if (p.Status) {
+            atomicOr(p.Status, code);
+        }
+    };
 
-    TRC(2);
-
-    if (warp == CTRL_WARP) {
-        // ---------------------------------------------------------------- control warp
-        if ((tid & 31) == 0 && cur.Valid) {
+    if (warp == FW_LOAD_WARP) {
+        // ------------------------------------------------------------------------------------ loader warp
+        if (lane == 0) {
             PrefetchTensorMap(&tmQ);
             PrefetchTensorMap(&tmK);
             PrefetchTensorMap(&tmV);
-            const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
-            TTileIter prod = cur;
-            int issued = 0, landed = 0;
-            bool failed = false;
-            auto issueLoad = [&](int slot, int j0) {
-                MbarExpectTx(&misc.BarFull[slot], 2 * SM::TILE_BYTES);
-                TmaLoad2D(sK + slot * SM::TILE_BYTES, &tmK, head * D, j0, &misc.BarFull[slot]);
-                TmaLoad2D(sV + slot * SM::TILE_BYTES, &tmV, head * D, j0, &misc.BarFull[slot]);
-            };
-            auto issuePV = [&](int slot, bool accumulate, bool withResidual) {
-                const uint32_t vAddr = sVa + slot * SM::TILE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < TILE_N / 32; ++ks) {
-                    uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                    uint32_t aCol = (ks >> 1) * HALF_N + (ks & 1) * 8; // P of half h sits at columns 64h .. 64h+15
-                    MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
-                }
-                if (withResidual) {
-#pragma unroll
-                    for (int ks = 0; ks < TILE_N / 32; ++ks) {
-                        uint64_t bDesc = MakeSmemDesc(vAddr + ks * 32 * D, 16, GROUP_BYTES, SWZ);
-                        uint32_t aCol = (ks >> 1) * HALF_N + 16 + (ks & 1) * 8;
-                        MmaF8TS(tmem + TMEM_O_COL, tmem + aCol, bDesc, IDESC_PV, 1u);
-                    }
-                }
-            };
-            auto issueQK = [&](int slot) {
-                const uint32_t kAddr = sKa + slot * SM::TILE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < D / 32; ++ks) {
-                    uint64_t aDesc = MakeSmemDesc(sQa + ks * 32, 16, GROUP_BYTES, SWZ);
-                    uint64_t bDesc = MakeSmemDesc(kAddr + ks * 32, 16, GROUP_BYTES, SWZ);
-                    if (QK_I8) {
-                        MmaI8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
-                    } else {
-                        MmaF8SS(tmem, aDesc, bDesc, IDESC_QK, ks > 0);
-                    }
-                }
-            };
-            auto fail = [&](int code) {
+        }
+        int kvCount = 0, qCount = 0, rCount = 0;
+        bool failed = false;
+        int item = 0;
+        if (lane == 0) {
+            item = atomicAdd(p.Counter, 1);
+        }
+        item = __shfl_sync(0xffffffffu, item, 0);
+        // waits of the whole warp on one barrier: every lane polls, all get the same answer
+        auto waitAll = [&](uint64_t *bar, uint32_t parity, int code) {
+            bool ok = WaitBarSleep<200>(bar, parity, abortFlag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok && !failed) {
                 failed = true;
-                *(volatile int *)&misc.Abort = 1;
-                if (p.Status) {
-                    atomicOr(p.Status, code);
+                if (lane == 0) {
+                    fail(code);
                 }
-            };
-
-            MbarExpectTx(&misc.BarQ, SM::TILE_BYTES);
-            TmaLoad2D(sQ, &tmQ, head * D, qTile * TILE_M, &misc.BarQ);
-            for (int s = 0; s < STAGES && prod.Valid; ++s) {
-                issueLoad(s, prod.J0);
-                prod.Advance();
-                ++issued;
             }
-            if (!WaitBar(&misc.BarQ, 0)) {
-                fail(kDevTimeoutTma);
+            return ok;
+        };
+        while (!failed) {
+            const bool end = item >= p.TotalItems;
+            int nextItem = 0;
+            if (!end && lane == 0) {
+                nextItem = atomicAdd(p.Counter, 1); // in flight while this item is set up
             }
-            int it = 0;
-            TTileIter ctl = cur;
-            for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
-                const int slot = it % STAGES;
-                if (!WaitBar(&misc.BarFull[slot], (it / STAGES) & 1)) {
-                    fail(kDevTimeoutTma);
+            const int qTile = end ? 0 : p.QTiles - 1 - item / p.HeadCount; // late (long) rows first
+            const int head = end ? 0 : item % p.HeadCount;
+            const int b0 = 2 * qTile;
+            int p0 = 0, n0 = 0, p1 = 0, n1 = 0, nRounds = 0;
+            int qSlot = qCount % Q_SLOTS;
+            float sqv[4] = {0, 0, 0, 0};
+            float kMul = 0; // power of two that brings the head's largest value scale into (1/2, 1]
+            if (!end) {
+                if (HAS_VSCALE) {
+                    const float vRef = p.VRef[head];
+                    if (vRef > 0) {
+                        kMul = __int_as_float((127 - ValueScaleExponent(vRef)) << 23);
+                    }
+                }
+                int pv = 0;
+                if (lane < 3 && b0 + lane <= p.LenAttTiles) {
+                    pv = p.SpanPtr[b0 + lane];
+                }
+                const int a = __shfl_sync(0xffffffffu, pv, 0), b = __shfl_sync(0xffffffffu, pv, 1), c = __shfl_sync(0xffffffffu, pv, 2);
+                if (b0 < p.LenAttTiles) {
+                    p0 = a;
+                    n0 = b - a;
+                }
+                if (b0 + 1 < p.LenAttTiles) {
+                    p1 = b;
+                    n1 = c - b;
+                }
+                nRounds = max(n0, n1);
+                // the query tile goes out first
+                if (!waitAll(&misc.QEmpty[qSlot], ((qCount / Q_SLOTS) & 1) ^ 1, kDevTimeoutTma)) {
                     break;
                 }
-                ++landed;
-                if (it > 0) {
-                    // P(it-1) written by all softmax threads
-                    if (!WaitBar(&misc.BarP, (it - 1) & 1)) {
-                        fail(kDevTimeoutMma);
+                if (lane == 0) {
+                    MbarExpectTx(&misc.QFull[qSlot], SM::TILE_BYTES);
+                    TmaLoad2D(sQ + qSlot * SM::TILE_BYTES, &tmQ, head * D, qTile * TILE_M, &misc.QFull[qSlot]);
+                }
+                ++qCount;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int row = qTile * TILE_M + lane + 32 * k;
+                    if (row < p.OutRows) {
+                        sqv[k] = p.QScale.Valid() ? p.QScale.Row(head)[row] : p.QkVecScale;
+                    }
+                }
+            }
+            // tile range of a round from the two blocks' group headers
+            auto roundRange = [&](int r, int &lo, int &hi) {
+                lo = 0x7fffffff;
+                hi = -1;
+                if (r < n0) {
+                    lo = min(lo, p.Spans[p0 + r].Start);
+                    hi = max(hi, p.Spans[p0 + r].Finish);
+                }
+                if (r < n1) {
+                    lo = min(lo, p.Spans[p1 + r].Start);
+                    hi = max(hi, p.Spans[p1 + r].Finish);
+                }
+                lo = max(lo, 0) & ~(TILE_N - 1);
+                hi = min(hi, p.KeyRows - 1) & ~(TILE_N - 1);
+            };
+            int firstRound = -1, lastRound = -1;
+            for (int r = 0; r < nRounds; ++r) {
+                int lo, hi;
+                roundRange(r, lo, hi);
+                if (lo <= hi) {
+                    if (firstRound < 0) {
+                        firstRound = r;
+                    }
+                    lastRound = r;
+                }
+            }
+            // an item without key tiles (or the end marker) still gets one record
+            const int rBegin = firstRound < 0 ? 0 : firstRound, rEnd = firstRound < 0 ? 0 : lastRound;
+            for (int r = rBegin; r <= rEnd && !failed; ++r) {
+                int lo = 0, hi = -1;
+                if (firstRound >= 0) {
+                    roundRange(r, lo, hi);
+                    if (lo > hi) {
+                        continue;
+                    }
+                }
+                int ss[4], sf[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    ss[k] = 1;
+                    sf[k] = 0;
+                }
+                if (firstRound >= 0) {
+                    if (r < n0) {
+                        const tsa_span_group *g = p.Spans + p0 + r;
+                        ss[0] = g->SpanStart[lane];
+                        sf[0] = g->SpanFinish[lane];
+                        ss[1] = g->SpanStart[lane + 32];
+                        sf[1] = g->SpanFinish[lane + 32];
+                    }
+                    if (r < n1) {
+                        const tsa_span_group *g = p.Spans + p1 + r;
+                        ss[2] = g->SpanStart[lane];
+                        sf[2] = g->SpanFinish[lane];
+                        ss[3] = g->SpanStart[lane + 32];
+                        sf[3] = g->SpanFinish[lane + 32];
+                    }
+                }
+                int mxS = -0x7fffffff, mnF = 0x7fffffff;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    ss[k] = max(ss[k], 0);
+                    sf[k] = min(sf[k], p.KeyRows - 1);
+                    if (ss[k] > sf[k]) {
+                        ss[k] = 1;
+                        sf[k] = 0;
+                    }
+                    mxS = max(mxS, ss[k]);
+                    mnF = min(mnF, sf[k]);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    mxS = max(mxS, __shfl_xor_sync(0xffffffffu, mxS, o));
+                    mnF = min(mnF, __shfl_xor_sync(0xffffffffu, mnF, o));
+                }
+                const int rSlot = rCount % ROUND_SLOTS;
+                if (!waitAll(&misc.REmpty[rSlot], ((rCount / ROUND_SLOTS) & 1) ^ 1, kDevTimeoutMma)) {
+                    break;
+                }
+                TFwdRound &rd = rounds[rSlot];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    rd.SpanS[lane + 32 * k] = ss[k];
+                    rd.SpanF[lane + 32 * k] = sf[k];
+                    rd.Sq[lane + 32 * k] = sqv[k];
+                }
+                const int nTiles = (lo <= hi) ? (hi - lo) / TILE_N + 1 : 0;
+                if (lane == 0) {
+                    rd.J0 = lo;
+                    rd.NTiles = nTiles;
+                    rd.Flags = end ? RF_END : ((r == rBegin ? RF_FIRST : 0) | (r == rEnd ? RF_LAST : 0));
+                    rd.QTile = qTile;
+                    rd.Head = head;
+                    rd.QSlot = qSlot;
+                    rd.FullLo = mxS;
+                    rd.FullHi = mnF;
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&misc.RFull[rSlot]);
+                }
+                ++rCount;
+                // the round's key / value tiles
+                for (int t = 0; t < nTiles; ++t) {
+                    const int j0 = lo + t * TILE_N;
+                    const int slot = kvCount % STAGES;
+                    const bool bulk = p.ScaleBulk && j0 + TILE_N <= p.KeyRows;
+                    // the scale rows this warp stages itself are requested before the wait for the slot: value scales
+                    // (multiplied by kMul on the way) always, key scales when a bulk copy cannot fetch them
+                    float skv[4] = {0, 0, 0, 0}, svv[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int j = j0 + lane + 32 * k;
+                        if (j < p.KeyRows) {
+                            if (!bulk) {
+                                skv[k] = p.KScale.Row(head)[j];
+                            }
+                            if (HAS_VSCALE) {
+                                svv[k] = p.VScale.Row(head)[j];
+                            }
+                        }
+                    }
+                    if (!waitAll(&misc.KvEmpty[slot], ((kvCount / STAGES) & 1) ^ 1, kDevTimeoutMma)) {
                         break;
                     }
-                    TcFenceAfter();
-                    issuePV((it - 1) % STAGES, it - 1 > 0, misc.TileMasked[(it - 1) & 1] != 0);
+                    if (lane == 0) {
+                        MbarExpectTx(&misc.KvFull[slot], 2 * SM::TILE_BYTES + (bulk ? TILE_N * 4 : 0));
+                        TmaLoad2D(sK + slot * SM::TILE_BYTES, &tmK, head * D, j0, &misc.KvFull[slot]);
+                        TmaLoad2D(sV + slot * SM::TILE_BYTES, &tmV, head * D, j0, &misc.KvFull[slot]);
+                        if (bulk) {
+                            BulkLoad(aux[slot].Sk, p.KScale.Row(head) + j0, TILE_N * 4, &misc.KvFull[slot]);
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (!bulk) {
+                            aux[slot].Sk[lane + 32 * k] = skv[k];
+                        }
+                        if (HAS_VSCALE) {
+                            aux[slot].Sv[lane + 32 * k] = svv[k] * kMul;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        MbarArrive(&misc.KvFull[slot]);
+                    }
+                    ++kvCount;
+                }
+            }
+            if (end) {
+                break;
+            }
+            item = __shfl_sync(0xffffffffu, nextItem, 0);
+        }
+        if (failed || *(volatile int *)&misc.Abort) {
+            // drain copies that were requested but may never be consumed, so none lands after the CTA is gone
+            for (int k = max(0, kvCount - STAGES); k < kvCount; ++k) {
+                WaitBar(&misc.KvFull[k % STAGES], (k / STAGES) & 1);
+            }
+            for (int k = max(0, qCount - Q_SLOTS); k < qCount; ++k) {
+                WaitBar(&misc.QFull[k % Q_SLOTS], (k / Q_SLOTS) & 1);
+            }
+        }
+        __syncwarp();
+    } else if (warp == FW_MMA_WARP) {
+        // ------------------------------------------------------------------------------------ MMA warp
+        // Software pipeline over the CTA's whole tile sequence: S(t+1) = Q K^T is issued directly behind O += P(t) V(t),
+        // and everything tile t+1 needs (its round record, Q, K/V stage) is waited for before the wait for P(t), so that
+        // between the softmax threads' "P written" and their next "S ready" lie only the two groups of MMA instructions.
+        if (lane == 0) {
+            const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
+            // descriptors without the tile's address: the address field (bits 0-13, in 16-byte units) is added per use
+            const uint64_t descBase = MakeSmemDesc(0, 16, GROUP_BYTES, SWZ);
+            int kvCount = 0, pCount = 0, rCount = 0, itemCount = 0, tilesInItem = 0;
+            bool failed = false;
+            // the tile whose QK^T has been issued and whose PV is still to come
+            bool pending = false, pendAccum = false, pendMasked = false, pendLast = false;
+            int pendSlot = 0, pendQSlot = 0;
+            auto wait = [&](uint64_t *bar, uint32_t parity, int code) {
+                if (WaitBarSleep<TSA_FWD_SLEEP_MMA>(bar, parity, abortFlag)) {
+                    return true;
+                }
+                if (!failed) {
+                    failed = true;
+                    fail(code);
+                }
+                return false;
+            };
+            constexpr uint32_t IDESC_QK_HALF = QK_I8 ? MakeInstrDesc(2, 1, 1, 0, 0, TILE_M, TILE_N / 2) : MakeInstrDesc(1, 0, 0, 0, 0, TILE_M, TILE_N / 2);
+            // S = Q K^T for the keys [64h, 64h + 64) of a tile
+            auto issueQKHalf = [&](int h, uint64_t qDesc, uint64_t kDesc) {
+                MmaGroupSSCommit<D / 32, QK_I8>(tmem + h * 64, qDesc, kDesc + ((h * 64 * D) >> 4), IDESC_QK_HALF, &misc.BarS[h]);
+            };
+            // waits for half h of the pending tile's weights and issues O += P V for it (item-end signals behind the last)
+            auto flushHalf = [&](int h) {
+                const uint64_t vDesc = descBase + ((sVa + pendSlot * SM::TILE_BYTES) >> 4);
+                if (!wait(&misc.BarP[h], pCount & 1, kDevTimeoutMma)) {
+                    return false;
                 }
                 TcFenceAfter();
-                issueQK(slot);
-                MmaCommit(&misc.BarMma);
-                if (it > 0 && prod.Valid) {
-                    // the slot of tile it-1 is free once PV(it-1) has retired, i.e. when this commit completes
-                    if (!WaitBar(&misc.BarMma, it & 1)) {
-                        fail(kDevTimeoutMma);
+                MmaPairF8TS(tmem + TMEM_O_COL, tmem + h * 64, vDesc + ((h * 64 * D) >> 4), (32 * D) >> 4, IDESC_PV,
+                    (pendAccum || h > 0) ? 1u : 0u, pendMasked);
+                if (h == 1) {
+                    MmaCommit(&misc.KvEmpty[pendSlot]);
+                    if (pendLast) {
+                        MmaCommit(&misc.BarOFull);
+                        MmaCommit(&misc.QEmpty[pendQSlot]);
+                    }
+                    ++pCount;
+                    pending = false;
+                }
+                return true;
+            };
+            while (!failed) {
+                const int rSlot = rCount % ROUND_SLOTS;
+                if (!wait(&misc.RFull[rSlot], (rCount / ROUND_SLOTS) & 1, kDevTimeoutTma)) {
+                    break;
+                }
+                const volatile TFwdRound &rd = rounds[rSlot];
+                const int j0r = rd.J0, nTiles = rd.NTiles, flags = rd.Flags, qSlot = rd.QSlot, fullLo = rd.FullLo, fullHi = rd.FullHi;
+                MbarArrive(&misc.REmpty[rSlot]);
+                ++rCount;
+                if (flags & RF_END) {
+                    break;
+                }
+                if (flags & RF_FIRST) {
+                    tilesInItem = 0;
+                    if (!wait(&misc.QFull[qSlot], (itemCount / Q_SLOTS) & 1, kDevTimeoutTma)) {
                         break;
                     }
-                    issueLoad((it - 1) % STAGES, prod.J0);
-                    prod.Advance();
-                    ++issued;
                 }
-                if (*(volatile int *)&misc.Abort) {
-                    failed = true;
+                const uint64_t qDesc = descBase + ((sQa + qSlot * SM::TILE_BYTES) >> 4);
+                for (int t = 0; t < nTiles; ++t) {
+                    const int j0 = j0r + t * TILE_N;
+                    const int slot = kvCount % STAGES;
+                    if (!wait(&misc.KvFull[slot], (kvCount / STAGES) & 1, kDevTimeoutTma)) {
+                        break;
+                    }
+                    const uint64_t kDesc = descBase + ((sKa + slot * SM::TILE_BYTES) >> 4);
+                    // O += P V of the previous tile's half h, then this tile's S into the columns that frees
+                    if (pending) {
+                        if (!flushHalf(0)) {
+                            break;
+                        }
+                        issueQKHalf(0, qDesc, kDesc);
+                        if (!flushHalf(1)) {
+                            break;
+                        }
+                        issueQKHalf(1, qDesc, kDesc);
+                    } else {
+                        TcFenceAfter();
+                        issueQKHalf(0, qDesc, kDesc);
+                        issueQKHalf(1, qDesc, kDesc);
+                    }
+                    pending = true;
+                    pendSlot = slot;
+                    pendQSlot = qSlot;
+                    pendAccum = tilesInItem > 0;
+                    pendMasked = !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
+                    pendLast = (flags & RF_LAST) && t == nTiles - 1;
+                    ++kvCount;
+                    ++tilesInItem;
+                }
+                if (failed) {
+                    break;
+                }
+                if (flags & RF_LAST) {
+                    if (tilesInItem == 0) {
+                        MbarArrive(&misc.QEmpty[qSlot]); // an item without key tiles: nothing was issued for it
+                    }
+                    ++itemCount;
                 }
             }
-            if (!failed && it > 0) {
-                if (WaitBar(&misc.BarP, (it - 1) & 1)) {
-                    TcFenceAfter();
-                    issuePV((it - 1) % STAGES, it - 1 > 0, misc.TileMasked[(it - 1) & 1] != 0);
-                } else {
-                    fail(kDevTimeoutMma);
-                }
-            }
-            MmaCommit(&misc.BarMma); // final phase (also releases softmax threads waiting after a failure)
-            if (failed) {
-                // drain copies that were requested but never consumed, so none lands after the CTA is gone
-                for (int t = landed; t < issued; ++t) {
-                    WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
+            if (pending && !failed) {
+                // the last tile: the commits that would follow the next tile's S stand in for it (a rescale in this tile's
+                // second half waits on them to know that the first half's PV has retired)
+                if (flushHalf(0)) {
+                    MmaCommit(&misc.BarS[0]);
+                    if (flushHalf(1)) {
+                        MmaCommit(&misc.BarS[1]);
+                    }
                 }
             }
         }
         __syncwarp();
     } else {
-        // ---------------------------------------------------------------- softmax warps
-        const int half = tid >> 7;
-        const int r = tid & (TILE_M - 1);
-        const int row = qTile * TILE_M + r;
-        const int colBase = half * HALF_N;
-        const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const int pairBar = BAR_PAIR0 + (warp & 3);
-
-        const bool rowOk = row < p.OutRows;
+        // ------------------------------------------------------------------------------------ softmax warps
+        const int r = tid; // row of the item's query tile = tensor-memory lane
+        const uint32_t tLane = tmem + ((uint32_t)(warp * 32) << 16);
         const float g = p.GlobalScale ? *p.GlobalScale : 1.0f;
-        float sq = 0;
-        if (rowOk) {
-            sq = p.QScale.Valid() ? p.QScale.Row(head)[row] : p.QkVecScale;
-        }
-        // a zero query scale would turn masked (-inf) scores into NaN; a tiny positive one keeps every logit at ~0
-        const float rowMult = fmaxf(sq * p.C * g, 1e-30f);
-        const float2 rowMult2 = make_float2(rowMult, rowMult);
-        const float vRef = HAS_VSCALE ? p.VRef[head] : 0.0f;
-        const float svMult = (HAS_VSCALE && vRef > 0) ? 1.0f / vRef : 0.0f; // sv_j / svRef <= 1; the factor 128 sits in the exponent
-
-        int spanS = 1, spanF = 0, spanRound = -1;
-        float m = 0;
-        float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this thread's weights
-        float pfSk = 0, pfSv = 0;
-        auto fetchScales = [&](int j0) {
-            pfSk = 0;
-            pfSv = 0;
-            int j = j0 + tid;
-            if (tid < TILE_N && j < p.KeyRows) {
-                pfSk = p.KScale.Row(head)[j];
-                if (HAS_VSCALE) {
-                    pfSv = p.VScale.Row(head)[j] * svMult;
-                }
+        int rCount = 0, sCount = 0, kvCount = 0, oCount = 0;
+        int pvEnabled = 0; // halves handed to the MMA so far = PV groups that have been or will be issued
+        int tilesInItem = 0, row = 0, head = 0, qTile = 0;
+        bool rowOk = false, failed = false;
+        float m = 0, rowMult = 0, invK = 0;
+        float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this row's weights
+        auto wait = [&](uint64_t *bar, uint32_t parity, int code) {
+            if (WaitBarSleep<TSA_FWD_SLEEP_SOFTMAX>(bar, parity, abortFlag)) {
+                return true;
             }
-        };
-        if (cur.Valid) {
-            fetchScales(cur.J0);
-        }
-        bool failed = false;
-        int it = 0;
-        while (cur.Valid) {
-            if (cur.Round != spanRound) {
-                spanS = 1;
-                spanF = 0;
-                const tsa_span_group *gp = (r < 64) ? cur.G0 : cur.G1;
-                const int n = (r < 64) ? cur.N0 : cur.N1;
-                if (cur.Round < n) {
-                    spanS = gp[cur.Round].SpanStart[r & 63];
-                    spanF = gp[cur.Round].SpanFinish[r & 63];
-                }
-                spanRound = cur.Round;
-            }
-            const int buf = it & 1;
-            if (tid < TILE_N) {
-                misc.Sk[buf][tid] = pfSk;
-                if (HAS_VSCALE) {
-                    misc.Sv[buf][tid] = pfSv;
-                }
-            }
-            const int j0 = cur.J0;
-            const int ls = spanS - j0, lf = spanF - j0; // span in tile-local columns
-            const bool rowFull = ls <= 0 && lf >= TILE_N - 1;
-            const bool warpMasked = !__all_sync(0xffffffffu, rowFull);
-            // 32-column chunks of this thread's half that some row of the warp attends
-            const bool any0 = __any_sync(0xffffffffu, ls <= colBase + 31 && lf >= colBase && ls <= lf);
-            const bool any1 = __any_sync(0xffffffffu, ls <= colBase + 63 && lf >= colBase + 32 && ls <= lf);
-            if (failed) {
-                *(volatile int *)&misc.Abort = 1;
-            }
-            const bool tileMasked = BarRedOr(BAR_STAGE, SOFTMAX_THREADS, warpMasked);
-            if (*(volatile int *)&misc.Abort) {
+            if (!failed) {
                 failed = true;
+                fail(code);
+            }
+            return false;
+        };
+        while (true) {
+            const int rSlot = rCount % ROUND_SLOTS;
+            if (!wait(&misc.RFull[rSlot], (rCount / ROUND_SLOTS) & 1, kDevTimeoutTma)) {
                 break;
             }
-            TTileIter nxt = cur;
-            nxt.Advance();
-            if (nxt.Valid) {
-                fetchScales(nxt.J0);
+            const TFwdRound &rd = rounds[rSlot];
+            const int spanS = rd.SpanS[r], spanF = rd.SpanF[r];
+            const float sq = rd.Sq[r];
+            const int j0r = rd.J0, nTiles = rd.NTiles, flags = rd.Flags, fullLo = rd.FullLo, fullHi = rd.FullHi;
+            const int rdQTile = rd.QTile, rdHead = rd.Head;
+            MbarArrive(&misc.REmpty[rSlot]);
+            ++rCount;
+            if (flags & RF_END) {
+                break;
             }
-            if (!WaitBar(&misc.BarMma, it & 1)) {
-                failed = true;
-                if (p.Status) {
-                    atomicOr(p.Status, kDevTimeoutMma);
+            if (flags & RF_FIRST) {
+                qTile = rdQTile;
+                head = rdHead;
+                row = qTile * TILE_M + r;
+                rowOk = row < p.OutRows;
+                // a zero query scale would turn masked (-inf) scores into NaN; a tiny positive one keeps every logit at ~0
+                rowMult = fmaxf(sq * p.C * g, 1e-30f);
+                m = 0;
+                lacc2 = make_float2(0.0f, 0.0f);
+                tilesInItem = 0;
+                if (HAS_VSCALE) {
+                    // the loader stages sv_j * K with 1 / K = the power of two at or above the head's largest value scale,
+                    // so the weights' e4m3 range is used whatever the scales' magnitude; O is in units of 1 / K
+                    const float vRef = p.VRef[head];
+                    invK = vRef > 0 ? __int_as_float((127 + ValueScaleExponent(vRef)) << 23) : 0.0f;
                 }
             }
-            TcFenceAfter();
-            if (it < 4) {
-                TRC(3 + 2 * it);
-            }
+            const float2 rowMult2 = make_float2(rowMult, rowMult);
+            for (int t = 0; t < nTiles; ++t) {
+                const int j0 = j0r + t * TILE_N;
+                const int slot = kvCount % STAGES;
+                const bool masked = !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
+                if (!wait(&misc.BarS[0], sCount & 1, kDevTimeoutMma)) {
+                    break;
+                }
+                // the tile's scale rows arrived with K and V; this wait makes them visible to this thread
+                if (!wait(&misc.KvFull[slot], (kvCount / STAGES) & 1, kDevTimeoutTma)) {
+                    break;
+                }
+                TcFenceAfter();
+                const float *skBuf = aux[slot].Sk;
+                const float *svBuf = aux[slot].Sv;
+                const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
+                const float headroom = P_HEADROOM;
+                const bool hasO = tilesInItem > 0;
+                // second half of S: ready long before it is needed (its MMAs were issued before this tile's first half was
+                // even handed over), the wait is for the memory model
+                auto waitSecondHalf = [&]() {
+                    const bool ok = wait(&misc.BarS[1], sCount & 1, kDevTimeoutMma);
+                    TcFenceAfter();
+                    return ok;
+                };
+                // hands the finished half h of P to the MMA thread
+                auto handOver = [&](int h) {
+                    TmemWaitSt();
+                    TcFenceBefore();
+                    MbarArrive(&misc.BarP[h]);
+                    ++pvEnabled;
+                };
 
-            // The scores are read from tensor memory twice, 32 columns at a time (first for the row maximum, then for
-            // the weights), which keeps the live registers of a thread at one chunk instead of its whole half row.
-            // Masked and unmasked tiles run separate copies of the code (warp-uniform branches), so the common
-            // unmasked tile pays for no compare / select.
-            // span in half-local columns, clipped so that (unsigned)(c - lsH) <= spanW  <=>  ls <= c <= lf
-            const int lsC = max(ls, colBase), lfC = min(lf, colBase + HALF_N - 1);
-            const int lsH = lsC - colBase;
-            const unsigned spanW = (lsC <= lfC) ? (unsigned)(lfC - lsC) : 0u;
-            const bool rowEmpty = lsC > lfC;
-            const float *skBuf = misc.Sk[buf] + colBase;
-            const float *svBuf = misc.Sv[buf] + colBase;
-            const float *alBuf = misc.Al + colBase;
-            auto loadScaled = [&](auto maskedTag, int ch, float2 *u) {
-                constexpr bool MASKED = decltype(maskedTag)::value;
-                uint32_t sreg[32];
-                TmemLd32(tLane + colBase + ch * 32, sreg);
-                TmemWaitLd();
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const int lc = ch * 32 + c; // column inside this thread's half
-                    float2 a = QK_I8 ? IntPairToFloat(sreg[c], sreg[c + 1]) : make_float2(__uint_as_float(sreg[c]), __uint_as_float(sreg[c + 1]));
-                    float2 x = __fmul2_rn(a, *reinterpret_cast<const float2 *>(skBuf + lc));
-                    if (HAS_ALIBI) {
-                        x = __ffma2_rn(x, rowMult2, *reinterpret_cast<const float2 *>(alBuf + lc));
-                    }
-                    if (MASKED) {
-                        // lsH / lfH: span in columns of this half; unsigned compare folds both bounds
-                        x.x = ((unsigned)(lc - lsH) <= spanW) ? x.x : -INFINITY;
-                        x.y = ((unsigned)(lc + 1 - lsH) <= spanW) ? x.y : -INFINITY;
-                    }
-                    u[c >> 1] = x;
-                }
-            };
-            auto chunkMax = [&](auto maskedTag, int ch, float mxIn) {
-                float2 u[16];
-                loadScaled(maskedTag, ch, u);
-                float mx = mxIn;
-#pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    mx = Max3(mx, u[k].x, u[k].y);
-                }
-                return mx;
-            };
-            float mx = -INFINITY;
-            if (warpMasked) {
-                if (any0) {
-                    mx = chunkMax(std::true_type(), 0, mx);
-                }
-                if (any1) {
-                    mx = chunkMax(std::true_type(), 1, mx);
-                }
-                if (rowEmpty) {
-                    mx = -INFINITY; // spanW = 0 would otherwise let column lsH through
-                }
-            } else {
+                if (QK_I8 && p.DumpScores && head == p.DumpHead && qTile == p.DumpQTile && tilesInItem == p.DumpTile) {
+                    waitSecondHalf();
 #pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    mx = chunkMax(std::false_type(), ch, mx);
-                }
-            }
-            const float rowOff = HAS_ALIBI ? -p.Slope * (float)(row - j0) : 0.0f;
-            float zmax = mx;
-            if (!HAS_ALIBI) {
-                zmax = (mx == -INFINITY) ? mx : mx * rowMult;
-            }
-            misc.RowX[half][r] = zmax + rowOff;
-            BarSync(pairBar, 64);
-            const float tileMax = fmaxf(zmax + rowOff, misc.RowX[half ^ 1][r]);
-            const float newM = fmaxf(m, floorf(tileMax)); // -inf stays below m
-            const float alpha = exp2f(m - newM);
-            if (it > 0 && __any_sync(0xffffffffu, newM != m)) {
+                    for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+                        uint32_t s[32];
+                        TmemLd32(tLane + c0, s);
+                        TmemWaitLdRegs(s);
 #pragma unroll
-                for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-                    uint32_t o[32];
-                    TmemLd32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
-                    TmemWaitLd();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                    }
-                    TmemSt32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
-                }
-            }
-            lacc2.x *= alpha;
-            lacc2.y *= alpha;
-            m = newM;
-            // weights, packed e4m3 into this half's own S columns (both chunks are re-read before the first store)
-            // an empty row gets eoff = -inf so that every weight is 0 whatever the compare above let through
-            const float eoff = rowEmpty && warpMasked ? -INFINITY : rowOff - m + 7.0f;
-            const float2 eoff2 = make_float2(eoff, eoff);
-            auto chunkWeights = [&](auto maskedTag, auto residTag, int ch) {
-                constexpr bool RESID = decltype(residTag)::value;
-                uint32_t pk[8], pl[8];
-                float2 u[16];
-                loadScaled(maskedTag, ch, u);
-#pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    float2 e[2];
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        float2 t = HAS_ALIBI ? __fadd2_rn(u[c + k], eoff2) : __ffma2_rn(u[c + k], rowMult2, eoff2);
-                        float2 w = make_float2(FastExp2(t.x), FastExp2(t.y));
-                        lacc2 = __fadd2_rn(lacc2, w);
-                        e[k] = HAS_VSCALE ? __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + ch * 32 + 2 * (c + k))) : w;
-                    }
-                    const uint32_t hi4 = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
-                    pk[c >> 1] = hi4;
-                    if (RESID) {
-                        pl[c >> 1] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
-                    }
-                }
-                // the packed weights of a chunk land in S columns of chunk 0 of this half, which has been read by then
-                TmemStN<8>(tLane + colBase + ch * 8, pk);
-                if (RESID) {
-                    TmemStN<8>(tLane + colBase + 16 + ch * 8, pl);
-                }
-            };
-            auto zeroChunk = [&](int ch) {
-                uint32_t z[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    z[k] = 0;
-                }
-                TmemStN<8>(tLane + colBase + ch * 8, z);
-                TmemStN<8>(tLane + colBase + 16 + ch * 8, z);
-            };
-            if (warpMasked) {
-                // masked tiles always carry the residual (tileMasked is true whenever any warp is masked)
-                if (any0) {
-                    chunkWeights(std::true_type(), std::true_type(), 0);
-                } else {
-                    zeroChunk(0);
-                }
-                if (any1) {
-                    chunkWeights(std::true_type(), std::true_type(), 1);
-                } else {
-                    zeroChunk(1);
-                }
-            } else if (tileMasked) {
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    chunkWeights(std::false_type(), std::true_type(), ch);
-                }
-            } else {
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    chunkWeights(std::false_type(), std::false_type(), ch);
-                }
-            }
-            TmemWaitSt();
-            TcFenceBefore();
-            if (tid == 0) {
-                misc.TileMasked[it & 1] = tileMasked ? 1 : 0;
-            }
-            MbarArrive(&misc.BarP);
-            if (it < 4) {
-                TRC(4 + 2 * it);
-            }
-            cur = nxt;
-            ++it;
-        }
-
-        const int tiles = it;
-        TRC(11);
-        if (tiles > 0 && !failed) {
-            if (!WaitBar(&misc.BarMma, tiles & 1)) {
-                failed = true;
-                if (p.Status) {
-                    atomicOr(p.Status, kDevTimeoutMma);
-                }
-            }
-            TcFenceAfter();
-        }
-        if (failed) {
-            *(volatile int *)&misc.Abort = 1;
-        }
-        TRC(14);
-        // total weight of the row: both halves
-        misc.RowX[half][r] = lacc2.x + lacc2.y;
-        BarSync(BAR_STAGE, SOFTMAX_THREADS);
-        TRC(15);
-        failed = failed || (*(volatile int *)&misc.Abort != 0);
-        if (!failed) {
-            const float lTot = (lacc2.x + lacc2.y + misc.RowX[half ^ 1][r]) * (1.0f / 128.0f) + exp2f(-m);
-            const float outMult = (HAS_VSCALE ? vRef : p.VVecScale) * (1.0f / 128.0f) / lTot;
-            if (rowOk && half == 0 && p.Lse.Valid()) {
-                p.Lse.Row(head)[row] = m + log2f(lTot);
-            }
-            const int esz = (p.OutDtype == TSA_F32) ? 4 : 2;
-            char *oRow = p.Out.Row(rowOk ? row : 0) + ((size_t)head * D + half * HALF_D) * esz;
-#pragma unroll
-            for (int c0 = 0; c0 < HALF_D; c0 += 32) {
-                uint32_t o[32];
-                if (tiles > 0) {
-                    TmemLd32(tLane + TMEM_O_COL + half * HALF_D + c0, o);
-                    TmemWaitLd();
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        o[c] = 0;
-                    }
-                }
-                if (rowOk) {
-                    if (p.OutDtype == TSA_F32) {
-                        float4 *dst = reinterpret_cast<float4 *>(oRow + c0 * 4);
-#pragma unroll
-                        for (int c = 0; c < 32; c += 4) {
-                            dst[c >> 2] = make_float4(__uint_as_float(o[c]) * outMult, __uint_as_float(o[c + 1]) * outMult,
-                                __uint_as_float(o[c + 2]) * outMult, __uint_as_float(o[c + 3]) * outMult);
+                        for (int c = 0; c < 32; ++c) {
+                            p.DumpScores[r * TILE_N + c0 + c] = (int32_t)s[c];
                         }
-                    } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>(oRow + c0 * 2);
+                    }
+                }
+
+                // scaled logit offsets of a pair of columns: t = S * sk * rowMult (+ alibi) + eoff, eoff = rowOff - m + 7
+                auto scalePair = [&](uint32_t s0, uint32_t s1, int col, float2 eoff2) {
+                    float2 a = QK_I8 ? IntPairToFloat(s0, s1) : make_float2(__uint_as_float(s0), __uint_as_float(s1));
+                    float2 x = __fmul2_rn(a, *reinterpret_cast<const float2 *>(skBuf + col));
+                    if (HAS_ALIBI) {
+                        x = __ffma2_rn(x, rowMult2, *reinterpret_cast<const float2 *>(misc.Al + col));
+                        return __fadd2_rn(x, eoff2);
+                    }
+                    return __ffma2_rn(x, rowMult2, eoff2);
+                };
+                float eoff = rowOff - m + 7.0f;
+
+                // One key tile in chunks of W columns: logits in place of the scores and their maximum, a vote whether the
+                // row's reference has to move, then the weights.  The packed weights of the 32-key block b go to columns
+                // [32b, 32b + 8) and their residuals to [32b + 8, 32b + 16): inside the block's own score columns, which are
+                // in registers by then, so no store can hit scores that are still to be read.
+                // Unmasked tiles: W = 16, the next chunk's tcgen05.ld in flight while this one is worked on.
+                // Tiles the mask cuts through: W = 32, one buffer, residual term, chunks no row of the warp attends skipped.
+                auto processTile = [&](auto maskedTag) {
+                    constexpr bool MASKED = decltype(maskedTag)::value;
+                    constexpr int W = MASKED ? 32 : 16;
+                    int lsC = 0;
+                    unsigned spanW = TILE_N - 1;
+                    bool rowEmpty = false;
+                    unsigned act = 0xf; // 32-column chunks some row of the warp attends
+                    if (MASKED) {
+                        const int ls = spanS - j0, lf = spanF - j0; // span in tile-local columns
+                        lsC = max(ls, 0);
+                        const int lfC = min(lf, TILE_N - 1);
+                        rowEmpty = lsC > lfC;
+                        spanW = rowEmpty ? 0u : (unsigned)(lfC - lsC);
+                        act = 0;
 #pragma unroll
-                        for (int c = 0; c < 32; c += 8) {
-                            uint32_t w[4];
+                        for (int ch = 0; ch < 4; ++ch) {
+                            if (__any_sync(0xffffffffu, !rowEmpty && lsC <= ch * 32 + 31 && lfC >= ch * 32)) {
+                                act |= 1u << ch;
+                            }
+                        }
+                    }
+                    // the reference moves up by d whole units: everything accumulated so far shrinks by 2^-d, and the
+                    // chunk's logits in s drop by d
+                    auto raise = [&](float mxc, int storedQuads, uint32_t *s) {
+                        const float d = (mxc > headroom) ? floorf(mxc - 7.0f) : 0.0f;
+                        const float alpha = exp2f(-d);
+                        // the chunk voted on is the next one to be stored: it lies in half storedQuads / 4, whose earlier
+                        // quads are still this thread's; O holds something once a PV group of this item has been enabled,
+                        // and may be touched once the last enabled group has retired
+                        const int firstQuad = storedQuads & ~3;
+                        const bool oLive = hasO || firstQuad > 0;
+                        if (oLive && pvEnabled > 0) {
+                            // the last PV group enabled must have retired: the S = Q K^T group issued right behind it has
+                            // when its commit arrived (first half: the second half of this tile's S; second half: the
+                            // first half of the next tile's S)
+                            if (firstQuad == 0) {
+                                wait(&misc.BarS[1], sCount & 1, kDevTimeoutMma);
+                            } else {
+                                wait(&misc.BarS[0], (sCount + 1) & 1, kDevTimeoutMma);
+                            }
+                            TcFenceAfter();
+                        }
+                        ShrinkAccumulated<D>(tLane, alpha, oLive ? 1 : 0, firstQuad, storedQuads - firstQuad, MASKED ? 1 : 0);
+                        lacc2.x *= alpha;
+                        lacc2.y *= alpha;
+                        m += d;
+                        eoff -= d;
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                float a = __uint_as_float(o[c + 2 * k]) * outMult, b = __uint_as_float(o[c + 2 * k + 1]) * outMult;
-                                if (p.OutDtype == TSA_BF16) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                                    w[k] = *reinterpret_cast<uint32_t *>(&h);
+                        for (int c = 0; c < W; ++c) {
+                            s[c] = __float_as_uint(__uint_as_float(s[c]) - d);
+                        }
+                    };
+                    // s: W scores of the columns from cb on; other: the buffer a tcgen05.ld may be filling meanwhile
+                    auto chunk = [&](uint32_t *s, uint32_t *other, int cb, uint32_t *pk, uint32_t *pl) {
+                        float mxc = -INFINITY;
+                        {
+                            const float2 eoff2 = make_float2(eoff, eoff);
+#pragma unroll
+                            for (int c = 0; c < W; c += 2) {
+                                float2 tt = scalePair(s[c], s[c + 1], cb + c, eoff2);
+                                if (MASKED) {
+                                    // unsigned compare folds both bounds: lsC <= col <= lfC
+                                    tt.x = ((unsigned)(cb + c - lsC) <= spanW) ? tt.x : -INFINITY;
+                                    tt.y = ((unsigned)(cb + c + 1 - lsC) <= spanW) ? tt.y : -INFINITY;
+                                }
+                                mxc = Max3(mxc, tt.x, tt.y);
+                                s[c] = __float_as_uint(tt.x);
+                                s[c + 1] = __float_as_uint(tt.y);
+                            }
+                        }
+                        if (MASKED && rowEmpty) {
+                            mxc = -INFINITY; // spanW = 0 would otherwise let column lsC through
+                        }
+                        if (__any_sync(0xffffffffu, mxc > headroom)) {
+                            if (!MASKED) {
+                                TmemWaitLdRegs16(other); // no load is in flight across the out-of-line call
+                            }
+                            raise(mxc, cb >> 4, s);
+                        }
+                        // an empty row gets -inf so that every weight is 0 whatever the compare let through
+                        const float kill = (MASKED && rowEmpty) ? -INFINITY : 0.0f;
+#pragma unroll
+                        for (int c = 0; c < W; c += 4) {
+                            float2 e[2];
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int cc = c + 2 * k;
+                                float2 tt = make_float2(__uint_as_float(s[cc]), __uint_as_float(s[cc + 1]));
+                                if (MASKED) {
+                                    tt.x += kill;
+                                    tt.y += kill;
+                                }
+                                float2 w;
+                                if (!MASKED && ((cc >> 1) & 7) < TSA_FWD_POLY_PAIRS) {
+                                    w = PolyExp2Pair(tt);
                                 } else {
-                                    w[k] = PackHalf2(a, b);
+                                    w = make_float2(FastExp2(tt.x), FastExp2(tt.y));
+                                }
+                                lacc2 = __fadd2_rn(lacc2, w);
+                                if (HAS_VSCALE) {
+                                    e[k] = __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + cb + cc));
+                                } else {
+                                    e[k] = w;
                                 }
                             }
-                            dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                            const uint32_t hi4 = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
+                            pk[c >> 2] = hi4;
+                            if (MASKED) {
+                                pl[c >> 2] = ResidualE4M3x2(e[0].x, e[0].y, hi4 & 0xffff) | (ResidualE4M3x2(e[1].x, e[1].y, hi4 >> 16) << 16);
+                            }
+                        }
+                    };
+                    if (MASKED) {
+#pragma unroll 1
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t s[32], pk[8], pl[8];
+                            if (act & (1u << ch)) {
+                                TmemLd32(tLane + ch * 32, s);
+                                TmemWaitLdRegs(s);
+                                chunk(s, s, ch * 32, pk, pl);
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) {
+                                    pk[k] = 0;
+                                    pl[k] = 0;
+                                }
+                            }
+                            TmemStN<8>(tLane + ch * 32, pk);
+                            TmemStN<8>(tLane + ch * 32 + 8, pl);
+                            if (ch == 1) {
+                                handOver(0);
+                                waitSecondHalf();
+                            }
+                        }
+                    } else {
+                        // Software pipeline over the 8 chunks, interleaved at the source level: in step c the exponentials
+                        // of chunk c (special-function pipe) alternate with the scaling of chunk c + 1 (FMA pipe) inside one
+                        // loop body, while chunk c + 2 is on its way from tensor memory; the vote on chunk c + 1 closes
+                        // the step.  Raw scores of chunk k live in rawBuf[k & 1], logits in tBuf[k & 1].
+                        uint32_t tBuf[2][16], rawBuf[2][16], pk[4];
+                        float mxN = -INFINITY;
+                        // c: chunk that becomes weights (even: buffers 0, odd: buffers 1).  A loop over pairs of steps: fully
+                        // unrolled, the eight copies no longer fit the instruction cache and every head size got slower.
+                        // MODE 0: chunks c + 1 and c + 2 exist; 1: only c + 1; 2: neither (the last step); 3: decided at run
+                        // time, and the last step scales whatever the raw registers hold and ignores the result.  Head size
+                        // 128 runs the loop over steps 0-5 in mode 0 and steps 6, 7 in modes 1, 2 (four copies of the step),
+                        // head size 64 all eight steps in mode 3 (two copies): measured, each is the faster one for its size.
+                        auto step = [&](auto modeTag, auto oddTag, int c) {
+                            constexpr int MODE = decltype(modeTag)::value;
+                            constexpr int ODD = decltype(oddTag)::value;
+                            constexpr bool HAS_NEXT = MODE != 2;
+                            const bool LOAD = MODE == 0 || (MODE == 3 && c < 6);
+                            uint32_t *cur = tBuf[ODD], *nxt = tBuf[ODD ^ 1];
+                            uint32_t *rawCur = rawBuf[ODD ^ 1], *rawNxt = rawBuf[ODD];
+                            if (HAS_NEXT) {
+                                TmemWaitLdRegs16(rawCur);
+                            }
+                            if (LOAD) {
+                                if (c == 2) {
+                                    waitSecondHalf(); // chunk 4 is the first of the second half
+                                }
+                                TmemLd16(tLane + (c + 2) * 16, rawNxt);
+                            }
+                            const float2 eoff2 = make_float2(eoff, eoff);
+                            mxN = -INFINITY;
+#pragma unroll
+                            for (int k = 0; k < 16; k += 4) {
+                                float2 e[2];
+#pragma unroll
+                                for (int kk = 0; kk < 4; kk += 2) {
+                                    const int cc = k + kk;
+                                    if (HAS_NEXT) {
+                                        float2 tt = scalePair(rawCur[cc], rawCur[cc + 1], (c + 1) * 16 + cc, eoff2);
+                                        mxN = Max3(mxN, tt.x, tt.y);
+                                        nxt[cc] = __float_as_uint(tt.x);
+                                        nxt[cc + 1] = __float_as_uint(tt.y);
+                                    }
+                                    float2 x = make_float2(__uint_as_float(cur[cc]), __uint_as_float(cur[cc + 1]));
+                                    float2 w;
+                                    if (((cc >> 1) & 7) < TSA_FWD_POLY_PAIRS) {
+                                        w = PolyExp2Pair(x);
+                                    } else {
+                                        w = make_float2(FastExp2(x.x), FastExp2(x.y));
+                                    }
+                                    lacc2 = __fadd2_rn(lacc2, w);
+                                    if (HAS_VSCALE) {
+                                        e[kk >> 1] = __fmul2_rn(w, *reinterpret_cast<const float2 *>(svBuf + c * 16 + cc));
+                                    } else {
+                                        e[kk >> 1] = w;
+                                    }
+                                }
+                                pk[k >> 2] = PackE4M3x4(e[0].x, e[0].y, e[1].x, e[1].y);
+                            }
+                            TmemStN<4>(tLane + 32 * (c >> 1) + 4 * (c & 1), pk);
+                            if (c == 3) {
+                                handOver(0);
+                            }
+                            if (HAS_NEXT && __any_sync(0xffffffffu, (MODE != 3 || c < 7) && mxN > headroom)) {
+                                TmemWaitLdRegs16(rawNxt); // no load is in flight across the out-of-line call
+                                raise(mxN, c + 1, nxt);
+                            }
+                        };
+                        TmemLd16(tLane, rawBuf[0]);
+                        TmemWaitLdRegs16(rawBuf[0]);
+                        TmemLd16(tLane + 16, rawBuf[1]);
+                        {
+                            const float2 eoff2 = make_float2(eoff, eoff);
+#pragma unroll
+                            for (int cc = 0; cc < 16; cc += 2) {
+                                float2 tt = scalePair(rawBuf[0][cc], rawBuf[0][cc + 1], cc, eoff2);
+                                mxN = Max3(mxN, tt.x, tt.y);
+                                tBuf[0][cc] = __float_as_uint(tt.x);
+                                tBuf[0][cc + 1] = __float_as_uint(tt.y);
+                            }
+                        }
+                        if (__any_sync(0xffffffffu, mxN > headroom)) {
+                            TmemWaitLdRegs16(rawBuf[1]);
+                            raise(mxN, 0, tBuf[0]);
+                        }
+                        using TEven = std::integral_constant<int, 0>;
+                        using TOdd = std::integral_constant<int, 1>;
+                        if (D == 128) {
+#pragma unroll 1
+                            for (int c = 0; c < 6; c += 2) {
+                                step(std::integral_constant<int, 0>(), TEven(), c);
+                                step(std::integral_constant<int, 0>(), TOdd(), c + 1);
+                            }
+                            step(std::integral_constant<int, 1>(), TEven(), 6);
+                            step(std::integral_constant<int, 2>(), TOdd(), 7);
+                        } else {
+#pragma unroll 1
+                            for (int c = 0; c < 8; c += 2) {
+                                step(std::integral_constant<int, 3>(), TEven(), c);
+                                step(std::integral_constant<int, 3>(), TOdd(), c + 1);
+                            }
+                        }
+                    }
+                };
+                if (masked) {
+                    processTile(std::true_type());
+                } else {
+                    processTile(std::false_type());
+                }
+                handOver(1);
+                ++sCount;
+                ++kvCount;
+                ++tilesInItem;
+            }
+            if (failed) {
+                break;
+            }
+            if (flags & RF_LAST) {
+                // ---- epilogue of the item
+                if (tilesInItem > 0) {
+                    if (!wait(&misc.BarOFull, oCount & 1, kDevTimeoutMma)) {
+                        break;
+                    }
+                    ++oCount;
+                    TcFenceAfter();
+                }
+                const float lTot = (lacc2.x + lacc2.y) * (1.0f / 128.0f) + exp2f(-m);
+                const float outMult = (HAS_VSCALE ? invK : p.VVecScale) * (1.0f / 128.0f) / lTot;
+                if (rowOk && p.Lse.Valid()) {
+                    p.Lse.Row(head)[row] = m + log2f(lTot);
+                }
+                const int esz = (p.OutDtype == TSA_F32) ? 4 : 2;
+                char *oRow = p.Out.Row(rowOk ? row : 0) + (size_t)head * D * esz;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t o[32];
+                    if (tilesInItem > 0) {
+                        TmemLd32(tLane + TMEM_O_COL + c0, o);
+                        TmemWaitLdRegs(o);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            o[c] = 0;
+                        }
+                    }
+                    if (rowOk) {
+                        if (p.OutDtype == TSA_F32) {
+                            float4 *dst = reinterpret_cast<float4 *>(oRow + c0 * 4);
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4) {
+                                dst[c >> 2] = make_float4(__uint_as_float(o[c]) * outMult, __uint_as_float(o[c + 1]) * outMult,
+                                    __uint_as_float(o[c + 2]) * outMult, __uint_as_float(o[c + 3]) * outMult);
+                            }
+                        } else {
+                            uint4 *dst = reinterpret_cast<uint4 *>(oRow + c0 * 2);
+#pragma unroll
+                            for (int c = 0; c < 32; c += 8) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    float a = __uint_as_float(o[c + 2 * k]) * outMult, b = __uint_as_float(o[c + 2 * k + 1]) * outMult;
+                                    if (p.OutDtype == TSA_BF16) {
+                                        __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
+                                        w[k] = *reinterpret_cast<uint32_t *>(&hh);
+                                    } else {
+                                        w[k] = PackHalf2(a, b);
+                                    }
+                                }
+                                dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
                         }
                     }
                 }
+                // no "O has been read" signal is needed: these same threads arrive on BarP for the next item's first
+                // tile only after this read-out, and the PV that overwrites O is issued after that arrival
             }
         }
     }
-    TRC(12);
     TcFenceBefore();
     __syncthreads();
-    if (warp == CTRL_WARP) {
+    if (warp == FW_MMA_WARP) {
         TmemDealloc(tmem, TMEM_COLS);
     }
-    TRC(13);
 }
 
 // per head maximum of the V scale plane (normalises the weights' e4m3 range).  Scales are non-negative, so
@@ -631,6 +1122,12 @@ __global__ void __launch_bounds__(256) VRefKernel(P2D<float> vScale, int keyRows
 }
 
 // ---- raw int32 score tiles (parity hook for the kind::i8 accumulators) -------------------------
+struct TScoresMisc {
+    uint64_t BarQ, BarMma;
+    uint32_t TmemBase;
+};
+constexpr int SCORE_THREADS = 128;
+
 template <int D>
 __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, int lenQ, int lenK, int32_t *scores, int *status)
@@ -641,7 +1138,7 @@ __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_con
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem, *sK = smem + 128 * D;
-    TFwdMisc &misc = *reinterpret_cast<TFwdMisc *>(smem + 2 * 128 * D);
+    TScoresMisc &misc = *reinterpret_cast<TScoresMisc *>(smem + 2 * 128 * D);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int head = blockIdx.z, qTile = blockIdx.y, kTile = blockIdx.x;
     if (tid == 0) {
@@ -713,6 +1210,7 @@ __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_con
 }
 
 // ---- host side ---------------------------------------------------------------------------------
+
 static bool TmaCompatible(tsa_ptr2d a)
 {
     return a.data && ((uintptr_t)a.data % 16 == 0) && (a.stride_bytes % 16 == 0) && a.xsize > 0 && a.ysize > 0;
@@ -732,22 +1230,43 @@ bool Sm100FwdSupports(const tsa_att_cfg *cfg, tsa_ptr2d qk, tsa_ptr2d qv, tsa_pt
     return TmaCompatible(qk) && TmaCompatible(qv) && TmaCompatible(v);
 }
 
-size_t Sm100FwdWorkspaceBytes(int headCount)
+// workspace: per-head V-scale maxima, then the work-item counter
+static size_t VRefBytes(int headCount)
 {
     return (size_t)((headCount * sizeof(float) + 255) / 256 * 256);
 }
+size_t Sm100FwdWorkspaceBytes(int headCount)
+{
+    return VRefBytes(headCount) + 256;
+}
+
+static TFwdDump g_dump;
+void SetFwdScoreDump(const TFwdDump &d)
+{
+    g_dump = d;
+}
 
 template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
-static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const TFwdParams &fp, int qTiles, cudaStream_t stream)
+static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const TFwdParams &fp, cudaStream_t stream)
 {
     auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI>;
     int smemBytes = TFwdSmem<D>::TOTAL;
-    int rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes), "cudaFuncSetAttribute(forward)");
+    int dev = 0, smCount = 0;
+    int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc == TSA_OK) {
+        rc = CheckCuda(cudaDeviceGetAttribute(&smCount, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+    }
+    if (rc == TSA_OK) {
+        rc = CheckCuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes), "cudaFuncSetAttribute(forward)");
+    }
     if (rc != TSA_OK) {
         return rc;
     }
-    dim3 grid(qTiles, fp.HeadCount);
-    kern<<<grid, FWD_THREADS, smemBytes, stream>>>(mq, mk, mv, fp);
+    int ctas = 2 * smCount;
+    if (ctas > fp.TotalItems) {
+        ctas = fp.TotalItems;
+    }
+    kern<<<ctas, FW_THREADS, smemBytes, stream>>>(mq, mk, mv, fp);
     return CheckCuda(cudaGetLastError(), "tcgen05 forward launch");
 }
 
@@ -766,17 +1285,24 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     if (rc != TSA_OK) {
         return rc;
     }
+    const bool hasVs = p.VScale.Data != nullptr;
+    const size_t vrefBytes = VRefBytes(p.HeadCount);
     TFwdParams fp;
     fp.HeadCount = p.HeadCount;
     fp.OutRows = p.Len;
     fp.KeyRows = keyRows;
     fp.LenAttTiles = lenAttTiles;
+    fp.QTiles = (lenAttTiles + 1) / 2;
+    fp.TotalItems = fp.QTiles * p.HeadCount;
+    fp.Counter = reinterpret_cast<int *>((char *)workspace + vrefBytes);
     fp.Spans = p.Spans;
     fp.SpanPtr = p.SpanPtr;
     fp.QScale = p.QScale;
     fp.KScale = p.KScale;
     fp.VScale = p.VScale;
-    fp.VRef = nullptr;
+    fp.VRef = hasVs ? (const float *)workspace : nullptr;
+    fp.ScaleBulk = ((uintptr_t)p.KScale.Data % 16 == 0 && p.KScale.Stride % 16 == 0 &&
+        (!hasVs || ((uintptr_t)p.VScale.Data % 16 == 0 && p.VScale.Stride % 16 == 0))) ? 1 : 0;
     fp.Out = p.Out;
     fp.Lse = p.Lse;
     fp.GlobalScale = p.GlobalScale;
@@ -786,23 +1312,25 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     fp.Slope = p.Slope;
     fp.OutDtype = p.OutDtype;
     fp.Status = statusWord;
-    const bool hasVs = p.VScale.Data != nullptr;
+    fp.DumpScores = g_dump.Dst;
+    fp.DumpHead = g_dump.Head;
+    fp.DumpQTile = g_dump.QTile;
+    fp.DumpTile = g_dump.Tile;
+    // one clear covers the V-scale maxima and the counter behind them
+    rc = CheckCuda(cudaMemsetAsync(hasVs ? workspace : (void *)fp.Counter, 0, hasVs ? vrefBytes + 256 : 256, stream), "clearing the forward workspace");
+    if (rc != TSA_OK) {
+        return rc;
+    }
     if (hasVs) {
-        fp.VRef = (const float *)workspace;
-        rc = CheckCuda(cudaMemsetAsync(workspace, 0, p.HeadCount * sizeof(float), stream), "clearing the V-scale maxima");
-        if (rc != TSA_OK) {
-            return rc;
-        }
         dim3 vgrid((keyRows + VREF_CHUNK - 1) / VREF_CHUNK, p.HeadCount);
         VRefKernel<<<vgrid, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
     }
-    const int qTiles = (lenAttTiles + 1) / 2;
     const bool i8 = cfg->qk_dtype == TSA_I8;
     const bool alibi = p.Slope != 0.0f;
 #define TSA_FWD_CASE(DD, I8, VS)                                                                         \
     if (D == DD && i8 == I8 && hasVs == VS) {                                                            \
-        return alibi ? LaunchFwdT<DD, I8, VS, true>(mq, mk, mv, fp, qTiles, stream)                      \
-                     : LaunchFwdT<DD, I8, VS, false>(mq, mk, mv, fp, qTiles, stream);                    \
+        return alibi ? LaunchFwdT<DD, I8, VS, true>(mq, mk, mv, fp, stream)                              \
+                     : LaunchFwdT<DD, I8, VS, false>(mq, mk, mv, fp, stream);                            \
     }
     TSA_FWD_CASE(64, false, false)
     TSA_FWD_CASE(64, false, true)
@@ -837,10 +1365,3 @@ int LaunchScoresI8(tsa_ptr2d qk, tsa_ptr2d qv, int headCount, int headDim, int l
 }
 
 } // namespace tsa
-
-#ifdef TSA_FWD_TRACE
-extern "C" __attribute__((visibility("default"))) int tsa_debug_trace(long long *dst, int n)
-{
-    return (int)cudaMemcpyFromSymbol(dst, tsa::g_trace, n * sizeof(long long));
-}
-#endif

@@ -38,6 +38,13 @@ int LaunchGenericBwd(const TGenParams &p, cudaStream_t stream);
 int LaunchDScale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa_ptr2d dScale,
     int headCount, int headDimV, int len, cudaStream_t stream);
 
+// parity hook of the int8 forward: where the kernel stores the raw s32 scores of one key tile as it read them
+struct TFwdDump {
+    int32_t *Dst = nullptr; // [128][128] int32 in device memory, null = off
+    int Head = 0, QTile = 0, Tile = 0;
+};
+void SetFwdScoreDump(const TFwdDump &d);
+
 // tcgen05 forward (att_fwd_sm100.cu).  Returns TSA_UNSUPPORTED when the configuration is outside
 // the tensor-core path (the caller then uses the generic kernels).
 bool Sm100FwdSupports(const tsa_att_cfg *cfg, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v);

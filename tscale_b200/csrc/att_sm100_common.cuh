@@ -50,6 +50,33 @@ __device__ __forceinline__ bool WaitBarA(uint64_t *bar, uint32_t parity, const i
     }
 }
 
+// Polling wait with a pause between polls: a waiting warp issues a handful of instructions every SLEEP_NS instead of
+// spinning, so it does not take issue slots from the warps that share its scheduler (a tight try_wait loop of the
+// MMA-issuing warp cost the softmax warp next to it a third of its issue rate).  Returns false when the CTA's abort
+// flag is set or after about a second.
+template <int SLEEP_NS>
+__device__ __forceinline__ bool WaitBarSleep(uint64_t *bar, uint32_t parity, const int *abortFlag)
+{
+    if (MbarTryWaitFast(bar, parity)) {
+        return true;
+    }
+    long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; ++i) {
+            __nanosleep(SLEEP_NS);
+            if (MbarTryWaitFast(bar, parity)) {
+                return true;
+            }
+        }
+        if (*(const volatile int *)abortFlag) {
+            return false;
+        }
+        if (clock64() - t0 > WAIT_CYCLES) {
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void MbarArrive(uint64_t *bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
@@ -141,11 +168,32 @@ struct TTileIter {
 template <int N>
 __device__ __forceinline__ void TmemStN(uint32_t taddr, const uint32_t *r);
 template <>
+__device__ __forceinline__ void TmemStN<4>(uint32_t taddr, const uint32_t *r)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+template <>
 __device__ __forceinline__ void TmemStN<8>(uint32_t taddr, const uint32_t *r)
 {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  :
                  : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ void TmemLd2(uint32_t taddr, uint32_t &a, uint32_t &b)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void TmemSt2(uint32_t taddr, uint32_t a, uint32_t b)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void TmemLd8(uint32_t taddr, uint32_t *r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
                  : "memory");
 }
 
@@ -334,6 +382,20 @@ __device__ __forceinline__ uint32_t ResidualE4M3x2(float a, float b, uint32_t hi
     uint16_t r;
     asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(diff));
     return r;
+}
+
+// four packed e4m3 values times a power of two given as an f16 pair (exact unless the result leaves the e4m3 range)
+__device__ __forceinline__ uint32_t ScaleE4M3x4(uint32_t w, uint32_t alphaH2)
+{
+    uint32_t lo, hi;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"((uint16_t)(w & 0xffff)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((uint16_t)(w >> 16)));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(lo) : "r"(alphaH2));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(hi) : "r"(alphaH2));
+    uint16_t a, b;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(a) : "r"(lo));
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(b) : "r"(hi));
+    return (uint32_t)a | ((uint32_t)b << 16);
 }
 
 // exact int32 -> float for |x| < 2^22 without the conversion pipe: bits(1.5 * 2^23 + x) - 1.5 * 2^23

@@ -99,6 +99,14 @@ __device__ __forceinline__ void TmaLoad2D(void *smemDst, const void *tensorMap, 
         : "r"(SmemAddr(smemDst)), "l"(tensorMap), "r"(x), "r"(y), "r"(SmemAddr(bar))
         : "memory");
 }
+// untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void BulkLoad(void *smemDst, const void *gsrc, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(SmemAddr(smemDst)), "l"(gsrc), "r"(bytes), "r"(SmemAddr(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void PrefetchTensorMap(const void *tensorMap)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensorMap) : "memory");
@@ -260,6 +268,148 @@ __device__ __forceinline__ void MmaF16TS(uint32_t dTmem, uint32_t aTmem, uint64_
         : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// ---- grouped issue -----------------------------------------------------------------------------
+// One asm block per group of MMAs on the same accumulator: the descriptor increments happen inside the block, so the
+// compiler moves the base values to the uniform datapath once per group instead of once per instruction, and the
+// issuing thread (a single thread whose instruction stream sits on the critical path between the softmax warps'
+// "weights written" and "scores ready") gets through a group in a fraction of the time.
+//
+// D[tmem] = A[smem] * B[smem] over KSTEPS steps of 32 bytes along K (both operands K-major, descriptor address field in
+// 16-byte units), then a commit on `bar`.  I8: kind::i8, else kind::f8f6f4.
+template <int KSTEPS, bool I8>
+__device__ __forceinline__ void MmaGroupSSCommit(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint64_t *bar)
+{
+    static_assert(KSTEPS == 2 || KSTEPS == 4, "two or four K steps");
+    if (KSTEPS == 2) {
+        if (I8) {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred pf, pt;\n\t"
+                ".reg .b64 a1, b1;\n\t"
+                "setp.ne.u32 pf, 0, 0;\n\t"
+                "setp.eq.u32 pt, 0, 0;\n\t"
+                "add.u64 a1, %1, 2;\n\t"
+                "add.u64 b1, %2, 2;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, pf;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, pt;\n\t"
+                "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"
+                "}"
+                :
+                : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(SmemAddr(bar))
+                : "memory");
+        } else {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred pf, pt;\n\t"
+                ".reg .b64 a1, b1;\n\t"
+                "setp.ne.u32 pf, 0, 0;\n\t"
+                "setp.eq.u32 pt, 0, 0;\n\t"
+                "add.u64 a1, %1, 2;\n\t"
+                "add.u64 b1, %2, 2;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pf;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, pt;\n\t"
+                "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"
+                "}"
+                :
+                : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(SmemAddr(bar))
+                : "memory");
+        }
+    } else {
+        if (I8) {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred pf, pt;\n\t"
+                ".reg .b64 a1, b1, a2, b2, a3, b3;\n\t"
+                "setp.ne.u32 pf, 0, 0;\n\t"
+                "setp.eq.u32 pt, 0, 0;\n\t"
+                "add.u64 a1, %1, 2;\n\t"
+                "add.u64 b1, %2, 2;\n\t"
+                "add.u64 a2, %1, 4;\n\t"
+                "add.u64 b2, %2, 4;\n\t"
+                "add.u64 a3, %1, 6;\n\t"
+                "add.u64 b3, %2, 6;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, pf;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, pt;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], a2, b2, %3, pt;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], a3, b3, %3, pt;\n\t"
+                "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"
+                "}"
+                :
+                : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(SmemAddr(bar))
+                : "memory");
+        } else {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred pf, pt;\n\t"
+                ".reg .b64 a1, b1, a2, b2, a3, b3;\n\t"
+                "setp.ne.u32 pf, 0, 0;\n\t"
+                "setp.eq.u32 pt, 0, 0;\n\t"
+                "add.u64 a1, %1, 2;\n\t"
+                "add.u64 b1, %2, 2;\n\t"
+                "add.u64 a2, %1, 4;\n\t"
+                "add.u64 b2, %2, 4;\n\t"
+                "add.u64 a3, %1, 6;\n\t"
+                "add.u64 b3, %2, 6;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pf;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a1, b1, %3, pt;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a2, b2, %3, pt;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a3, b3, %3, pt;\n\t"
+                "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"
+                "}"
+                :
+                : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(SmemAddr(bar))
+                : "memory");
+        }
+    }
+}
+
+// D[tmem] (+)= A[tmem] * B[smem], kind::f8f6f4, two K steps of 32: A at aTmem and aTmem + 32 columns, B descriptors
+// bDesc and bDesc + bStep (16-byte units); `accumulate` applies to the first step.  With residual: two more steps with A
+// 8 columns further on and the same B.
+__device__ __forceinline__ void MmaPairF8TS(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t bStep, uint32_t idesc,
+    uint32_t accumulate, bool withResidual)
+{
+    if (!withResidual) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p0, pt;\n\t"
+            ".reg .b64 b1, st;\n\t"
+            ".reg .b32 a1;\n\t"
+            "setp.ne.b32 p0, %4, 0;\n\t"
+            "setp.eq.u32 pt, 0, 0;\n\t"
+            "cvt.u64.u32 st, %5;\n\t"
+            "add.u64 b1, %2, st;\n\t"
+            "add.u32 a1, %1, 32;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a1], b1, %3, pt;\n\t"
+            "}"
+            :
+            : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(bStep)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p0, pt;\n\t"
+            ".reg .b64 b1, st;\n\t"
+            ".reg .b32 a1, a2, a3;\n\t"
+            "setp.ne.b32 p0, %4, 0;\n\t"
+            "setp.eq.u32 pt, 0, 0;\n\t"
+            "cvt.u64.u32 st, %5;\n\t"
+            "add.u64 b1, %2, st;\n\t"
+            "add.u32 a1, %1, 32;\n\t"
+            "add.u32 a2, %1, 8;\n\t"
+            "add.u32 a3, %1, 40;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a1], b1, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a2], %2, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a3], b1, %3, pt;\n\t"
+            "}"
+            :
+            : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(bStep)
+            : "memory");
+    }
+}
+
 // arrive on the mbarrier when all MMAs issued so far by this thread have completed
 __device__ __forceinline__ void MmaCommit(uint64_t *bar)
 {

@@ -141,11 +141,24 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_
     }
     cudaStream_t s = (cudaStream_t)stream;
     if (Sm100FwdSupports(cfg, qk, qv, v)) {
-        size_t need = vScale.data ? Sm100FwdWorkspaceBytes(headCount) : 0; // per-head V-scale maxima
-        TSA_REQUIRE(need == 0 || (workspace && workspaceBytes >= need), "tsa_att_fwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
+        size_t need = Sm100FwdWorkspaceBytes(headCount); // per-head V-scale maxima and the work-item counter
+        TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_fwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
+        TSA_REQUIRE((uintptr_t)workspace % 16 == 0, "tsa_att_fwd: workspace must be 16-byte aligned");
         return LaunchSm100Fwd(cfg, p, qk, qv, v, lenAttTiles, qv.ysize, workspace, statusWord, s);
     }
     return LaunchGenericFwd(p, s);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_set_score_dump(int32_t *dst, int head, int queryTile, int keyTile)
+{
+    TSA_REQUIRE(dst == nullptr || (head >= 0 && queryTile >= 0 && keyTile >= 0), "tsa_att_fwd_set_score_dump: negative index");
+    TFwdDump d;
+    d.Dst = dst;
+    d.Head = head;
+    d.QTile = queryTile;
+    d.Tile = keyTile;
+    SetFwdScoreDump(d);
+    return TSA_OK;
 }
 
 extern "C" __attribute__((visibility("default"))) size_t tsa_att_bwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len)
