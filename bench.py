@@ -1,17 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the quantized attention path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--workload prefill125m|train15b|decode|longctx|infer|neighbours] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload longctx|prefill125m|train15b|decode|infer|neighbours] [--impl reference]
 
-Default workload `prefill125m` is the 125M-style prefill forward: 16 fragments x 4096 tokens, 12 heads x 64,
-e4m3 Q/K/V with per-row f32 scales, bf16 output; one step = 3 window-64 layers (ALiBi slope 0.5) + 1 full
-causal layer.  Inputs are seeded synthetic N(0,1)*0.5, quantised on the GPU by the library's abs-max
-quantiser.  The metric is algorithmic attention TFLOP/s: 4 * D * (attended pairs) per (fragment, head),
-masked-out work inside partially filled tiles not counted.
+Default workload `longctx` is the long-context prefill, the largest single-GPU configuration of the path:
+4 fragments x 32768 tokens, 32 heads x 128, full causal, e4m3 Q/K/V with per-row f32 scales, bf16 output.
+Inputs are seeded synthetic N(0,1)*0.5, quantised on the GPU by the library's abs-max quantiser.  The metric is
+algorithmic attention TFLOP/s: 4 * D * (attended pairs) per (fragment, head), masked-out work inside partially
+filled tiles not counted.
 
-One process per GPU.  With N > 1 every rank runs the same per-GPU workload on its own fragments (the path
-shards by fragment x head with no exchange step), so scaling is weak and `value` is the sum over ranks
-divided by the slowest rank's time; `--gather` adds the NCCL all-gather of the bf16 outputs.
+One process per GPU.  With N > 1 the 128 (fragment, head) units of the ONE batch are split contiguously over the
+ranks (tsa_shard_range / tsa_shard_rects), every rank runs tsa_att_fwd on its units only, and the bf16 output
+blocks are all-gathered over NCCL inside the timed region, slice by slice so that the gather of one slice runs
+under the next slice's kernel: strong scaling, `value` = the whole batch's flops / the slowest rank's step.
+At N = 1 the line also carries short runs of the other workloads (`also`: prefill125m, train15b, decode).
+
+The other workloads (`--workload prefill125m|train15b|decode|infer`) keep per-GPU work fixed (weak scaling).
 
 `--impl reference` times the reference's own CPU attention (oracle/_ref, else the oracle port) on the host
 cores, on a bounded sample of the same workload.
@@ -28,7 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from tscale_b200.benchutil import ClockSampler, load_peaks  # noqa: E402
+from benchlib.util import ClockSampler, load_peaks  # noqa: E402
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -48,48 +52,92 @@ WORKLOADS = {
                      layers=[(0, 0.0), (256, 0.0)], bwd=True, seed=2),
     "longctx": dict(frags=4, seq=32768, heads=32, d=128, qk="e4m3", v="e4m3", layers=[(0, 0.0)], bwd=False, seed=4),
 }
+SM_COUNT = 148           # B200
+EX2_PER_CLK_PER_SM = 16  # special-function results per clock and SM: one exponential per attended pair
 
 
 def layer_flops(w, window):
     return 4.0 * w["d"] * pairs_window(w["seq"], window) * w["frags"] * w["heads"]
 
 
+def workload_config(name, w, strong=False):
+    cfg = {"workload": name, "fragments": w["frags"], "seq_len": w["seq"], "heads": w["heads"], "head_dim": w["d"],
+           "qk_dtype": w["qk"], "v_dtype": w["v"],
+           "layers": [{"window": "full" if win <= 0 else win, "alibi_slope": sl} for win, sl in w["layers"]],
+           "backward": w["bwd"], "l2": "inputs larger than L2 (each layer has its own Q/K/V set)"}
+    if strong:
+        cfg["sharding"] = ("the batch's fragment x head units split contiguously over the ranks; "
+                           "bf16 outputs all-gathered over NCCL inside the timed region")
+    else:
+        cfg["sharding"] = "fragment x head, per-GPU work fixed"
+    return cfg
+
+
 # ----------------------------------------------------------------------------------------------------
-# CPU arm
-def cpu_sample_inputs(w, layer_idx, n_frags, seed):
-    """A bounded sample of the workload for the CPU arm: the first n_frags fragments of one layer, generated
-    with the same recipe as the GPU inputs (N(0,1)*0.5, abs-max 8-bit quantisation) through the oracle."""
+# CPU arm: the reference's own CPU attention on a bounded sample
+def cpu_sample_inputs(w, layer_idx, heads, seed):
+    """One fragment of the workload's inputs for `heads` heads, generated with the GPU recipe (N(0,1)*0.5, abs-max 8-bit
+    quantisation) through the oracle, dequantised to the f32 the reference's CPU code takes."""
     from oracle import oracle as O
     rng = np.random.default_rng(seed * 1000 + layer_idx)
-    length = n_frags * w["seq"]
-    hd = w["heads"] * w["d"]
+    length, hd = w["seq"], heads * w["d"]
     res = []
-    for name, dt in (("q", w["qk"]), ("k", w["qk"]), ("v", w["v"])):
+    for _, dt in (("q", w["qk"]), ("k", w["qk"]), ("v", w["v"])):
         x = (rng.standard_normal((length, hd)) * 0.5).astype(np.float32)
         b, s = O.quant_rows("absmax", dt, 0.0, x, w["d"])
-        deq = (O.dequant(b, dt).reshape(length, w["heads"], w["d"]) * s.T[:, :, None]).reshape(length, hd)
+        deq = (O.dequant(b, dt).reshape(length, heads, w["d"]) * s.T[:, :, None]).reshape(length, hd)
         res.append(np.ascontiguousarray(deq, dtype=np.float32))
     return res
 
 
+def row_sample_spans(seq, window, every):
+    """Spans of one fragment in which only every `every`-th query row attends (rows without spans cost the reference's
+    ComputeValLookup nothing, code/gpt/compute/gpt_cpu.cpp:411-431): a row subsample of the workload.  Returns
+    (spans, span_ptr, attended pairs)."""
+    spans, ptr, pairs = [], [0], 0
+    for i in range(seq):
+        lo = 0 if window <= 0 else max(0, i - window)
+        if i % every == every - 1 and i - 1 >= lo:
+            spans.append((lo, i - 1))
+            pairs += i - lo
+        ptr.append(len(spans))
+    return np.array(spans, dtype=np.int32).reshape(-1, 2), np.array(ptr, dtype=np.int32), pairs
+
+
+def make_cpu_sample(w):
+    """About 10-20 s of host work: per distinct layer type one fragment, a few heads, every k-th query row."""
+    budget_pairs = 6.0e7  # attended pairs per pass over the sample (all layer types together)
+    kinds = []
+    for idx, (window, slope) in enumerate(w["layers"]):
+        if (window, slope) not in [(k[1], k[2]) for k in kinds]:
+            kinds.append((idx, window, slope))
+    sample = []
+    for idx, window, slope in kinds:
+        heads = min(w["heads"], 8)
+        full = pairs_window(w["seq"], window) * heads
+        every = max(1, int(np.ceil(full / (budget_pairs / len(kinds)))))
+        spans, ptr, pairs = row_sample_spans(w["seq"], window, every)
+        q, k, v = cpu_sample_inputs(w, idx, heads, w["seed"])
+        sample.append(dict(window=window, slope=slope, heads=heads, every=every, spans=spans, ptr=ptr, pairs=pairs, q=q, k=k, v=v))
+    return sample
+
+
 def run_cpu_sample(w, sample, threads):
-    """Runs the reference's CPU forward on the sample; returns (seconds, flops, kind)."""
+    """Runs the reference's CPU forward on the sample, one (layer type, head) job per host thread; returns
+    (seconds, flops, kind)."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import oracle as O
-    use_ref = O.ref() is not None
+    use_ref = "fast" if O.ref(fast=True) is not None else (O.ref() is not None)
     kind = "reference" if use_ref else "port"
     O.set_threads(1)
-    jobs = []
-    flops = 0.0
-    for (window, slope, n_frags, q, k, v) in sample:
-        spans, ptr = O.window_spans([w["seq"]], window)
-        for f in range(n_frags):
-            rows = slice(f * w["seq"], (f + 1) * w["seq"])
-            for h in range(w["heads"]):
-                cols = slice(h * w["d"], (h + 1) * w["d"])
-                jobs.append((np.ascontiguousarray(q[rows, cols]), np.ascontiguousarray(k[rows, cols]),
-                             np.ascontiguousarray(v[rows, cols]), spans, ptr, slope))
-        flops += 4.0 * w["d"] * pairs_window(w["seq"], window) * n_frags * w["heads"]
+    jobs, flops = [], 0.0
+    d = w["d"]
+    for smp in sample:
+        for h in range(smp["heads"]):
+            cols = slice(h * d, (h + 1) * d)
+            jobs.append((np.ascontiguousarray(smp["q"][:, cols]), np.ascontiguousarray(smp["k"][:, cols]),
+                         np.ascontiguousarray(smp["v"][:, cols]), smp["spans"], smp["ptr"], smp["slope"]))
+        flops += 4.0 * d * smp["pairs"] * smp["heads"]
 
     def one(job):
         q1, k1, v1, spans, ptr, slope = job
@@ -101,26 +149,32 @@ def run_cpu_sample(w, sample, threads):
     return time.perf_counter() - t0, flops, kind
 
 
-def make_cpu_sample(w):
-    # about 10-20 s of host work: one fragment of a window layer and one of the widest layer, all heads
-    sample = []
-    done = set()
-    for idx, (window, slope) in enumerate(w["layers"]):
-        if (window, slope) in done:
-            continue
-        done.add((window, slope))
-        q, k, v = cpu_sample_inputs(w, idx, 1, w["seed"])
-        sample.append((window, slope, 1, q, k, v))
-    return sample
-
-
 def sample_text(w, sample):
-    return "; ".join("%d fragment(s) x %d tokens x %d heads, window %s, slope %g" %
-                     (n, w["seq"], w["heads"], "full" if win <= 0 else win, sl) for (win, sl, n, _, _, _) in sample)
+    return "; ".join("1 fragment x %d tokens x %d heads, window %s, slope %g, every %squery row" %
+                     (w["seq"], s["heads"], "full" if s["window"] <= 0 else s["window"], s["slope"],
+                      "" if s["every"] == 1 else "%d-th " % s["every"]) for s in sample)
 
 
-# ----------------------------------------------------------------------------------------------------
-def reference_arm(args, w, rank):
+def cpu_build_text(kind):
+    if kind != "reference":
+        return "oracle port (oracle/tsa_oracle.cpp)"
+    return "the reference's own sources, -O3 -march=x86-64-v3 -mavxvnni (oracle/_ref/libtsa_ref_fast.so), one job per host thread"
+
+
+def cpu_baseline_block(w, seconds_target=10.0):
+    sample = make_cpu_sample(w)
+    threads = os.cpu_count() or 1
+    total, reps = 0.0, 0
+    while reps < 2 or (total < seconds_target and reps < 50):
+        sec, flops, kind = run_cpu_sample(w, sample, threads)
+        total += sec
+        reps += 1
+    sec = total / reps
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": sample_text(w, sample) + " (forward only), %d passes" % reps, "seconds": total, "build": cpu_build_text(kind)}
+
+
+def reference_arm(args, name, w, rank):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
@@ -134,229 +188,20 @@ def reference_arm(args, w, rank):
     value = flops / (ms * 1e-3) / 1e12
     line = {
         "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, w),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample_text(w, sample)},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if name == "longctx" else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(name, w, strong=(name == "longctx")),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample_text(w, sample),
+                         "build": cpu_build_text(kind)},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def workload_config(args, w):
-    return {"workload": args.workload, "fragments": w["frags"], "seq_len": w["seq"], "heads": w["heads"], "head_dim": w["d"],
-            "qk_dtype": w["qk"], "v_dtype": w["v"], "layers": [{"window": "full" if win <= 0 else win, "alibi_slope": sl} for win, sl in w["layers"]],
-            "backward": w["bwd"], "l2": "inputs larger than L2 (each layer has its own Q/K/V set)", "sharding": "fragment x head, per-GPU work fixed"}
-
-
 # ----------------------------------------------------------------------------------------------------
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill125m", choices=sorted(WORKLOADS) + ["decode", "infer", "neighbours"])
-    ap.add_argument("--gather", action="store_true", help="all-gather the bf16 outputs over NCCL inside the timed region")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
-    if args.workload == "decode":
-        from tscale_b200 import bench_decode
-        return bench_decode.run(args, rank, world, local_rank)
-    if args.workload == "infer":
-        from tscale_b200 import bench_infer
-        return bench_infer.run(args, rank, world, local_rank)
-    if args.workload == "neighbours":
-        from tscale_b200 import bench_neighbours
-        return bench_neighbours.run(args, rank, world, local_rank)
-
-    w = dict(WORKLOADS[args.workload])
-    if args.frags > 0:
-        w["frags"] = args.frags
-    if args.impl == "reference":
-        return reference_arm(args, w, rank)
-
-    import torch
-    import torch.distributed as dist
-    from tscale_b200 import ops
-
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
-    frag_lens = [w["seq"]] * w["frags"]
-    length = sum(frag_lens)
-    heads, d = w["heads"], w["d"]
-    hd = heads * d
-    masks = {}
-    for window, _ in w["layers"]:
-        if window not in masks:
-            masks[window] = ops.Mask.window(frag_lens, window)
-            masks[window].dev(dev)
-    grad_dtype = torch.bfloat16
-    cfg = ops.make_cfg(w["qk"], w["v"], d, d, out_dtype=torch.bfloat16, grad_dtype=grad_dtype)
-
-    # inputs: one Q/K/V set per layer (each rank its own fragments: seed offset by rank)
-    gen = torch.Generator(device=dev)
-    layers = []
-    for idx, (window, slope) in enumerate(w["layers"]):
-        gen.manual_seed(w["seed"] * 1000 + idx + 100000 * rank)
-        item = {"window": window, "slope": slope}
-        for name, dt in (("q", w["qk"]), ("k", w["qk"]), ("v", w["v"])):
-            x = torch.randn((length, hd), generator=gen, device=dev, dtype=torch.float32) * 0.5
-            item[name], item["s" + name] = ops.quant_rows(x, "absmax", dt, d)
-            del x
-        item["out"] = torch.empty((length, hd), dtype=torch.bfloat16, device=dev)
-        item["lse"] = torch.empty((heads, length), dtype=torch.float32, device=dev)
-        if w["bwd"]:
-            item["d_out"] = (torch.randn((length, hd), generator=gen, device=dev, dtype=torch.float32) * 1e-2).to(grad_dtype)
-        layers.append(item)
-    workspace = torch.empty(1 << 20, dtype=torch.uint8, device=dev)
-    bwd_ws = None
-    if w["bwd"]:
-        from tscale_b200 import abi
-        import ctypes
-        bwd_ws = torch.empty(max(1, abi.lib().tsa_att_bwd_workspace_bytes(ctypes.byref(cfg), heads, length)), dtype=torch.uint8, device=dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    gathered = None
-    pending = []
-    if args.gather and world > 1:
-        gathered = [torch.empty((world, length, hd), dtype=torch.bfloat16, device=dev) for _ in layers]
-
-    launches = [0]
-    dom = max(range(len(layers)), key=lambda i: layer_flops(w, layers[i]["window"]))  # dominant layer
-    dom_events = []
-
-    def run_layer(item, record=None):
-        if record is not None:
-            e0 = torch.cuda.Event(enable_timing=True)
-            e1 = torch.cuda.Event(enable_timing=True)
-            e0.record()
-        ops.att_fwd(cfg, item["q"], item["k"], item["v"], item["sk"], masks[item["window"]], item["slope"], heads,
-                    qk_scale=item["sq"], v_scale=item["sv"], out=item["out"], lse=item["lse"], workspace=workspace, status=status)
-        launches[0] += 2  # per-head V-scale maximum + attention kernel
-        if record is not None:
-            e1.record()
-            record.append((e0, e1))
-        if w["bwd"]:
-            ops.att_bwd(cfg, item["q"], item["k"], item["v"], item["sk"], item["d_out"], item["out"], item["lse"],
-                        masks[item["window"]], item["slope"], heads, qk_scale=item["sq"], v_scale=item["sv"], workspace=bwd_ws,
-                        status=status)
-            launches[0] += 6  # dScale, bf16 widening of Q / K / V, dQ kernel, dK/dV kernel
-        if gathered is not None:
-            # NCCL runs the gather on its own stream: the next layer's kernels overlap with it
-            pending.append(dist.all_gather_into_tensor(gathered[len(pending) % len(gathered)].view(-1), item["out"].view(-1), async_op=True))
-
-    def step(record=None):
-        for i, item in enumerate(layers):
-            run_layer(item, record if i == dom else None)
-        while pending:
-            pending.pop().wait()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    assert int(status.item()) == 0, "device status %#x during warm-up" % int(status.item())
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    launches[0] = 0
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        step(dom_events)
-    t1.record()
-    barrier()
-    ms_total = t0.elapsed_time(t1)
-    clocks = sampler.stop() if rank == 0 else None
-    assert int(status.item()) == 0, "device status %#x in the timed region" % int(status.item())
-    tt = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms_step = float(tt.item()) / args.steps
-    fl_step = sum(layer_flops(w, it["window"]) for it in layers) * (3.5 if w["bwd"] else 1.0)  # bwd = 10*D*pairs (5 GEMMs)
-    value = fl_step * world / (ms_step * 1e-3) / 1e12
-
-    dom_ms = float(np.mean([a.elapsed_time(b) for a, b in dom_events]))
-    dom_flops = layer_flops(w, layers[dom]["window"])
-
-    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step)
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    peaks = load_peaks()
-    fp8_peak = measure_fp8_peak(torch, dev)
-    int8_peak = measure_int8_peak(torch, dev)
-    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
-    roofline = {
-        "bound": "tensor", "kernel": "FwdSm100Kernel (full-causal layer, %s QK^T, e4m3 PV)" % w["qk"],
-        "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-        "peak_source": "MEASURED_PEAKS.json bf16 burst (%s)" % peaks["_source"],
-        "peak_fp8_measured": fp8_peak, "frac_fp8_measured": (achieved / fp8_peak) if fp8_peak else None,
-        "peak_fp8_nominal": 4500.0, "frac_fp8_nominal": achieved / 4500.0,
-        "peak_int8_measured": int8_peak, "frac_int8_measured": (achieved / int8_peak) if int8_peak else None,
-        "ms_per_launch": dom_ms, "algorithmic_flops_per_launch": dom_flops, "traffic": None,
-        "timed": "CUDA events around the layer's tsa_att_fwd call (V-scale maximum kernel of a few microseconds + the attention kernel)",
-    }
-    if args.workload == "prefill125m":
-        # ncu capture of this kernel on 2 fragments (profiles/fwd_sm100_e4m3_d64_fullcausal_2frag.md): 20.2 MB read, 0 written
-        # to DRAM while the kernel runs; traffic grows with the fragment count
-        roofline["traffic"] = 20.2e6 / 2 * w["frags"]
-        roofline["traffic_source"] = "dram bytes of a 2-fragment ncu capture scaled by fragments; algorithmic input bytes %.1f MB" % (
-            3 * w["frags"] * w["seq"] * heads * d / 1e6)
-    cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline:
-        sample = make_cpu_sample(w)
-        threads = os.cpu_count() or 1
-        # repeated until about 10 s of host work have been timed (at least 3 passes over the sample)
-        total, reps = 0.0, 0
-        while reps < 3 or (total < 10.0 and reps < 50):
-            sec, flops, kind = run_cpu_sample(w, sample, threads)
-            total += sec
-            reps += 1
-        sec = total / reps
-        cpu_baseline = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
-                        "sample": sample_text(w, sample) + " (forward only), %d passes" % reps, "seconds": total}
-    line = {
-        "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "e4m3" if w["qk"] == "e4m3" else "i8+e4m3", "data": "synthetic", "config": workload_config(args, w),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches[0], "roofline": roofline, "cpu_baseline": cpu_baseline,
-    }
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-
-
+# peaks measured on this GPU (cuBLASLt through torch), the way MEASURED_PEAKS.json measured bf16
 def measure_fp8_peak(torch, dev):
-    """Dense e4m3 GEMM rate of this GPU (cuBLASLt through torch._scaled_mm), the way the bf16 peak was measured."""
     try:
         n = 8192
         a = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn)
@@ -379,8 +224,6 @@ def measure_fp8_peak(torch, dev):
 
 
 def measure_int8_peak(torch, dev):
-    """Dense int8 x int8 -> int32 GEMM rate of this GPU (cuBLASLt through torch._int_mm), in TOP/s; None if the library
-    has no such kernel here."""
     try:
         n = 8192
         a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
@@ -397,11 +240,412 @@ def measure_int8_peak(torch, dev):
             torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1))
         return 2.0 * n ** 3 / (best * 1e-3) / 1e12
-    except Exception:  # noqa: BLE001  (a peak probe must not break the benchmark)
+    except Exception:  # noqa: BLE001
         return None
 
 
-def run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step):
+_PEAK_CACHE = {}
+
+
+def tensor_roofline(torch, dev, w, kernel, achieved, ms, flops, clocks):
+    """Roofline block of a tensor-bound attention kernel: the denominator is the measured dense GEMM rate of the operand
+    type the kernel's MMAs run in (e4m3 or int8), the bf16 figure of MEASURED_PEAKS.json is kept beside it, and
+    frac_mufu_bound compares with the ceiling one exponential per attended pair puts on the path at the sampled clock."""
+    peaks = load_peaks()
+    if "fp8" not in _PEAK_CACHE:
+        _PEAK_CACHE["fp8"] = measure_fp8_peak(torch, dev)
+        _PEAK_CACHE["int8"] = measure_int8_peak(torch, dev)
+    fp8_peak, int8_peak = _PEAK_CACHE["fp8"], _PEAK_CACHE["int8"]
+    if w["qk"] == "i8":
+        peak, src = int8_peak, "int8 x int8 -> int32 GEMM 8192^3 through cuBLASLt, measured in this run (QK^T runs as kind::i8, PV as kind::f8f6f4)"
+    else:
+        peak, src = fp8_peak, "e4m3 GEMM 8192^3 through cuBLASLt, measured in this run"
+    if not peak:
+        peak, src = 2.0 * peaks["bf16_tflops"], "2 x MEASURED_PEAKS.json bf16 burst (the 8-bit GEMM probe failed)"
+    mhz = (clocks or {}).get("sm_mhz") or 1965.0
+    mufu = EX2_PER_CLK_PER_SM * SM_COUNT * mhz * 1e6 * 4.0 * w["d"] / 1e12
+    return {
+        "bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+        "peak_source": src, "peak_fp8_measured": fp8_peak, "peak_int8_measured": int8_peak,
+        "peak_bf16_measured": peaks["bf16_tflops"], "frac_bf16_measured": achieved / peaks["bf16_tflops"],
+        "peak_fp8_nominal": 4500.0, "frac_fp8_nominal": achieved / 4500.0,
+        "mufu_bound_tflops": mufu, "frac_mufu_bound": achieved / mufu,
+        "mufu_bound_note": "one ex2 per attended pair at %d results/clk/SM x %d SMs x %.0f MHz, 4*D flops per pair" % (
+            EX2_PER_CLK_PER_SM, SM_COUNT, mhz),
+        "ms_per_launch": ms, "algorithmic_flops_per_launch": flops, "traffic": None,
+    }
+
+
+# ----------------------------------------------------------------------------------------------------
+# default workload: one long-context batch, strong scaling over the ranks
+def run_longctx(args, name, w, rank, world, local_rank, quick=False):
+    import torch
+    import torch.distributed as dist
+    from tscale_b200 import ops, shard
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    frags, seq, heads, d = w["frags"], w["seq"], w["heads"], w["d"]
+    hd = heads * d
+    window, slope = w["layers"][0]
+    rects = shard.rank_rects(frags, heads, world, rank)
+    assert len(rects) == 1, "the bench shards %d units over %d ranks into one rectangle per rank" % (frags * heads, world)
+    f0, f1, h0, h1 = rects[0]
+    nf, nh = f1 - f0, h1 - h0
+    rows = nf * seq
+    n_slices = 4 if nh % 4 == 0 else 1
+    hs = nh // n_slices
+    cfg = ops.make_cfg(w["qk"], w["v"], d, d, out_dtype=torch.bfloat16)
+    mask = ops.Mask.window([seq] * nf, window)
+    mask.dev(dev)
+
+    # the rank's fragments at full width: the same bytes whatever the number of ranks (seeded per fragment and tensor)
+    gen = torch.Generator(device=dev)
+    t = {}
+    for idx, (nm, dt) in enumerate((("q", w["qk"]), ("k", w["qk"]), ("v", w["v"]))):
+        t[nm] = torch.empty((rows, hd), dtype=torch.uint8, device=dev)
+        t["s" + nm] = torch.empty((heads, rows), dtype=torch.float32, device=dev)
+        for f in range(f0, f1):
+            gen.manual_seed(w["seed"] * 100000 + f * 10 + idx)
+            x = torch.randn((seq, hd), generator=gen, device=dev, dtype=torch.float32) * 0.5
+            b, s = ops.quant_rows(x, "absmax", dt, d)
+            t[nm][(f - f0) * seq:(f - f0 + 1) * seq] = b
+            t["s" + nm][:, (f - f0) * seq:(f - f0 + 1) * seq] = s
+            del x, b, s
+    out_local = [torch.empty((rows, hs * d), dtype=torch.bfloat16, device=dev) for _ in range(n_slices)]
+    gathered = [torch.empty((world, rows, hs * d), dtype=torch.bfloat16, device=dev) for _ in range(n_slices)] if world > 1 else None
+    lse = torch.empty((heads, rows), dtype=torch.float32, device=dev)
+    workspace = torch.empty(1 << 16, dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    launches = [0]
+
+    def launch_slice(s, src=None):
+        src = t if src is None else src
+        ha = h0 + s * hs
+        cols = slice(ha * d, (ha + hs) * d)
+        ops.att_fwd(cfg, src["q"][:, cols], src["k"][:, cols], src["v"][:, cols], src["sk"][ha:ha + hs], mask, slope, hs,
+                    qk_scale=src["sq"][ha:ha + hs], v_scale=src["sv"][ha:ha + hs], out=out_local[s], lse=lse[ha:ha + hs],
+                    workspace=workspace, status=status)
+        launches[0] += 2  # per-head V-scale maximum + attention kernel
+
+    def step(gather=True, events=None):
+        pending = []
+        for s in range(n_slices):
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            launch_slice(s)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                events.append((e0, e1))
+            if gather and world > 1:
+                # NCCL runs the gather on its own stream behind this slice's kernel: the next slice's kernel overlaps it
+                pending.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
+        for h in pending:
+            h.wait()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        barrier()
+        tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item()) / n
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert int(status.item()) == 0, "device status %#x during warm-up" % int(status.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches[0] = 0
+    kernel_events = []
+    ms_step = timed(lambda: step(True, kernel_events), args.steps)
+    timed_launches = launches[0]
+    clocks = sampler.stop() if rank == 0 else None
+    assert int(status.item()) == 0, "device status %#x in the timed region" % int(status.item())
+    flops = layer_flops(w, window)
+    value = flops / (ms_step * 1e-3) / 1e12
+    # the rank's kernel time per step (sum over its slices), max over ranks
+    k_ms = sum(a.elapsed_time(b) for a, b in kernel_events) / args.steps
+    kt = torch.tensor([k_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(kt, op=dist.ReduceOp.MAX)
+    k_ms = float(kt.item())
+
+    gather = None
+    if world > 1:
+        n_probe = max(3, min(args.steps, 10))
+        compute_ms = timed(lambda: step(False), n_probe)
+
+        def only_gather():
+            hs_ = [shard.gather_blocks(out_local[s], gathered[s], async_op=True) for s in range(n_slices)]
+            for h in hs_:
+                h.wait()
+        gather_ms = timed(only_gather, n_probe)
+        gather = {"gather_ms": gather_ms, "gather_exposed_ms": max(0.0, ms_step - compute_ms), "compute_only_ms": compute_ms,
+                  "gather_bytes": (world - 1) * rows * nh * d * 2, "slices": n_slices,
+                  "gather_note": "gather_ms: the step's all-gathers alone, back to back; gather_exposed_ms: step time minus the same step "
+                                 "without them; gather_bytes: bytes this rank receives per step"}
+
+    # per-unit integer checksums of the whole batch's output as this rank holds it after the gather
+    table = torch.zeros((frags, heads), dtype=torch.int64, device=dev)
+    for r in range(world):
+        (g0, g1, k0, k1), = shard.rank_rects(frags, heads, world, r)
+        for s in range(n_slices):
+            blk = gathered[s][r] if world > 1 else out_local[s]
+            table[g0:g1, k0 + s * hs:k0 + (s + 1) * hs] = shard.unit_checksums(blk, g1 - g0, seq, hs, d)
+    weights = torch.arange(1, frags * heads + 1, dtype=torch.int64, device=dev).view(frags, heads)
+    check = int(((table * weights).sum() % (1 << 61)).item())
+    same = True
+    if world > 1:
+        lo = torch.tensor([check], dtype=torch.int64, device=dev)
+        hi = lo.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = int(lo.item()) == int(hi.item())
+
+    e2e = None
+    if not args.no_e2e and not quick:
+        e2e = longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, n_slices, world, dev, flops)
+
+    if rank != 0:
+        return None
+    achieved = (flops / world) / (k_ms * 1e-3) / 1e12
+    roofline = tensor_roofline(torch, dev, w, "FwdSm100Kernel<128> (full causal, e4m3 QK^T and PV), this rank's %d (fragment, head) units" % (nf * nh),
+                               achieved, k_ms, flops / world, clocks)
+    roofline["timed"] = ("CUDA events around each slice's tsa_att_fwd call in the timed region (memset + V-scale maximum kernel of a few "
+                         "microseconds + the attention kernel), summed per step")
+    line = {
+        "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3", "data": "synthetic", "config": workload_config(name, w, strong=True),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": timed_launches, "roofline": roofline,
+        "gather_check": {"hash": check, "identical_on_all_ranks": same, "units": frags * heads,
+                         "what": "sum over (fragment, head) units of (unit index + 1) x the integer sum of the unit's bf16 bit patterns, "
+                                 "mod 2^61, over the gathered output; the same number at every N"},
+    }
+    if gather:
+        line.update(gather)
+    return line
+
+
+def longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, n_slices, world, dev, flops):
+    """The same step with HOST buffers: the rank's inputs come from pinned host memory every step, its output blocks go
+    back to pinned host memory; copies, kernels and the gather inside the timed region."""
+    names = ("q", "k", "v", "sq", "sk", "sv")
+    host_in = {n: t[n].cpu().pin_memory() for n in names}
+    host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in out_local]
+    stage = {n: torch.empty_like(t[n]) for n in names}
+    h2d = torch.cuda.Stream(device=dev)
+    d2h = torch.cuda.Stream(device=dev)
+    main_s = torch.cuda.current_stream()
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h_bytes = sum(v.numel() * v.element_size() for v in host_out)
+
+    def step():
+        with torch.cuda.stream(h2d):
+            h2d.wait_stream(main_s)  # the staging buffers are free once the previous step's kernels are done
+            for n in names:
+                stage[n].copy_(host_in[n], non_blocking=True)
+        main_s.wait_stream(h2d)
+        pending = []
+        for s in range(n_slices):
+            launch_slice(s, stage)
+            done = torch.cuda.Event()
+            done.record(main_s)
+            if world > 1:
+                pending.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                host_out[s].copy_(out_local[s], non_blocking=True)
+        for h in pending:
+            h.wait()
+        main_s.wait_stream(d2h)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps = max(2, min(args.steps, 4))
+    step()
+    barrier()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    barrier()
+    tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = float(tt.item()) / steps
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
+            "d2h_bytes_per_step": d2h_bytes, "ms_per_step": ms, "steps": steps,
+            "note": "bytes are this rank's: every rank copies its own shard in and its own output block out"}
+
+
+# ----------------------------------------------------------------------------------------------------
+# layer-mix workloads (prefill125m, train15b): per-GPU work fixed
+def run_layers(args, name, w, rank, world, local_rank, quick=False):
+    import torch
+    import torch.distributed as dist
+    from tscale_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    frag_lens = [w["seq"]] * w["frags"]
+    length = sum(frag_lens)
+    heads, d = w["heads"], w["d"]
+    hd = heads * d
+    masks = {}
+    for window, _ in w["layers"]:
+        if window not in masks:
+            masks[window] = ops.Mask.window(frag_lens, window)
+            masks[window].dev(dev)
+    grad_dtype = torch.bfloat16
+    cfg = ops.make_cfg(w["qk"], w["v"], d, d, out_dtype=torch.bfloat16, grad_dtype=grad_dtype)
+
+    # inputs: one Q/K/V set per layer (each rank its own fragments: seed offset by rank)
+    gen = torch.Generator(device=dev)
+    layers = []
+    for idx, (window, slope) in enumerate(w["layers"]):
+        gen.manual_seed(w["seed"] * 1000 + idx + 100000 * rank)
+        item = {"window": window, "slope": slope}
+        for nm, dt in (("q", w["qk"]), ("k", w["qk"]), ("v", w["v"])):
+            x = torch.randn((length, hd), generator=gen, device=dev, dtype=torch.float32) * 0.5
+            item[nm], item["s" + nm] = ops.quant_rows(x, "absmax", dt, d)
+            del x
+        item["out"] = torch.empty((length, hd), dtype=torch.bfloat16, device=dev)
+        item["lse"] = torch.empty((heads, length), dtype=torch.float32, device=dev)
+        if w["bwd"]:
+            item["d_out"] = (torch.randn((length, hd), generator=gen, device=dev, dtype=torch.float32) * 1e-2).to(grad_dtype)
+        layers.append(item)
+    workspace = torch.empty(1 << 20, dtype=torch.uint8, device=dev)
+    bwd_ws = None
+    if w["bwd"]:
+        import ctypes
+        from tscale_b200 import abi
+        bwd_ws = torch.empty(max(1, abi.lib().tsa_att_bwd_workspace_bytes(ctypes.byref(cfg), heads, length)), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    launches = [0]
+    dom = max(range(len(layers)), key=lambda i: layer_flops(w, layers[i]["window"]))  # dominant layer
+    layer_events = [[] for _ in layers]
+
+    def run_layer(i, item, record):
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+        ops.att_fwd(cfg, item["q"], item["k"], item["v"], item["sk"], masks[item["window"]], item["slope"], heads,
+                    qk_scale=item["sq"], v_scale=item["sv"], out=item["out"], lse=item["lse"], workspace=workspace, status=status)
+        launches[0] += 2  # per-head V-scale maximum + attention kernel
+        if record:
+            e1.record()
+            layer_events[i].append((e0, e1))
+        if w["bwd"]:
+            ops.att_bwd(cfg, item["q"], item["k"], item["v"], item["sk"], item["d_out"], item["out"], item["lse"],
+                        masks[item["window"]], item["slope"], heads, qk_scale=item["sq"], v_scale=item["sv"], workspace=bwd_ws,
+                        status=status)
+            launches[0] += 6  # dScale, bf16 widening of Q / K / V, dQ kernel, dK/dV kernel
+
+    def step(record=False):
+        for i, item in enumerate(layers):
+            run_layer(i, item, record)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert int(status.item()) == 0, "device status %#x during warm-up" % int(status.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches[0] = 0
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step(True)
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+    clocks = sampler.stop() if rank == 0 else None
+    assert int(status.item()) == 0, "device status %#x in the timed region" % int(status.item())
+    tt = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms_step = float(tt.item()) / args.steps
+    fl_step = sum(layer_flops(w, it["window"]) for it in layers) * (3.5 if w["bwd"] else 1.0)  # bwd = 10*D*pairs (5 GEMMs)
+    value = fl_step * world / (ms_step * 1e-3) / 1e12
+
+    dom_ms = float(np.mean([a.elapsed_time(b) for a, b in layer_events[dom]]))
+    dom_flops = layer_flops(w, layers[dom]["window"])
+
+    e2e = None
+    if not args.no_e2e and not quick:
+        e2e = layers_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step)
+
+    if rank != 0:
+        return None
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    roofline = tensor_roofline(torch, dev, w, "FwdSm100Kernel<%d> (full-causal layer, %s QK^T, e4m3 PV)" % (d, w["qk"]),
+                               achieved, dom_ms, dom_flops, clocks)
+    roofline["timed"] = "CUDA events around the layer's tsa_att_fwd call (memset + V-scale maximum kernel of a few microseconds + the attention kernel)"
+    per_layer = []
+    for i, it in enumerate(layers):
+        ms = float(np.mean([a.elapsed_time(b) for a, b in layer_events[i]]))
+        per_layer.append({"window": "full" if it["window"] <= 0 else it["window"], "alibi_slope": it["slope"], "fwd_ms": ms,
+                          "fwd_tflops": layer_flops(w, it["window"]) / (ms * 1e-3) / 1e12})
+    line = {
+        "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "e4m3" if w["qk"] == "e4m3" else "i8+e4m3", "data": "synthetic", "config": workload_config(name, w),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches[0], "roofline": roofline, "layers": per_layer,
+    }
+    if w["bwd"]:
+        line["flop_counting"] = ("forward 4*D per attended pair + backward 10*D (5 GEMMs); the reference's own count credits the "
+                                 "backward with 7 GEMMs (14*D)")
+    return line
+
+
+def layers_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, status, world, dist, fl_step):
     """Same step through the public call with HOST buffers: every step copies the layer inputs (and dOut for the
     training workload) from pinned host memory to the device, runs the layer, and copies the bf16 result (forward:
     out; training: dQ, dK, dV) back to pinned host memory."""
@@ -479,6 +723,78 @@ def run_e2e(torch, ops, args, w, cfg, layers, masks, heads, workspace, bwd_ws, s
     ms = float(tt.item()) / steps
     return {"value": fl_step * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
             "d2h_bytes_per_step": d2h_bytes, "ms_per_step": ms, "steps": steps}
+
+
+# ----------------------------------------------------------------------------------------------------
+def short(line):
+    """What an `also` entry keeps of a workload's line."""
+    keys = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "dtype", "scaling", "config", "roofline", "layers",
+            "gpu_launches", "flop_counting")
+    return {k: line[k] for k in keys if k in line}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="longctx", choices=sorted(WORKLOADS) + ["decode", "infer", "neighbours"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other workloads")
+    ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
+    ap.add_argument("--heads", type=int, default=0, help="override the number of heads (profiling on a small case)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.workload == "decode":
+        from benchlib import decode
+        return decode.run(args, rank, world, local_rank)
+    if args.workload == "infer":
+        from benchlib import infer
+        return infer.run(args, rank, world, local_rank)
+    if args.workload == "neighbours":
+        from benchlib import neighbours
+        return neighbours.run(args, rank, world, local_rank)
+
+    name = args.workload
+    w = dict(WORKLOADS[name])
+    if args.frags > 0:
+        w["frags"] = args.frags
+    if args.heads > 0:
+        w["heads"] = args.heads
+    if args.impl == "reference":
+        return reference_arm(args, name, w, rank)
+
+    runner = run_longctx if name == "longctx" else run_layers
+    line = runner(args, name, w, rank, world, local_rank)
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline_block(w) if (world == 1 and not args.no_cpu_baseline) else None
+        if world == 1 and name == "longctx" and not args.no_also:
+            # the other workloads of the path, short runs, so that one record carries their numbers too
+            import copy
+            import torch
+            quick = copy.copy(args)
+            quick.steps, quick.warmup = 5, 3
+            also = []
+            for other in ("prefill125m", "train15b"):
+                torch.cuda.empty_cache()
+                also.append(short(run_layers(quick, other, dict(WORKLOADS[other]), 0, 1, local_rank, quick=True)))
+            from benchlib import decode
+            torch.cuda.empty_cache()
+            quick.steps = 20
+            also.append(short(decode.run(quick, 0, 1, local_rank, emit=False, quick=True)))
+            line["also"] = also
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -10,7 +10,7 @@ import time
 
 import numpy as np
 
-from .benchutil import ClockSampler, load_peaks
+from .util import ClockSampler, load_peaks
 
 N_SEQ, HEADS, D = 64, 16, 128
 CTX_LO, CTX_HI = 1024, 8192
@@ -60,7 +60,9 @@ def config(args):
             "l2": "KV cache (about 1.2 GB per step) is larger than L2", "sharding": "sequences, per-GPU work fixed"}
 
 
-def run(args, rank, world, local_rank):
+def run(args, rank, world, local_rank, emit=True, quick=False):
+    """emit=False: return the line instead of printing it; quick: no end-to-end leg and no CPU baseline (the short run
+    bench.py adds to its default line)."""
     if args.impl == "reference":
         if rank != 0:
             return
@@ -81,11 +83,11 @@ def run(args, rank, world, local_rank):
 
     import torch
     import torch.distributed as dist
-    from . import ops
+    from tscale_b200 import ops
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     steps, warmup = args.steps, max(args.warmup, 3)
@@ -167,40 +169,42 @@ def run(args, rank, world, local_rank):
     k_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
     k_bytes = step_bytes(lens, HEADS, D, 2)
 
-    # end to end: the step's host inputs (query, new K/V rows and scales) come from pinned memory, the result goes back
-    host = {n: t.cpu().pin_memory() for n, t in (("q", q), ("qs", qs), ("k", k_new), ("v", v_new), ("ks", ks_new), ("vs", vs_new))}
-    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = host_out.numel() * host_out.element_size()
-    e_steps = min(steps, 50)
+    e2e = None
+    if not quick and not getattr(args, "no_e2e", False):
+        # end to end: the step's host inputs (query, new K/V rows and scales) come from pinned memory, the result goes back
+        host = {n: t.cpu().pin_memory() for n, t in (("q", q), ("qs", qs), ("k", k_new), ("v", v_new), ("ks", ks_new), ("vs", vs_new))}
+        host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host.values())
+        d2h = host_out.numel() * host_out.element_size()
+        e_steps = min(steps, 50)
 
-    def e2e_step():
-        q.copy_(host["q"], non_blocking=True)
-        qs.copy_(host["qs"], non_blocking=True)
-        k_new.copy_(host["k"], non_blocking=True)
-        v_new.copy_(host["v"], non_blocking=True)
-        ks_new.copy_(host["ks"], non_blocking=True)
-        vs_new.copy_(host["vs"], non_blocking=True)
-        step()
-        host_out.copy_(out, non_blocking=True)
+        def e2e_step():
+            q.copy_(host["q"], non_blocking=True)
+            qs.copy_(host["qs"], non_blocking=True)
+            k_new.copy_(host["k"], non_blocking=True)
+            v_new.copy_(host["v"], non_blocking=True)
+            ks_new.copy_(host["ks"], non_blocking=True)
+            vs_new.copy_(host["vs"], non_blocking=True)
+            step()
+            host_out.copy_(out, non_blocking=True)
 
-    e2e_step()
-    lens = [n + 1 for n in lens]
-    barrier()
-    e_bytes = 0.0
-    t0.record()
-    for _ in range(e_steps):
         e2e_step()
         lens = [n + 1 for n in lens]
-        e_bytes += step_bytes(lens, HEADS, D, 2)
-    t1.record()
-    barrier()
-    tt = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    e_ms = float(tt.item()) / e_steps
-    e2e = {"value": e_bytes / e_steps * world / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "steps": e_steps}
+        barrier()
+        e_bytes = 0.0
+        t0.record()
+        for _ in range(e_steps):
+            e2e_step()
+            lens = [n + 1 for n in lens]
+            e_bytes += step_bytes(lens, HEADS, D, 2)
+        t1.record()
+        barrier()
+        tt = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e_ms = float(tt.item()) / e_steps
+        e2e = {"value": e_bytes / e_steps * world / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "steps": e_steps}
 
     if rank != 0:
         if world > 1:
@@ -212,17 +216,22 @@ def run(args, rank, world, local_rank):
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_source": "MEASURED_PEAKS.json copy bandwidth (%s)" % peaks["_source"], "frac_of_8tbs_nominal": achieved / 8000.0,
                 "ms_per_launch": k_ms, "algorithmic_bytes_per_launch": k_bytes,
-                # ncu capture at this size (profiles/decode_partial_i8_d128_64seq.md): 1.1588 GB of DRAM traffic for 1.166 GB algorithmic
-                "traffic": 0.994 * k_bytes, "traffic_source": "dram bytes / algorithmic bytes = 0.994 in the ncu capture of this workload"}
+                # not measured in this run: the ratio comes from the ncu capture of this workload at this size
+                # (profiles/decode_partial_i8_d128_64seq.md: 1.1588 GB of DRAM traffic for 1.166 GB algorithmic)
+                "traffic": 0.994 * k_bytes, "traffic_source": "algorithmic bytes x 0.994, the dram/algorithmic ratio of the committed ncu capture "
+                                                                "profiles/decode_partial_i8_d128_64seq.md (same workload and size); not re-measured per run"}
     cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not quick:
         threads = os.cpu_count() or 1
         gbs, kind, sample, sec = cpu_decode_sample(8, threads)
         cpu_baseline = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample, "seconds": sec}
-    print(json.dumps({
+    line = {
         "metric": "decode_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
         "config": config(args), "clocks": clocks, "e2e": e2e, "gpu_launches": timed_launches, "roofline": roofline,
-        "cpu_baseline": cpu_baseline}))
+        "cpu_baseline": cpu_baseline}
+    if not emit:
+        return line
+    print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -12,7 +12,7 @@ import time
 
 import numpy as np
 
-from .benchutil import ClockSampler, load_peaks
+from .util import ClockSampler, load_peaks
 
 N_SEQ, DIM, HEADS, D, RELU_MULT, VOCAB, LAYERS = 64, 768, 12, 64, 1, 50304, 12
 CTX_LO, CTX_HI = 1024, 8192
@@ -120,7 +120,7 @@ def run(args, rank, world, local_rank):
 
     import torch
     import torch.distributed as dist
-    from . import infer
+    from tscale_b200 import infer
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

@@ -12,7 +12,7 @@ import json
 
 import numpy as np
 
-from .benchutil import ClockSampler, load_peaks
+from .util import ClockSampler, load_peaks
 
 SHAPES = ((65536, 768, 12, 64), (32768, 2048, 16, 128))
 
@@ -23,7 +23,7 @@ def run(args, rank, world, local_rank):
             print(json.dumps({"impl": "reference", "unavailable": "the neighbours workload times GPU kernels only; the CPU arm covers prefill125m, decode and infer"}))
         return
     import torch
-    from . import ops
+    from tscale_b200 import ops
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

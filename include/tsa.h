@@ -256,6 +256,22 @@ int tsa_group_attention(int len, const int *spans, const int *spanPtr, int maxGr
 int tsa_group_window_spans(int fragCount, const int *fragLens, int window, int transposed, int maxGroups,
     tsa_span_group *groups, int *groupPtr);
 
+/* ---- partition over the GPUs of one box ---------------------------------------------------------------------
+ * Replaces the per-device batch split of TMultiComputeContext (code/gpt/compute/gpt_cuda.cu:1478-1738; the split itself
+ * code/gpt/train_ctx/backprop.cpp:10-23), at the granularity the attention path allows: one unit = one (fragment, head)
+ * pair, unit = fragment * heads + head.  tsa_shard_range gives rank `rank` of `world` its contiguous, balanced block
+ * [begin, end) of `units` (earlier ranks take the remainder).  tsa_shard_rects writes that block as at most three
+ * rectangles of whole fragments x a head range; each rectangle is one tsa_att_fwd / tsa_att_bwd call on the
+ * rectangle's rows, with qk / qv / v / out advanced by head_begin * D columns and the scale planes by head_begin rows.
+ * No input crosses GPUs; the outputs are gathered with one NCCL all-gather per call (INTEGRATION.md shows the
+ * per-rank call sequence).  Host functions; tsa_shard_rects returns the rectangle count or a negative tsa_status. */
+typedef struct {
+    int frag_begin, frag_end; /* fragments [frag_begin, frag_end) */
+    int head_begin, head_end; /* heads [head_begin, head_end) */
+} tsa_shard_rect;
+int tsa_shard_range(int units, int world, int rank, int *begin, int *end);
+int tsa_shard_rects(int begin, int end, int heads, tsa_shard_rect *rects);
+
 /* ---- device-side span generation ("next" scope row: the mask preparation on the input side of the path) -------
  * The same records as tsa_group_window_spans, written by a kernel into device memory: no host work and no copy of the
  * mask per step (the reference prepares the spans on the CPU and uploads them, gpt_cuda.cu:1346-1353).

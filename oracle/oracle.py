@@ -14,6 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "libtsa_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libtsa_ref.so")
+_REF_FAST_SO = os.path.join(_HERE, "_ref", "libtsa_ref_fast.so")
 
 c_int = ctypes.c_int
 c_float = ctypes.c_float
@@ -23,10 +24,11 @@ _bp = ctypes.POINTER(ctypes.c_int8)
 
 
 def build(reference=True):
-    """Compile the oracle (and the reference shim when a reference checkout is present)."""
+    """Compile the oracle and, when the Makefile finds a reference checkout (its REF variable, which the environment
+    may override), the two builds of the reference's own CPU code."""
     subprocess.run(["make", "-C", _HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
-    if reference and os.path.exists("/root/reference/code/gpt/compute/gpt_cpu.cpp"):
-        subprocess.run(["make", "-C", _HERE, "ref", "-j8"], check=True, stdout=subprocess.DEVNULL)
+    if reference:
+        subprocess.run(["make", "-C", _HERE, "ref", "ref_fast", "-j8"], check=True, stdout=subprocess.DEVNULL)
 
 
 def _f(a):
@@ -70,23 +72,24 @@ def _cpu_has(*flags):
     return all(f in have for f in flags)
 
 
-_ref = None
+_ref = {}
 
 
-def ref():
+def ref(fast=False):
     """The reference's own CPU attention, or None when it was not built or this CPU cannot run it
-    (the decode path uses AVX-VNNI intrinsics)."""
-    global _ref
-    if _ref is None:
-        if not os.path.exists(_REF_SO) or not _cpu_has("avx2", "fma", "avx_vnni"):
-            _ref = False
+    (the decode path uses AVX-VNNI intrinsics).  fast: the -O3 build with fused multiply-adds that the CPU
+    baseline times (results differ from the parity build in the last bits)."""
+    if fast not in _ref:
+        path = _REF_FAST_SO if fast else _REF_SO
+        if not os.path.exists(path) or not _cpu_has("avx2", "fma", "avx_vnni"):
+            _ref[fast] = False
         else:
-            r = ctypes.CDLL(_REF_SO)
+            r = ctypes.CDLL(path)
             r.ref_vec_scale.restype = c_float
             r.ref_e4m3_to_float.restype = c_float
             r.ref_float2i8.argtypes = [c_float]
-            _ref = r
-    return _ref or None
+            _ref[fast] = r
+    return _ref[fast] or None
 
 
 def set_threads(n):
@@ -286,8 +289,9 @@ def att_fwd(q, k, v, spans, span_ptr, heads, slope, global_scale=1.0, use_ref=Fa
     sw = np.zeros((heads, ln), dtype=np.float32)
     mx = np.zeros((heads, ln), dtype=np.float32)
     if use_ref:
+        # use_ref == "fast": the -O3 build that the CPU baseline times
         assert global_scale == 1.0
-        ref().ref_att_fwd(ln, heads, dq, dv, c_float(slope), qp, kp, vp, sp, pp,
+        ref(fast=(use_ref == "fast")).ref_att_fwd(ln, heads, dq, dv, c_float(slope), qp, kp, vp, sp, pp,
                           out.ctypes.data_as(_fp), sw.ctypes.data_as(_fp), mx.ctypes.data_as(_fp))
         lse = mx + np.log2(sw)
     else:

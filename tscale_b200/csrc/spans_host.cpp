@@ -258,3 +258,49 @@ extern "C" __attribute__((visibility("default"))) int tsa_group_window_spans(int
     }
     return total > maxGroups ? -(int)total : (int)total;
 }
+
+// ---- partition of one batch over the GPUs of a box --------------------------------------------------
+// The reference splits a batch over its devices by fragments and gives every device its own context, host thread and
+// stream (TMultiComputeContext, code/gpt/compute/gpt_cuda.cu:1478-1738; batch split code/gpt/train_ctx/backprop.cpp:10-23).
+// Here the unit is one (fragment, head) pair, numbered fragment-major: unit = fragment * heads + head.  Units are
+// independent (spans never cross fragments, heads never mix), so a contiguous block of units per rank needs no exchange
+// on the way in.
+extern "C" __attribute__((visibility("default"))) int tsa_shard_range(int units, int world, int rank, int *begin, int *end)
+{
+    if (units < 0 || world <= 0 || rank < 0 || rank >= world || !begin || !end) {
+        return TSA_BAD_ARG;
+    }
+    const int base = units / world, rem = units % world;
+    *begin = rank * base + std::min(rank, rem);
+    *end = *begin + base + (rank < rem ? 1 : 0);
+    return TSA_OK;
+}
+
+// A contiguous unit range as at most three rectangles (fragment range x head range), in unit order: the tail of the
+// first fragment, the whole fragments in the middle, the head of the last fragment.  Each rectangle is one tsa_att_fwd
+// call on the rectangle's rows and head columns.  Returns the number of rectangles written, or a negative tsa_status.
+extern "C" __attribute__((visibility("default"))) int tsa_shard_rects(int begin, int end, int heads, tsa_shard_rect *rects)
+{
+    if (begin < 0 || end < begin || heads <= 0 || !rects) {
+        return -TSA_BAD_ARG;
+    }
+    int n = 0;
+    int cur = begin;
+    while (cur < end && n < 3) {
+        const int frag = cur / heads, head = cur % heads;
+        tsa_shard_rect r;
+        r.frag_begin = frag;
+        r.head_begin = head;
+        if (head != 0 || end - cur < heads) {
+            // part of one fragment
+            r.frag_end = frag + 1;
+            r.head_end = std::min(heads, head + (end - cur));
+        } else {
+            r.frag_end = frag + (end - cur) / heads;
+            r.head_end = heads;
+        }
+        cur += (r.frag_end - r.frag_begin) * (r.head_end - r.head_begin);
+        rects[n++] = r;
+    }
+    return n;
+}

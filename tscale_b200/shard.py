@@ -1,23 +1,52 @@
-"""Partition of the attention work over the GPUs of one box and the gather of the results.
+"""Partition of one attention batch over the GPUs of one box and the gather of the results.
 
 Every (fragment, head) pair is independent (spans never cross fragments), so ranks take contiguous blocks of
-heads (or of fragments) and no data crosses GPUs on the way in.  The only collective is the all-gather of the
-output column blocks.  One process per GPU; `torch.distributed` carries the collective (NCCL on GPUs, gloo in
-the CPU tests).
+units (unit = fragment * heads + head) and no data crosses GPUs on the way in.  The partition itself is the
+library's (tsa_shard_range / tsa_shard_rects, C ABI); this module binds it and carries the one collective of the
+path, the all-gather of the output blocks, through `torch.distributed` (NCCL on GPUs, gloo in the CPU tests).
+One process per GPU, as the reference runs one context and host thread per device
+(code/gpt/compute/gpt_cuda.cu:1478-1738).
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
+
+from . import abi
+
+
+class Rect(ctypes.Structure):
+    """tsa_shard_rect: fragments [frag_begin, frag_end) x heads [head_begin, head_end)"""
+    _fields_ = [("frag_begin", ctypes.c_int), ("frag_end", ctypes.c_int), ("head_begin", ctypes.c_int), ("head_end", ctypes.c_int)]
+
+    def as_tuple(self):
+        return (self.frag_begin, self.frag_end, self.head_begin, self.head_end)
 
 
 def split_range(n_units, world, rank):
     """Contiguous, balanced [begin, end) block of n_units for this rank (earlier ranks take the remainder)."""
-    base, rem = divmod(n_units, world)
-    begin = rank * base + min(rank, rem)
-    return begin, begin + base + (1 if rank < rem else 0)
+    b, e = ctypes.c_int(0), ctypes.c_int(0)
+    abi.check(abi.lib().tsa_shard_range(n_units, world, rank, ctypes.byref(b), ctypes.byref(e)))
+    return b.value, e.value
+
+
+def unit_rects(begin, end, heads):
+    """The unit range [begin, end) as at most three (frag_begin, frag_end, head_begin, head_end) rectangles."""
+    rects = (Rect * 3)()
+    n = abi.lib().tsa_shard_rects(begin, end, heads, ctypes.cast(rects, ctypes.c_void_p))
+    if n < 0:
+        abi.check(-n)
+    return [rects[i].as_tuple() for i in range(n)]
+
+
+def rank_rects(fragments, heads, world, rank):
+    """Rectangles of the (fragment, head) units this rank computes."""
+    b, e = split_range(fragments * heads, world, rank)
+    return unit_rects(b, e, heads)
 
 
 def head_shard(heads, world, rank):
-    """Heads owned by this rank when a layer is sharded by heads."""
+    """Heads owned by this rank when a single fragment is sharded by heads."""
     return split_range(heads, world, rank)
 
 
@@ -37,3 +66,16 @@ def gather_head_blocks(local_out, heads, head_dim, world, group=None):
     dist.all_gather_into_tensor(recv.view(-1), send.contiguous().view(-1), group=group)
     parts = [recv[r, :, :counts[r] * head_dim] for r in range(world)]
     return torch.cat(parts, dim=1)
+
+
+def gather_blocks(local_block, gathered, group=None, async_op=False):
+    """All-gather of equally shaped compact output blocks: local_block [rows][cols] (contiguous) from every rank into
+    gathered [world][rows][cols].  Returns the work handle when async_op."""
+    return dist.all_gather_into_tensor(gathered.view(-1), local_block.view(-1), group=group, async_op=async_op)
+
+
+def unit_checksums(block, n_frag, seq, n_heads, head_dim):
+    """Order-independent integer checksum of every (fragment, head) unit of a [n_frag * seq][n_heads * head_dim] block of
+    16-bit values: the sum of the bit patterns (as signed 16-bit integers) of the unit's elements.  int64 [n_frag][n_heads]."""
+    bits = block.view(torch.int16).to(torch.int64)
+    return bits.view(n_frag, seq, n_heads, head_dim).sum(dim=(1, 3))
