@@ -431,6 +431,9 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
 
     if rank != 0:
         return None
+    ref_gpu = None
+    if world == 1 and not quick:
+        ref_gpu = reference_gpu_kernel(torch, ops, w, t, mask, seq, d, cfg, workspace, status)
     achieved = (flops / world) / (k_ms * 1e-3) / 1e12
     roofline = tensor_roofline(torch, dev, w, "FwdSm100Kernel<128> (full causal, e4m3 QK^T and PV), this rank's %d (fragment, head) units" % (nf * nh),
                                achieved, k_ms, flops / world, clocks)
@@ -447,7 +450,59 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     }
     if gather:
         line.update(gather)
+    if ref_gpu:
+        line["reference_gpu_kernel"] = ref_gpu
     return line
+
+
+def reference_gpu_kernel(torch, ops, w, t, mask, seq, d, cfg, workspace, status, n_heads=8):
+    """The reference's own GPU kernel Fp8Att (mma.sync e4m3, rebuilt for sm_100a behind oracle/ref_gpu_harness.cu) timed on
+    this GPU on one fragment x n_heads heads of the workload, beside this library's kernel on the same slice.  The
+    reference kernel takes a constant query scale and a transposed V; same shapes, spans and key scales."""
+    from oracle import oracle as O
+    if O.ref_gpu() is None or d != 128:
+        return None
+    dev = t["q"].device
+    rows = seq
+    cols = slice(0, n_heads * d)
+    q = t["q"][:rows, cols].contiguous()
+    k = t["k"][:rows, cols].contiguous()
+    v = t["v"][:rows, cols].contiguous()
+    sk = t["sk"][:n_heads, :rows].contiguous()
+    sq = t["sq"][:n_heads, :rows].contiguous()
+    sv = t["sv"][:n_heads, :rows].contiguous()
+    v_tr = v.t().contiguous()
+    m1 = ops.Mask.window([seq], w["layers"][0][0])
+    groups, gptr, _, _ = m1.dev(dev)
+    out_ref = torch.empty((rows, n_heads * d), dtype=torch.float16, device=dev)
+    swl = torch.empty((n_heads, rows), dtype=torch.float32, device=dev)
+    one = torch.ones(1, dtype=torch.float32, device=dev)
+    try:
+        O.ref_gpu_fp8_att(one, q, k, sk, v_tr, groups, gptr, 0.0, out_ref, swl, n_heads, rows, reps=1)   # warm-up
+        ms_ref = O.ref_gpu_fp8_att(one, q, k, sk, v_tr, groups, gptr, 0.0, out_ref, swl, n_heads, rows, reps=3)
+    except RuntimeError as e:
+        return {"unavailable": str(e)}
+    out = torch.empty((rows, n_heads * d), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((n_heads, rows), dtype=torch.float32, device=dev)
+
+    def ours():
+        ops.att_fwd(cfg, q, k, v, sk, m1, 0.0, n_heads, qk_scale=sq, v_scale=sv, out=out, lse=lse, workspace=workspace, status=status)
+    for _ in range(2):
+        ours()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        ours()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_ours = e0.elapsed_time(e1) / 3
+    fl = 4.0 * d * pairs_window(seq, w["layers"][0][0]) * n_heads
+    return {"kernel": "Fp8Att of the reference (mma.sync e4m3, 4 warps per 64 query rows), rebuilt for sm_100a",
+            "shape": "1 fragment x %d tokens x %d heads x %d, full causal" % (seq, n_heads, d),
+            "ms": ms_ref, "tflops": fl / (ms_ref * 1e-3) / 1e12,
+            "this_library_ms": ms_ours, "this_library_tflops": fl / (ms_ours * 1e-3) / 1e12,
+            "speedup": ms_ref / ms_ours}
 
 
 def longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, n_slices, world, dev, flops):

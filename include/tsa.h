@@ -143,6 +143,20 @@ int tsa_qk_scores_i32(tsa_ptr2d qk, tsa_ptr2d qv, int headCount, int headDim, in
  * (ring slots, barrier phases) rather than in tsa_qk_scores_i32's separate kernel. */
 int tsa_att_fwd_set_score_dump(int32_t *dst, int head, int queryTile, int keyTile);
 
+/* ---- status word and failure-path self-tests --------------------------------------------------------------------
+ * The reference aborts the process on any CUDA error (code/lib/cuda/cuda_graph.cuh:147-150); here a kernel that gives up
+ * ORs a code into the caller's status word and returns.  tsa_status_from_word maps a word read back from the device to a
+ * tsa_status: 0 -> TSA_OK, a timed-out barrier wait (0x10 copy, 0x20 MMA) -> TSA_TIMEOUT, anything else -> TSA_BAD_ARG.
+ * The two self-tests make a wait run out on purpose, without faulting or hanging anything:
+ * tsa_selftest_bounded_wait launches one thread that waits, for at most limitCycles clock cycles, on a barrier nobody
+ * arrives on, and must come back with 0x10 in *statusWord; tsa_selftest_fwd_withhold_copy makes the following
+ * tsa_att_fwd calls (tensor-core path) wait at most waitCycles cycles per barrier and leave out the copy of every CTA's
+ * withholdTile-th key tile, so the forward must notice, drain its other copies, free its tensor memory and return with
+ * the time-out bits set (waitCycles = 0, withholdTile = -1 restores production behaviour).  Process-wide, for tests. */
+int tsa_status_from_word(int statusWord);
+int tsa_selftest_bounded_wait(long long limitCycles, int *statusWord, tsa_stream_t stream);
+int tsa_selftest_fwd_withhold_copy(long long waitCycles, int withholdTile);
+
 /* ---- per-row quantisers ----------------------------------------------------------------------
  * Replaces NormalizeVecsRowTile / NormalizeVecsRowTileMax (code/gpt/compute/row_tile_scale.cuh:11-34,
  * 59-82) and the stand-alone use of the TStoreRowTileNormalize epilogue (lib/cuda/cuda_matmul.cuh:147-204).
@@ -193,7 +207,8 @@ int tsa_kv_product_bwd(int inDtype, int gradDtype, tsa_ptr2d k, tsa_ptr2d valLoo
 /* ---- KV-cache decode -------------------------------------------------------------------------
  * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
  * batched over sequences.  Per sequence the cache is caller-owned device memory:
- *   k, v    int8 [capacity][H*D] (row stride H*D bytes);  kScale, vScale scaleDtype [capacity][H].
+ *   k, v    int8 [capacity][H*D] (row stride H*D bytes, base 16-byte aligned, H*D a multiple of 16);
+ *   kScale, vScale scaleDtype [capacity][H].
  * tsa_kv_append writes each sequence's new token at row ctxLens[s] and then increments ctxLens[s]
  * (AddVectors, cpu_infer.cpp:403-408).  tsa_att_decode then attends, like the reference, to the keys
  * [cur - window, cur - 1] with cur = ctxLens[s] - 1 (window 0: the new token itself); logits use the exact
@@ -235,7 +250,9 @@ size_t tsa_att_decode_workspace_bytes(const tsa_decode_cfg *cfg, int nSeq, int h
  * The first call on each device looks up the array's device address (a one-time set-up step on the host);
  * make that first call outside any stream capture.  All calls on a device share the one array and it keeps
  * whatever the previous call left there (each call overwrites every slot it later reads, so nothing has to be
- * cleared); two such calls that overlap in time on the same GPU, e.g. on different streams, race on it. */
+ * cleared); two such calls that overlap in time on the same GPU, e.g. on different streams, race on it.  The
+ * address found by the first call is kept for the life of the process, so do not call this entry point again on a
+ * device after a cudaDeviceReset. */
 int tsa_att_decode_static(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const int *ctxLens, int nSeq, int maxCtx,
     tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
     int *statusWord, tsa_stream_t stream);

@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "libtsa_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libtsa_ref.so")
 _REF_FAST_SO = os.path.join(_HERE, "_ref", "libtsa_ref_fast.so")
+_REF_GPU_SO = os.path.join(_HERE, "_ref", "libtsa_ref_gpu.so")
 
 c_int = ctypes.c_int
 c_float = ctypes.c_float
@@ -28,7 +29,7 @@ def build(reference=True):
     may override), the two builds of the reference's own CPU code."""
     subprocess.run(["make", "-C", _HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
     if reference:
-        subprocess.run(["make", "-C", _HERE, "ref", "ref_fast", "-j8"], check=True, stdout=subprocess.DEVNULL)
+        subprocess.run(["make", "-C", _HERE, "ref", "ref_fast", "ref_gpu", "-j8"], check=True, stdout=subprocess.DEVNULL)
 
 
 def _f(a):
@@ -90,6 +91,43 @@ def ref(fast=False):
             r.ref_float2i8.argtypes = [c_float]
             _ref[fast] = r
     return _ref[fast] or None
+
+
+_ref_gpu = None
+
+
+def ref_gpu():
+    """The reference's own GPU attention kernel behind its finite harness (oracle/_ref/libtsa_ref_gpu.so), or None when
+    it was not built.  Needs a GPU."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        if not os.path.exists(_REF_GPU_SO):
+            _ref_gpu = False
+        else:
+            r = ctypes.CDLL(_REF_GPU_SO)
+            vp = ctypes.c_void_p
+            r.ref_gpu_fp8_att.argtypes = [vp, vp, c_int, vp, c_int, vp, c_int, vp, c_int, vp, c_int, vp, c_float,
+                                          vp, c_int, vp, c_int, c_int, c_int, c_int, ctypes.POINTER(c_float), vp]
+            _ref_gpu = r
+    return _ref_gpu or None
+
+
+def ref_gpu_fp8_att(global_scale, qk, qv, qv_scale, v_t, groups, group_ptr, slope, out, sum_weight_log, heads, length, reps=1):
+    """Launches the reference's Fp8Att `reps` times on CUDA tensors (torch): qk, qv uint8 e4m3 [len][H*128]; qv_scale f32
+    [H][len]; v_t uint8 [H*128][len] (V transposed); groups / group_ptr the grouped spans on the device; out float16
+    [len][H*128]; sum_weight_log f32 [H][len]; global_scale f32 [1] on the device.  len must be a multiple of 128.
+    Returns the mean milliseconds per launch.  The query scale is the harness constant 1/32 and the result is in
+    stored-V units, as in the reference's own kernel test (code/gpt/compute/gpt_att.cu:21-25)."""
+    assert length % 128 == 0
+    ms = c_float(0)
+    sb = lambda t: t.stride(0) * t.element_size()
+    rc = ref_gpu().ref_gpu_fp8_att(global_scale.data_ptr(), qk.data_ptr(), sb(qk), qv.data_ptr(), sb(qv), qv_scale.data_ptr(), sb(qv_scale),
+                                   v_t.data_ptr(), sb(v_t), groups.data_ptr(), groups.shape[0], group_ptr.data_ptr(), c_float(slope),
+                                   out.data_ptr(), sb(out), sum_weight_log.data_ptr(), sb(sum_weight_log), heads, length, reps,
+                                   ctypes.byref(ms), None)
+    if rc != 0:
+        raise RuntimeError("reference GPU kernel: CUDA error %d" % rc)
+    return float(ms.value)
 
 
 def set_threads(n):

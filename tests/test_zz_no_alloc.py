@@ -39,12 +39,21 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
     for seed, ctx_lens, heads, d, window, slope in ((0, [1500, 700, 257, 3], 8, 128, 100000, 0.0),
                                                     (1, [300, 40], 12, 64, 64, 0.5)):
         cache, q, qs = _filled_cache(seed, ctx_lens, heads, d)
-        want = cache.decode(q, qs, window, slope)
-        got = cache.decode_static(q, qs, window, slope)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        want = cache.decode(q, qs, window, slope, status=status)
+        got = cache.decode_static(q, qs, window, slope, status=status)
         torch.cuda.synchronize()
+        assert int(status.item()) == 0                           # no device-side complaint from either entry point
         scale = max(1.0, float(want.abs().max()))
         assert float((got - want).abs().max()) <= 2e-4 * scale   # tolerance of the decode parity tests
         assert torch.equal(got, want)                            # same kernels, same order: in fact identical
+        # and against the CPU oracle directly, sequence by sequence (the cache already holds the token that attends)
+        from oracle import oracle as O
+        for s_i, n in enumerate(ctx_lens):
+            ref = O.decode_step(cache.k[s_i, :n].cpu().numpy(), cache.k_scale[s_i, :n].float().cpu().numpy(),
+                                cache.v[s_i, :n].cpu().numpy(), cache.v_scale[s_i, :n].float().cpu().numpy(),
+                                q[s_i].cpu().numpy(), qs[s_i].cpu().numpy(), heads, window, slope)
+            assert np.abs(got[s_i].cpu().numpy() - ref).max() <= 2e-4 * max(1.0, np.abs(ref).max())
 
 
 def test_static_scratch_decode_rejects_oversized_problem():

@@ -74,7 +74,8 @@ EXPORTS = [
     "tsa_att_decode", "tsa_att_decode_workspace_bytes", "tsa_make_window_spans", "tsa_transpose_attention",
     "tsa_group_attention", "tsa_group_window_spans", "tsa_att_decode_static", "tsa_att_decode_static_capacity_bytes",
     "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device", "tsa_kv_product", "tsa_kv_product_bwd",
-    "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects",
+    "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects", "tsa_status_from_word", "tsa_selftest_bounded_wait",
+    "tsa_selftest_fwd_withhold_copy",
 ]
 
 
@@ -93,6 +94,9 @@ def _declare(lib):
     lib.tsa_att_bwd_workspace_bytes.argtypes = [ctypes.POINTER(AttCfg), c_int, c_int]
     lib.tsa_calc_dscale.argtypes = [c_int, c_int, P, P, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_qk_scores_i32.argtypes = [P, P, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.tsa_status_from_word.argtypes = [c_int]
+    lib.tsa_selftest_bounded_wait.argtypes = [ctypes.c_longlong, c_void_p, c_void_p]
+    lib.tsa_selftest_fwd_withhold_copy.argtypes = [ctypes.c_longlong, c_int]
     lib.tsa_shard_range.argtypes = [c_int, c_int, c_int, c_int_p, c_int_p]
     lib.tsa_shard_rects.argtypes = [c_int, c_int, c_int, c_void_p]
     lib.tsa_att_fwd_set_score_dump.argtypes = [c_void_p, c_int, c_int, c_int]

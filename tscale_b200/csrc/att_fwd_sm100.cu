@@ -80,6 +80,10 @@ struct TFwdParams {
     // parity hook: raw s32 scores of one tile as this kernel read them from tensor memory (null in production)
     int32_t *DumpScores;
     int DumpHead, DumpQTile, DumpTile;
+    // self-test of the failure path: bound of every barrier wait in clock cycles (about a second in production) and the
+    // index, in a CTA's own tile sequence, of a key tile whose copy the loader requests but never issues (-1: none)
+    long long WaitCycles;
+    int WithholdTile;
 };
 
 // one span round of a work item, published by the loader
@@ -114,14 +118,15 @@ struct TFwdMisc {
     float Al[TILE_N];    // ALiBi term slope * column
 };
 
-template <int D>
+template <int D, bool V_I8>
 struct TFwdSmem {
-    static constexpr int STAGES = (D == 64) ? 4 : 2;
+    static constexpr int STAGES = (D == 64) ? (V_I8 ? 3 : 4) : 2;
+    static constexpr int NV = V_I8 ? 2 : 1; // value tiles per stage (int8 values come as two e4m3 planes)
     static constexpr int TILE_BYTES = 128 * D;
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = Q_SLOTS * TILE_BYTES;
     static constexpr int V_OFF = K_OFF + STAGES * TILE_BYTES;
-    static constexpr int AUX_OFF = V_OFF + STAGES * TILE_BYTES;
+    static constexpr int AUX_OFF = V_OFF + STAGES * NV * TILE_BYTES;
     static constexpr int ROUND_OFF = AUX_OFF + STAGES * (int)sizeof(TFwdAux);
     static constexpr int MISC_OFF = ROUND_OFF + ROUND_SLOTS * (int)sizeof(TFwdRound);
     static constexpr int TOTAL = MISC_OFF + (int)sizeof(TFwdMisc) + 1024; // + alignment slack
@@ -232,11 +237,18 @@ __device__ __forceinline__ int ValueScaleExponent(float x)
 #define TSA_FWD_POLY_PAIRS 0
 #endif
 
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
+// V_I8: the values are int8.  They reach the tensor cores exactly, as the sum of two e4m3 planes a pre-pass writes
+// (v = 16 * floor(v / 16) + (v mod 16): multiples of 16 up to 128 in magnitude and integers 0..15 are all e4m3 numbers),
+// so every O += P V becomes two MMAs on the same weights; every tile also carries the weights' e4m3 residual term, which
+// brings the result within 1e-3 of the reference's fp32 accumulation (the reference's int8 mode keeps its weights in
+// half precision, gpt_att_fp16.cuh:121-318).
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
 __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
-    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TFwdParams p)
+    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV2,
+    TFwdParams p)
 {
-    using SM = TFwdSmem<D>;
+    using SM = TFwdSmem<D, V_I8>;
+    constexpr int NV = SM::NV;
     constexpr int STAGES = SM::STAGES;
     constexpr int SWZ = (D == 128) ? 128 : 64;
     constexpr uint32_t GROUP_BYTES = 8 * D; // 8 rows of a tile
@@ -306,6 +318,9 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             PrefetchTensorMap(&tmQ);
             PrefetchTensorMap(&tmK);
             PrefetchTensorMap(&tmV);
+            if (V_I8) {
+                PrefetchTensorMap(&tmV2);
+            }
         }
         int kvCount = 0, qCount = 0, rCount = 0;
         bool failed = false;
@@ -316,7 +331,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
         item = __shfl_sync(0xffffffffu, item, 0);
         // waits of the whole warp on one barrier: every lane polls, all get the same answer
         auto waitAll = [&](uint64_t *bar, uint32_t parity, int code) {
-            bool ok = WaitBarSleep<200>(bar, parity, abortFlag);
+            bool ok = WaitBarSleep<200>(bar, parity, abortFlag, p.WaitCycles);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok && !failed) {
                 failed = true;
@@ -503,9 +518,14 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                         break;
                     }
                     if (lane == 0) {
-                        MbarExpectTx(&misc.KvFull[slot], 2 * SM::TILE_BYTES + (bulk ? TILE_N * 4 : 0));
-                        TmaLoad2D(sK + slot * SM::TILE_BYTES, &tmK, head * D, j0, &misc.KvFull[slot]);
-                        TmaLoad2D(sV + slot * SM::TILE_BYTES, &tmV, head * D, j0, &misc.KvFull[slot]);
+                        MbarExpectTx(&misc.KvFull[slot], (1 + NV) * SM::TILE_BYTES + (bulk ? TILE_N * 4 : 0));
+                        if (kvCount != p.WithholdTile) { // self-test: the bytes of a withheld copy never arrive
+                            TmaLoad2D(sK + slot * SM::TILE_BYTES, &tmK, head * D, j0, &misc.KvFull[slot]);
+                        }
+                        TmaLoad2D(sV + slot * NV * SM::TILE_BYTES, &tmV, head * D, j0, &misc.KvFull[slot]);
+                        if (V_I8) {
+                            TmaLoad2D(sV + (slot * NV + 1) * SM::TILE_BYTES, &tmV2, head * D, j0, &misc.KvFull[slot]);
+                        }
                         if (bulk) {
                             BulkLoad(aux[slot].Sk, p.KScale.Row(head) + j0, TILE_N * 4, &misc.KvFull[slot]);
                         }
@@ -534,10 +554,10 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
         if (failed || *(volatile int *)&misc.Abort) {
             // drain copies that were requested but may never be consumed, so none lands after the CTA is gone
             for (int k = max(0, kvCount - STAGES); k < kvCount; ++k) {
-                WaitBar(&misc.KvFull[k % STAGES], (k / STAGES) & 1);
+                WaitBar(&misc.KvFull[k % STAGES], (k / STAGES) & 1, p.WaitCycles);
             }
             for (int k = max(0, qCount - Q_SLOTS); k < qCount; ++k) {
-                WaitBar(&misc.QFull[k % Q_SLOTS], (k / Q_SLOTS) & 1);
+                WaitBar(&misc.QFull[k % Q_SLOTS], (k / Q_SLOTS) & 1, p.WaitCycles);
             }
         }
         __syncwarp();
@@ -556,7 +576,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             bool pending = false, pendAccum = false, pendMasked = false, pendLast = false;
             int pendSlot = 0, pendQSlot = 0;
             auto wait = [&](uint64_t *bar, uint32_t parity, int code) {
-                if (WaitBarSleep<TSA_FWD_SLEEP_MMA>(bar, parity, abortFlag)) {
+                if (WaitBarSleep<TSA_FWD_SLEEP_MMA>(bar, parity, abortFlag, p.WaitCycles)) {
                     return true;
                 }
                 if (!failed) {
@@ -572,13 +592,17 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             };
             // waits for half h of the pending tile's weights and issues O += P V for it (item-end signals behind the last)
             auto flushHalf = [&](int h) {
-                const uint64_t vDesc = descBase + ((sVa + pendSlot * SM::TILE_BYTES) >> 4);
+                const uint64_t vDesc = descBase + ((sVa + pendSlot * NV * SM::TILE_BYTES) >> 4);
                 if (!wait(&misc.BarP[h], pCount & 1, kDevTimeoutMma)) {
                     return false;
                 }
                 TcFenceAfter();
                 MmaPairF8TS(tmem + TMEM_O_COL, tmem + h * 64, vDesc + ((h * 64 * D) >> 4), (32 * D) >> 4, IDESC_PV,
                     (pendAccum || h > 0) ? 1u : 0u, pendMasked);
+                if (V_I8) {
+                    MmaPairF8TS(tmem + TMEM_O_COL, tmem + h * 64, vDesc + ((SM::TILE_BYTES + h * 64 * D) >> 4), (32 * D) >> 4, IDESC_PV,
+                        1u, pendMasked);
+                }
                 if (h == 1) {
                     MmaCommit(&misc.KvEmpty[pendSlot]);
                     if (pendLast) {
@@ -635,7 +659,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                     pendSlot = slot;
                     pendQSlot = qSlot;
                     pendAccum = tilesInItem > 0;
-                    pendMasked = !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
+                    pendMasked = V_I8 || !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
                     pendLast = (flags & RF_LAST) && t == nTiles - 1;
                     ++kvCount;
                     ++tilesInItem;
@@ -674,7 +698,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
         float m = 0, rowMult = 0, invK = 0;
         float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this row's weights
         auto wait = [&](uint64_t *bar, uint32_t parity, int code) {
-            if (WaitBarSleep<TSA_FWD_SLEEP_SOFTMAX>(bar, parity, abortFlag)) {
+            if (WaitBarSleep<TSA_FWD_SLEEP_SOFTMAX>(bar, parity, abortFlag, p.WaitCycles)) {
                 return true;
             }
             if (!failed) {
@@ -719,7 +743,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             for (int t = 0; t < nTiles; ++t) {
                 const int j0 = j0r + t * TILE_N;
                 const int slot = kvCount % STAGES;
-                const bool masked = !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
+                const bool masked = V_I8 || !(fullLo <= j0 && j0 + TILE_N - 1 <= fullHi);
                 if (!wait(&misc.BarS[0], sCount & 1, kDevTimeoutMma)) {
                     break;
                 }
@@ -1018,10 +1042,14 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                         }
                     }
                 };
-                if (masked) {
+                if constexpr (V_I8) {
                     processTile(std::true_type());
                 } else {
-                    processTile(std::false_type());
+                    if (masked) {
+                        processTile(std::true_type());
+                    } else {
+                        processTile(std::false_type());
+                    }
                 }
                 handOver(1);
                 ++sCount;
@@ -1097,6 +1125,36 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
     if (warp == FW_MMA_WARP) {
         TmemDealloc(tmem, TMEM_COLS);
     }
+}
+
+// int8 values as two e4m3 planes whose sum is the value: a = 16 * floor(v / 16), b = v - a in 0..15 (both exact in e4m3).
+// One thread per 16 bytes of a row; rows are rowBytes wide (a multiple of 16), planes have the pitch `pitch`.
+__global__ void __launch_bounds__(256) SplitI8ValuesKernel(P2D<uint8_t> v, int rows, int rowBytes, uint8_t *va, uint8_t *vb, int pitch)
+{
+    const int perRow = rowBytes / 16;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)rows * perRow) {
+        return;
+    }
+    const int row = (int)(idx / perRow), c16 = (int)(idx % perRow);
+    const int4 src = *reinterpret_cast<const int4 *>(v.Row(row) + c16 * 16);
+    const uint32_t w[4] = {(uint32_t)src.x, (uint32_t)src.y, (uint32_t)src.z, (uint32_t)src.w};
+    uint32_t oa[4], ob[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float fa[4], fb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int x = (int)(int8_t)(w[k] >> (8 * j));
+            const int a = (x >> 4) * 16;
+            fa[j] = (float)a;
+            fb[j] = (float)(x - a);
+        }
+        oa[k] = PackE4M3x4(fa[0], fa[1], fa[2], fa[3]);
+        ob[k] = PackE4M3x4(fb[0], fb[1], fb[2], fb[3]);
+    }
+    *reinterpret_cast<int4 *>(va + (size_t)row * pitch + c16 * 16) = make_int4((int)oa[0], (int)oa[1], (int)oa[2], (int)oa[3]);
+    *reinterpret_cast<int4 *>(vb + (size_t)row * pitch + c16 * 16) = make_int4((int)ob[0], (int)ob[1], (int)ob[2], (int)ob[3]);
 }
 
 // per head maximum of the V scale plane (normalises the weights' e4m3 range).  Scales are non-negative, so
@@ -1209,6 +1267,27 @@ __global__ void __launch_bounds__(SCORE_THREADS) ScoresI8Kernel(const __grid_con
     }
 }
 
+// ---- self-test of a bounded wait ----------------------------------------------------------------
+// One thread arms a barrier nobody will ever arrive on and waits for it with the given bound: the wait must give up,
+// report through the status word and return, leaving the context usable.
+__global__ void BoundedWaitSelfTestKernel(long long limitCycles, int *status)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        MbarInit(&bar, 1);
+        FenceBarrierInit();
+        if (!WaitBar(&bar, 0, limitCycles) && status) {
+            atomicOr(status, kDevTimeoutTma);
+        }
+    }
+}
+
+int LaunchBoundedWaitSelfTest(long long limitCycles, int *statusWord, cudaStream_t stream)
+{
+    BoundedWaitSelfTestKernel<<<1, 32, 0, stream>>>(limitCycles, statusWord);
+    return CheckCuda(cudaGetLastError(), "bounded-wait self-test launch");
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 
 static bool TmaCompatible(tsa_ptr2d a)
@@ -1224,8 +1303,8 @@ bool Sm100FwdSupports(const tsa_att_cfg *cfg, tsa_ptr2d qk, tsa_ptr2d qv, tsa_pt
     if (cfg->head_dim_qk != cfg->head_dim_v || (cfg->head_dim_qk != 64 && cfg->head_dim_qk != 128)) {
         return false;
     }
-    if (cfg->v_dtype != TSA_E4M3) {
-        return false; // int8 values take the generic kernels (exact fp32 accumulation)
+    if (cfg->v_dtype == TSA_I8 && cfg->qk_dtype != TSA_I8) {
+        return false; // int8 values with e4m3 queries and keys: no counterpart in the reference, generic kernels
     }
     return TmaCompatible(qk) && TmaCompatible(qv) && TmaCompatible(v);
 }
@@ -1235,9 +1314,17 @@ static size_t VRefBytes(int headCount)
 {
     return (size_t)((headCount * sizeof(float) + 255) / 256 * 256);
 }
-size_t Sm100FwdWorkspaceBytes(int headCount)
+static int ValuePlanePitch(int headCount, int headDim)
 {
-    return VRefBytes(headCount) + 256;
+    return (headCount * headDim + 15) / 16 * 16;
+}
+size_t Sm100FwdWorkspaceBytes(const tsa_att_cfg *cfg, int headCount, int keyRows)
+{
+    size_t bytes = VRefBytes(headCount) + 256;
+    if (cfg && cfg->v_dtype == TSA_I8) {
+        bytes += 2 * (size_t)keyRows * ValuePlanePitch(headCount, cfg->head_dim_v); // the two e4m3 planes of the int8 values
+    }
+    return bytes;
 }
 
 static TFwdDump g_dump;
@@ -1246,11 +1333,11 @@ void SetFwdScoreDump(const TFwdDump &d)
     g_dump = d;
 }
 
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI>
-static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const TFwdParams &fp, cudaStream_t stream)
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
+static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
 {
-    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI>;
-    int smemBytes = TFwdSmem<D>::TOTAL;
+    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8>;
+    int smemBytes = TFwdSmem<D, V_I8>::TOTAL;
     int dev = 0, smCount = 0;
     int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
     if (rc == TSA_OK) {
@@ -1266,7 +1353,7 @@ static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtens
     if (ctas > fp.TotalItems) {
         ctas = fp.TotalItems;
     }
-    kern<<<ctas, FW_THREADS, smemBytes, stream>>>(mq, mk, mv, fp);
+    kern<<<ctas, FW_THREADS, smemBytes, stream>>>(mq, mk, mv, mv2, fp);
     return CheckCuda(cudaGetLastError(), "tcgen05 forward launch");
 }
 
@@ -1274,13 +1361,35 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     int lenAttTiles, int keyRows, void *workspace, int *statusWord, cudaStream_t stream)
 {
     const int D = cfg->head_dim_qk;
-    CUtensorMap mq, mk, mv;
+    const bool vI8 = cfg->v_dtype == TSA_I8;
+    const size_t headBytes = VRefBytes(p.HeadCount) + 256; // value-scale maxima and the counter
+    CUtensorMap mq, mk, mv, mv2;
     int rc = MakeTileMap(&mq, qk, D, "qk");
     if (rc == TSA_OK) {
         rc = MakeTileMap(&mk, qv, D, "qv");
     }
-    if (rc == TSA_OK) {
+    if (rc == TSA_OK && !vI8) {
         rc = MakeTileMap(&mv, v, D, "v");
+        mv2 = mv;
+    }
+    if (rc == TSA_OK && vI8) {
+        // the two e4m3 planes of the int8 values live behind the head of the workspace
+        const int pitch = ValuePlanePitch(p.HeadCount, D);
+        const int rowBytes = p.HeadCount * D / 16 * 16;
+        if (rowBytes != p.HeadCount * D) {
+            return Fail(TSA_UNSUPPORTED, "tcgen05 forward with int8 values: H * D must be a multiple of 16");
+        }
+        uint8_t *va = (uint8_t *)workspace + headBytes, *vb = va + (size_t)keyRows * pitch;
+        tsa_ptr2d pa = {va, pitch, p.HeadCount * D, keyRows}, pb = {vb, pitch, p.HeadCount * D, keyRows};
+        rc = MakeTileMap(&mv, pa, D, "v (upper e4m3 plane)");
+        if (rc == TSA_OK) {
+            rc = MakeTileMap(&mv2, pb, D, "v (lower e4m3 plane)");
+        }
+        if (rc == TSA_OK) {
+            const long long items = (long long)keyRows * (rowBytes / 16);
+            SplitI8ValuesKernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(p.V, keyRows, rowBytes, va, vb, pitch);
+            rc = CheckCuda(cudaGetLastError(), "int8 value split launch");
+        }
     }
     if (rc != TSA_OK) {
         return rc;
@@ -1316,6 +1425,8 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     fp.DumpHead = g_dump.Head;
     fp.DumpQTile = g_dump.QTile;
     fp.DumpTile = g_dump.Tile;
+    fp.WaitCycles = g_dump.WaitCycles > 0 ? g_dump.WaitCycles : WAIT_CYCLES;
+    fp.WithholdTile = g_dump.WithholdTile;
     // one clear covers the V-scale maxima and the counter behind them
     rc = CheckCuda(cudaMemsetAsync(hasVs ? workspace : (void *)fp.Counter, 0, hasVs ? vrefBytes + 256 : 256, stream), "clearing the forward workspace");
     if (rc != TSA_OK) {
@@ -1328,9 +1439,13 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     const bool i8 = cfg->qk_dtype == TSA_I8;
     const bool alibi = p.Slope != 0.0f;
 #define TSA_FWD_CASE(DD, I8, VS)                                                                         \
-    if (D == DD && i8 == I8 && hasVs == VS) {                                                            \
-        return alibi ? LaunchFwdT<DD, I8, VS, true>(mq, mk, mv, fp, stream)                              \
-                     : LaunchFwdT<DD, I8, VS, false>(mq, mk, mv, fp, stream);                            \
+    if (D == DD && i8 == I8 && hasVs == VS && !vI8) {                                                    \
+        return alibi ? LaunchFwdT<DD, I8, VS, true, false>(mq, mk, mv, mv2, fp, stream)                  \
+                     : LaunchFwdT<DD, I8, VS, false, false>(mq, mk, mv, mv2, fp, stream);                \
+    }                                                                                                    \
+    if (D == DD && i8 == I8 && hasVs == VS && vI8 && I8) {                                               \
+        return alibi ? LaunchFwdT<DD, I8, VS, true, I8>(mq, mk, mv, mv2, fp, stream)                     \
+                     : LaunchFwdT<DD, I8, VS, false, I8>(mq, mk, mv, mv2, fp, stream);                   \
     }
     TSA_FWD_CASE(64, false, false)
     TSA_FWD_CASE(64, false, true)

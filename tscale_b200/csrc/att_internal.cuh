@@ -42,13 +42,16 @@ int LaunchDScale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa
 struct TFwdDump {
     int32_t *Dst = nullptr; // [128][128] int32 in device memory, null = off
     int Head = 0, QTile = 0, Tile = 0;
+    long long WaitCycles = 0; // self-test: bound of the forward's barrier waits (0: the production bound)
+    int WithholdTile = -1;    // self-test: a key tile copy every CTA requests but never issues (-1: none)
 };
+int LaunchBoundedWaitSelfTest(long long limitCycles, int *statusWord, cudaStream_t stream);
 void SetFwdScoreDump(const TFwdDump &d);
 
 // tcgen05 forward (att_fwd_sm100.cu).  Returns TSA_UNSUPPORTED when the configuration is outside
 // the tensor-core path (the caller then uses the generic kernels).
 bool Sm100FwdSupports(const tsa_att_cfg *cfg, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v);
-size_t Sm100FwdWorkspaceBytes(int headCount);
+size_t Sm100FwdWorkspaceBytes(const tsa_att_cfg *cfg, int headCount, int keyRows);
 int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v,
     int lenAttTiles, int keyRows, void *workspace, int *statusWord, cudaStream_t stream);
 

@@ -13,14 +13,14 @@ using namespace sm100;
 constexpr long long WAIT_CYCLES = 1ll << 31; // about a second
 constexpr int TILE_ROWS = 128;               // rows / columns of a score tile
 
-__device__ __forceinline__ bool WaitBar(uint64_t *bar, uint32_t parity)
+__device__ __forceinline__ bool WaitBar(uint64_t *bar, uint32_t parity, long long limit = WAIT_CYCLES)
 {
     long long t0 = clock64();
     for (;;) {
         if (MbarWaitBounded(bar, parity, 64)) {
             return true;
         }
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             return false;
         }
     }
@@ -55,7 +55,7 @@ __device__ __forceinline__ bool WaitBarA(uint64_t *bar, uint32_t parity, const i
 // MMA-issuing warp cost the softmax warp next to it a third of its issue rate).  Returns false when the CTA's abort
 // flag is set or after about a second.
 template <int SLEEP_NS>
-__device__ __forceinline__ bool WaitBarSleep(uint64_t *bar, uint32_t parity, const int *abortFlag)
+__device__ __forceinline__ bool WaitBarSleep(uint64_t *bar, uint32_t parity, const int *abortFlag, long long limit = WAIT_CYCLES)
 {
     if (MbarTryWaitFast(bar, parity)) {
         return true;
@@ -71,7 +71,7 @@ __device__ __forceinline__ bool WaitBarSleep(uint64_t *bar, uint32_t parity, con
         if (*(const volatile int *)abortFlag) {
             return false;
         }
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             return false;
         }
     }

@@ -495,6 +495,13 @@ __global__ void KvAppendKernel(const tsa_kv_seq *seqs, int *ctxLens, int nSeq, i
         return;
     }
     tsa_kv_seq sq = seqs[seq];
+    if ((((uintptr_t)sq.k | (uintptr_t)sq.v) & 15) != 0) {
+        // the cache blocks are written 16 bytes at a time: a misaligned base is reported, not stored through
+        if (threadIdx.x == 0 && statusWord) {
+            atomicOr(statusWord, kDevBadSpan);
+        }
+        return;
+    }
     for (int i = threadIdx.x * 16; i < rowBytes; i += blockDim.x * 16) {
         *reinterpret_cast<int4 *>((int8_t *)sq.k + (size_t)pos * rowBytes + i) = *reinterpret_cast<const int4 *>(kNew.Row(seq) + i);
         *reinterpret_cast<int4 *>((int8_t *)sq.v + (size_t)pos * rowBytes + i) = *reinterpret_cast<const int4 *>(vNew.Row(seq) + i);
@@ -620,6 +627,7 @@ int DecodeWithKvProduct(const tsa_decode_cfg *cfg, const tsa_kv_seq *seqs, const
     int rowSize = headCount * cfg->head_dim;
     TSA_REQUIRE(q.xsize >= rowSize && q.ysize >= nSeq && out.xsize >= rowSize && out.ysize >= nSeq, "tsa_att_decode: q/out extents");
     TSA_REQUIRE((uintptr_t)q.data % 16 == 0 && q.stride_bytes % 16 == 0, "tsa_att_decode: q must be 16-byte aligned");
+    TSA_REQUIRE((uintptr_t)out.data % 16 == 0 && out.stride_bytes % 16 == 0, "tsa_att_decode: out must be 16-byte aligned");
     if (qScale.data) {
         TSA_REQUIRE(qScale.xsize >= headCount && qScale.ysize >= nSeq, "tsa_att_decode: qScale extents");
     }
@@ -666,8 +674,12 @@ extern "C" __attribute__((visibility("default"))) int tsa_kv_append(const tsa_de
     if (nSeq <= 0) {
         return nSeq == 0 ? TSA_OK : Fail(TSA_BAD_ARG, "tsa_kv_append: negative nSeq");
     }
+    TSA_REQUIRE(headCount > 0 && capacity > 0, "tsa_kv_append: headCount %d / capacity %d must be positive", headCount, capacity);
     int rowBytes = headCount * cfg->head_dim;
+    TSA_REQUIRE(rowBytes % 16 == 0, "tsa_kv_append: H * D = %d must be a multiple of 16 (rows are copied 16 bytes at a time)", rowBytes);
     TSA_REQUIRE(kNew.xsize >= rowBytes && vNew.xsize >= rowBytes && kNew.ysize >= nSeq && vNew.ysize >= nSeq, "tsa_kv_append: kNew/vNew extents");
+    TSA_REQUIRE(kScaleNew.xsize >= headCount && vScaleNew.xsize >= headCount && kScaleNew.ysize >= nSeq && vScaleNew.ysize >= nSeq,
+        "tsa_kv_append: kScaleNew/vScaleNew must be [nSeq][H]");
     TSA_REQUIRE((uintptr_t)kNew.data % 16 == 0 && kNew.stride_bytes % 16 == 0 && (uintptr_t)vNew.data % 16 == 0 && vNew.stride_bytes % 16 == 0,
         "tsa_kv_append: kNew/vNew must be 16-byte aligned");
     KvAppendKernel<<<nSeq, 128, 0, (cudaStream_t)stream>>>(seqs, ctxLens, nSeq, capacity, rowBytes, headCount, DtypeSize(cfg->scale_dtype),
@@ -691,7 +703,9 @@ std::mutex g_scratchLock;
 void *g_scratchAddr[kMaxDevices]; // device address of g_decodeScratch, per device, filled on first use
 
 // The array's name is only a host-side handle; the address a kernel can use has to be asked for, on the
-// device that is current, once per device.
+// device that is current, once per device.  The answer is kept for the life of the process: after a cudaDeviceReset
+// the module is loaded afresh and the kept address is stale, so a process that resets a device must not call
+// tsa_att_decode_static on it again.
 int StaticScratchAddress(void **out)
 {
     int dev = -1;
@@ -725,20 +739,11 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_decode_static(cons
     tsa_ptr2d q, tsa_ptr2d qScale, int window, float alibiSlope, tsa_ptr2d out, int headCount,
     int *statusWord, tsa_stream_t stream)
 {
-    int rc = CheckDecodeCfg(cfg, "tsa_att_decode_static");
-    if (rc != TSA_OK) {
-        return rc;
-    }
-    TSA_REQUIRE(seqs && ctxLens && q.data && out.data, "tsa_att_decode_static: null buffer");
-    TSA_REQUIRE(nSeq >= 0 && headCount > 0 && maxCtx >= 0 && window >= 0, "tsa_att_decode_static: negative size");
+    // only the size check and the address look-up are this entry point's own; validation and launch are tsa_att_decode's
+    TSA_REQUIRE(cfg != nullptr && (cfg->head_dim == 64 || cfg->head_dim == 128), "tsa_att_decode_static: head_dim must be 64 or 128");
+    TSA_REQUIRE(nSeq >= 0 && headCount > 0 && maxCtx >= 0, "tsa_att_decode_static: negative size");
     if (nSeq == 0) {
         return TSA_OK;
-    }
-    int rowSize = headCount * cfg->head_dim;
-    TSA_REQUIRE(q.xsize >= rowSize && q.ysize >= nSeq && out.xsize >= rowSize && out.ysize >= nSeq, "tsa_att_decode_static: q/out extents");
-    TSA_REQUIRE((uintptr_t)q.data % 16 == 0 && q.stride_bytes % 16 == 0, "tsa_att_decode_static: q must be 16-byte aligned");
-    if (qScale.data) {
-        TSA_REQUIRE(qScale.xsize >= headCount && qScale.ysize >= nSeq, "tsa_att_decode_static: qScale extents");
     }
     size_t need = DecodeWorkspaceBytes(cfg->head_dim, nSeq, headCount, maxCtx);
     if (need > kStaticScratchBytes) {
@@ -748,25 +753,10 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_decode_static(cons
             nSeq, maxCtx, headCount, need, kStaticScratchBytes);
     }
     void *scratch = nullptr;
-    rc = StaticScratchAddress(&scratch);
+    int rc = StaticScratchAddress(&scratch);
     if (rc != TSA_OK) {
         return rc;
     }
-    TDecodeParams p;
-    p.Status = statusWord;
-    p.Seqs = seqs;
-    p.CtxLens = ctxLens;
-    p.NSeq = nSeq;
-    p.HeadCount = headCount;
-    p.Window = window;
-    p.ScaleDtype = cfg->scale_dtype;
-    p.OutDtype = cfg->out_dtype;
-    p.Slope = alibiSlope;
-    p.DotScale = HostAttDotScale(cfg->head_dim);
-    p.QVecScale = cfg->qk_vec_scale;
-    p.Q = P2D<int8_t>(q);
-    p.QScale = P2D<float>(qScale);
-    p.Out = P2D<char>(out);
-    p.Partial = (float *)scratch;
-    return LaunchDecode(cfg, p, maxCtx, (cudaStream_t)stream);
+    return DecodeWithKvProduct(cfg, seqs, ctxLens, nSeq, maxCtx, q, qScale, window, alibiSlope, out, headCount, scratch, kStaticScratchBytes,
+        statusWord, stream, nullptr, nullptr, 0);
 }

@@ -280,8 +280,10 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
         // commit round trip)
         constexpr int GEMM_AHEAD = GEMM_STAGES - 2;
         const int chunks = a.Chunks / KS;
+        int issued = 0, landed = 0; // chunks requested / chunks whose copies were seen to arrive
         for (int c = 0; c < GEMM_AHEAD && c < chunks; ++c) {
             load(c);
+            ++issued;
         }
         for (int c = 0; c < chunks && !failed; ++c) {
             const int ahead = c + GEMM_AHEAD;
@@ -294,6 +296,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
                     break;
                 }
                 load(ahead);
+                ++issued;
             }
             const int s = c % GEMM_STAGES;
             if (!WaitBar(&misc.Full[s], (uint32_t)((c / GEMM_STAGES) & 1))) {
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
                 }
                 break;
             }
+            ++landed;
             TcFenceAfter();
             const uint32_t sA = SmemAddr(smem + s * GEMM_STAGE_BYTES), sB = sA + GEMM_M * GEMM_KB;
 #pragma unroll
@@ -312,6 +316,12 @@ __global__ void __launch_bounds__(128, 1) InferGemmI8Kernel(const __grid_constan
                 MmaI8SS(tmem, aDesc, bDesc, IDESC, (c > 0 || ks > 0) ? 1u : 0u);
             }
             MmaCommit(&misc.Empty[s]);
+        }
+        if (failed) {
+            // copies that were requested but never consumed must not land after the CTA is gone: wait (bounded) for them
+            for (int t = landed; t < issued; ++t) {
+                WaitBar(&misc.Full[t % GEMM_STAGES], (uint32_t)((t / GEMM_STAGES) & 1));
+            }
         }
         MmaCommit(&misc.Done);
     }

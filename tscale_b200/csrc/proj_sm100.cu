@@ -99,8 +99,10 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
         // PROJ_AHEAD chunks in flight; a stage is refilled once the MMAs of two iterations ago have released it
         constexpr int PROJ_AHEAD = PROJ_STAGES - 2;
         const int chunks = a.Chunks;
+        int issued = 0, landed = 0; // chunks requested / chunks whose copies were seen to arrive
         for (int c = 0; c < PROJ_AHEAD && c < chunks; ++c) {
             load(c);
+            ++issued;
         }
         for (int c = 0; c < chunks; ++c) {
             const int ahead = c + PROJ_AHEAD;
@@ -113,6 +115,7 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                     break;
                 }
                 load(ahead);
+                ++issued;
             }
             const int s = c % PROJ_STAGES;
             if (!ProjWait(&misc.Full[s], (uint32_t)((c / PROJ_STAGES) & 1))) {
@@ -122,6 +125,7 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                 }
                 break;
             }
+            ++landed;
             TcFenceAfter();
             const uint32_t sA = SmemAddr(smem + s * PROJ_STAGE_BYTES), sB = sA + PROJ_M * PROJ_KB;
 #pragma unroll
@@ -135,6 +139,12 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                 }
             }
             MmaCommit(&misc.Empty[s]);
+        }
+        if (failed) {
+            // copies that were requested but never consumed must not land after the CTA is gone: wait (bounded) for them
+            for (int t = landed; t < issued; ++t) {
+                ProjWait(&misc.Full[t % PROJ_STAGES], (uint32_t)((t / PROJ_STAGES) & 1));
+            }
         }
         MmaCommit(&misc.Done);
     }

@@ -105,9 +105,7 @@ extern "C" __attribute__((visibility("default"))) const char *tsa_last_error(voi
 
 extern "C" __attribute__((visibility("default"))) size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len)
 {
-    (void)cfg;
-    (void)len;
-    return headCount > 0 ? Sm100FwdWorkspaceBytes(headCount) : 0;
+    return headCount > 0 ? Sm100FwdWorkspaceBytes(cfg, headCount, len > 0 ? len : 0) : 0;
 }
 
 extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
@@ -141,7 +139,7 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_
     }
     cudaStream_t s = (cudaStream_t)stream;
     if (Sm100FwdSupports(cfg, qk, qv, v)) {
-        size_t need = Sm100FwdWorkspaceBytes(headCount); // per-head V-scale maxima and the work-item counter
+        size_t need = Sm100FwdWorkspaceBytes(cfg, headCount, qv.ysize); // per-head V-scale maxima, the work-item counter, e4m3 planes of int8 values
         TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_fwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
         TSA_REQUIRE((uintptr_t)workspace % 16 == 0, "tsa_att_fwd: workspace must be 16-byte aligned");
         return LaunchSm100Fwd(cfg, p, qk, qv, v, lenAttTiles, qv.ysize, workspace, statusWord, s);
@@ -149,16 +147,43 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_
     return LaunchGenericFwd(p, s);
 }
 
+static TFwdDump g_hooks; // process-wide test hooks of the forward (score dump, failure-path self-test)
+
 extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_set_score_dump(int32_t *dst, int head, int queryTile, int keyTile)
 {
     TSA_REQUIRE(dst == nullptr || (head >= 0 && queryTile >= 0 && keyTile >= 0), "tsa_att_fwd_set_score_dump: negative index");
-    TFwdDump d;
-    d.Dst = dst;
-    d.Head = head;
-    d.QTile = queryTile;
-    d.Tile = keyTile;
-    SetFwdScoreDump(d);
+    g_hooks.Dst = dst;
+    g_hooks.Head = head;
+    g_hooks.QTile = queryTile;
+    g_hooks.Tile = keyTile;
+    SetFwdScoreDump(g_hooks);
     return TSA_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_selftest_fwd_withhold_copy(long long waitCycles, int withholdTile)
+{
+    TSA_REQUIRE(waitCycles >= 0, "tsa_selftest_fwd_withhold_copy: negative bound");
+    g_hooks.WaitCycles = waitCycles;
+    g_hooks.WithholdTile = withholdTile;
+    SetFwdScoreDump(g_hooks);
+    return TSA_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_selftest_bounded_wait(long long limitCycles, int *statusWord, tsa_stream_t stream)
+{
+    TSA_REQUIRE(statusWord != nullptr && limitCycles > 0 && limitCycles <= (1ll << 31), "tsa_selftest_bounded_wait: status word and a bound of at most 2^31 cycles");
+    return LaunchBoundedWaitSelfTest(limitCycles, statusWord, (cudaStream_t)stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_status_from_word(int statusWord)
+{
+    if (statusWord == 0) {
+        return TSA_OK;
+    }
+    if (statusWord & (kDevTimeoutTma | kDevTimeoutMma)) {
+        return Fail(TSA_TIMEOUT, "a bounded device wait ran out (status word %#x)", statusWord);
+    }
+    return Fail(TSA_BAD_ARG, "the device rejected its inputs (status word %#x)", statusWord);
 }
 
 extern "C" __attribute__((visibility("default"))) size_t tsa_att_bwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len)
