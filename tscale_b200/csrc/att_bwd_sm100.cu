@@ -200,59 +200,44 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         }
         __syncwarp();
     } else if (warp == BWD_CTRL_WARP) {
-        // ---------------------------------------------------------------- MMA warp: lane 0 issues every MMA
-        if (lane == 0 && cur.Valid) {
+        // ---------------------------------------------------------------- MMA warp: the whole warp runs the loop and
+        // waits; one elected lane issues (descriptors stay in uniform registers that way)
+        if (cur.Valid) {
             const uint32_t sR1a = SmemAddr(sR1), sR2a = SmemAddr(sR2), sCa = SmemAddr(sC);
             bool failed = false;
+            // descriptor of a K-major / MN-major tile without its address (added per use, in 16-byte units)
+            const uint64_t kDescBase = MakeSmemDesc(0, 16, 1024, 128), mnDescBase = MakeSmemDesc(0, BLOCK_BYTES, 1024, 128);
             // columns [64h, 64h + 64) of S = R1 C1^T and dP = R2 C2^T: both operands K-major, D / 16 steps of 16
             // elements (32 bytes); the B operand starts 64 rows (8 KB per 128-byte block) into the column tile
             auto issueScores = [&](int slot, int h) {
                 const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES + h * 8192, c2 = c1 + SM::TILE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * BLOCK_BYTES + (ks & 3) * 32;
-                    MmaF16SS(tmem + BWD_S_COL + h * 64, MakeSmemDesc(sR1a + off, 16, 1024, 128), MakeSmemDesc(c1 + off, 16, 1024, 128), IDESC_SS, ks > 0);
-                }
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * BLOCK_BYTES + (ks & 3) * 32;
-                    MmaF16SS(tmem + BWD_DP_COL + h * 64, MakeSmemDesc(sR2a + off, 16, 1024, 128), MakeSmemDesc(c2 + off, 16, 1024, 128), IDESC_SS, ks > 0);
-                }
+                MmaGroupF16SS<D / 16>(tmem + BWD_S_COL + h * 64, kDescBase + (sR1a >> 4), kDescBase + (c1 >> 4), IDESC_SS);
+                MmaGroupF16SS<D / 16>(tmem + BWD_DP_COL + h * 64, kDescBase + (sR2a >> 4), kDescBase + (c2 >> 4), IDESC_SS);
             };
             // out1 += A1 C1 (and out2 += A2 C2) over the half's 64 tile columns = 4 steps of 16: A from tensor memory
             // (quarter q of the tile keeps its bf16 pairs in columns 32q .. 32q+15), B = the column tile read MN-major
             auto issueOutputs = [&](int slot, int h, bool accumulate) {
                 const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES, c2 = c1 + SM::TILE_BYTES;
-#pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) {
-                    const int ks = h * 4 + k4;
-                    const uint32_t aCol = (ks >> 1) * 32 + (ks & 1) * 8;
-                    MmaF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + aCol, MakeSmemDesc(c1 + ks * 16 * 128, BLOCK_BYTES, 1024, 128), IDESC_OUT,
-                        (accumulate || k4 > 0) ? 1u : 0u);
-                }
+                MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + ((c1 + h * 4 * 16 * 128) >> 4), IDESC_OUT, accumulate ? 1u : 0u);
                 if (MODE_DKV) {
-#pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) {
-                        const int ks = h * 4 + k4;
-                        const uint32_t aCol = (ks >> 1) * 32 + (ks & 1) * 8;
-                        MmaF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + aCol, MakeSmemDesc(c2 + ks * 16 * 128, BLOCK_BYTES, 1024, 128), IDESC_OUT,
-                            (accumulate || k4 > 0) ? 1u : 0u);
-                    }
+                    MmaQuadF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + h * 64, mnDescBase + ((c2 + h * 4 * 16 * 128) >> 4), IDESC_OUT, accumulate ? 1u : 0u);
                 }
             };
             auto fail = [&](int code) {
                 failed = true;
-                *(volatile int *)&misc.Abort = 1;
-                if (p.Status) {
-                    atomicOr(p.Status, code);
+                if (lane == 0) {
+                    *(volatile int *)&misc.Abort = 1;
+                    if (p.Status) {
+                        atomicOr(p.Status, code);
+                    }
                 }
             };
-            if (!WaitBarA(&misc.BarR, 0, abortFlag)) {
+            if (!__all_sync(0xffffffffu, WaitBarA(&misc.BarR, 0, abortFlag))) {
                 fail(kDevTimeoutTma);
             }
             // Tensor-pipe order per tile: out(h0, it-1), scores(h0, it), out(h1, it-1), scores(h1, it).  The outputs of a
             // half must read its A columns before the next scores of that half overwrite them; the pipe runs in order.
-            // This thread never waits for its own MMAs, so the pipe stays fed; the loader refills a stage when the
+            // The warp never waits for its own MMAs, so the pipe stays fed; the loader refills a stage when the
             // commit made after the stage's last output product completes.
             int it = 0;
             TTileIter ctl = cur;
@@ -262,40 +247,54 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (it > 0) {
-                        if (!WaitBarA<true>(&misc.BarP[h], (it - 1) & 1, abortFlag)) {
+                        if (!__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
                             fail(kDevTimeoutMma);
                             break;
                         }
                         TcFenceAfter();
                         TRB(it, 9 + 2 * h);
-                        issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
-                        if (h == 1) {
-                            MmaCommit(&misc.BarEmpty[(it - 1) % STAGES]);
-                        }
                     }
-                    if (h == 0 && !WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag)) {
+                    if (h == 0 && !__all_sync(0xffffffffu, WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag))) {
                         fail(kDevTimeoutTma);
                         break;
                     }
                     TcFenceAfter();
-                    issueScores(slot, h);
-                    MmaCommit(&misc.BarS[h]);
+                    if (h == 0) {
+                        TRB(it, 13);
+                    }
+                    if (ElectOne()) {
+                        if (it > 0) {
+                            issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                            if (h == 1) {
+                                MmaCommit(&misc.BarEmpty[(it - 1) % STAGES]);
+                            }
+                        }
+                        issueScores(slot, h);
+                        MmaCommit(&misc.BarS[h]);
+                    }
+                    __syncwarp();
                     TRB(it, 10 + 2 * h);
                 }
             }
             if (!failed && it > 0) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (WaitBarA<true>(&misc.BarP[h], (it - 1) & 1, abortFlag)) {
+                    if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
                         TcFenceAfter();
-                        issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                        if (ElectOne()) {
+                            issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                        }
+                        __syncwarp();
                     } else {
                         fail(kDevTimeoutMma);
                         break;
                     }
                 }
             }
-            MmaCommit(&misc.BarDone);
+            __syncwarp();
+            if (ElectOne()) {
+                MmaCommit(&misc.BarDone);
+            }
         }
         __syncwarp();
     } else {

@@ -566,7 +566,9 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
         // Software pipeline over the CTA's whole tile sequence: S(t+1) = Q K^T is issued directly behind O += P(t) V(t),
         // and everything tile t+1 needs (its round record, Q, K/V stage) is waited for before the wait for P(t), so that
         // between the softmax threads' "P written" and their next "S ready" lie only the two groups of MMA instructions.
-        if (lane == 0) {
+        // The whole warp runs the loop and the waits; one elected lane (always the same one) issues, so descriptors and
+        // addresses stay in uniform registers instead of being moved there per instruction.
+        {
             const uint32_t sQa = SmemAddr(sQ), sKa = SmemAddr(sK), sVa = SmemAddr(sV);
             // descriptors without the tile's address: the address field (bits 0-13, in 16-byte units) is added per use
             const uint64_t descBase = MakeSmemDesc(0, 16, GROUP_BYTES, SWZ);
@@ -576,27 +578,25 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             bool pending = false, pendAccum = false, pendMasked = false, pendLast = false;
             int pendSlot = 0, pendQSlot = 0;
             auto wait = [&](uint64_t *bar, uint32_t parity, int code) {
-                if (WaitBarSleep<TSA_FWD_SLEEP_MMA>(bar, parity, abortFlag, p.WaitCycles)) {
+                if (__all_sync(0xffffffffu, WaitBarSleep<TSA_FWD_SLEEP_MMA>(bar, parity, abortFlag, p.WaitCycles))) {
                     return true;
                 }
                 if (!failed) {
                     failed = true;
-                    fail(code);
+                    if (lane == 0) {
+                        fail(code);
+                    }
                 }
                 return false;
             };
             constexpr uint32_t IDESC_QK_HALF = QK_I8 ? MakeInstrDesc(2, 1, 1, 0, 0, TILE_M, TILE_N / 2) : MakeInstrDesc(1, 0, 0, 0, 0, TILE_M, TILE_N / 2);
-            // S = Q K^T for the keys [64h, 64h + 64) of a tile
+            // S = Q K^T for the keys [64h, 64h + 64) of a tile (elected lane)
             auto issueQKHalf = [&](int h, uint64_t qDesc, uint64_t kDesc) {
                 MmaGroupSSCommit<D / 32, QK_I8>(tmem + h * 64, qDesc, kDesc + ((h * 64 * D) >> 4), IDESC_QK_HALF, &misc.BarS[h]);
             };
-            // waits for half h of the pending tile's weights and issues O += P V for it (item-end signals behind the last)
-            auto flushHalf = [&](int h) {
+            // O += P V for half h of the pending tile, item-end signals behind the last (elected lane)
+            auto issuePVHalf = [&](int h) {
                 const uint64_t vDesc = descBase + ((sVa + pendSlot * NV * SM::TILE_BYTES) >> 4);
-                if (!wait(&misc.BarP[h], pCount & 1, kDevTimeoutMma)) {
-                    return false;
-                }
-                TcFenceAfter();
                 MmaPairF8TS(tmem + TMEM_O_COL, tmem + h * 64, vDesc + ((h * 64 * D) >> 4), (32 * D) >> 4, IDESC_PV,
                     (pendAccum || h > 0) ? 1u : 0u, pendMasked);
                 if (V_I8) {
@@ -609,10 +609,21 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                         MmaCommit(&misc.BarOFull);
                         MmaCommit(&misc.QEmpty[pendQSlot]);
                     }
+                }
+            };
+            // waits for half h of the pending tile's weights (whole warp)
+            auto waitWeights = [&](int h) {
+                if (!wait(&misc.BarP[h], pCount & 1, kDevTimeoutMma)) {
+                    return false;
+                }
+                TcFenceAfter();
+                return true;
+            };
+            auto retireHalf = [&](int h) {
+                if (h == 1) {
                     ++pCount;
                     pending = false;
                 }
-                return true;
             };
             while (!failed) {
                 const int rSlot = rCount % ROUND_SLOTS;
@@ -621,7 +632,10 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                 }
                 const volatile TFwdRound &rd = rounds[rSlot];
                 const int j0r = rd.J0, nTiles = rd.NTiles, flags = rd.Flags, qSlot = rd.QSlot, fullLo = rd.FullLo, fullHi = rd.FullHi;
-                MbarArrive(&misc.REmpty[rSlot]);
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&misc.REmpty[rSlot]);
+                }
                 ++rCount;
                 if (flags & RF_END) {
                     break;
@@ -642,18 +656,30 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                     const uint64_t kDesc = descBase + ((sKa + slot * SM::TILE_BYTES) >> 4);
                     // O += P V of the previous tile's half h, then this tile's S into the columns that frees
                     if (pending) {
-                        if (!flushHalf(0)) {
+                        if (!waitWeights(0)) {
                             break;
                         }
-                        issueQKHalf(0, qDesc, kDesc);
-                        if (!flushHalf(1)) {
+                        if (ElectOne()) {
+                            issuePVHalf(0);
+                            issueQKHalf(0, qDesc, kDesc);
+                        }
+                        __syncwarp();
+                        if (!waitWeights(1)) {
                             break;
                         }
-                        issueQKHalf(1, qDesc, kDesc);
+                        if (ElectOne()) {
+                            issuePVHalf(1);
+                            issueQKHalf(1, qDesc, kDesc);
+                        }
+                        __syncwarp();
+                        retireHalf(1);
                     } else {
                         TcFenceAfter();
-                        issueQKHalf(0, qDesc, kDesc);
-                        issueQKHalf(1, qDesc, kDesc);
+                        if (ElectOne()) {
+                            issueQKHalf(0, qDesc, kDesc);
+                            issueQKHalf(1, qDesc, kDesc);
+                        }
+                        __syncwarp();
                     }
                     pending = true;
                     pendSlot = slot;
@@ -668,7 +694,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                     break;
                 }
                 if (flags & RF_LAST) {
-                    if (tilesInItem == 0) {
+                    if (tilesInItem == 0 && lane == 0) {
                         MbarArrive(&misc.QEmpty[qSlot]); // an item without key tiles: nothing was issued for it
                     }
                     ++itemCount;
@@ -677,10 +703,19 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             if (pending && !failed) {
                 // the last tile: the commits that would follow the next tile's S stand in for it (a rescale in this tile's
                 // second half waits on them to know that the first half's PV has retired)
-                if (flushHalf(0)) {
-                    MmaCommit(&misc.BarS[0]);
-                    if (flushHalf(1)) {
-                        MmaCommit(&misc.BarS[1]);
+                if (waitWeights(0)) {
+                    if (ElectOne()) {
+                        issuePVHalf(0);
+                        MmaCommit(&misc.BarS[0]);
+                    }
+                    __syncwarp();
+                    if (waitWeights(1)) {
+                        if (ElectOne()) {
+                            issuePVHalf(1);
+                            MmaCommit(&misc.BarS[1]);
+                        }
+                        __syncwarp();
+                        retireHalf(1);
                     }
                 }
             }

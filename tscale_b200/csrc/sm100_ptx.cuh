@@ -204,6 +204,23 @@ __host__ __device__ constexpr uint32_t MakeInstrDesc(int cFormat, int aFormat, i
         ((uint32_t)bMnMajor << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// One lane of a converged warp, chosen by the hardware.  Code that issues tcgen05.mma runs warp-uniform up to the
+// instruction itself and wraps only the issue in `if (ElectOne())`: descriptors and addresses then stay in uniform
+// registers.  Issued from a divergent `if (lane == 0)` region instead, every operand is moved per instruction, and under
+// busy arithmetic warps the issuing thread was measured three times slower (216 against 70 clocks per MMA).
+__device__ __forceinline__ uint32_t ElectOne()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred;
+}
+
 // ---- MMA issue (one thread) ------------------------------------------------------------------
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void MmaF8SS(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
@@ -408,6 +425,99 @@ __device__ __forceinline__ void MmaPairF8TS(uint32_t dTmem, uint32_t aTmem, uint
             : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(bStep)
             : "memory");
     }
+}
+
+
+// bf16: D[tmem] = A[smem] * B[smem] over KSTEPS steps of 16 elements along K, both operands K-major tiles made of
+// [128 rows][128 bytes] blocks (16 KB each) with the 128-byte swizzle: four steps per block, then the next block.
+// One asm block per group for the reason given above.
+template <int KSTEPS>
+__device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc)
+{
+    static_assert(KSTEPS == 4 || KSTEPS == 8, "four or eight K steps");
+    if (KSTEPS == 4) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred pf, pt;\n\t"
+            ".reg .b64 a<4>, b<4>;\n\t"
+            "setp.ne.u32 pf, 0, 0;\n\t"
+            "setp.eq.u32 pt, 0, 0;\n\t"
+            "add.u64 a1, %1, 2;\n\t"
+            "add.u64 b1, %2, 2;\n\t"
+            "add.u64 a2, %1, 4;\n\t"
+            "add.u64 b2, %2, 4;\n\t"
+            "add.u64 a3, %1, 6;\n\t"
+            "add.u64 b3, %2, 6;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t"
+            "}"
+            :
+            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred pf, pt;\n\t"
+            ".reg .b64 a<8>, b<8>;\n\t"
+            "setp.ne.u32 pf, 0, 0;\n\t"
+            "setp.eq.u32 pt, 0, 0;\n\t"
+            "add.u64 a1, %1, 2;\n\t"
+            "add.u64 b1, %2, 2;\n\t"
+            "add.u64 a2, %1, 4;\n\t"
+            "add.u64 b2, %2, 4;\n\t"
+            "add.u64 a3, %1, 6;\n\t"
+            "add.u64 b3, %2, 6;\n\t"
+            "add.u64 a4, %1, 1024;\n\t"
+            "add.u64 b4, %2, 1024;\n\t"
+            "add.u64 a5, %1, 1026;\n\t"
+            "add.u64 b5, %2, 1026;\n\t"
+            "add.u64 a6, %1, 1028;\n\t"
+            "add.u64 b6, %2, 1028;\n\t"
+            "add.u64 a7, %1, 1030;\n\t"
+            "add.u64 b7, %2, 1030;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a4, b4, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a5, b5, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a6, b6, %3, pt;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], a7, b7, %3, pt;\n\t"
+            "}"
+            :
+            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc)
+            : "memory");
+    }
+}
+
+// bf16: D[tmem] (+)= A[tmem] * B[smem] over four K steps of 16: A at aTmem + 0, 8, 32, 40 columns (two 32-key blocks,
+// each with its packed pairs in its first 16 columns), B descriptors bDesc + 0, 128, 256, 384 (16 rows of 128 bytes per
+// step, MN-major); `accumulate` applies to the first step.
+__device__ __forceinline__ void MmaQuadF16TS(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, pt;\n\t"
+        ".reg .b64 b1, b2, b3;\n\t"
+        ".reg .b32 a1, a2, a3;\n\t"
+        "setp.ne.b32 p0, %4, 0;\n\t"
+        "setp.eq.u32 pt, 0, 0;\n\t"
+        "add.u64 b1, %2, 128;\n\t"
+        "add.u64 b2, %2, 256;\n\t"
+        "add.u64 b3, %2, 384;\n\t"
+        "add.u32 a1, %1, 8;\n\t"
+        "add.u32 a2, %1, 32;\n\t"
+        "add.u32 a3, %1, 40;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, pt;\n\t"
+        "}"
+        :
+        : "r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 // arrive on the mbarrier when all MMAs issued so far by this thread have completed
