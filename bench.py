@@ -427,7 +427,7 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
 
     e2e = None
     if not args.no_e2e and not quick:
-        e2e = longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, n_slices, world, dev, flops)
+        e2e = longctx_e2e(torch, dist, shard, ops, args, cfg, mask, slope, t, out_local, h0, nh, d, world, dev, flops, status)
 
     if rank != 0:
         return None
@@ -505,38 +505,29 @@ def reference_gpu_kernel(torch, ops, w, t, mask, seq, d, cfg, workspace, status,
             "speedup": ms_ref / ms_ours}
 
 
-def longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, n_slices, world, dev, flops):
-    """The same step with HOST buffers: the rank's inputs come from pinned host memory every step, its output blocks go
-    back to pinned host memory; copies, kernels and the gather inside the timed region."""
-    names = ("q", "k", "v", "sq", "sk", "sv")
-    host_in = {n: t[n].cpu().pin_memory() for n in names}
-    host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in out_local]
-    stage = {n: torch.empty_like(t[n]) for n in names}
-    h2d = torch.cuda.Stream(device=dev)
-    d2h = torch.cuda.Stream(device=dev)
-    main_s = torch.cuda.current_stream()
-    h2d_bytes = sum(v.numel() * v.element_size() for v in host_in.values())
-    d2h_bytes = sum(v.numel() * v.element_size() for v in host_out)
+def longctx_e2e(torch, dist, shard, ops, args, cfg, mask, slope, t, out_local, h0, nh, d, world, dev, flops, status):
+    """The same step through the library's host-buffer entry (tsa_att_fwd_host): the rank's vectors start in pinned host
+    memory every step and its output block ends there; the library copies head slices in, computes and copies out
+    concurrently.  With several ranks the result is also kept on the device and all-gathered.  Copies, kernels and the
+    gather are inside the timed region."""
+    cols = slice(h0 * d, (h0 + nh) * d)
+    pin = lambda x: x.contiguous().cpu().pin_memory()
+    hq, hk, hv = pin(t["q"][:, cols]), pin(t["k"][:, cols]), pin(t["v"][:, cols])
+    hsq, hsk, hsv = pin(t["sq"][h0:h0 + nh]), pin(t["sk"][h0:h0 + nh]), pin(t["sv"][h0:h0 + nh])
+    rows = hq.shape[0]
+    host_out = torch.empty((rows, nh * d), dtype=torch.bfloat16).pin_memory()
+    out_dev = torch.empty((rows, nh * d), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    gathered = torch.empty((world, rows, nh * d), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    slices = next(k for k in (8, 4, 2, 1) if nh % k == 0)
+    h2d_bytes = sum(v.numel() * v.element_size() for v in (hq, hk, hv, hsq, hsk, hsv))
+    d2h_bytes = host_out.numel() * host_out.element_size()
+    box = [None]
 
     def step():
-        with torch.cuda.stream(h2d):
-            h2d.wait_stream(main_s)  # the staging buffers are free once the previous step's kernels are done
-            for n in names:
-                stage[n].copy_(host_in[n], non_blocking=True)
-        main_s.wait_stream(h2d)
-        pending = []
-        for s in range(n_slices):
-            launch_slice(s, stage)
-            done = torch.cuda.Event()
-            done.record(main_s)
-            if world > 1:
-                pending.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
-            with torch.cuda.stream(d2h):
-                d2h.wait_event(done)
-                host_out[s].copy_(out_local[s], non_blocking=True)
-        for h in pending:
-            h.wait()
-        main_s.wait_stream(d2h)
+        box[0] = ops.att_fwd_host(cfg, hq, hk, hv, hsk, mask, slope, nh, host_out, qk_scale=hsq, v_scale=hsv, slices=slices,
+                                  staging=box[0], status=status, device=dev, out_device=out_dev)
+        if world > 1:
+            shard.gather_blocks(out_dev, gathered)
 
     def barrier():
         torch.cuda.synchronize()
@@ -547,6 +538,10 @@ def longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, 
     steps = max(2, min(args.steps, 4))
     step()
     barrier()
+    # the host copy carries the bits of the device-resident run
+    n_loc = len(out_local)
+    hs = nh // n_loc
+    same = all(bool(torch.equal(host_out[:, s * hs * d:(s + 1) * hs * d], out_local[s].cpu())) for s in range(n_loc))
     a = torch.cuda.Event(enable_timing=True)
     b = torch.cuda.Event(enable_timing=True)
     a.record()
@@ -554,13 +549,16 @@ def longctx_e2e(torch, dist, shard, args, t, out_local, gathered, launch_slice, 
         step()
     b.record()
     barrier()
+    assert int(status.item()) == 0, "device status %#x in the end-to-end run" % int(status.item())
     tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     ms = float(tt.item()) / steps
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
-            "d2h_bytes_per_step": d2h_bytes, "ms_per_step": ms, "steps": steps,
-            "note": "bytes are this rank's: every rank copies its own shard in and its own output block out"}
+            "d2h_bytes_per_step": d2h_bytes, "ms_per_step": ms, "steps": steps, "entry": "tsa_att_fwd_host", "slices": slices,
+            "matches_device_run": same,
+            "note": "bytes are this rank's: every rank copies its own shard in and its own output block out; head slices are "
+                    "copied in, computed and copied out concurrently by the library"}
 
 
 # ----------------------------------------------------------------------------------------------------

@@ -104,6 +104,28 @@ int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
  * plane and the work-item counter of the persistent kernel); the call clears what it uses. */
 size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len);
 
+/* Forward for vectors that live in page-locked HOST memory.  Same arguments and results as tsa_att_fwd, except that qk,
+ * qv, qkScale, qvScale, v, vScale, out and sumWeightLog point to host memory (cudaHostAlloc / cudaHostRegister; pageable
+ * memory works but its copies do not overlap anything) while attSpans, attSpanPtr, qvGlobalScale and statusWord stay
+ * device memory.  The heads are cut into `slices` groups of ceil(H / slices) heads; the head columns of slice s+1 are
+ * copied in, slice s is computed and the output columns of slice s-1 are copied out at the same time, on three streams
+ * the library keeps per device, ordered behind everything queued on `stream` before the call; `stream` continues when
+ * the last output copy has landed, so the caller synchronises `stream` (or an event recorded on it) before reading out.
+ * The reference moves whole arrays with TCuda2DArray::CopyToDevice / CopyToHost on its compute stream
+ * (code/lib/cuda/cuda_arrays.h:353-369), copy - compute - copy in sequence; this entry overlaps the three.
+ * outDevice (may be absent): device matrix [len][H*Dv] of cfg->out_dtype that also keeps the result, for a caller that
+ * goes on with it on the GPU (an all-gather across ranks, the next layer); the host copy is made from it.
+ * staging: tsa_att_fwd_host_staging_bytes(cfg, H, len, slices) bytes of 256-byte aligned device memory (two sets of one
+ * slice's inputs, outputs and forward workspace).  One call at a time per device enqueues (the library serialises
+ * callers); two calls on different streams that share a staging area are the caller's to order. */
+int tsa_att_fwd_host(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    tsa_ptr2d out, tsa_ptr2d sumWeightLog, tsa_ptr2d outDevice, int headCount, int lenAttTiles, int slices,
+    void *staging, size_t stagingBytes, int *statusWord, tsa_stream_t stream);
+size_t tsa_att_fwd_host_staging_bytes(const tsa_att_cfg *cfg, int headCount, int len, int slices);
+
 /* ---- backward --------------------------------------------------------------------------------
  * Replaces Fp8AttGradQK + Fp8AttGradQV (gpt_att_fp8.cuh:277-284, 599-606) and Fp16AttGradQK/QV
  * (gpt_att_fp16.cuh:332, 459).  Additional inputs: dOut [len][H*Dv] of cfg->grad_dtype, out (forward

@@ -91,6 +91,40 @@ def test_fwd_config0_full_size_default_dispatch(slope, golden_dir):
     assert util.err_stats(out, out_g)[0] < 5e-3 * vmax
 
 
+@pytest.mark.parametrize("heads,slices,qk_dtype,d", [(6, 4, "i8", 128), (5, 2, "e4m3", 64), (3, 3, "i8", 64), (4, 1, "e4m3", 128)])
+def test_fwd_host_buffers_match_device_call(heads, slices, qk_dtype, d):
+    """tsa_att_fwd_host (pinned host vectors, head slices copied in, computed and copied out concurrently) gives the bits of
+    tsa_att_fwd on the same vectors in device memory, ragged last slice included, and the oracle's values; the optional
+    device copy of the result holds the same bits; rows and columns around the host output stay untouched."""
+    from tscale_b200 import ops
+    frag_lens, window, slope = [384, 256, 128], 256, 0.25
+    out_d, lse_d, ref, (g, mask, cfg, _, _, _) = _run_fwd(3, frag_lens, window, slope, heads, d, qk_dtype, "e4m3", out_dtype=torch.bfloat16, scale=0.5)
+    rows = sum(frag_lens)
+    pin = lambda x: x.cpu().pin_memory()
+    h = {n: pin(g[n]) for n in ("q8", "k8", "v8", "sq", "sk", "sv")}
+    # host output inside a guard band: one row before and after, 8 columns to the right
+    guard = torch.full((rows + 2, heads * d + 8), -7.0, dtype=torch.bfloat16).pin_memory()
+    out_h = guard[1:rows + 1, :heads * d]
+    lse_h = torch.zeros((heads, rows), dtype=torch.float32).pin_memory()
+    out_dev = torch.zeros((rows, heads * d), dtype=torch.bfloat16, device=_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    staging = None
+    for _ in range(2):  # the second call reuses the staging area and the library's streams
+        staging = ops.att_fwd_host(cfg, h["q8"], h["k8"], h["v8"], h["sk"], mask, slope, heads, out_h, lse=lse_h, qk_scale=h["sq"],
+                                   v_scale=h["sv"], slices=slices, staging=staging, status=status, out_device=out_dev)
+        torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(util.to_np(out_h.contiguous()), out_d)
+    assert np.array_equal(util.to_np(out_dev), out_d)
+    assert np.array_equal(lse_h.numpy(), lse_d)
+    assert util.err_stats(out_d, ref["out"])[0] < util.OUT_MAX_ABS
+    assert bool((guard[0] == -7.0).all()) and bool((guard[rows + 1] == -7.0).all()) and bool((guard[:, heads * d:] == -7.0).all())
+    # too small a staging area is refused with a message, nothing is queued
+    with pytest.raises(Exception):
+        ops.att_fwd_host(cfg, h["q8"], h["k8"], h["v8"], h["sk"], mask, slope, heads, out_h, qk_scale=h["sq"], v_scale=h["sv"],
+                         slices=slices, staging=staging[:1024], status=status)
+
+
 @pytest.mark.parametrize("d", [64, 128])
 def test_fwd_tcgen05_constant_scales(d):
     # the reference's call shape: constant query and value scales (QK_VEC_SCALE / V_VEC_SCALE), per-row key scale

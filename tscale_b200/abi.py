@@ -75,7 +75,7 @@ EXPORTS = [
     "tsa_group_attention", "tsa_group_window_spans", "tsa_att_decode_static", "tsa_att_decode_static_capacity_bytes",
     "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device", "tsa_kv_product", "tsa_kv_product_bwd",
     "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects", "tsa_status_from_word", "tsa_selftest_bounded_wait",
-    "tsa_selftest_fwd_withhold_copy",
+    "tsa_selftest_fwd_withhold_copy", "tsa_att_fwd_host", "tsa_att_fwd_host_staging_bytes",
 ]
 
 
@@ -85,6 +85,10 @@ def _declare(lib):
     lib.tsa_last_error.restype = ctypes.c_char_p
     lib.tsa_att_fwd.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, c_void_p, c_void_p, c_float,
                                 P, P, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
+    lib.tsa_att_fwd_host.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, c_void_p, c_void_p, c_float,
+                                     P, P, P, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
+    lib.tsa_att_fwd_host_staging_bytes.restype = c_size_t
+    lib.tsa_att_fwd_host_staging_bytes.argtypes = [ctypes.POINTER(AttCfg), c_int, c_int, c_int]
     lib.tsa_att_fwd_workspace_bytes.restype = c_size_t
     lib.tsa_att_fwd_workspace_bytes.argtypes = [ctypes.POINTER(AttCfg), c_int, c_int]
     lib.tsa_att_bwd.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, P, P, P, P,

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     constexpr uint32_t BLOCK_BYTES = 128 * 128;         // one [128 rows][128 bytes] block of a tile
     constexpr uint32_t IDESC_SS = MakeInstrDesc(1, 1, 1, 0, 0, TILE_ROWS, 64); // bf16 x bf16 -> f32, both K-major, 64 columns
     constexpr uint32_t IDESC_OUT = MakeInstrDesc(1, 1, 1, 0, 1, TILE_ROWS, D); // A from tensor memory, B MN-major
-    constexpr int BAR_HALF0 = 1;                        // + h: named barrier of the 256 threads of half h
+    constexpr int BAR_ARITH = 1;                        // named barrier of the 512 arithmetic threads
     constexpr int QUARTER_D = D / 4;
     constexpr int OUTPUTS = MODE_DKV ? 2 : 1;
 
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         }
         for (int h = 0; h < 2; ++h) {
             MbarInit(&misc.BarS[h], 1);
-            MbarInit(&misc.BarP[h], BWD_HALF_THREADS / 32);
+            MbarInit(&misc.BarP[h], BWD_ARITH_THREADS / 32);
         }
         MbarInit(&misc.BarDone, 1);
         misc.Abort = 0;
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 MmaGroupF16SS<D / 16>(tmem + BWD_DP_COL + h * 64, kDescBase + (sR2a >> 4), kDescBase + (c2 >> 4), IDESC_SS);
             };
             // out1 += A1 C1 (and out2 += A2 C2) over the half's 64 tile columns = 4 steps of 16: A from tensor memory
-            // (quarter q of the tile keeps its bf16 pairs in columns 32q .. 32q+15), B = the column tile read MN-major
+            // (the bf16 pairs of tile columns [16k, 16k + 16) sit in columns 16k .. 16k+7), B = the column tile read MN-major
             auto issueOutputs = [&](int slot, int h, bool accumulate) {
                 const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES, c2 = c1 + SM::TILE_BYTES;
                 MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + ((c1 + h * 4 * 16 * 128) >> 4), IDESC_OUT, accumulate ? 1u : 0u);
@@ -299,9 +299,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- arithmetic warps
-        const int quarter = tid >> 7;          // 32-column block of the tile
-        const int h = quarter >> 1;            // half: its own barriers and staging
-        const int hl = tid & (BWD_HALF_THREADS - 1);
+        const int quarter = tid >> 7;          // 16-column block of each 64-column half
         const int r = tid & (TILE_ROWS - 1);
         const int row = rowTile * TILE_ROWS + r;
         const uint32_t tLane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -327,22 +325,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         const float2 negDeltaM2 = make_float2(-rowDelta * dsMult, -rowDelta * dsMult);
 
         int spanS = 1, spanF = 0, spanRound = -1;
-        // columns [64h, 64h + 64) of the tile are staged by the first 64 threads of the half, one tile ahead
+        // the tile's 128 column factors are staged by the first 128 threads, one tile ahead
         float pfA = 0, pfT = 0, pfB = 0;
         auto fetchCols = [&](int c0) {
             pfA = 0;
             pfT = 0;
             pfB = 0;
-            const int lc = h * 64 + hl;
-            const int c = c0 + lc;
-            if (hl < 64 && c < p.Rows) {
+            const int c = c0 + tid;
+            if (tid < TILE_ROWS && c < p.Rows) {
                 if (!MODE_DKV) {
                     pfA = p.KScale.Row(head)[c];
-                    pfT = p.Slope * (float)lc;
+                    pfT = p.Slope * (float)tid;
                     pfB = (p.VScale.Valid() ? p.VScale.Row(head)[c] : p.VVecScale) * dsMult;
                 } else {
                     pfA = p.QScale.Valid() ? p.QScale.Row(head)[c] : p.QkVecScale;
-                    pfT = -p.Lse.Row(head)[c] - p.Slope * (float)lc;
+                    pfT = -p.Lse.Row(head)[c] - p.Slope * (float)tid;
                     pfB = -p.DScale.Row(head)[c] * dsMult;
                 }
             }
@@ -364,23 +361,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                 }
                 spanRound = cur.Round;
             }
-            TRB(it, 4 * h);
+            TRB(it, 0);
             const int buf = it & 1;
-            if (hl < 64) {
-                misc.ColA[buf][h * 64 + hl] = pfA;
-                misc.ColT[buf][h * 64 + hl] = pfT;
-                misc.ColB[buf][h * 64 + hl] = pfB;
+            if (tid < TILE_ROWS) {
+                misc.ColA[buf][tid] = pfA;
+                misc.ColT[buf][tid] = pfT;
+                misc.ColB[buf][tid] = pfB;
             }
             const int c0 = cur.J0;
             const int ls = spanS - c0, lf = min(spanF, p.Rows - 1) - c0; // span in tile-local columns
             const bool rowFull = ls <= 0 && lf >= TILE_ROWS - 1;
             const bool warpMasked = !__all_sync(0xffffffffu, rowFull);
-            // publishes the staged columns to the half; a failed wait is carried here so the half leaves together
-            if (BarRedOr(BAR_HALF0 + h, BWD_HALF_THREADS, failed || (*(volatile int *)&misc.Abort != 0))) {
+            // publishes the staged columns; a failed wait is carried here so the arithmetic threads leave together
+            if (BarRedOr(BAR_ARITH, BWD_ARITH_THREADS, failed || (*(volatile int *)&misc.Abort != 0))) {
                 failed = true;
                 break;
             }
-            TRB(it, 4 * h + 1);
+            TRB(it, 1);
             {
                 TTileIter nxt = cur;
                 nxt.Advance();
@@ -388,28 +385,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     fetchCols(nxt.J0);
                 }
             }
-            if (!WaitBarA(&misc.BarS[h], it & 1, abortFlag)) {
-                failed = true;
-                *(volatile int *)&misc.Abort = 1;
-                if (p.Status) {
-                    atomicOr(p.Status, kDevTimeoutMma);
-                }
-                cur.Advance();
-                ++it;
-                continue; // to the half's next barrier
-            }
-            TcFenceAfter();
-            TRB(it, 4 * h + 2);
-
             // exponent = u * rowMult + (ColT + rowConst):  dQ: ALiBi + rowOff - lse_i;  dK/dV: -lse_i - ALiBi with the sign of the
             // transposed tile
             const float rowOff = -p.Slope * (float)(row - c0);
             const float rowConst = MODE_DKV ? -rowOff : rowOff - rowLse;
             const float2 rowConst2 = make_float2(rowConst, rowConst);
 #pragma unroll 1
-            for (int sc = 0; sc < 2; ++sc) {
-                const int cb = quarter * 32 + sc * 16; // first tile column of this step
-                // span clipped to this step, step-local: (unsigned)(c - lsQ) <= spanW  <=>  inside the span
+            for (int h = 0; h < 2; ++h) {
+                if (!WaitBarA(&misc.BarS[h], it & 1, abortFlag)) {
+                    failed = true;
+                    *(volatile int *)&misc.Abort = 1;
+                    if (p.Status) {
+                        atomicOr(p.Status, kDevTimeoutMma);
+                    }
+                    break; // to the next barrier of the arithmetic threads
+                }
+                TcFenceAfter();
+                TRB(it, 4 * h + 2);
+                const int cb = h * 64 + quarter * 16; // first tile column of this thread's block in the half
+                // span clipped to this block, block-local: (unsigned)(c - lsQ) <= spanW  <=>  inside the span
                 const int lsC = max(ls, cb), lfC = min(lf, cb + 15);
                 const bool rowEmpty = lsC > lfC;
                 const int lsQ = lsC - cb;
@@ -451,19 +445,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                         a2[k] = 0;
                     }
                 }
-                // 16 bf16 values = 8 columns, written over columns this thread has already read
-                TmemStN<8>(tLane + BWD_S_COL + quarter * 32 + sc * 8, a1);
+                // 16 bf16 values = 8 columns, written over the first half of the 16 columns this thread has just read
+                TmemStN<8>(tLane + BWD_S_COL + cb, a1);
                 if (MODE_DKV) {
-                    TmemStN<8>(tLane + BWD_DP_COL + quarter * 32 + sc * 8, a2);
+                    TmemStN<8>(tLane + BWD_DP_COL + cb, a2);
                 }
+                TmemWaitSt();
+                TcFenceBefore();
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&misc.BarP[h]);
+                }
+                TRB(it, 4 * h + 3);
             }
-            TmemWaitSt();
-            TcFenceBefore();
-            __syncwarp();
-            if (lane == 0) {
-                MbarArrive(&misc.BarP[h]);
-            }
-            TRB(it, 4 * h + 3);
             cur.Advance();
             ++it;
         }

@@ -492,8 +492,8 @@ __device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, ui
     }
 }
 
-// bf16: D[tmem] (+)= A[tmem] * B[smem] over four K steps of 16: A at aTmem + 0, 8, 32, 40 columns (two 32-key blocks,
-// each with its packed pairs in its first 16 columns), B descriptors bDesc + 0, 128, 256, 384 (16 rows of 128 bytes per
+// bf16: D[tmem] (+)= A[tmem] * B[smem] over four K steps of 16: A at aTmem + 0, 16, 32, 48 columns (each block of 16
+// keys keeps its packed pairs in the first 8 of its own 16 columns), B descriptors bDesc + 0, 128, 256, 384 (16 rows of 128 bytes per
 // step, MN-major); `accumulate` applies to the first step.
 __device__ __forceinline__ void MmaQuadF16TS(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
 {
@@ -507,9 +507,9 @@ __device__ __forceinline__ void MmaQuadF16TS(uint32_t dTmem, uint32_t aTmem, uin
         "add.u64 b1, %2, 128;\n\t"
         "add.u64 b2, %2, 256;\n\t"
         "add.u64 b3, %2, 384;\n\t"
-        "add.u32 a1, %1, 8;\n\t"
+        "add.u32 a1, %1, 16;\n\t"
         "add.u32 a2, %1, 32;\n\t"
-        "add.u32 a3, %1, 40;\n\t"
+        "add.u32 a3, %1, 48;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, pt;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, pt;\n\t"

@@ -216,6 +216,25 @@ def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale
     return out, lse
 
 
+def att_fwd_host(cfg, qk, qv, v, qv_scale, mask, slope, heads, out, lse=None, qk_scale=None, v_scale=None, global_scale=None,
+                 slices=4, staging=None, status=None, device=None, out_device=None):
+    """Forward on page-locked HOST tensors (qk, qv, v, the scale planes, out and lse on the CPU, pinned): head slices are
+    copied in, computed and copied out concurrently by the library.  Asynchronous: synchronise the current stream before
+    reading `out`.  out_device: optional CUDA tensor [len][H*Dv] that also keeps the result.  Returns the staging tensor
+    so that the caller can pass it again."""
+    L = abi.lib()
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    rows = qk.shape[0]
+    need = L.tsa_att_fwd_host_staging_bytes(ctypes.byref(cfg), heads, rows, slices)
+    if staging is None:
+        staging = torch.empty(need, dtype=torch.uint8, device=dev)
+    groups, gptr, _, _ = mask.dev(dev)
+    check(L.tsa_att_fwd_host(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
+                             p2d(v), p2d(v_scale), _ptr(groups), _ptr(gptr), slope, p2d(out), p2d(lse), p2d(out_device),
+                             heads, mask.len_att_tiles, slices, _ptr(staging), staging.numel(), _ptr(status), _stream()))
+    return staging
+
+
 def att_bwd(cfg, qk, qv, v, qv_scale, d_out, out, lse, mask, slope, heads, qk_scale=None, v_scale=None,
             global_scale=None, d_scale=None, grad_mult=1.0, workspace=None, status=None):
     """Backward.  Returns (dQK, dQV, dV) with respect to the true-scale vectors."""
