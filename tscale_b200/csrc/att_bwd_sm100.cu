@@ -67,9 +67,12 @@ template <int D>
 struct TBwdSmem {
     static constexpr int STAGES = (D == 64) ? 3 : 2;
     static constexpr int TILE_BYTES = 128 * D * 2;
+    // column tiles travel in halves of 64 rows: a ring of HSTAGES half stages, each [C1 half][C2 half]
+    static constexpr int HSTAGES = 2 * STAGES;
+    static constexpr int HALF_TILE_BYTES = TILE_BYTES / 2;
     static constexpr int R1_OFF = 0;
     static constexpr int R2_OFF = TILE_BYTES;
-    static constexpr int C_OFF = 2 * TILE_BYTES;              // stage s: C1 at C_OFF + s * 2 * TILE, C2 right after
+    static constexpr int C_OFF = 2 * TILE_BYTES;              // half stage s: C1 rows at C_OFF + s * TILE, C2 rows right after
     static constexpr int MISC_OFF = C_OFF + STAGES * 2 * TILE_BYTES;
     static constexpr int TOTAL = MISC_OFF + 8192;
 };
@@ -81,8 +84,8 @@ struct TBwdMisc {
     float ColB[2][TILE_ROWS]; // dQ: sv_j c ln2;  dK/dV: -delta_i c ln2
     int Abort;
     uint64_t BarR;            // TMA: row tiles landed
-    uint64_t BarFull[4];      // TMA: column stage landed
-    uint64_t BarEmpty[4];     // MMA warp -> loader: the stage's last output product has retired
+    uint64_t BarFull[8];      // TMA: half stage (64 rows of C1 and C2) landed
+    uint64_t BarEmpty[8];     // MMA warp -> loader: the half stage's output products have retired
     uint64_t BarS[2];         // control -> half h: S and dP columns of the half ready
     uint64_t BarP[2];         // half h -> control: A1 / A2 of the half written (8 warp arrivals)
     uint64_t BarDone;         // control -> all: every output product has retired
@@ -103,7 +106,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     const __grid_constant__ TBwdParams p)
 {
     using SM = TBwdSmem<D>;
-    constexpr int STAGES = SM::STAGES;
+    constexpr int HSTAGES = SM::HSTAGES;
+    constexpr uint32_t HALF_BLOCK_BYTES = 64 * 128;     // one [64 rows][128 bytes] block of a half column tile
     constexpr int KBLOCKS = D / 64;                     // 64-element (128-byte) blocks along the head dimension
     constexpr uint32_t BLOCK_BYTES = 128 * 128;         // one [128 rows][128 bytes] block of a tile
     constexpr uint32_t IDESC_SS = MakeInstrDesc(1, 1, 1, 0, 0, TILE_ROWS, 64); // bf16 x bf16 -> f32, both K-major, 64 columns
@@ -130,7 +134,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     }
     if (tid == 0) {
         MbarInit(&misc.BarR, 1);
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < HSTAGES; ++s) {
             MbarInit(&misc.BarFull[s], 1);
             MbarInit(&misc.BarEmpty[s], 1);
         }
@@ -165,36 +169,47 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             PrefetchTensorMap(&tmR2);
             PrefetchTensorMap(&tmC1);
             PrefetchTensorMap(&tmC2);
+            // every tensor map has boxes of 64 rows x 64 elements (128 bytes): a row tile is two boxes per block
             auto loadTile = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
 #pragma unroll
                 for (int kb = 0; kb < KBLOCKS; ++kb) {
                     TmaLoad2D(dst + kb * BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
+                    TmaLoad2D(dst + kb * BLOCK_BYTES + HALF_BLOCK_BYTES, tm, head * D + kb * 64, rowBase + 64, bar);
+                }
+            };
+            auto loadHalf = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
+#pragma unroll
+                for (int kb = 0; kb < KBLOCKS; ++kb) {
+                    TmaLoad2D(dst + kb * HALF_BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
                 }
             };
             MbarExpectTx(&misc.BarR, 2 * SM::TILE_BYTES);
             loadTile(sR1, &tmR1, rowTile * TILE_ROWS, &misc.BarR);
             loadTile(sR2, &tmR2, rowTile * TILE_ROWS, &misc.BarR);
-            int g = 0;
+            int g = 0; // half stages requested
             bool failed = false;
-            for (TTileIter prod = cur; prod.Valid && !failed; prod.Advance(), ++g) {
-                const int slot = g % STAGES;
-                if (g >= STAGES && !WaitBarA(&misc.BarEmpty[slot], ((g / STAGES) - 1) & 1, abortFlag)) {
-                    failed = true;
-                    *(volatile int *)&misc.Abort = 1;
-                    if (p.Status) {
-                        atomicOr(p.Status, kDevTimeoutMma);
+            for (TTileIter prod = cur; prod.Valid && !failed; prod.Advance()) {
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h, ++g) {
+                    const int slot = g % HSTAGES;
+                    if (g >= HSTAGES && !WaitBarA(&misc.BarEmpty[slot], ((g / HSTAGES) - 1) & 1, abortFlag)) {
+                        failed = true;
+                        *(volatile int *)&misc.Abort = 1;
+                        if (p.Status) {
+                            atomicOr(p.Status, kDevTimeoutMma);
+                        }
+                        break;
                     }
-                    break;
+                    MbarExpectTx(&misc.BarFull[slot], 2 * SM::HALF_TILE_BYTES);
+                    loadHalf(sC + slot * 2 * SM::HALF_TILE_BYTES, &tmC1, prod.J0 + 64 * h, &misc.BarFull[slot]);
+                    loadHalf(sC + slot * 2 * SM::HALF_TILE_BYTES + SM::HALF_TILE_BYTES, &tmC2, prod.J0 + 64 * h, &misc.BarFull[slot]);
                 }
-                MbarExpectTx(&misc.BarFull[slot], 2 * SM::TILE_BYTES);
-                loadTile(sC + slot * 2 * SM::TILE_BYTES, &tmC1, prod.J0, &misc.BarFull[slot]);
-                loadTile(sC + slot * 2 * SM::TILE_BYTES + SM::TILE_BYTES, &tmC2, prod.J0, &misc.BarFull[slot]);
             }
             if (*(volatile int *)&misc.Abort) {
                 // drain copies that were requested, so none lands after the CTA is gone
                 WaitBar(&misc.BarR, 0);
-                for (int t = max(0, g - STAGES); t < g; ++t) {
-                    WaitBar(&misc.BarFull[t % STAGES], (t / STAGES) & 1);
+                for (int t = max(0, g - HSTAGES); t < g; ++t) {
+                    WaitBar(&misc.BarFull[t % HSTAGES], (t / HSTAGES) & 1);
                 }
             }
         }
@@ -205,22 +220,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         if (cur.Valid) {
             const uint32_t sR1a = SmemAddr(sR1), sR2a = SmemAddr(sR2), sCa = SmemAddr(sC);
             bool failed = false;
-            // descriptor of a K-major / MN-major tile without its address (added per use, in 16-byte units)
-            const uint64_t kDescBase = MakeSmemDesc(0, 16, 1024, 128), mnDescBase = MakeSmemDesc(0, BLOCK_BYTES, 1024, 128);
-            // columns [64h, 64h + 64) of S = R1 C1^T and dP = R2 C2^T: both operands K-major, D / 16 steps of 16
-            // elements (32 bytes); the B operand starts 64 rows (8 KB per 128-byte block) into the column tile
+            // descriptors of a K-major tile and of an MN-major half column tile without the address (added per use, in
+            // 16-byte units)
+            const uint64_t kDescBase = MakeSmemDesc(0, 16, 1024, 128), mnDescBase = MakeSmemDesc(0, HALF_BLOCK_BYTES, 1024, 128);
+            // columns [64h, 64h + 64) of S = R1 C1^T and dP = R2 C2^T from half stage `slot` (the 64 rows of C1 and C2 that
+            // belong to the half): both operands K-major, D / 16 steps of 16 elements (32 bytes), the B blocks 8 KB apart
             auto issueScores = [&](int slot, int h) {
-                const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES + h * 8192, c2 = c1 + SM::TILE_BYTES;
-                MmaGroupF16SS<D / 16>(tmem + BWD_S_COL + h * 64, kDescBase + (sR1a >> 4), kDescBase + (c1 >> 4), IDESC_SS);
-                MmaGroupF16SS<D / 16>(tmem + BWD_DP_COL + h * 64, kDescBase + (sR2a >> 4), kDescBase + (c2 >> 4), IDESC_SS);
+                const uint32_t c1 = sCa + slot * 2 * SM::HALF_TILE_BYTES, c2 = c1 + SM::HALF_TILE_BYTES;
+                MmaGroupF16SS<D / 16>(tmem + BWD_S_COL + h * 64, kDescBase + (sR1a >> 4), kDescBase + (c1 >> 4), IDESC_SS, HALF_BLOCK_BYTES >> 4);
+                MmaGroupF16SS<D / 16>(tmem + BWD_DP_COL + h * 64, kDescBase + (sR2a >> 4), kDescBase + (c2 >> 4), IDESC_SS, HALF_BLOCK_BYTES >> 4);
             };
             // out1 += A1 C1 (and out2 += A2 C2) over the half's 64 tile columns = 4 steps of 16: A from tensor memory
-            // (the bf16 pairs of tile columns [16k, 16k + 16) sit in columns 16k .. 16k+7), B = the column tile read MN-major
+            // (the bf16 pairs of tile columns [16k, 16k + 16) sit in columns 16k .. 16k+7), B = the half column tile read
+            // MN-major (16 rows of 128 bytes per step)
             auto issueOutputs = [&](int slot, int h, bool accumulate) {
-                const uint32_t c1 = sCa + slot * 2 * SM::TILE_BYTES, c2 = c1 + SM::TILE_BYTES;
-                MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + ((c1 + h * 4 * 16 * 128) >> 4), IDESC_OUT, accumulate ? 1u : 0u);
+                const uint32_t c1 = sCa + slot * 2 * SM::HALF_TILE_BYTES, c2 = c1 + SM::HALF_TILE_BYTES;
+                MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + (c1 >> 4), IDESC_OUT, accumulate ? 1u : 0u);
                 if (MODE_DKV) {
-                    MmaQuadF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + h * 64, mnDescBase + ((c2 + h * 4 * 16 * 128) >> 4), IDESC_OUT, accumulate ? 1u : 0u);
+                    MmaQuadF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + h * 64, mnDescBase + (c2 >> 4), IDESC_OUT, accumulate ? 1u : 0u);
                 }
             };
             auto fail = [&](int code) {
@@ -237,15 +254,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             }
             // Tensor-pipe order per tile: out(h0, it-1), scores(h0, it), out(h1, it-1), scores(h1, it).  The outputs of a
             // half must read its A columns before the next scores of that half overwrite them; the pipe runs in order.
-            // The warp never waits for its own MMAs, so the pipe stays fed; the loader refills a stage when the
-            // commit made after the stage's last output product completes.
+            // The warp never waits for its own MMAs, so the pipe stays fed; the loader refills a half stage when the
+            // commit made after its output products completes.  Half (it, h) lives in half stage (2 it + h) % HSTAGES.
             int it = 0;
             TTileIter ctl = cur;
             for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
-                const int slot = it % STAGES;
                 TRB(it, 8);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    const int g = 2 * it + h;
+                    const int slot = g % HSTAGES, prevSlot = (g - 2 + HSTAGES) % HSTAGES;
                     if (it > 0) {
                         if (!__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
                             fail(kDevTimeoutMma);
@@ -254,7 +272,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                         TcFenceAfter();
                         TRB(it, 9 + 2 * h);
                     }
-                    if (h == 0 && !__all_sync(0xffffffffu, WaitBarA(&misc.BarFull[slot], (it / STAGES) & 1, abortFlag))) {
+                    if (!__all_sync(0xffffffffu, WaitBarA(&misc.BarFull[slot], (g / HSTAGES) & 1, abortFlag))) {
                         fail(kDevTimeoutTma);
                         break;
                     }
@@ -264,10 +282,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     }
                     if (ElectOne()) {
                         if (it > 0) {
-                            issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
-                            if (h == 1) {
-                                MmaCommit(&misc.BarEmpty[(it - 1) % STAGES]);
-                            }
+                            issueOutputs(prevSlot, h, it - 1 > 0 || h > 0);
+                            MmaCommit(&misc.BarEmpty[prevSlot]);
                         }
                         issueScores(slot, h);
                         MmaCommit(&misc.BarS[h]);
@@ -282,7 +298,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
                         TcFenceAfter();
                         if (ElectOne()) {
-                            issueOutputs((it - 1) % STAGES, h, it - 1 > 0 || h > 0);
+                            issueOutputs((2 * (it - 1) + h) % HSTAGES, h, it - 1 > 0 || h > 0);
                         }
                         __syncwarp();
                     } else {
@@ -603,7 +619,7 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     }
     auto mapOf = [&](CUtensorMap *m, __nv_bfloat16 *ptr, const char *what) {
         tsa_ptr2d a = {ptr, cols * 2, cols, rows};
-        return MakeTileMapEx(m, a, 2, 64, 128, what);
+        return MakeTileMapEx(m, a, 2, 64, 64, what);
     };
     CUtensorMap mq, mk, mv, mdo;
     rc = mapOf(&mq, qb, "q bf16");
@@ -616,7 +632,7 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     if (rc == TSA_OK) {
         if (dOutInPlace) {
             tsa_ptr2d a = {dOut.data, dOut.stride_bytes, cols, rows};
-            rc = MakeTileMapEx(&mdo, a, 2, 64, 128, "dOut bf16 (in place)");
+            rc = MakeTileMapEx(&mdo, a, 2, 64, 64, "dOut bf16 (in place)");
         } else {
             rc = mapOf(&mdo, dob, "dOut bf16");
         }

@@ -432,9 +432,12 @@ __device__ __forceinline__ void MmaPairF8TS(uint32_t dTmem, uint32_t aTmem, uint
 // [128 rows][128 bytes] blocks (16 KB each) with the 128-byte swizzle: four steps per block, then the next block.
 // One asm block per group for the reason given above.
 template <int KSTEPS>
-__device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc)
+__device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t bBlockUnits = 1024)
 {
     static_assert(KSTEPS == 4 || KSTEPS == 8, "four or eight K steps");
+    // A: [128 rows][128 bytes] blocks, 1024 descriptor units (16 KB) apart; B: blocks bBlockUnits apart (a B tile of 64 rows
+    // has 8 KB blocks = 512 units)
+    const uint64_t bDesc2 = bDesc + bBlockUnits;
     if (KSTEPS == 4) {
         asm volatile(
             "{\n\t"
@@ -454,7 +457,7 @@ __device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, ui
             "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t"
             "}"
             :
-            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc)
+            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "l"(bDesc2)
             : "memory");
     } else {
         asm volatile(
@@ -470,13 +473,13 @@ __device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, ui
             "add.u64 a3, %1, 6;\n\t"
             "add.u64 b3, %2, 6;\n\t"
             "add.u64 a4, %1, 1024;\n\t"
-            "add.u64 b4, %2, 1024;\n\t"
+            "add.u64 b4, %4, 0;\n\t"
             "add.u64 a5, %1, 1026;\n\t"
-            "add.u64 b5, %2, 1026;\n\t"
+            "add.u64 b5, %4, 2;\n\t"
             "add.u64 a6, %1, 1028;\n\t"
-            "add.u64 b6, %2, 1028;\n\t"
+            "add.u64 b6, %4, 4;\n\t"
             "add.u64 a7, %1, 1030;\n\t"
-            "add.u64 b7, %2, 1030;\n\t"
+            "add.u64 b7, %4, 6;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
@@ -487,7 +490,7 @@ __device__ __forceinline__ void MmaGroupF16SS(uint32_t dTmem, uint64_t aDesc, ui
             "tcgen05.mma.cta_group::1.kind::f16 [%0], a7, b7, %3, pt;\n\t"
             "}"
             :
-            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc)
+            : "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "l"(bDesc2)
             : "memory");
     }
 }
