@@ -628,7 +628,7 @@ def run_layers(args, name, w, rank, world, local_rank, quick=False):
             ops.att_bwd(cfg, item["q"], item["k"], item["v"], item["sk"], item["d_out"], item["out"], item["lse"],
                         masks[item["window"]], item["slope"], heads, qk_scale=item["sq"], v_scale=item["sv"], workspace=bwd_ws,
                         status=status)
-            launches[0] += 6  # dScale, bf16 widening of Q / K / V, dQ kernel, dK/dV kernel
+            launches[0] += 4  # dScale, bf16 widening of Q, K and V (one launch), dQ kernel, dK/dV kernel
 
     def step(record=False):
         for i, item in enumerate(layers):

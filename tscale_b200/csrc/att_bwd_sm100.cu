@@ -19,20 +19,22 @@
 // A1 / A2 (bf16, two per column) are written back over the S / dP columns the writing thread has already consumed.
 //
 // A tile is worked on as two 64-column halves with their own barriers, so the tensor pipe and the arithmetic
-// overlap: while the 8 warps of one half turn S / dP into A1 / A2, the MMAs of the other half (its output
-// products, then its S / dP of the next tile) run.  512 arithmetic threads, four per tile row, 32 columns each in
-// two steps of 16; packed f32x2 arithmetic on per-column factors staged in shared memory by each half's own warps;
-// one warp issues the MMAs, one the TMA copies.  Row tiles stay in shared memory, column tiles stream through a TMA ring.
-// All waits are bounded; a failed wait is carried to the half's next named barrier so its threads leave together.
+// overlap: while the 16 arithmetic warps turn S / dP of one half into A1 / A2 (four threads per tile row, 16 columns
+// each; packed f32x2 arithmetic on per-column factors staged in shared memory one tile ahead), the MMAs of the other
+// half (its output products, then its S / dP of the next tile) run.  Each half has its own MMA-issuing warp (an elected
+// lane of a converged warp issues, in grouped asm blocks), so the pipe is fed by one while the other is between issue
+// blocks; one more warp issues the TMA copies.  Row tiles stay in shared memory; column tiles stream through a ring of
+// half stages (64 rows of C1 and C2), freed per half.  All waits are bounded; a failed wait is carried to the
+// arithmetic threads' next named barrier so they leave together.
 #include "att_sm100_common.cuh"
 
 namespace tsa {
 
 constexpr int BWD_ARITH_THREADS = 512;
 constexpr int BWD_HALF_THREADS = 256;
-constexpr int BWD_CTRL_WARP = BWD_ARITH_THREADS / 32;
-constexpr int BWD_LOAD_WARP = BWD_CTRL_WARP + 1;
-constexpr int BWD_THREADS = BWD_ARITH_THREADS + 64;
+constexpr int BWD_CTRL_WARP = BWD_ARITH_THREADS / 32; // and the next one: control warp h issues the products of half h
+constexpr int BWD_LOAD_WARP = BWD_CTRL_WARP + 2;
+constexpr int BWD_THREADS = BWD_ARITH_THREADS + 96;
 constexpr uint32_t BWD_TMEM_COLS = 512;
 constexpr uint32_t BWD_S_COL = 0, BWD_DP_COL = 128, BWD_OUT_COL = 256;
 
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             MbarInit(&misc.BarS[h], 1);
             MbarInit(&misc.BarP[h], BWD_ARITH_THREADS / 32);
         }
-        MbarInit(&misc.BarDone, 1);
+        MbarInit(&misc.BarDone, 2);
         misc.Abort = 0;
         FenceBarrierInit();
     }
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     const uint32_t tmem = misc.TmemBase;
     const int *abortFlag = &misc.Abort;
 #ifdef TSA_BWD_TRACE
-    const bool traceOn = blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (warp == 0 || warp == 8 || warp == BWD_CTRL_WARP);
+    const bool traceOn = blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (warp == 0 || warp == 8 || warp == BWD_CTRL_WARP || warp == BWD_CTRL_WARP + 1);
 #endif
 
     TTileIter cur;
@@ -214,9 +216,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             }
         }
         __syncwarp();
-    } else if (warp == BWD_CTRL_WARP) {
-        // ---------------------------------------------------------------- MMA warp: the whole warp runs the loop and
-        // waits; one elected lane issues (descriptors stay in uniform registers that way)
+    } else if (warp == BWD_CTRL_WARP || warp == BWD_CTRL_WARP + 1) {
+        // ---------------------------------------------------------------- two MMA warps, one per 64-column half of the
+        // tiles: the whole warp runs the loop and the waits, one elected lane issues (descriptors stay in uniform
+        // registers that way).  The halves share nothing but the output accumulators, which the arithmetic threads
+        // clear before their first hand-over so that every output product accumulates, whichever warp comes first; while
+        // one warp is between two issue blocks (waits, votes, loop code) the other keeps the tensor pipe fed.
+        const int h = warp - BWD_CTRL_WARP;
         if (cur.Valid) {
             const uint32_t sR1a = SmemAddr(sR1), sR2a = SmemAddr(sR2), sCa = SmemAddr(sC);
             bool failed = false;
@@ -233,11 +239,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             // out1 += A1 C1 (and out2 += A2 C2) over the half's 64 tile columns = 4 steps of 16: A from tensor memory
             // (the bf16 pairs of tile columns [16k, 16k + 16) sit in columns 16k .. 16k+7), B = the half column tile read
             // MN-major (16 rows of 128 bytes per step)
-            auto issueOutputs = [&](int slot, int h, bool accumulate) {
+            auto issueOutputs = [&](int slot, int h) {
                 const uint32_t c1 = sCa + slot * 2 * SM::HALF_TILE_BYTES, c2 = c1 + SM::HALF_TILE_BYTES;
-                MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + (c1 >> 4), IDESC_OUT, accumulate ? 1u : 0u);
+                MmaQuadF16TS(tmem + BWD_OUT_COL, tmem + BWD_S_COL + h * 64, mnDescBase + (c1 >> 4), IDESC_OUT, 1u);
                 if (MODE_DKV) {
-                    MmaQuadF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + h * 64, mnDescBase + (c2 >> 4), IDESC_OUT, accumulate ? 1u : 0u);
+                    MmaQuadF16TS(tmem + BWD_OUT_COL + D, tmem + BWD_DP_COL + h * 64, mnDescBase + (c2 >> 4), IDESC_OUT, 1u);
                 }
             };
             auto fail = [&](int code) {
@@ -252,59 +258,48 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             if (!__all_sync(0xffffffffu, WaitBarA(&misc.BarR, 0, abortFlag))) {
                 fail(kDevTimeoutTma);
             }
-            // Tensor-pipe order per tile: out(h0, it-1), scores(h0, it), out(h1, it-1), scores(h1, it).  The outputs of a
-            // half must read its A columns before the next scores of that half overwrite them; the pipe runs in order.
-            // The warp never waits for its own MMAs, so the pipe stays fed; the loader refills a half stage when the
-            // commit made after its output products completes.  Half (it, h) lives in half stage (2 it + h) % HSTAGES.
+            // Order inside a half: out(h, it-1) then scores(h, it): the outputs read the half's A columns before the next
+            // scores overwrite them, and a thread's products run in order.  The warp never waits for its own MMAs; the
+            // loader refills a half stage when the commit made after its output products completes.  Half (it, h) lives
+            // in half stage (2 it + h) % HSTAGES.
             int it = 0;
             TTileIter ctl = cur;
             for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
-                TRB(it, 8);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int g = 2 * it + h;
-                    const int slot = g % HSTAGES, prevSlot = (g - 2 + HSTAGES) % HSTAGES;
-                    if (it > 0) {
-                        if (!__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
-                            fail(kDevTimeoutMma);
-                            break;
-                        }
-                        TcFenceAfter();
-                        TRB(it, 9 + 2 * h);
-                    }
-                    if (!__all_sync(0xffffffffu, WaitBarA(&misc.BarFull[slot], (g / HSTAGES) & 1, abortFlag))) {
-                        fail(kDevTimeoutTma);
-                        break;
-                    }
-                    TcFenceAfter();
-                    if (h == 0) {
-                        TRB(it, 13);
-                    }
-                    if (ElectOne()) {
-                        if (it > 0) {
-                            issueOutputs(prevSlot, h, it - 1 > 0 || h > 0);
-                            MmaCommit(&misc.BarEmpty[prevSlot]);
-                        }
-                        issueScores(slot, h);
-                        MmaCommit(&misc.BarS[h]);
-                    }
-                    __syncwarp();
-                    TRB(it, 10 + 2 * h);
+                const int g = 2 * it + h;
+                const int slot = g % HSTAGES, prevSlot = (g - 2 + HSTAGES) % HSTAGES;
+                TRB(it, 8 + 4 * h);
+                if (!__all_sync(0xffffffffu, WaitBarA(&misc.BarFull[slot], (g / HSTAGES) & 1, abortFlag))) {
+                    fail(kDevTimeoutTma);
+                    break;
                 }
-            }
-            if (!failed && it > 0) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
-                        TcFenceAfter();
-                        if (ElectOne()) {
-                            issueOutputs((2 * (it - 1) + h) % HSTAGES, h, it - 1 > 0 || h > 0);
-                        }
-                        __syncwarp();
-                    } else {
+                if (it > 0) {
+                    if (!__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
                         fail(kDevTimeoutMma);
                         break;
                     }
+                }
+                TcFenceAfter();
+                TRB(it, 9 + 4 * h);
+                if (ElectOne()) {
+                    if (it > 0) {
+                        issueOutputs(prevSlot, h);
+                        MmaCommit(&misc.BarEmpty[prevSlot]);
+                    }
+                    issueScores(slot, h);
+                    MmaCommit(&misc.BarS[h]);
+                }
+                __syncwarp();
+                TRB(it, 10 + 4 * h);
+            }
+            if (!failed && it > 0) {
+                if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
+                    TcFenceAfter();
+                    if (ElectOne()) {
+                        issueOutputs((2 * (it - 1) + h) % HSTAGES, h);
+                    }
+                    __syncwarp();
+                } else {
+                    fail(kDevTimeoutMma);
                 }
             }
             __syncwarp();
@@ -362,6 +357,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         };
         if (cur.Valid) {
             fetchCols(cur.J0);
+            // clear this thread's quarter of the output accumulators: every output product accumulates
+            uint32_t zero[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                zero[k] = 0;
+            }
+#pragma unroll
+            for (int o = 0; o < OUTPUTS; ++o) {
+#pragma unroll
+                for (int c = 0; c < QUARTER_D; c += 8) {
+                    TmemStN<8>(tLane + BWD_OUT_COL + o * D + quarter * QUARTER_D + c, zero);
+                }
+            }
+            TmemWaitSt();
+            TcFenceBefore();
         }
         bool failed = false;
         int it = 0;
@@ -559,6 +569,49 @@ __global__ void __launch_bounds__(256) ToBf16Kernel(int srcDtype, P2D<char> src,
     }
 }
 
+// Q, K and V in one launch when all three are 8-bit with 16-byte aligned rows: blockIdx.y picks the matrix, a thread
+// widens 16 elements (one 16-byte load, two 16-byte stores)
+struct TWiden3 {
+    const char *Src[3];
+    int Stride[3];
+    int Dtype[3];
+    __nv_bfloat16 *Dst[3];
+};
+
+__device__ __forceinline__ uint32_t Widen2(uint32_t w, int shift, int dtype)
+{
+    if (dtype == TSA_I8) {
+        const float a = (float)(int8_t)(w >> shift), b = (float)(int8_t)(w >> (shift + 8));
+        return PackBf16x2(a, b);
+    }
+    return PackBf16x2(E4M3ToFloat((uint8_t)(w >> shift)), E4M3ToFloat((uint8_t)(w >> (shift + 8))));
+}
+
+__global__ void __launch_bounds__(256) Widen8x3Kernel(TWiden3 t, int rows, int cols)
+{
+    const int m = blockIdx.y;
+    const char *src = t.Src[m];
+    const int stride = t.Stride[m], dtype = t.Dtype[m];
+    __nv_bfloat16 *dst = t.Dst[m];
+    const int perRow = cols / 16;
+    const long long groups = (long long)rows * perRow;
+    for (long long gidx = blockIdx.x * (long long)blockDim.x + threadIdx.x; gidx < groups; gidx += (long long)gridDim.x * blockDim.x) {
+        const int rowIdx = (int)(gidx / perRow);
+        const int c0 = (int)(gidx - (long long)rowIdx * perRow) * 16;
+        const uint4 in = *reinterpret_cast<const uint4 *>(src + (size_t)rowIdx * stride + c0);
+        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o[2 * k] = Widen2(w[k], 0, dtype);
+            o[2 * k + 1] = Widen2(w[k], 16, dtype);
+        }
+        uint4 *out = reinterpret_cast<uint4 *>(dst + (size_t)rowIdx * cols + c0);
+        out[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 bool Sm100BwdSupports(const tsa_att_cfg *cfg, int headCount)
 {
@@ -605,9 +658,25 @@ int LaunchSm100Bwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     __nv_bfloat16 *dob = (__nv_bfloat16 *)((char *)workspace + 3 * mat);
     const long long groups = (long long)rows * (cols / 8);
     const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
-    ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qk), rows, cols, qb);
-    ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qv), rows, cols, kb);
-    ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->v_dtype, P2D<char>(v), rows, cols, vb);
+    auto aligned16 = [](const tsa_ptr2d &a) { return (uintptr_t)a.data % 16 == 0 && a.stride_bytes % 16 == 0; };
+    if (cols % 16 == 0 && aligned16(qk) && aligned16(qv) && aligned16(v)) {
+        TWiden3 t;
+        const tsa_ptr2d *srcs[3] = {&qk, &qv, &v};
+        __nv_bfloat16 *dsts[3] = {qb, kb, vb};
+        for (int m = 0; m < 3; ++m) {
+            t.Src[m] = (const char *)srcs[m]->data;
+            t.Stride[m] = srcs[m]->stride_bytes;
+            t.Dtype[m] = (m < 2) ? cfg->qk_dtype : cfg->v_dtype;
+            t.Dst[m] = dsts[m];
+        }
+        const long long g16 = (long long)rows * (cols / 16);
+        const int b16 = (int)((g16 + 255) / 256 < 148 * 8 ? (g16 + 255) / 256 : 148 * 8);
+        Widen8x3Kernel<<<dim3(b16, 3), 256, 0, stream>>>(t, rows, cols);
+    } else {
+        ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qk), rows, cols, qb);
+        ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->qk_dtype, P2D<char>(qv), rows, cols, kb);
+        ToBf16Kernel<<<blocks, 256, 0, stream>>>(cfg->v_dtype, P2D<char>(v), rows, cols, vb);
+    }
     // dO that already is bf16 in a TMA-compatible layout is read where it lies
     const bool dOutInPlace = cfg->grad_dtype == TSA_BF16 && (uintptr_t)dOut.data % 16 == 0 && dOut.stride_bytes % 16 == 0 && dOut.xsize >= cols;
     if (!dOutInPlace) {
