@@ -179,6 +179,16 @@ int tsa_status_from_word(int statusWord);
 int tsa_selftest_bounded_wait(long long limitCycles, int *statusWord, tsa_stream_t stream);
 int tsa_selftest_fwd_withhold_copy(long long waitCycles, int withholdTile);
 
+/* Bounds-check build (make -C tscale_b200/csrc bounds -> libtsa_b200_bounds.so, tests only): every row lookup the kernels make
+ * through a tsa_ptr2d is checked against its ysize; a lookup outside is counted and redirected to row 0 instead of touching
+ * memory outside the buffer (the reference has no counterpart: an index past a TCuda2DPtr goes unnoticed or ends in
+ * cudaErrorIllegalAddress and the abort of code/lib/cuda/cuda_graph.cuh:147-150).  tsa_bounds_check_hits synchronises the
+ * device and returns the count since the last reset (reset != 0 clears it), -1 in a production build.
+ * tsa_selftest_bounds_check makes one out-of-range lookup on purpose on a one-row f32 plane (plane, sink: device memory,
+ * one float each) and returns the number caught (1), -1 in a production build. */
+int tsa_bounds_check_hits(int reset);
+int tsa_selftest_bounds_check(float *plane, float *sink);
+
 /* ---- per-row quantisers ----------------------------------------------------------------------
  * Replaces NormalizeVecsRowTile / NormalizeVecsRowTileMax (code/gpt/compute/row_tile_scale.cuh:11-34,
  * 59-82) and the stand-alone use of the TStoreRowTileNormalize epilogue (lib/cuda/cuda_matmul.cuh:147-204).

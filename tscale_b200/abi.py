@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtsa_b200.so")
+# TSA_B200_LIB selects another build of the same ABI (the bounds-check build of the tests)
+LIB_PATH = os.environ.get("TSA_B200_LIB") or os.path.join(_HERE, "libtsa_b200.so")
 
 TSA_OK, TSA_BAD_ARG, TSA_UNSUPPORTED, TSA_CUDA_ERROR, TSA_TIMEOUT = range(5)
 TSA_I8, TSA_E4M3, TSA_F16, TSA_BF16, TSA_F32 = range(5)
@@ -76,6 +77,7 @@ EXPORTS = [
     "tsa_norm_rope_quant", "tsa_rope_norm_bwd", "tsa_group_window_spans_device", "tsa_kv_product", "tsa_kv_product_bwd",
     "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects", "tsa_status_from_word", "tsa_selftest_bounded_wait",
     "tsa_selftest_fwd_withhold_copy", "tsa_att_fwd_host", "tsa_att_fwd_host_staging_bytes",
+    "tsa_bounds_check_hits", "tsa_selftest_bounds_check",
 ]
 
 
@@ -98,6 +100,8 @@ def _declare(lib):
     lib.tsa_att_bwd_workspace_bytes.argtypes = [ctypes.POINTER(AttCfg), c_int, c_int]
     lib.tsa_calc_dscale.argtypes = [c_int, c_int, P, P, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_qk_scores_i32.argtypes = [P, P, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.tsa_bounds_check_hits.argtypes = [c_int]
+    lib.tsa_selftest_bounds_check.argtypes = [c_void_p, c_void_p]
     lib.tsa_status_from_word.argtypes = [c_int]
     lib.tsa_selftest_bounded_wait.argtypes = [ctypes.c_longlong, c_void_p, c_void_p]
     lib.tsa_selftest_fwd_withhold_copy.argtypes = [ctypes.c_longlong, c_int]

@@ -31,7 +31,6 @@
 namespace tsa {
 
 constexpr int BWD_ARITH_THREADS = 512;
-constexpr int BWD_HALF_THREADS = 256;
 constexpr int BWD_CTRL_WARP = BWD_ARITH_THREADS / 32; // and the next one: control warp h issues the products of half h
 constexpr int BWD_LOAD_WARP = BWD_CTRL_WARP + 2;
 constexpr int BWD_THREADS = BWD_ARITH_THREADS + 96;

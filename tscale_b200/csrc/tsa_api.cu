@@ -98,6 +98,60 @@ extern "C" __attribute__((visibility("default"))) const char *tsa_version(void)
     return "tsa-b200 0.1 (sm_100a)";
 }
 
+#ifdef TSA_BOUNDS_CHECK
+namespace tsa {
+static int (*g_boundsReaders[64])(int);
+static int g_boundsReaderCount = 0;
+int RegisterBoundsReader(int (*reader)(int reset))
+{
+    if (g_boundsReaderCount < 64) {
+        g_boundsReaders[g_boundsReaderCount++] = reader;
+    }
+    return g_boundsReaderCount;
+}
+__global__ void BoundsSelfTestKernel(P2D<float> plane, int row, float *sink)
+{
+    *sink = plane.Row(row)[0];
+}
+} // namespace tsa
+#endif
+
+// number of out-of-range row lookups the kernels of a bounds-check build have caught (and redirected) since the last
+// reset; -1 in a production build, which carries no checks
+extern "C" __attribute__((visibility("default"))) int tsa_bounds_check_hits(int reset)
+{
+#ifdef TSA_BOUNDS_CHECK
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        return -2;
+    }
+    int total = 0;
+    for (int i = 0; i < tsa::g_boundsReaderCount; ++i) {
+        total += tsa::g_boundsReaders[i](reset);
+    }
+    return total;
+#else
+    (void)reset;
+    return -1;
+#endif
+}
+
+// bounds-check build: looks up row `rows` of a one-row plane on purpose (device memory plane[0..0], sink) and returns the
+// number of lookups caught (1 when the check works); the lookup is redirected to row 0, so no memory outside the plane
+// is read.  -1 in a production build.
+extern "C" __attribute__((visibility("default"))) int tsa_selftest_bounds_check(float *plane, float *sink)
+{
+#ifdef TSA_BOUNDS_CHECK
+    tsa_bounds_check_hits(1);
+    tsa_ptr2d a = {plane, 4, 1, 1};
+    tsa::BoundsSelfTestKernel<<<1, 1>>>(tsa::P2D<float>(a), 1, sink);
+    return tsa_bounds_check_hits(1);
+#else
+    (void)plane;
+    (void)sink;
+    return -1;
+#endif
+}
+
 extern "C" __attribute__((visibility("default"))) const char *tsa_last_error(void)
 {
     return g_err;

@@ -35,13 +35,48 @@ int CheckCuda(cudaError_t err, const char *what);
         }                                            \
     } while (0)
 
+#ifdef TSA_BOUNDS_CHECK
+// Bounds-check build (make -C tscale_b200/csrc bounds): every row lookup through P2D is checked against the row count of
+// the caller's tsa_ptr2d.  A row outside it is counted in a device word of the translation unit and redirected to row 0,
+// so nothing outside the buffer is touched and nothing traps; tsa_bounds_check_hits() adds the words up.
+static __device__ int g_tsaBoundsHits;
+int RegisterBoundsReader(int (*reader)(int reset));
+static int ReadBoundsHitsOfThisFile(int reset)
+{
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tsaBoundsHits, sizeof(int)) != cudaSuccess) {
+        return 0;
+    }
+    if (reset) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tsaBoundsHits, &zero, sizeof(int));
+    }
+    return v;
+}
+static const int g_tsaBoundsRegistered = RegisterBoundsReader(ReadBoundsHitsOfThisFile);
+#endif
+
 template <class T>
 struct P2D {
     char *Data;
     int Stride;
+#ifdef TSA_BOUNDS_CHECK
+    int YSize;
+    __host__ __device__ P2D() : Data(nullptr), Stride(0), YSize(0) {}
+    __host__ __device__ explicit P2D(const tsa_ptr2d &p) : Data((char *)p.data), Stride(p.stride_bytes), YSize(p.ysize) {}
+    __device__ __forceinline__ T *Row(int y) const
+    {
+        if ((unsigned)y >= (unsigned)YSize) {
+            atomicAdd(&g_tsaBoundsHits, 1);
+            y = 0;
+        }
+        return (T *)(Data + (size_t)y * Stride);
+    }
+#else
     __host__ __device__ P2D() : Data(nullptr), Stride(0) {}
     __host__ __device__ explicit P2D(const tsa_ptr2d &p) : Data((char *)p.data), Stride(p.stride_bytes) {}
     __device__ __forceinline__ T *Row(int y) const { return (T *)(Data + (size_t)y * Stride); }
+#endif
     __device__ __forceinline__ bool Valid() const { return Data != nullptr; }
 };
 
