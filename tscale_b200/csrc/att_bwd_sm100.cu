@@ -22,8 +22,8 @@
 // overlap: while the 16 arithmetic warps turn S / dP of one half into A1 / A2 (four threads per tile row, 16 columns
 // each; packed f32x2 arithmetic on per-column factors staged in shared memory one tile ahead), the MMAs of the other
 // half (its output products, then its S / dP of the next tile) run.  Each half has its own MMA-issuing warp (an elected
-// lane of a converged warp issues, in grouped asm blocks), so the pipe is fed by one while the other is between issue
-// blocks; one more warp issues the TMA copies.  Row tiles stay in shared memory; column tiles stream through a ring of
+// lane of a converged warp issues, in grouped asm blocks); the two take turns block by block, so one does its waits
+// while the other issues and the accumulation order is fixed; one more warp issues the TMA copies.  Row tiles stay in shared memory; column tiles stream through a ring of
 // half stages (64 rows of C1 and C2), freed per half.  All waits are bounded; a failed wait is carried to the
 // arithmetic threads' next named barrier so they leave together.
 #include "att_sm100_common.cuh"
@@ -84,6 +84,7 @@ struct TBwdMisc {
     float ColT[2][TILE_ROWS]; // additive term of the exponent (dQ: ALiBi column part, dK/dV: -lse_i - ALiBi column part)
     float ColB[2][TILE_ROWS]; // dQ: sv_j c ln2;  dK/dV: -delta_i c ln2
     int Abort;
+    int Turn;                 // issue blocks handed to the tensor pipe so far: control warp h issues the blocks with index = h (mod 2)
     uint64_t BarR;            // TMA: row tiles landed
     uint64_t BarFull[8];      // TMA: half stage (64 rows of C1 and C2) landed
     uint64_t BarEmpty[8];     // MMA warp -> loader: the half stage's output products have retired
@@ -145,6 +146,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
         }
         MbarInit(&misc.BarDone, 2);
         misc.Abort = 0;
+        misc.Turn = 0;
         FenceBarrierInit();
     }
     if (warp == BWD_CTRL_WARP) {
@@ -261,6 +263,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             // scores overwrite them, and a thread's products run in order.  The warp never waits for its own MMAs; the
             // loader refills a half stage when the commit made after its output products completes.  Half (it, h) lives
             // in half stage (2 it + h) % HSTAGES.
+            // The two warps take turns: issue blocks go to the pipe whole and in a fixed order, h0 h1 h0 h1 ..., so the
+            // output accumulators, which both halves add to, receive their terms in the same order on every run (f32
+            // addition does not commute with rounding: without the turns the results differed in the last bit from run
+            // to run).  The waits of one warp still overlap the issue block of the other.
+            auto takeTurn = [&](int index) {
+                const volatile int *turn = &misc.Turn;
+                if (*turn == index) {
+                    return true;
+                }
+                const long long t0 = clock64();
+                for (;;) {
+                    for (int i = 0; i < 64; ++i) {
+                        __nanosleep(20);
+                        if (*turn == index) {
+                            return true;
+                        }
+                    }
+                    if (*(const volatile int *)abortFlag || clock64() - t0 > WAIT_CYCLES) {
+                        return false;
+                    }
+                }
+            };
+            auto passTurn = [&](int index) {
+                __syncwarp();
+                if (lane == 0) {
+                    *(volatile int *)&misc.Turn = index + 1;
+                }
+            };
             int it = 0;
             TTileIter ctl = cur;
             for (; ctl.Valid && !failed; ++it, ctl.Advance()) {
@@ -277,6 +307,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                         break;
                     }
                 }
+                if (!__all_sync(0xffffffffu, takeTurn(g))) {
+                    fail(kDevTimeoutMma);
+                    break;
+                }
                 TcFenceAfter();
                 TRB(it, 9 + 4 * h);
                 if (ElectOne()) {
@@ -287,16 +321,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                     issueScores(slot, h);
                     MmaCommit(&misc.BarS[h]);
                 }
-                __syncwarp();
+                passTurn(g);
                 TRB(it, 10 + 4 * h);
             }
             if (!failed && it > 0) {
-                if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag))) {
+                if (__all_sync(0xffffffffu, WaitBarSleep<20>(&misc.BarP[h], (it - 1) & 1, abortFlag) && takeTurn(2 * it + h))) {
                     TcFenceAfter();
                     if (ElectOne()) {
                         issueOutputs((2 * (it - 1) + h) % HSTAGES, h);
                     }
-                    __syncwarp();
+                    passTurn(2 * it + h);
                 } else {
                     fail(kDevTimeoutMma);
                 }
