@@ -254,6 +254,32 @@ def test_bwd_against_oracle(window, slope, d):
 
 
 @pytest.mark.parametrize("d", [64, 128])
+def test_bwd_bits_are_stable_from_run_to_run(d):
+    """Both 64-column halves of a tile add into the same output accumulators and each half has its own MMA-issuing warp:
+    the warps take turns, so the f32 sums see their terms in one order and repeated runs agree bit for bit."""
+    from tscale_b200 import ops
+    frag_lens, heads, slope = [1024, 640, 384], 4, 0.0
+    out, lse, ref, (g, mask, cfg, _, _, _) = _run_fwd(9, frag_lens, 0, slope, heads, d, "i8", "e4m3", out_dtype=torch.float32, scale=0.5)
+    cfg.grad_dtype = 4  # f32: no output rounding that could hide a difference
+    gen = torch.Generator(device=_dev())
+    gen.manual_seed(3)
+    d_out = torch.randn(out.shape, generator=gen, device=_dev()) * 1e-2
+    out_t, lse_t = torch.from_numpy(out).to(_dev()), torch.from_numpy(lse).to(_dev())
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    first = None
+    for _ in range(6):
+        res = ops.att_bwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], d_out, out_t, lse_t, mask, slope, heads, qk_scale=g["sq"],
+                          v_scale=g["sv"], status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        if first is None:
+            first = res
+        else:
+            for a, b in zip(first, res):
+                assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("d", [64, 128])
 def test_bwd_ragged_and_multispan(d):
     """Backward on a ragged length with empty rows and rows of two spans: the tensor-core path (transposed spans from
     the library's own transpose) and the SIMT path against the oracle."""
