@@ -614,7 +614,11 @@ struct TWiden3 {
 __device__ __forceinline__ uint32_t Widen2(uint32_t w, int shift, int dtype)
 {
     if (dtype == TSA_I8) {
-        const float a = (float)(int8_t)(w >> shift), b = (float)(int8_t)(w >> (shift + 8));
+        // int8 -> f32 without a conversion instruction: the byte, biased by 128, becomes the low mantissa bits of 2^23
+        // (ulp 1), and 2^23 + 128 is subtracted again; exact
+        const uint32_t biased = w ^ 0x80808080u;
+        const float a = __uint_as_float(__byte_perm(biased, 0x4B000000u, shift == 0 ? 0x7440 : 0x7442)) - 8388736.0f;
+        const float b = __uint_as_float(__byte_perm(biased, 0x4B000000u, shift == 0 ? 0x7441 : 0x7443)) - 8388736.0f;
         return PackBf16x2(a, b);
     }
     return PackBf16x2(E4M3ToFloat((uint8_t)(w >> shift)), E4M3ToFloat((uint8_t)(w >> (shift + 8))));
@@ -628,20 +632,35 @@ __global__ void __launch_bounds__(256) Widen8x3Kernel(TWiden3 t, int rows, int c
     __nv_bfloat16 *dst = t.Dst[m];
     const int perRow = cols / 16;
     const long long groups = (long long)rows * perRow;
-    for (long long gidx = blockIdx.x * (long long)blockDim.x + threadIdx.x; gidx < groups; gidx += (long long)gridDim.x * blockDim.x) {
-        const int rowIdx = (int)(gidx / perRow);
-        const int c0 = (int)(gidx - (long long)rowIdx * perRow) * 16;
-        const uint4 in = *reinterpret_cast<const uint4 *>(src + (size_t)rowIdx * stride + c0);
-        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-        uint32_t o[8];
+    const long long step = (long long)gridDim.x * blockDim.x;
+    // four independent 16-byte loads in flight per thread
+    for (long long g0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; g0 < groups; g0 += 4 * step) {
+        uint4 in[4];
+        int rowIdx[4], c0[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            o[2 * k] = Widen2(w[k], 0, dtype);
-            o[2 * k + 1] = Widen2(w[k], 16, dtype);
+        for (int u = 0; u < 4; ++u) {
+            const long long gidx = g0 + u * step;
+            rowIdx[u] = (int)(gidx / perRow);
+            c0[u] = (int)(gidx - (long long)rowIdx[u] * perRow) * 16;
+            if (gidx < groups) {
+                in[u] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)rowIdx[u] * stride + c0[u]));
+            }
         }
-        uint4 *out = reinterpret_cast<uint4 *>(dst + (size_t)rowIdx * cols + c0);
-        out[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (g0 + u * step < groups) {
+                const uint32_t w[4] = {in[u].x, in[u].y, in[u].z, in[u].w};
+                uint32_t o[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o[2 * k] = Widen2(w[k], 0, dtype);
+                    o[2 * k + 1] = Widen2(w[k], 16, dtype);
+                }
+                uint4 *out = reinterpret_cast<uint4 *>(dst + (size_t)rowIdx[u] * cols + c0[u]);
+                out[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+        }
     }
 }
 
