@@ -149,6 +149,17 @@ def test_train_15b_full_size(window):
         for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
             r = util.rel_l2(util.to_np(got[rows, cols]), gref[name])
             assert r < 1.5 * util.GRAD_REL_L2, (name, r)  # + bf16 rounding of out, dOut and the gradients
+    else:
+        # full causal: dQ of the first n rows of a fragment depends only on the fragment's first n keys, so the oracle on that
+        # prefix checks it (dK / dV of those rows also collect from later queries and are left to the invariances above)
+        frag, h0, nh, n = 6, 3, 2, 1024
+        ref, (qd, kd, vd, spans, ptr) = _oracle_prefix(g, "i8", frag, seq, n, h0, nh, d, 0, 0.0)
+        rows = slice(frag * seq, frag * seq + n)
+        cols = slice(h0 * d, (h0 + nh) * d)
+        do_np = np.ascontiguousarray(d_out[rows, cols].float().cpu().numpy())
+        gref = O.att_bwd(qd, kd, vd, do_np, spans, ptr, nh, 0.0, fwd=ref)
+        r = util.rel_l2(util.to_np(dq[rows, cols]), gref["dq"])
+        assert r < 1.5 * util.GRAD_REL_L2, ("dq prefix", r)
 
 
 def test_decode_full_size():
