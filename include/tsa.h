@@ -330,6 +330,21 @@ int tsa_shard_rects(int begin, int end, int heads, tsa_shard_rect *rects);
 int tsa_group_window_spans_device(const int *fragStarts, int fragCount, int len, int window, int transposed,
     int maxGroups, tsa_span_group *groups, int *groupPtr, tsa_stream_t stream);
 
+/* Device-side tsa_transpose_attention / tsa_group_attention for ARBITRARY span lists that already live in device memory
+ * (TransposeAttention code/gpt/att/att.cpp:26-56, GroupAttention<64,128> code/gpt/att/att.h:95-181; the reference runs both on
+ * the host for every batch, gpt_cuda.cu:1346-1353).  spans / spanPtr: device CSR of inclusive (start, finish) pairs per row,
+ * every row's spans sorted by start and disjoint (what AddAttSpans produces).  Results are bit-identical to the host helpers.
+ * The sizes are data: count (device, int[2]) receives the number of spans / groups and a flag that is set when the caller's
+ * arrays (maxSpans / maxGroups entries) are too small, in which case only resSpanPtr / groupPtr are written.
+ * maxInputSpans: upper bound of spanPtr[len] (sizes the workspace).  Typical use for the backward's transposed mask:
+ * transpose, then group the result (the transposed CSR is sorted and disjoint by construction). */
+int tsa_transpose_attention_device(int len, const int *spans, const int *spanPtr, int maxInputSpans,
+    int maxSpans, int *resSpans, int *resSpanPtr, int *count, void *workspace, size_t workspaceBytes, tsa_stream_t stream);
+size_t tsa_transpose_attention_device_workspace_bytes(int len, int maxInputSpans);
+int tsa_group_attention_device(int len, const int *spans, const int *spanPtr, int maxGroups,
+    tsa_span_group *groups, int *groupPtr, int *count, void *workspace, size_t workspaceBytes, tsa_stream_t stream);
+size_t tsa_group_attention_device_workspace_bytes(int len);
+
 /* ---- projection fused with the producer ("next" scope row: the GEMM epilogue in front of the path) ------------
  * Replaces MulForwardInt8 / MulForwardFp8 <TStoreRowTileNormalizeRope> and <TStoreRowTileNormalize>
  * (code/gpt/compute/gpt_cuda.cu:488-496; store ops code/lib/cuda/cuda_matmul.cuh:147-204; rope code/gpt/compute/gpt_rope.cuh:4-66):

@@ -78,6 +78,8 @@ EXPORTS = [
     "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects", "tsa_status_from_word", "tsa_selftest_bounded_wait",
     "tsa_selftest_fwd_withhold_copy", "tsa_att_fwd_host", "tsa_att_fwd_host_staging_bytes",
     "tsa_bounds_check_hits", "tsa_selftest_bounds_check",
+    "tsa_transpose_attention_device", "tsa_transpose_attention_device_workspace_bytes", "tsa_group_attention_device",
+    "tsa_group_attention_device_workspace_bytes",
 ]
 
 
@@ -100,6 +102,12 @@ def _declare(lib):
     lib.tsa_att_bwd_workspace_bytes.argtypes = [ctypes.POINTER(AttCfg), c_int, c_int]
     lib.tsa_calc_dscale.argtypes = [c_int, c_int, P, P, P, c_int, c_int, c_int, c_void_p]
     lib.tsa_qk_scores_i32.argtypes = [P, P, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.tsa_transpose_attention_device.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.tsa_transpose_attention_device_workspace_bytes.restype = c_size_t
+    lib.tsa_transpose_attention_device_workspace_bytes.argtypes = [c_int, c_int]
+    lib.tsa_group_attention_device.argtypes = [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.tsa_group_attention_device_workspace_bytes.restype = c_size_t
+    lib.tsa_group_attention_device_workspace_bytes.argtypes = [c_int]
     lib.tsa_bounds_check_hits.argtypes = [c_int]
     lib.tsa_selftest_bounds_check.argtypes = [c_void_p, c_void_p]
     lib.tsa_status_from_word.argtypes = [c_int]

@@ -117,6 +117,42 @@ class Mask:
         m.rev_spans, m.rev_span_ptr = rev, rev_ptr
         return m
 
+    @classmethod
+    def from_spans_device(cls, spans_dev, span_ptr_dev, max_rev_spans=None, max_groups=None):
+        """General mask built entirely on the GPU from per-row inclusive spans that are already in device memory (int32
+        CSR: spans [n][2], span_ptr [len + 1]; every row's spans sorted by start and disjoint): transpose, then group the
+        mask and its transpose.  The capacities default to bounds that always suffice for causal masks; the device
+        counters are read back once at the end to size the result views (the kernels themselves never wait for the host)."""
+        L = abi.lib()
+        dev = spans_dev.device
+        length = span_ptr_dev.numel() - 1
+        n_in = spans_dev.shape[0]
+        tiles = (length + abi.ATT_GROUP - 1) // abi.ATT_GROUP
+        cap_rev = max_rev_spans if max_rev_spans is not None else max(16, 2 * n_in + length)
+        i32 = dict(dtype=torch.int32, device=dev)
+        rev = torch.zeros((cap_rev, 2), **i32)
+        rev_ptr = torch.zeros(length + 1, **i32)
+        counts = torch.zeros((3, 2), **i32)
+        ws = torch.empty(max(64, L.tsa_transpose_attention_device_workspace_bytes(length, n_in)), dtype=torch.uint8, device=dev)
+        check(L.tsa_transpose_attention_device(length, _ptr(spans_dev), _ptr(span_ptr_dev), n_in, cap_rev, _ptr(rev), _ptr(rev_ptr),
+                                               _ptr(counts[0]), _ptr(ws), ws.numel(), _stream()))
+        gws = torch.empty(max(64, L.tsa_group_attention_device_workspace_bytes(length)), dtype=torch.uint8, device=dev)
+        res = []
+        for i, (sp, pt) in enumerate(((spans_dev, span_ptr_dev), (rev, rev_ptr))):
+            cap = max_groups if max_groups is not None else max(16, 4 * tiles + 16)
+            groups = torch.zeros((cap, ctypes.sizeof(abi.SpanGroup)), dtype=torch.uint8, device=dev)
+            gptr = torch.zeros(tiles + 1, **i32)
+            check(L.tsa_group_attention_device(length, _ptr(sp), _ptr(pt), cap, _ptr(groups), _ptr(gptr), _ptr(counts[1 + i]),
+                                               _ptr(gws), gws.numel(), _stream()))
+            res += [groups, gptr]
+        c = counts.cpu().numpy()
+        if c[:, 1].any():
+            raise RuntimeError("from_spans_device: capacity too small (needed %d transposed spans, %d / %d groups)" % (c[0, 0], c[1, 0], c[2, 0]))
+        m = cls(length, None, None, None, None)
+        m._dev[str(dev)] = (res[0][:int(c[1, 0])], res[1], res[2][:int(c[2, 0])], res[3])
+        m.rev_spans_dev, m.rev_span_ptr_dev, m.counts = rev[:int(c[0, 0])], rev_ptr, c
+        return m
+
     def dev(self, device):
         key = str(device)
         if key not in self._dev:
