@@ -531,13 +531,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
             }
             TcFenceAfter();
         }
-        if (!failed) {
-            // each of the four threads of a row stores a quarter of the output columns
+        // Outputs: tensor memory -> registers -> shared memory -> global memory in whole rows.  A thread holds a quarter of
+        // one row, so stores straight from the registers would put 32 different rows into every store instruction (32
+        // sectors each, serialised in the load/store unit: 4 K clocks per CTA); staged through shared memory (the tile
+        // buffers are idle by now; row pitch padded by 16 bytes against bank conflicts) a warp writes two whole rows per
+        // instruction.  The vote makes the staging barrier safe when some thread has given up.
+        if (!BarRedOr(BAR_ARITH, BWD_ARITH_THREADS, failed)) {
             const int esz = (p.GradDtype == TSA_F32) ? 4 : 2;
+            const int rowBytes = D * esz, pitch = rowBytes + 16;
+            constexpr int STAGE_BYTES = TILE_ROWS * (D * 4 + 16);
 #pragma unroll
             for (int o = 0; o < OUTPUTS; ++o) {
-                const P2D<char> &outp = (o == 0) ? p.Out1 : p.Out2;
-                char *oRow = outp.Row(rowOk ? row : 0) + ((size_t)head * D + quarter * QUARTER_D) * esz;
                 uint32_t v[QUARTER_D];
                 if (tiles > 0) {
                     if (QUARTER_D == 32) {
@@ -552,26 +556,40 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
                         v[c] = 0;
                     }
                 }
-                if (rowOk) {
-                    if (p.GradDtype == TSA_F32) {
-                        float4 *dst = reinterpret_cast<float4 *>(oRow);
+                uint8_t *dstS = smem + o * STAGE_BYTES + r * pitch + quarter * QUARTER_D * esz;
+                if (p.GradDtype == TSA_F32) {
+                    float4 *dst = reinterpret_cast<float4 *>(dstS);
 #pragma unroll
-                        for (int c = 0; c < QUARTER_D; c += 4) {
-                            dst[c >> 2] = make_float4(__uint_as_float(v[c]) * p.GradMult, __uint_as_float(v[c + 1]) * p.GradMult,
-                                __uint_as_float(v[c + 2]) * p.GradMult, __uint_as_float(v[c + 3]) * p.GradMult);
+                    for (int c = 0; c < QUARTER_D; c += 4) {
+                        dst[c >> 2] = make_float4(__uint_as_float(v[c]) * p.GradMult, __uint_as_float(v[c + 1]) * p.GradMult,
+                            __uint_as_float(v[c + 2]) * p.GradMult, __uint_as_float(v[c + 3]) * p.GradMult);
+                    }
+                } else {
+                    uint4 *dst = reinterpret_cast<uint4 *>(dstS);
+#pragma unroll
+                    for (int c = 0; c < QUARTER_D; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float a = __uint_as_float(v[c + 2 * k]) * p.GradMult, b = __uint_as_float(v[c + 2 * k + 1]) * p.GradMult;
+                            w[k] = (p.GradDtype == TSA_BF16) ? PackBf16x2(a, b) : PackHalf2(a, b);
                         }
-                    } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>(oRow);
+                        dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            BarRedOr(BAR_ARITH, BWD_ARITH_THREADS, false);
+            const int chunksPerRow = rowBytes >> 4;
 #pragma unroll
-                        for (int c = 0; c < QUARTER_D; c += 8) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const float a = __uint_as_float(v[c + 2 * k]) * p.GradMult, b = __uint_as_float(v[c + 2 * k + 1]) * p.GradMult;
-                                w[k] = (p.GradDtype == TSA_BF16) ? PackBf16x2(a, b) : PackHalf2(a, b);
-                            }
-                            dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+            for (int o = 0; o < OUTPUTS; ++o) {
+                const P2D<char> &outp = (o == 0) ? p.Out1 : p.Out2;
+                const uint8_t *stage = smem + o * STAGE_BYTES;
+                for (int id = tid; id < TILE_ROWS * chunksPerRow; id += BWD_ARITH_THREADS) {
+                    const int rr = id / chunksPerRow, cc = id - rr * chunksPerRow;
+                    const int grow = rowTile * TILE_ROWS + rr;
+                    if (grow < p.Rows) {
+                        *reinterpret_cast<uint4 *>(outp.Row(grow) + (size_t)head * D * esz + cc * 16) =
+                            *reinterpret_cast<const uint4 *>(stage + rr * pitch + cc * 16);
                     }
                 }
             }
