@@ -162,33 +162,41 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) BwdSm100Kernel(const __grid_co
     const bool traceOn = blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (warp == 0 || warp == 8 || warp == BWD_CTRL_WARP || warp == BWD_CTRL_WARP + 1);
 #endif
 
+    // The row tiles depend only on the CTA's coordinates: their copies start before the span lookup (two dependent global
+    // loads) instead of behind it.
+    if (warp == BWD_LOAD_WARP && lane == 0) {
+        PrefetchTensorMap(&tmR1);
+        PrefetchTensorMap(&tmR2);
+        // every tensor map has boxes of 64 rows x 64 elements (128 bytes): a row tile is two boxes per block
+        auto loadTile = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
+#pragma unroll
+            for (int kb = 0; kb < KBLOCKS; ++kb) {
+                TmaLoad2D(dst + kb * BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
+                TmaLoad2D(dst + kb * BLOCK_BYTES + HALF_BLOCK_BYTES, tm, head * D + kb * 64, rowBase + 64, bar);
+            }
+        };
+        MbarExpectTx(&misc.BarR, 2 * SM::TILE_BYTES);
+        loadTile(sR1, &tmR1, rowTile * TILE_ROWS, &misc.BarR);
+        loadTile(sR2, &tmR2, rowTile * TILE_ROWS, &misc.BarR);
+    }
+
     TTileIter cur;
     cur.Init(p.Spans, p.SpanPtr, p.LenAttTiles, rowTile, p.Rows);
 
     if (warp == BWD_LOAD_WARP) {
         // ---------------------------------------------------------------- loader warp: every TMA copy
+        if (lane == 0 && !cur.Valid) {
+            WaitBar(&misc.BarR, 0); // a CTA without column tiles: the row tiles must have landed before it ends
+        }
         if (lane == 0 && cur.Valid) {
-            PrefetchTensorMap(&tmR1);
-            PrefetchTensorMap(&tmR2);
             PrefetchTensorMap(&tmC1);
             PrefetchTensorMap(&tmC2);
-            // every tensor map has boxes of 64 rows x 64 elements (128 bytes): a row tile is two boxes per block
-            auto loadTile = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
-#pragma unroll
-                for (int kb = 0; kb < KBLOCKS; ++kb) {
-                    TmaLoad2D(dst + kb * BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
-                    TmaLoad2D(dst + kb * BLOCK_BYTES + HALF_BLOCK_BYTES, tm, head * D + kb * 64, rowBase + 64, bar);
-                }
-            };
             auto loadHalf = [&](uint8_t *dst, const CUtensorMap *tm, int rowBase, uint64_t *bar) {
 #pragma unroll
                 for (int kb = 0; kb < KBLOCKS; ++kb) {
                     TmaLoad2D(dst + kb * HALF_BLOCK_BYTES, tm, head * D + kb * 64, rowBase, bar);
                 }
             };
-            MbarExpectTx(&misc.BarR, 2 * SM::TILE_BYTES);
-            loadTile(sR1, &tmR1, rowTile * TILE_ROWS, &misc.BarR);
-            loadTile(sR2, &tmR2, rowTile * TILE_ROWS, &misc.BarR);
             int g = 0; // half stages requested
             bool failed = false;
             for (TTileIter prod = cur; prod.Valid && !failed; prod.Advance()) {
