@@ -529,7 +529,7 @@ def longctx_e2e(torch, dist, shard, ops, args, cfg, mask, slope, t, out_local, s
     host_out = torch.empty((rows, nh * d), dtype=torch.bfloat16).pin_memory()
     out_dev = torch.empty((rows, nh * d), dtype=torch.bfloat16, device=dev) if world > 1 else None
     gathered = torch.empty((world, rows, nh * d), dtype=torch.bfloat16, device=dev) if world > 1 else None
-    slices = next(k for k in (16, 8, 4, 2, 1) if nh % k == 0)
+    slices = next(k for k in (16, 8, 4, 2, 1) if nh % k == 0 and (nh // k >= 2 or k == 1))
     h2d_bytes = sum(v.numel() * v.element_size() for v in (hq, hk, hv, hsq, hsk, hsv))
     d2h_bytes = host_out.numel() * host_out.element_size()
     box = [None]
