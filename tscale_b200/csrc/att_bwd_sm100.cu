@@ -682,9 +682,8 @@ __global__ void __launch_bounds__(256) Widen8x3Kernel(TWiden3 t, int rows, int c
                     o[2 * k] = Widen2(w[k], 0, dtype);
                     o[2 * k + 1] = Widen2(w[k], 16, dtype);
                 }
-                uint4 *out = reinterpret_cast<uint4 *>(dst + (size_t)rowIdx[u] * cols + c0[u]);
-                out[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                // one 32-byte store: a whole sector per thread (the workspace is 256-byte aligned, cols a multiple of 16)
+                StGlobal256(dst + (size_t)rowIdx[u] * cols + c0[u], o);
             }
         }
     }

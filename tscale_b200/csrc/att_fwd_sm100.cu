@@ -1110,6 +1110,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                 }
                 const int esz = (p.OutDtype == TSA_F32) ? 4 : 2;
                 char *oRow = p.Out.Row(rowOk ? row : 0) + (size_t)head * D * esz;
+                const bool wideStores = (((uintptr_t)p.Out.Data | (uintptr_t)p.Out.Stride) & 31) == 0;
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t o[32];
@@ -1123,20 +1124,29 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                         }
                     }
                     if (rowOk) {
+                        // 32-byte stores where the output rows allow them (whole sectors, half the store instructions)
                         if (p.OutDtype == TSA_F32) {
-                            float4 *dst = reinterpret_cast<float4 *>(oRow + c0 * 4);
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4) {
-                                dst[c >> 2] = make_float4(__uint_as_float(o[c]) * outMult, __uint_as_float(o[c + 1]) * outMult,
-                                    __uint_as_float(o[c + 2]) * outMult, __uint_as_float(o[c + 3]) * outMult);
-                            }
-                        } else {
-                            uint4 *dst = reinterpret_cast<uint4 *>(oRow + c0 * 2);
 #pragma unroll
                             for (int c = 0; c < 32; c += 8) {
-                                uint32_t w[4];
+                                uint32_t w[8];
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) {
+                                for (int k = 0; k < 8; ++k) {
+                                    w[k] = __float_as_uint(__uint_as_float(o[c + k]) * outMult);
+                                }
+                                if (wideStores) {
+                                    StGlobal256(oRow + (c0 + c) * 4, w);
+                                } else {
+                                    uint4 *dst = reinterpret_cast<uint4 *>(oRow + (c0 + c) * 4);
+                                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; c += 16) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) {
                                     float a = __uint_as_float(o[c + 2 * k]) * outMult, b = __uint_as_float(o[c + 2 * k + 1]) * outMult;
                                     if (p.OutDtype == TSA_BF16) {
                                         __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
@@ -1145,7 +1155,13 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                                         w[k] = PackHalf2(a, b);
                                     }
                                 }
-                                dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                                if (wideStores) {
+                                    StGlobal256(oRow + (c0 + c) * 2, w);
+                                } else {
+                                    uint4 *dst = reinterpret_cast<uint4 *>(oRow + (c0 + c) * 2);
+                                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                                }
                             }
                         }
                     }

@@ -165,6 +165,15 @@ struct TTileIter {
     }
 };
 
+// one 32-byte store (the address must be 32-byte aligned): a thread that writes its own row fills whole 32-byte sectors
+// with half as many store instructions as with 16-byte stores
+__device__ __forceinline__ void StGlobal256(void *p, const uint32_t *v)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+                 "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void TmemStN(uint32_t taddr, const uint32_t *r);
 template <>

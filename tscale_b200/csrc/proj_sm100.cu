@@ -264,11 +264,17 @@ __global__ void __launch_bounds__(256, 2) ProjNormRopeKernel(const __grid_consta
                     }
                 }
                 if (inBuf && ES == 1) {
-                    uint4 *d4 = reinterpret_cast<uint4 *>(dstRow + blk);
-                    d4[0] = make_uint4(outLo[0], outLo[1], outLo[2], outLo[3]);
-                    d4[1] = make_uint4(outLo[4], outLo[5], outLo[6], outLo[7]);
-                    d4[2] = make_uint4(outHi[0], outHi[1], outHi[2], outHi[3]);
-                    d4[3] = make_uint4(outHi[4], outHi[5], outHi[6], outHi[7]);
+                    if ((((uintptr_t)a.Dst.Data | (uintptr_t)a.Dst.Stride) & 31) == 0) {
+                        // two 32-byte stores: whole sectors from a thread that owns the row
+                        StGlobal256(dstRow + blk, outLo);
+                        StGlobal256(dstRow + blk + 32, outHi);
+                    } else {
+                        uint4 *d4 = reinterpret_cast<uint4 *>(dstRow + blk);
+                        d4[0] = make_uint4(outLo[0], outLo[1], outLo[2], outLo[3]);
+                        d4[1] = make_uint4(outLo[4], outLo[5], outLo[6], outLo[7]);
+                        d4[2] = make_uint4(outHi[0], outHi[1], outHi[2], outHi[3]);
+                        d4[3] = make_uint4(outHi[4], outHi[5], outHi[6], outHi[7]);
+                    }
                 }
             }
             if (a.Scale.Valid() && inBuf) {
