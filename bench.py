@@ -443,9 +443,9 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     roofline["timed"] = ("CUDA events around each slice's tsa_att_fwd call in the timed region (memset + V-scale maximum kernel of a few "
                          "microseconds + the attention kernel), summed per step")
     # DRAM bytes per step (this rank's launches together, like ms_per_launch): the committed ncu capture of one launch over 8
-    # (fragment, head) units of this workload (profiles/fwd_sm100_e4m3_d128_longctx_1frag.md: 182.9 MB read + 35.1 MB written,
+    # (fragment, head) units of this workload (profiles/fwd_sm100_e4m3_d128_longctx_1frag.md: 188.7 MB read + 39.2 MB written,
     # against 171 MB of inputs and output), scaled by the units this rank processes; traffic grows in proportion to the units
-    roofline["traffic"] = (182.926080e6 + 35.087104e6) * (nf * nh) / 8.0
+    roofline["traffic"] = (188.742144e6 + 39.153152e6) * (nf * nh) / 8.0
     roofline["traffic_unit"] = "bytes per step"
     roofline["traffic_source"] = ("dram__bytes_read.sum + dram__bytes_write.sum of the committed ncu capture of one 8-unit launch, scaled to this "
                                   "rank's %d units; the kernel is not DRAM-bound (1.3 %% of the DRAM peak)" % (nf * nh))
