@@ -517,55 +517,39 @@ template <class T16>
 __global__ void __launch_bounds__(256) DScaleVecKernel(int len, int headCount, int headDim, int chunksPerRow,
     P2D<char> out, P2D<char> dOut, P2D<float> dScale)
 {
-    // a warp takes four 256-element chunks, a quarter of the grid apart: its eight 16-byte loads are issued before any is used
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    const long long chunks = (long long)len * chunksPerRow;
-    const long long quarter = (chunks + 3) / 4;
-    if (warp >= quarter) {
+    if (warp >= (long long)len * chunksPerRow) {
         return;
     }
+    const int t = (int)(warp / chunksPerRow);
+    const int x = ((int)(warp - (long long)t * chunksPerRow) * 32 + lane) * 8; // first element of this thread
     const int width = headCount * headDim;
-    const int lanesPerHead = headDim / 8; // 2, 4, 8, 16 or 32
-    uint4 a[4], b[4];
-    int t[4], x[4];
-    bool ok[4];
+    float sum = 0;
+    if (x < width) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(out.Row(t) + (size_t)x * 2));
+        const uint4 b = __ldg(reinterpret_cast<const uint4 *>(dOut.Row(t) + (size_t)x * 2));
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        const long long c = warp + u * quarter;
-        t[u] = (int)(c / chunksPerRow);
-        x[u] = ((int)(c - (long long)t[u] * chunksPerRow) * 32 + lane) * 8; // first element of this thread
-        ok[u] = c < chunks && x[u] < width;
-        if (ok[u]) {
-            a[u] = __ldg(reinterpret_cast<const uint4 *>(out.Row(t[u]) + (size_t)x[u] * 2));
-            b[u] = __ldg(reinterpret_cast<const uint4 *>(dOut.Row(t[u]) + (size_t)x[u] * 2));
+        for (int k = 0; k < 4; ++k) {
+            float2 fa, fb;
+            if (std::is_same<T16, __half>::value) {
+                fa = __half22float2(*reinterpret_cast<const __half2 *>(&aw[k]));
+                fb = __half22float2(*reinterpret_cast<const __half2 *>(&bw[k]));
+            } else {
+                fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&aw[k]));
+                fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&bw[k]));
+            }
+            sum = fmaf(fa.x, fb.x, sum);
+            sum = fmaf(fa.y, fb.y, sum);
         }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        float sum = 0;
-        if (ok[u]) {
-            const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float2 fa, fb;
-                if (std::is_same<T16, __half>::value) {
-                    fa = __half22float2(*reinterpret_cast<const __half2 *>(&aw[k]));
-                    fb = __half22float2(*reinterpret_cast<const __half2 *>(&bw[k]));
-                } else {
-                    fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&aw[k]));
-                    fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&bw[k]));
-                }
-                sum = fmaf(fa.x, fb.x, sum);
-                sum = fmaf(fa.y, fb.y, sum);
-            }
-        }
-        for (int o = lanesPerHead >> 1; o > 0; o >>= 1) {
-            sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        }
-        if (ok[u] && (lane & (lanesPerHead - 1)) == 0) {
-            dScale.Row(x[u] / headDim)[t[u]] = sum;
-        }
+    const int lanesPerHead = headDim / 8; // 2, 4, 8, 16 or 32
+    for (int o = lanesPerHead >> 1; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    }
+    if (x < width && (lane & (lanesPerHead - 1)) == 0) {
+        dScale.Row(x / headDim)[t] = sum;
     }
 }
 
@@ -581,7 +565,7 @@ int LaunchDScale(int outDtype, int gradDtype, tsa_ptr2d out, tsa_ptr2d dOut, tsa
     if (outDtype == gradDtype && (outDtype == TSA_F16 || outDtype == TSA_BF16) && pow2 && aligned) {
         const int chunksPerRow = (headCount * headDimV + 255) / 256;
         const long long vecWarps = (long long)len * chunksPerRow;
-        const int vblocks = (int)((((vecWarps + 3) / 4) * 32 + 255) / 256);
+        const int vblocks = (int)((vecWarps * 32 + 255) / 256);
         if (outDtype == TSA_F16) {
             DScaleVecKernel<__half><<<vblocks, 256, 0, stream>>>(len, headCount, headDimV, chunksPerRow, P2D<char>(out), P2D<char>(dOut), P2D<float>(dScale));
         } else {
