@@ -104,6 +104,23 @@ int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
  * plane and the work-item counter of the persistent kernel); the call clears what it uses. */
 size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int len);
 
+/* Forward with the all-gather of its output fused in: the kernel stores every output row to outs[0] and to the outCount - 1
+ * further matrices outs[1..] of the same shape, dtype and column offset, which may be the buffers of OTHER GPUs of the box
+ * mapped into this process (CUDA peer access / IPC / symmetric memory over NVLink): each rank of a (fragment x head)-sharded
+ * batch writes its block straight into every rank's copy of the whole output from the attention epilogue, so that no
+ * separate collective has to move it afterwards (the reference gathers by copying device arrays between its per-device
+ * contexts, code/gpt/compute/gpt_cuda.cu:1478-1738).  Plain 16- or 32-byte stores; no multicast.  The callers order the
+ * step themselves (a stream-ordered barrier across the ranks before anybody reads a gathered buffer).  Everything else as
+ * tsa_att_fwd; outCount = 1 is tsa_att_fwd.  At most TSA_MAX_OUT_COPIES + 1 destinations; only the tensor-core path
+ * takes more than one (TSA_UNSUPPORTED otherwise). */
+#define TSA_MAX_OUT_COPIES 7
+int tsa_att_fwd_to(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    const tsa_ptr2d *outs, int outCount, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+
 /* Forward for vectors that live in page-locked HOST memory.  Same arguments and results as tsa_att_fwd, except that qk,
  * qv, qkScale, qvScale, v, vScale, out and sumWeightLog point to host memory (cudaHostAlloc / cudaHostRegister; pageable
  * memory works but its copies do not overlap anything) while attSpans, attSpanPtr, qvGlobalScale and statusWord stay

@@ -125,6 +125,34 @@ def test_fwd_host_buffers_match_device_call(heads, slices, qk_dtype, d):
                          slices=slices, staging=staging[:1024], status=status)
 
 
+@pytest.mark.parametrize("d,out_dtype,ragged", [(128, torch.bfloat16, False), (64, torch.float32, False), (64, torch.bfloat16, True)])
+def test_fwd_extra_destinations_receive_the_same_rows(d, out_dtype, ragged):
+    """tsa_att_fwd_to (the forward with its all-gather fused in) stores every output row to each destination it is given: here
+    three more buffers of the same GPU stand in for the peers' (the multi-GPU bench passes peer pointers).  Bits equal to
+    tsa_att_fwd, rows and columns around each destination untouched, also when a destination is only 16-byte aligned."""
+    from tscale_b200 import ops
+    frag_lens, heads, window, slope = [384, 200], 3, 128, 0.25
+    out_ref, lse_ref, _, (g, mask, cfg, _, _, _) = _run_fwd(6, frag_lens, window, slope, heads, d, "e4m3", "e4m3", out_dtype=out_dtype, scale=0.5)
+    rows, width = sum(frag_lens), heads * d
+    pad = 8 if ragged else 16  # bf16: 8 columns = 16 bytes: rows of the copies are then 16- but not 32-byte aligned
+    guards = [torch.full((rows + 2, width + pad), -3.0, dtype=out_dtype, device=_dev()) for _ in range(4)]
+    views = [x[1:rows + 1, :width] for x in guards]
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out, lse = ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status,
+                           out=views[0], out_copies=[views[1], views[2], (views[3].data_ptr(), views[3].stride(0) * views[3].element_size())])
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for x, v in zip(guards, views):
+        assert np.array_equal(util.to_np(v.contiguous()), out_ref)
+        assert bool((x[0] == -3.0).all()) and bool((x[rows + 1] == -3.0).all()) and bool((x[:, width:] == -3.0).all())
+    assert np.array_equal(util.to_np(lse), lse_ref)
+    # the SIMT path has one destination only
+    cfg.flags |= 1
+    with pytest.raises(Exception):
+        ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status,
+                    out=views[0], out_copies=[views[1]])
+
+
 @pytest.mark.parametrize("d", [64, 128])
 def test_fwd_tcgen05_constant_scales(d):
     # the reference's call shape: constant query and value scales (QK_VEC_SCALE / V_VEC_SCALE), per-row key scale

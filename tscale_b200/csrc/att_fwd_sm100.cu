@@ -70,6 +70,9 @@ struct TFwdParams {
     const float *VRef; // per head max of VScale (workspace), null without VScale
     int ScaleBulk;     // key / value scale rows may be fetched with 16-byte bulk copies
     P2D<char> Out;
+    P2D<char> OutCopy[TSA_MAX_OUT_COPIES]; // further destinations of the output rows (other GPUs' buffers among them)
+    int OutCopies;
+    int WideStores;   // every destination's rows are 32-byte aligned
     P2D<float> Lse;
     const float *GlobalScale;
     float C;
@@ -1110,7 +1113,25 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                 }
                 const int esz = (p.OutDtype == TSA_F32) ? 4 : 2;
                 char *oRow = p.Out.Row(rowOk ? row : 0) + (size_t)head * D * esz;
-                const bool wideStores = (((uintptr_t)p.Out.Data | (uintptr_t)p.Out.Stride) & 31) == 0;
+                const bool wideStores = p.WideStores != 0;
+                const size_t headOff = (size_t)head * D * esz;
+                // 32 bytes of the row to the output and to every further destination (fused all-gather: peer GPUs' buffers)
+                auto storeAll = [&](char *local, size_t rowOff, const uint32_t *w) {
+                    auto put = [&](char *dstp) {
+                        if (wideStores) {
+                            StGlobal256(dstp, w);
+                        } else {
+                            uint4 *dst = reinterpret_cast<uint4 *>(dstp);
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    };
+                    put(local);
+#pragma unroll 1
+                    for (int k = 0; k < p.OutCopies; ++k) {
+                        put(p.OutCopy[k].Row(row) + rowOff);
+                    }
+                };
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t o[32];
@@ -1133,13 +1154,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                                 for (int k = 0; k < 8; ++k) {
                                     w[k] = __float_as_uint(__uint_as_float(o[c + k]) * outMult);
                                 }
-                                if (wideStores) {
-                                    StGlobal256(oRow + (c0 + c) * 4, w);
-                                } else {
-                                    uint4 *dst = reinterpret_cast<uint4 *>(oRow + (c0 + c) * 4);
-                                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                                }
+                                storeAll(oRow + (c0 + c) * 4, headOff + (c0 + c) * 4, w);
                             }
                         } else {
 #pragma unroll
@@ -1155,13 +1170,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                                         w[k] = PackHalf2(a, b);
                                     }
                                 }
-                                if (wideStores) {
-                                    StGlobal256(oRow + (c0 + c) * 2, w);
-                                } else {
-                                    uint4 *dst = reinterpret_cast<uint4 *>(oRow + (c0 + c) * 2);
-                                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                                }
+                                storeAll(oRow + (c0 + c) * 2, headOff + (c0 + c) * 2, w);
                             }
                         }
                     }
@@ -1464,6 +1473,14 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     fp.ScaleBulk = ((uintptr_t)p.KScale.Data % 16 == 0 && p.KScale.Stride % 16 == 0 &&
         (!hasVs || ((uintptr_t)p.VScale.Data % 16 == 0 && p.VScale.Stride % 16 == 0))) ? 1 : 0;
     fp.Out = p.Out;
+    fp.OutCopies = p.OutCopies;
+    fp.WideStores = ((((uintptr_t)p.Out.Data | (uintptr_t)p.Out.Stride) & 31) == 0) ? 1 : 0;
+    for (int k = 0; k < TSA_MAX_OUT_COPIES; ++k) {
+        fp.OutCopy[k] = k < p.OutCopies ? p.OutCopy[k] : P2D<char>();
+        if (k < p.OutCopies && ((((uintptr_t)p.OutCopy[k].Data | (uintptr_t)p.OutCopy[k].Stride) & 31) != 0)) {
+            fp.WideStores = 0;
+        }
+    }
     fp.Lse = p.Lse;
     fp.GlobalScale = p.GlobalScale;
     fp.C = p.C;

@@ -22,6 +22,8 @@ struct TGenParams {
     P2D<uint8_t> Q, K, V;
     P2D<float> QScale, KScale, VScale;
     P2D<char> Out;
+    P2D<char> OutCopy[TSA_MAX_OUT_COPIES]; // further destinations of the forward's output (same shape as Out; peer-GPU memory allowed)
+    int OutCopies = 0;
     P2D<float> Lse;
     P2D<char> DOut;
     P2D<float> DScale;

@@ -162,11 +162,11 @@ extern "C" __attribute__((visibility("default"))) size_t tsa_att_fwd_workspace_b
     return headCount > 0 ? Sm100FwdWorkspaceBytes(cfg, headCount, len > 0 ? len : 0) : 0;
 }
 
-extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+static int AttFwdImpl(const tsa_att_cfg *cfg, const float *qvGlobalScale,
     tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
     tsa_ptr2d v, tsa_ptr2d vScale,
     const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
-    tsa_ptr2d out, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
+    tsa_ptr2d out, const tsa_ptr2d *copies, int copyCount, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
 {
     TGenParams p;
@@ -192,6 +192,16 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_
         return TSA_OK;
     }
     cudaStream_t s = (cudaStream_t)stream;
+    TSA_REQUIRE(copyCount >= 0 && copyCount <= TSA_MAX_OUT_COPIES && (copyCount == 0 || copies), "tsa_att_fwd_to: %d destinations", copyCount + 1);
+    for (int k = 0; k < copyCount; ++k) {
+        TSA_REQUIRE(copies[k].data && copies[k].xsize >= headCount * cfg->head_dim_v && copies[k].ysize >= p.Len &&
+            (uintptr_t)copies[k].data % 16 == 0 && copies[k].stride_bytes % 16 == 0, "tsa_att_fwd_to: destination %d missing, too small or not 16-byte aligned", k + 1);
+        p.OutCopy[k] = P2D<char>(copies[k]);
+    }
+    p.OutCopies = copyCount;
+    if (copyCount > 0 && !Sm100FwdSupports(cfg, qk, qv, v)) {
+        return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_to: more than one destination needs the tensor-core forward (head size 64 or 128, aligned buffers)");
+    }
     if (Sm100FwdSupports(cfg, qk, qv, v)) {
         size_t need = Sm100FwdWorkspaceBytes(cfg, headCount, qv.ysize); // per-head V-scale maxima, the work-item counter, e4m3 planes of int8 values
         TSA_REQUIRE(workspace && workspaceBytes >= need, "tsa_att_fwd: workspace of %zu bytes needed, %zu given", need, workspaceBytes);
@@ -199,6 +209,29 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_
         return LaunchSm100Fwd(cfg, p, qk, qv, v, lenAttTiles, qv.ysize, workspace, statusWord, s);
     }
     return LaunchGenericFwd(p, s);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    tsa_ptr2d out, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+{
+    return AttFwdImpl(cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, out, nullptr, 0, sumWeightLog,
+        headCount, lenAttTiles, workspace, workspaceBytes, statusWord, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_to(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    const tsa_ptr2d *outs, int outCount, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+{
+    TSA_REQUIRE(outs != nullptr && outCount >= 1 && outCount <= TSA_MAX_OUT_COPIES + 1, "tsa_att_fwd_to: between 1 and %d destinations", TSA_MAX_OUT_COPIES + 1);
+    return AttFwdImpl(cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, outs[0], outs + 1, outCount - 1,
+        sumWeightLog, headCount, lenAttTiles, workspace, workspaceBytes, statusWord, stream);
 }
 
 static TFwdDump g_hooks; // process-wide test hooks of the forward (score dump, failure-path self-test)

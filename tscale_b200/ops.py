@@ -233,8 +233,9 @@ def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat1
 
 
 def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale=None, global_scale=None,
-            out=None, lse=None, workspace=None, status=None):
-    """Forward.  Returns (out [len][H*Dv], sumWeightLog f32 [H][len])."""
+            out=None, lse=None, workspace=None, status=None, out_copies=None):
+    """Forward.  Returns (out [len][H*Dv], sumWeightLog f32 [H][len]).  out_copies: further destinations of the output rows,
+    either tensors or (data_ptr, stride_bytes) pairs for buffers of other GPUs mapped into this process (tsa_att_fwd_to)."""
     L = abi.lib()
     dev = qk.device
     rows = qk.shape[0]
@@ -246,6 +247,15 @@ def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale
     if workspace is None:
         workspace = torch.empty(max(1, L.tsa_att_fwd_workspace_bytes(ctypes.byref(cfg), heads, rows)), dtype=torch.uint8, device=dev)
     groups, gptr, _, _ = mask.dev(dev)
+    if out_copies:
+        outs = (Ptr2D * (1 + len(out_copies)))()
+        outs[0] = p2d(out)
+        for i, c in enumerate(out_copies):
+            outs[1 + i] = p2d(c) if isinstance(c, torch.Tensor) else Ptr2D(int(c[0]), int(c[1]), out.shape[1], out.shape[0])
+        check(L.tsa_att_fwd_to(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
+                               p2d(v), p2d(v_scale), _ptr(groups), _ptr(gptr), slope, outs, len(outs), p2d(lse), heads,
+                               mask.len_att_tiles, _ptr(workspace), workspace.numel(), _ptr(status), _stream()))
+        return out, lse
     check(L.tsa_att_fwd(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
                         p2d(v), p2d(v_scale), _ptr(groups), _ptr(gptr), slope, p2d(out), p2d(lse), heads,
                         mask.len_att_tiles, _ptr(workspace), workspace.numel(), _ptr(status), _stream()))
