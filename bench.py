@@ -10,9 +10,10 @@ algorithmic attention TFLOP/s: 4 * D * (attended pairs) per (fragment, head), ma
 filled tiles not counted.
 
 One process per GPU.  With N > 1 the 128 (fragment, head) units of the ONE batch are split contiguously over the
-ranks (tsa_shard_range / tsa_shard_rects), every rank runs tsa_att_fwd on its units only, and the bf16 output
-blocks are all-gathered over NCCL inside the timed region, slice by slice so that the gather of one slice runs
-under the next slice's kernel: strong scaling, `value` = the whole batch's flops / the slowest rank's step.
+ranks (tsa_shard_range / tsa_shard_rects), every rank runs the forward on its units only, and every rank ends
+the step with the whole bf16 output: by default the attention kernel itself stores its rows into all ranks'
+buffers (tsa_att_fwd_to over symmetric memory, one cross-rank barrier per step); `--gather nccl` all-gathers the
+blocks over NCCL slice by slice instead.  Strong scaling, `value` = the whole batch's flops / the slowest rank's step.
 At N = 1 the line also carries short runs of the other workloads (`also`: prefill125m, train15b, decode).
 
 The other workloads (`--workload prefill125m|train15b|decode|infer`) keep per-GPU work fixed (weak scaling).
@@ -66,8 +67,8 @@ def workload_config(name, w, strong=False):
            "layers": [{"window": "full" if win <= 0 else win, "alibi_slope": sl} for win, sl in w["layers"]],
            "backward": w["bwd"], "l2": "inputs larger than L2 (each layer has its own Q/K/V set)"}
     if strong:
-        cfg["sharding"] = ("the batch's fragment x head units split contiguously over the ranks; "
-                           "bf16 outputs all-gathered over NCCL inside the timed region")
+        cfg["sharding"] = ("the batch's fragment x head units split contiguously over the ranks; every rank ends the step with the whole "
+                           "bf16 output (gathered inside the timed region: by the attention kernel's own peer stores, or over NCCL)")
     else:
         cfg["sharding"] = "fragment x head, per-GPU work fixed"
     return cfg
@@ -319,20 +320,46 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
             t[nm][(f - f0) * seq:(f - f0 + 1) * seq] = b
             t["s" + nm][:, (f - f0) * seq:(f - f0 + 1) * seq] = s
             del x, b, s
-    out_local = [torch.empty((rows, wd * d), dtype=torch.bfloat16, device=dev) for wd in widths]
-    gathered = [torch.empty((world, rows, wd * d), dtype=torch.bfloat16, device=dev) for wd in widths] if world > 1 else None
+    # Several ranks: the gathered output lives in symmetric memory (every rank's buffer mapped into every process), so that
+    # the attention kernel can store its rows straight into the peers' copies (tsa_att_fwd_to: the all-gather fused into the
+    # epilogue, plain peer stores over NVLink, no multicast).  --gather nccl, or a torch without symmetric memory, keeps the
+    # per-slice NCCL all-gather.
+    fused, symm_handle, peer_out = False, None, None
+    if world > 1:
+        if args.gather == "fused":
+            try:
+                import torch.distributed._symmetric_memory as symm
+                assert len(set(widths)) == 1
+                whole = symm.empty((n_slices, world, rows, widths[0] * d), dtype=torch.bfloat16, device=dev)
+                symm_handle = symm.rendezvous(whole, dist.group.WORLD)
+                ptrs = [int(x) for x in symm_handle.buffer_ptrs]
+                gathered = [whole[s] for s in range(n_slices)]
+                block = rows * widths[0] * d * 2
+                peer_out = [[(ptrs[q] + (s * world + rank) * block, widths[0] * d * 2) for q in range(world) if q != rank] for s in range(n_slices)]
+                fused = True
+            except Exception as exc:  # noqa: BLE001 - any failure of the symmetric-memory set-up falls back to NCCL
+                sys.stderr.write("symmetric memory unavailable (%s): gathering with NCCL\n" % (exc,))
+        if fused:
+            # a rank's own block sits inside its gathered buffer: the kernel writes it there
+            out_local = [gathered[s][rank] for s in range(n_slices)]
+        else:
+            gathered = [torch.empty((world, rows, wd * d), dtype=torch.bfloat16, device=dev) for wd in widths]
+            out_local = [torch.empty((rows, wd * d), dtype=torch.bfloat16, device=dev) for wd in widths]
+    else:
+        gathered = None
+        out_local = [torch.empty((rows, wd * d), dtype=torch.bfloat16, device=dev) for wd in widths]
     lse = torch.empty((heads, rows), dtype=torch.float32, device=dev)
     workspace = torch.empty(1 << 16, dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     launches = [0]
 
-    def launch_slice(s, src=None):
+    def launch_slice(s, src=None, peers=False):
         src = t if src is None else src
         ha, hs = h0 + starts[s], widths[s]
         cols = slice(ha * d, (ha + hs) * d)
         ops.att_fwd(cfg, src["q"][:, cols], src["k"][:, cols], src["v"][:, cols], src["sk"][ha:ha + hs], mask, slope, hs,
                     qk_scale=src["sq"][ha:ha + hs], v_scale=src["sv"][ha:ha + hs], out=out_local[s], lse=lse[ha:ha + hs],
-                    workspace=workspace, status=status)
+                    workspace=workspace, status=status, out_copies=peer_out[s] if peers else None)
         launches[0] += 2  # per-head V-scale maximum + attention kernel
 
     def step(gather=True, events=None):
@@ -341,16 +368,19 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            launch_slice(s)
+            launch_slice(s, peers=gather and fused)
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
                 events.append((e0, e1))
-            if gather and world > 1:
+            if gather and world > 1 and not fused:
                 # NCCL runs the gather on its own stream behind this slice's kernel: the next slice's kernel overlaps it
                 pending.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
         for h in pending:
             h.wait()
+        if gather and fused:
+            # every rank's kernels have stored into every buffer once all ranks are past this stream-ordered barrier
+            symm_handle.barrier()
 
     def barrier():
         torch.cuda.synchronize()
@@ -408,8 +438,21 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
         gather_ms = timed(only_gather, n_probe)
         gather = {"gather_ms": gather_ms, "gather_exposed_ms": max(0.0, ms_step - compute_ms), "compute_only_ms": compute_ms,
                   "gather_bytes": (world - 1) * rows * nh * d * 2, "slices": n_slices, "slice_heads": widths,
-                  "gather_note": "gather_ms: the step's all-gathers alone, back to back; gather_exposed_ms: step time minus the same step "
-                                 "without them; gather_bytes: bytes this rank receives per step"}
+                  "gather_note": "gather_ms: the step's NCCL all-gathers alone, back to back; gather_exposed_ms: step time minus the same "
+                                 "step without any gather; gather_bytes: bytes this rank receives per step"}
+        if fused:
+            def nccl_step():
+                pend = []
+                for s in range(n_slices):
+                    launch_slice(s)
+                    pend.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
+                for h in pend:
+                    h.wait()
+            gather["mode"] = ("fused: tsa_att_fwd_to stores every output row into all ranks' buffers (symmetric memory, peer stores over "
+                              "NVLink) from the attention epilogue; one stream-ordered cross-rank barrier per step")
+            gather["nccl_variant_ms_per_step"] = timed(nccl_step, n_probe)
+        else:
+            gather["mode"] = "per-slice NCCL all-gather behind each slice's kernel"
 
     # per-unit integer checksums of the whole batch's output as this rank holds it after the gather
     table = torch.zeros((frags, heads), dtype=torch.int64, device=dev)
@@ -805,6 +848,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other workloads")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="several GPUs: output rows stored into every rank's buffer by the attention kernel itself, or per-slice NCCL all-gathers")
     ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
     ap.add_argument("--heads", type=int, default=0, help="override the number of heads (profiling on a small case)")
     args = ap.parse_args()
