@@ -328,14 +328,10 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     if world > 1:
         if args.gather == "fused":
             try:
-                import torch.distributed._symmetric_memory as symm
                 assert len(set(widths)) == 1
-                whole = symm.empty((n_slices, world, rows, widths[0] * d), dtype=torch.bfloat16, device=dev)
-                symm_handle = symm.rendezvous(whole, dist.group.WORLD)
-                ptrs = [int(x) for x in symm_handle.buffer_ptrs]
-                gathered = [whole[s] for s in range(n_slices)]
-                block = rows * widths[0] * d * 2
-                peer_out = [[(ptrs[q] + (s * world + rank) * block, widths[0] * d * 2) for q in range(world) if q != rank] for s in range(n_slices)]
+                symm_handle = shard.FusedGather(n_slices, rows, widths[0] * d, torch.bfloat16, dev)
+                gathered = [symm_handle.gathered(s) for s in range(n_slices)]
+                peer_out = [symm_handle.peers(s) for s in range(n_slices)]
                 fused = True
             except Exception as exc:  # noqa: BLE001 - any failure of the symmetric-memory set-up falls back to NCCL
                 sys.stderr.write("symmetric memory unavailable (%s): gathering with NCCL\n" % (exc,))

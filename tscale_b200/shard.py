@@ -3,7 +3,8 @@
 Every (fragment, head) pair is independent (spans never cross fragments), so ranks take contiguous blocks of
 units (unit = fragment * heads + head) and no data crosses GPUs on the way in.  The partition itself is the
 library's (tsa_shard_range / tsa_shard_rects, C ABI); this module binds it and carries the one collective of the
-path, the all-gather of the output blocks, through `torch.distributed` (NCCL on GPUs, gloo in the CPU tests).
+path, the all-gather of the output blocks, through `torch.distributed` (NCCL on GPUs, gloo in the CPU tests) or, fused into the attention kernel, as stores into the
+other ranks' buffers (FusedGather: symmetric memory + tsa_att_fwd_to).
 One process per GPU, as the reference runs one context and host thread per device
 (code/gpt/compute/gpt_cuda.cu:1478-1738).
 """
@@ -79,3 +80,36 @@ def unit_checksums(block, n_frag, seq, n_heads, head_dim):
     16-bit values: the sum of the bit patterns (as signed 16-bit integers) of the unit's elements.  int64 [n_frag][n_heads]."""
     bits = block.view(torch.int16).to(torch.int64)
     return bits.view(n_frag, seq, n_heads, head_dim).sum(dim=(1, 3))
+
+
+class FusedGather:
+    """Buffers for the all-gather that the forward kernel does itself (tsa_att_fwd_to): every rank holds the whole output,
+    [slices][world][rows][cols], in symmetric memory, i.e. mapped into every process of the box, and a rank's attention
+    kernel stores its block of slice s into `local(s)` and, through `peers(s)`, into the same place of every other rank's
+    buffer (plain peer stores over NVLink; no collective, no multicast).  `barrier()` is the stream-ordered cross-rank
+    barrier that ends a step: past it every block of every buffer is complete."""
+
+    def __init__(self, n_slices, rows, cols, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.whole = symm.empty((n_slices, self.world, rows, cols), dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.whole, group)
+        self._ptrs = [int(x) for x in self.handle.buffer_ptrs]
+        self._block = rows * cols * self.whole.element_size()
+        self._stride = cols * self.whole.element_size()
+
+    def gathered(self, s):
+        """[world][rows][cols]: slice s of every rank's block, as this rank holds it"""
+        return self.whole[s]
+
+    def local(self, s):
+        return self.whole[s][self.rank]
+
+    def peers(self, s):
+        """(address, row stride in bytes) of this rank's block of slice s inside every OTHER rank's buffer"""
+        off = (s * self.world + self.rank) * self._block
+        return [(self._ptrs[q] + off, self._stride) for q in range(self.world) if q != self.rank]
+
+    def barrier(self):
+        self.handle.barrier()
