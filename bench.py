@@ -11,9 +11,9 @@ filled tiles not counted.
 
 One process per GPU.  With N > 1 the 128 (fragment, head) units of the ONE batch are split contiguously over the
 ranks (tsa_shard_range / tsa_shard_rects), every rank runs the forward on its units only, and every rank ends
-the step with the whole bf16 output: by default the attention kernel itself stores its rows into all ranks'
-buffers (tsa_att_fwd_to over symmetric memory, one cross-rank barrier per step); `--gather nccl` all-gathers the
-blocks over NCCL slice by slice instead.  Strong scaling, `value` = the whole batch's flops / the slowest rank's step.
+the step with the whole bf16 output: on two GPUs the attention kernel itself stores its rows into both ranks'
+buffers (tsa_att_fwd_to over symmetric memory, one cross-rank barrier per step), on more the blocks are all-gathered
+over NCCL slice by slice (`--gather fused|scatter|nccl` chooses).  Strong scaling, `value` = the whole batch's flops / the slowest rank's step.
 At N = 1 the line also carries short runs of the other workloads (`also`: prefill125m, train15b, decode).
 
 The other workloads (`--workload prefill125m|train15b|decode|infer`) keep per-GPU work fixed (weak scaling).
@@ -324,18 +324,23 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     # the attention kernel can store its rows straight into the peers' copies (tsa_att_fwd_to: the all-gather fused into the
     # epilogue, plain peer stores over NVLink, no multicast).  --gather nccl, or a torch without symmetric memory, keeps the
     # per-slice NCCL all-gather.
-    fused, symm_handle, peer_out = False, None, None
+    fused, scatter, symm_handle, peer_out, side = False, False, None, None, None
     if world > 1:
-        if args.gather == "fused":
+        # measured: fused wins on two GPUs (15.16 against 15.53 ms with NCCL); with three or seven peers the epilogue's extra store
+        # instructions cost more than NCCL's exposed tail (N = 8: 5.35 against 4.89 ms), and the copy kernel was slower than NCCL (N = 2: 15.81 ms)
+        mode = args.gather if args.gather != "auto" else ("fused" if world <= 2 else "nccl")
+        if mode in ("fused", "scatter"):
             try:
                 assert len(set(widths)) == 1
                 symm_handle = shard.FusedGather(n_slices, rows, widths[0] * d, torch.bfloat16, dev)
                 gathered = [symm_handle.gathered(s) for s in range(n_slices)]
                 peer_out = [symm_handle.peers(s) for s in range(n_slices)]
-                fused = True
+                fused = mode == "fused"
+                scatter = mode == "scatter"
+                side = torch.cuda.Stream(device=dev)
             except Exception as exc:  # noqa: BLE001 - any failure of the symmetric-memory set-up falls back to NCCL
                 sys.stderr.write("symmetric memory unavailable (%s): gathering with NCCL\n" % (exc,))
-        if fused:
+        if fused or scatter:
             # a rank's own block sits inside its gathered buffer: the kernel writes it there
             out_local = [gathered[s][rank] for s in range(n_slices)]
         else:
@@ -369,13 +374,21 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
                 events.append((e0, e1))
-            if gather and world > 1 and not fused:
+            if gather and scatter:
+                # the library's copy kernel pushes this slice's block to the peers on a side stream, under the next slice's attention
+                done = torch.cuda.Event()
+                done.record()
+                side.wait_event(done)
+                symm_handle.scatter(s, stream=side)
+            elif gather and world > 1 and not fused:
                 # NCCL runs the gather on its own stream behind this slice's kernel: the next slice's kernel overlaps it
                 pending.append(shard.gather_blocks(out_local[s], gathered[s], async_op=True))
         for h in pending:
             h.wait()
-        if gather and fused:
-            # every rank's kernels have stored into every buffer once all ranks are past this stream-ordered barrier
+        if gather and (fused or scatter):
+            if scatter:
+                torch.cuda.current_stream().wait_stream(side)
+            # every rank's blocks are in every buffer once all ranks are past this stream-ordered barrier
             symm_handle.barrier()
 
     def barrier():
@@ -436,7 +449,7 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                   "gather_bytes": (world - 1) * rows * nh * d * 2, "slices": n_slices, "slice_heads": widths,
                   "gather_note": "gather_ms: the step's NCCL all-gathers alone, back to back; gather_exposed_ms: step time minus the same "
                                  "step without any gather; gather_bytes: bytes this rank receives per step"}
-        if fused:
+        if fused or scatter:
             def nccl_step():
                 pend = []
                 for s in range(n_slices):
@@ -445,7 +458,9 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                 for h in pend:
                     h.wait()
             gather["mode"] = ("fused: tsa_att_fwd_to stores every output row into all ranks' buffers (symmetric memory, peer stores over "
-                              "NVLink) from the attention epilogue; one stream-ordered cross-rank barrier per step")
+                              "NVLink) from the attention epilogue; one stream-ordered cross-rank barrier per step") if fused else (
+                              "scatter: the library's copy kernel (tsa_peer_scatter, peer stores over NVLink into symmetric memory) pushes each "
+                              "slice's block to the other ranks on a side stream under the next slice's attention; one cross-rank barrier per step")
             gather["nccl_variant_ms_per_step"] = timed(nccl_step, n_probe)
         else:
             gather["mode"] = "per-slice NCCL all-gather behind each slice's kernel"
@@ -844,8 +859,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the short runs of the other workloads")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="several GPUs: output rows stored into every rank's buffer by the attention kernel itself, or per-slice NCCL all-gathers")
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "scatter", "nccl"],
+                    help="several GPUs: how every rank gets the whole output: 'fused' = the attention kernel stores its rows into every rank's "
+                         "buffer itself, 'scatter' = the library's copy kernel pushes each slice's block to the peers under the next slice's "
+                         "attention, 'nccl' = per-slice NCCL all-gathers; 'auto' = fused on two GPUs, nccl on more")
     ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
     ap.add_argument("--heads", type=int, default=0, help="override the number of heads (profiling on a small case)")
     args = ap.parse_args()

@@ -121,6 +121,13 @@ int tsa_att_fwd_to(const tsa_att_cfg *cfg, const float *qvGlobalScale,
     const tsa_ptr2d *outs, int outCount, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
     void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
 
+/* One rank's part of an all-gather over peer memory, as a small kernel of the library: rows [0, rows) x rowBytes of src
+ * (this rank's block) are copied to each of the dstCount destinations (the same block inside the other GPUs' buffers,
+ * mapped into this process: peer access / IPC / symmetric memory).  Its CTAs (`ctas` of them, 0 = one per SM; 256 threads,
+ * no shared memory) fit beside the attention kernel's, so that on a side stream the copy of one head slice runs under the
+ * attention of the next; plain 32-byte loads and stores over NVLink, no multicast.  All rows 32-byte aligned. */
+int tsa_peer_scatter(tsa_ptr2d src, const tsa_ptr2d *dsts, int dstCount, int rows, int rowBytes, int ctas, tsa_stream_t stream);
+
 /* Forward for vectors that live in page-locked HOST memory.  Same arguments and results as tsa_att_fwd, except that qk,
  * qv, qkScale, qvScale, v, vScale, out and sumWeightLog point to host memory (cudaHostAlloc / cudaHostRegister; pageable
  * memory works but its copies do not overlap anything) while attSpans, attSpanPtr, qvGlobalScale and statusWord stay

@@ -99,6 +99,38 @@ int GetPipe(THostPipe **res)
 
 } // namespace tsa
 
+namespace tsa {
+
+// One rank's part of an all-gather over peer memory: the rows of src go to every destination (the same block inside the
+// other GPUs' buffers).  No shared memory and few registers, so its CTAs fit beside the attention CTAs of the next head
+// slice and the copy runs under that kernel (a library collective's kernels waited for the attention CTAs to leave).
+// A thread moves 32 bytes at a time: one load, one store per destination.
+struct TPeerDsts {
+    char *Data[TSA_MAX_OUT_COPIES];
+    long long Stride[TSA_MAX_OUT_COPIES];
+    int Count;
+};
+
+__global__ void __launch_bounds__(256) PeerScatterKernel(const char *src, long long srcStride, TPeerDsts dsts, int rows, int rowBytes)
+{
+    const int chunksPerRow = rowBytes >> 5;
+    const long long total = (long long)rows * chunksPerRow;
+    for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < total; id += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(id / chunksPerRow), c = (int)(id - (long long)r * chunksPerRow);
+        uint32_t v[8];
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                     : "l"(src + r * srcStride + c * 32));
+        for (int k = 0; k < dsts.Count; ++k) {
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dsts.Data[k] + r * dsts.Stride[k] + c * 32), "r"(v[0]), "r"(v[1]),
+                         "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                         : "memory");
+        }
+    }
+}
+
+} // namespace tsa
+
 using namespace tsa;
 
 extern "C" __attribute__((visibility("default"))) size_t tsa_att_fwd_host_staging_bytes(const tsa_att_cfg *cfg, int headCount, int len, int slices)
@@ -230,4 +262,32 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_host(const tsa
     }
 #undef TSA_TRY
     return rc;
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_peer_scatter(tsa_ptr2d src, const tsa_ptr2d *dsts, int dstCount, int rows, int rowBytes,
+    int ctas, tsa_stream_t stream)
+{
+    TSA_REQUIRE(src.data && dsts && dstCount >= 1 && dstCount <= TSA_MAX_OUT_COPIES, "tsa_peer_scatter: between 1 and %d destinations", TSA_MAX_OUT_COPIES);
+    TSA_REQUIRE(rows >= 0 && rowBytes > 0 && rowBytes % 32 == 0, "tsa_peer_scatter: rowBytes %d must be a multiple of 32", rowBytes);
+    TSA_REQUIRE(((uintptr_t)src.data | (uintptr_t)src.stride_bytes) % 32 == 0 && src.ysize >= rows, "tsa_peer_scatter: source rows must be 32-byte aligned");
+    TPeerDsts d;
+    d.Count = dstCount;
+    for (int k = 0; k < TSA_MAX_OUT_COPIES; ++k) {
+        d.Data[k] = nullptr;
+        d.Stride[k] = 0;
+    }
+    for (int k = 0; k < dstCount; ++k) {
+        TSA_REQUIRE(dsts[k].data && ((uintptr_t)dsts[k].data | (uintptr_t)dsts[k].stride_bytes) % 32 == 0 && dsts[k].ysize >= rows,
+            "tsa_peer_scatter: destination %d missing, too small or not 32-byte aligned", k);
+        d.Data[k] = (char *)dsts[k].data;
+        d.Stride[k] = dsts[k].stride_bytes;
+    }
+    if (rows == 0) {
+        return TSA_OK;
+    }
+    const long long total = (long long)rows * (rowBytes / 32);
+    long long want = (total + 255) / 256;
+    int grid = (int)(want < (ctas > 0 ? ctas : 148) ? want : (ctas > 0 ? ctas : 148));
+    PeerScatterKernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const char *)src.data, src.stride_bytes, d, rows, rowBytes);
+    return CheckCuda(cudaGetLastError(), "tsa_peer_scatter launch");
 }

@@ -113,3 +113,16 @@ class FusedGather:
 
     def barrier(self):
         self.handle.barrier()
+
+    def scatter(self, s, ctas=0, stream=None):
+        """Copies this rank's block of slice s into every other rank's buffer with the library's own copy kernel
+        (tsa_peer_scatter) on `stream` (default: the current one)."""
+        from . import ops
+        src = self.local(s)
+        peers = self.peers(s)
+        dsts = (ops.Ptr2D * len(peers))()
+        for i, (ptr, stride) in enumerate(peers):
+            dsts[i] = ops.Ptr2D(ptr, stride, src.shape[1], src.shape[0])
+        st = stream if stream is not None else torch.cuda.current_stream()
+        abi.check(abi.lib().tsa_peer_scatter(ops.p2d(src), dsts, len(peers), src.shape[0], src.shape[1] * src.element_size(), ctas,
+                                             ctypes.c_void_p(st.cuda_stream)))
