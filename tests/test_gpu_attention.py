@@ -153,6 +153,25 @@ def test_fwd_extra_destinations_receive_the_same_rows(d, out_dtype, ragged):
                     out=views[0], out_copies=[views[1]])
 
 
+def test_peer_scatter_copies_block_to_every_destination():
+    """tsa_peer_scatter (one rank's part of the all-gather over peer memory, the library's own copy kernel): the rows of the
+    source land in every destination, nothing else is touched; local buffers stand in for the peers'."""
+    import ctypes
+    from tscale_b200 import abi, ops
+    rows, cols = 777, 384  # bf16: 768-byte rows
+    src = torch.randn((rows, cols), device=_dev()).to(torch.bfloat16)
+    guards = [torch.full((rows + 2, cols + 16), -5.0, dtype=torch.bfloat16, device=_dev()) for _ in range(3)]
+    views = [g[1:rows + 1, :cols] for g in guards]
+    dsts = (ops.Ptr2D * 3)(*[ops.p2d(v) for v in views])
+    abi.check(abi.lib().tsa_peer_scatter(ops.p2d(src), dsts, 3, rows, cols * 2, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    for g, v in zip(guards, views):
+        assert torch.equal(v, src)
+        assert bool((g[0] == -5.0).all()) and bool((g[rows + 1] == -5.0).all()) and bool((g[:, cols:] == -5.0).all())
+    with pytest.raises(Exception):  # rows that are not 32-byte aligned are refused
+        abi.check(abi.lib().tsa_peer_scatter(ops.p2d(src[:, 8:]), dsts, 3, rows, (cols - 8) * 2, 0, None))
+
+
 @pytest.mark.parametrize("d", [64, 128])
 def test_fwd_tcgen05_constant_scales(d):
     # the reference's call shape: constant query and value scales (QK_VEC_SCALE / V_VEC_SCALE), per-row key scale
