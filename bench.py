@@ -11,9 +11,9 @@ filled tiles not counted.
 
 One process per GPU.  With N > 1 the 128 (fragment, head) units of the ONE batch are split contiguously over the
 ranks (tsa_shard_range / tsa_shard_rects), every rank runs the forward on its units only, and every rank ends
-the step with the whole bf16 output: on two GPUs the attention kernel itself stores its rows into both ranks'
-buffers (tsa_att_fwd_to over symmetric memory, one cross-rank barrier per step), on more the blocks are all-gathered
-over NCCL slice by slice (`--gather fused|scatter|nccl` chooses).  Strong scaling, `value` = the whole batch's flops / the slowest rank's step.
+the step with the whole bf16 output: the attention kernel itself stores its rows into all ranks' buffers
+(tsa_att_fwd_to over symmetric memory, one cross-rank barrier per step); `--gather nccl` all-gathers the blocks over
+NCCL slice by slice instead, `--gather scatter` uses the library's copy kernel.  Strong scaling, `value` = the whole batch's flops / the slowest rank's step.
 At N = 1 the line also carries short runs of the other workloads (`also`: prefill125m, train15b, decode).
 
 The other workloads (`--workload prefill125m|train15b|decode|infer`) keep per-GPU work fixed (weak scaling).
@@ -326,9 +326,8 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     # per-slice NCCL all-gather.
     fused, scatter, symm_handle, peer_out, side = False, False, None, None, None
     if world > 1:
-        # measured: fused wins on two GPUs (15.16 against 15.53 ms with NCCL); with three or seven peers the epilogue's extra store
-        # instructions cost more than NCCL's exposed tail (N = 8: 5.35 against 4.89 ms), and the copy kernel was slower than NCCL (N = 2: 15.81 ms)
-        mode = args.gather if args.gather != "auto" else ("fused" if world <= 2 else "nccl")
+        # measured: fused is ahead at every N (two GPUs: 15.16 against 15.53 ms with NCCL; eight: 4.45 against 4.94 ms)
+        mode = args.gather if args.gather != "auto" else "fused"
         if mode in ("fused", "scatter"):
             try:
                 assert len(set(widths)) == 1
@@ -862,7 +861,7 @@ def main():
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "scatter", "nccl"],
                     help="several GPUs: how every rank gets the whole output: 'fused' = the attention kernel stores its rows into every rank's "
                          "buffer itself, 'scatter' = the library's copy kernel pushes each slice's block to the peers under the next slice's "
-                         "attention, 'nccl' = per-slice NCCL all-gathers; 'auto' = fused on two GPUs, nccl on more")
+                         "attention, 'nccl' = per-slice NCCL all-gathers; 'auto' = fused")
     ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
     ap.add_argument("--heads", type=int, default=0, help="override the number of heads (profiling on a small case)")
     args = ap.parse_args()

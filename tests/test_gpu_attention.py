@@ -146,6 +146,13 @@ def test_fwd_extra_destinations_receive_the_same_rows(d, out_dtype, ragged):
         assert np.array_equal(util.to_np(v.contiguous()), out_ref)
         assert bool((x[0] == -3.0).all()) and bool((x[rows + 1] == -3.0).all()) and bool((x[:, width:] == -3.0).all())
     assert np.array_equal(util.to_np(lse), lse_ref)
+    # a single further destination is stored by the softmax threads themselves (three went through the forwarding warp)
+    one = torch.full((rows, width), -3.0, dtype=out_dtype, device=_dev())
+    ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status,
+                out=views[0], out_copies=[one])
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(util.to_np(one), out_ref) and np.array_equal(util.to_np(views[0].contiguous()), out_ref)
     # the SIMT path has one destination only
     cfg.flags |= 1
     with pytest.raises(Exception):

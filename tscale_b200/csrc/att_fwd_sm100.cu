@@ -44,7 +44,9 @@ using namespace sm100;
 constexpr int FW_SOFTMAX_THREADS = 128;
 constexpr int FW_MMA_WARP = 4;
 constexpr int FW_LOAD_WARP = 5;
+constexpr int FW_COPY_WARP = 6; // forwards finished output rows to the further destinations (kernels built with FORWARD only)
 constexpr int FW_THREADS = 192;
+constexpr int FW_THREADS_FORWARD = 224;
 constexpr int TILE_M = 128;
 constexpr int TILE_N = 128;
 constexpr uint32_t TMEM_COLS = 256;
@@ -119,7 +121,11 @@ struct TFwdMisc {
     uint32_t TmemBase;
     int Abort;           // a bounded wait ran out somewhere in the CTA
     float Al[TILE_N];    // ALiBi term slope * column
+    // softmax threads -> forwarding warp: the rows of an item are in the local output (ring of COPY_SLOTS records)
+    uint64_t CopyFull[4], CopyEmpty[4];
+    int CopyRow0[4], CopyHead[4];
 };
+constexpr int COPY_SLOTS = 4;
 
 template <int D, bool V_I8>
 struct TFwdSmem {
@@ -245,8 +251,10 @@ __device__ __forceinline__ int ValueScaleExponent(float x)
 // so every O += P V becomes two MMAs on the same weights; every tile also carries the weights' e4m3 residual term, which
 // brings the result within 1e-3 of the reference's fp32 accumulation (the reference's int8 mode keeps its weights in
 // half precision, gpt_att_fp16.cuh:121-318).
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
-__global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
+// FORWARD: the kernel carries the warp that forwards output rows to two or more further destinations (a seventh warp;
+// built as its own kernel so that the usual launch keeps its 192 threads and register allocation)
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD = false>
+__global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV2,
     TFwdParams p)
 {
@@ -293,6 +301,10 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             MbarInit(&misc.BarP[h], FW_SOFTMAX_THREADS);
         }
         MbarInit(&misc.BarOFull, 1);
+        for (int s = 0; s < COPY_SLOTS; ++s) {
+            MbarInit(&misc.CopyFull[s], FW_SOFTMAX_THREADS);
+            MbarInit(&misc.CopyEmpty[s], 1);
+        }
         misc.Abort = 0;
         FenceBarrierInit();
     }
@@ -724,6 +736,59 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
             }
         }
         __syncwarp();
+    } else if (FORWARD && warp == FW_COPY_WARP) {
+        // ------------------------------------------------------------------------------------ forwarding warp
+        // The all-gather fused into the kernel: every finished item's rows go from the local output (still in L2) to the
+        // further destinations, the other GPUs' buffers, 1 KB per instruction (whole 256-byte rows side by side), while the
+        // softmax threads are already on their next item.  Stored by the softmax threads themselves, one row per thread, every
+        // peer multiplied their store instructions (measured: slower than a separate NCCL all-gather from three peers on).
+        if (FORWARD && p.OutCopies > 1) {
+            const int esz = (p.OutDtype == TSA_F32) ? 4 : 2;
+            const int rowBytes = D * esz;
+            for (int n = 0;; ++n) {
+                const int cs = n % COPY_SLOTS;
+                if (!__all_sync(0xffffffffu, WaitBarSleep<100>(&misc.CopyFull[cs], (n / COPY_SLOTS) & 1, abortFlag, p.WaitCycles))) {
+                    if (lane == 0) {
+                        fail(kDevTimeoutMma);
+                    }
+                    break;
+                }
+                const int row0 = *(volatile int *)&misc.CopyRow0[cs], headC = *(volatile int *)&misc.CopyHead[cs];
+                __syncwarp();
+                if (lane == 0) {
+                    MbarArrive(&misc.CopyEmpty[cs]);
+                }
+                if (headC < 0) {
+                    break;
+                }
+                const int nRows = min(TILE_M, p.OutRows - row0);
+                const size_t colOff = (size_t)headC * rowBytes;
+                if (p.WideStores) {
+                    const int chunks = rowBytes >> 5;
+                    for (int id = lane; id < nRows * chunks; id += 32) {
+                        const int rr = id / chunks, cc = id - rr * chunks;
+                        const char *src = p.Out.Row(row0 + rr) + colOff + cc * 32;
+                        const uint4 a = __ldcg(reinterpret_cast<const uint4 *>(src)), b = __ldcg(reinterpret_cast<const uint4 *>(src) + 1);
+                        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll 1
+                        for (int k = 0; k < p.OutCopies; ++k) {
+                            StGlobal256(p.OutCopy[k].Row(row0 + rr) + colOff + cc * 32, w);
+                        }
+                    }
+                } else {
+                    const int chunks = rowBytes >> 4;
+                    for (int id = lane; id < nRows * chunks; id += 32) {
+                        const int rr = id / chunks, cc = id - rr * chunks;
+                        const uint4 a = __ldcg(reinterpret_cast<const uint4 *>(p.Out.Row(row0 + rr) + colOff + cc * 16));
+#pragma unroll 1
+                        for (int k = 0; k < p.OutCopies; ++k) {
+                            *reinterpret_cast<uint4 *>(p.OutCopy[k].Row(row0 + rr) + colOff + cc * 16) = a;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------------------------ softmax warps
         const int r = tid; // row of the item's query tile = tensor-memory lane
@@ -732,6 +797,7 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
         int rCount = 0, sCount = 0, kvCount = 0, oCount = 0;
         int pvEnabled = 0; // halves handed to the MMA so far = PV groups that have been or will be issued
         int tilesInItem = 0, row = 0, head = 0, qTile = 0;
+        int copyCount = 0; // items handed to the forwarding warp
         bool rowOk = false, failed = false;
         float m = 0, rowMult = 0, invK = 0;
         float2 lacc2 = make_float2(0.0f, 0.0f); // 128 * sum of this row's weights
@@ -744,6 +810,22 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                 fail(code);
             }
             return false;
+        };
+        // hands an item (or, with a negative head, the end of the work) to the forwarding warp: the record, a device-wide
+        // fence behind this thread's output stores, one arrival per softmax thread
+        auto postCopy = [&](int row0, int headOrEnd) {
+            const int cs = copyCount % COPY_SLOTS;
+            if (copyCount >= COPY_SLOTS && !wait(&misc.CopyEmpty[cs], ((copyCount / COPY_SLOTS) - 1) & 1, kDevTimeoutMma)) {
+                return false;
+            }
+            if (tid == 0) {
+                misc.CopyRow0[cs] = row0;
+                misc.CopyHead[cs] = headOrEnd;
+            }
+            __threadfence();
+            MbarArrive(&misc.CopyFull[cs]);
+            ++copyCount;
+            return true;
         };
         while (true) {
             const int rSlot = rCount % ROUND_SLOTS;
@@ -1127,9 +1209,10 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                         }
                     };
                     put(local);
-#pragma unroll 1
-                    for (int k = 0; k < p.OutCopies; ++k) {
-                        put(p.OutCopy[k].Row(row) + rowOff);
+                    if (p.OutCopies == 1) {
+                        // a single further destination: the row's own thread stores there too (measured faster than the hand-over
+                        // to the forwarding warp, which takes over from two destinations on)
+                        put(p.OutCopy[0].Row(row) + rowOff);
                     }
                 };
 #pragma unroll 1
@@ -1177,7 +1260,13 @@ __global__ void __launch_bounds__(FW_THREADS, 2) FwdSm100Kernel(const __grid_con
                 }
                 // no "O has been read" signal is needed: these same threads arrive on BarP for the next item's first
                 // tile only after this read-out, and the PV that overwrites O is issued after that arrival
+                if (FORWARD && p.OutCopies > 1 && !postCopy(qTile * TILE_M, head)) {
+                    break;
+                }
             }
+        }
+        if (FORWARD && p.OutCopies > 1 && !failed) {
+            postCopy(0, -1); // no more items: the forwarding warp leaves
         }
     }
     TcFenceBefore();
@@ -1393,10 +1482,10 @@ void SetFwdScoreDump(const TFwdDump &d)
     g_dump = d;
 }
 
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
-static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD>
+static int LaunchFwdT2(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
 {
-    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8>;
+    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8, FORWARD>;
     int smemBytes = TFwdSmem<D, V_I8>::TOTAL;
     int dev = 0, smCount = 0;
     int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
@@ -1413,8 +1502,21 @@ static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtens
     if (ctas > fp.TotalItems) {
         ctas = fp.TotalItems;
     }
-    kern<<<ctas, FW_THREADS, smemBytes, stream>>>(mq, mk, mv, mv2, fp);
+    kern<<<ctas, FORWARD ? FW_THREADS_FORWARD : FW_THREADS, smemBytes, stream>>>(mq, mk, mv, mv2, fp);
     return CheckCuda(cudaGetLastError(), "tcgen05 forward launch");
+}
+
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
+static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
+{
+    // two or more further destinations: the kernel with the forwarding warp (e4m3 values only: the all-gather is a prefill feature)
+    if (fp.OutCopies > 1) {
+        if (V_I8) {
+            return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_to: more than two destinations with int8 values");
+        }
+        return LaunchFwdT2<D, QK_I8, HAS_VSCALE, HAS_ALIBI, false, true>(mq, mk, mv, mv2, fp, stream);
+    }
+    return LaunchFwdT2<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8, false>(mq, mk, mv, mv2, fp, stream);
 }
 
 int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d v,
