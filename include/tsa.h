@@ -109,7 +109,9 @@ size_t tsa_att_fwd_workspace_bytes(const tsa_att_cfg *cfg, int headCount, int le
  * mapped into this process (CUDA peer access / IPC / symmetric memory over NVLink): each rank of a (fragment x head)-sharded
  * batch writes its block straight into every rank's copy of the whole output from the attention epilogue, so that no
  * separate collective has to move it afterwards (the reference gathers by copying device arrays between its per-device
- * contexts, code/gpt/compute/gpt_cuda.cu:1478-1738).  Plain 16- or 32-byte stores; no multicast.  The callers order the
+ * contexts, code/gpt/compute/gpt_cuda.cu:1478-1738).  Plain 16- or 32-byte stores; no multicast.  One further destination
+ * is stored by the thread that owns the row; two or more are served by a forwarding warp that re-reads finished rows from
+ * L2 (e4m3 values only).  The callers order the
  * step themselves (a stream-ordered barrier across the ranks before anybody reads a gathered buffer).  Everything else as
  * tsa_att_fwd; outCount = 1 is tsa_att_fwd.  At most TSA_MAX_OUT_COPIES + 1 destinations; only the tensor-core path
  * takes more than one (TSA_UNSUPPORTED otherwise). */
