@@ -4,6 +4,7 @@ the shapes of the prefill (65536 rows, 12 heads x 64) and training (32768 rows, 
   producer  tsa_norm_rope_quant / tsa_rope_norm_bwd      HBM-bound, algorithmic bytes = source + rope + bytes out + scales
   fused     tsa_matmul_norm_rope_quant                   int8 projection (tensor) with the producer as its epilogue
   consumer  tsa_kv_product / tsa_kv_product_bwd          HBM-bound
+  fused consumer  tsa_att_fwd_kv against tsa_att_fwd followed by tsa_kv_product (same buffers, same results)
 
 One JSON line: `value` is the producer's forward bandwidth on the first shape, `kernels` lists every measurement.
 Inputs are larger than L2 except the fused kernel's int8 operands; each kernel runs 3 warm-up and 20 timed launches.
@@ -84,6 +85,43 @@ def run(args, rank, world, local_rank):
         note("tsa_kv_product bf16", shape, timed(lambda: ops.kv_product(k, v, heads, d)), nbytes=2 * (2 + 4) * n)
         note("tsa_kv_product_bwd bf16", shape, timed(lambda: ops.kv_product_bwd(k, v, gk, heads, d)), nbytes=2 * (2 + 4 + 2) * n + rows * heads * 4)
         del k, v, gk
+    # the consumer fused into the attention kernel against the two launches it replaces
+    for name, frags, seq, heads, d, window in (("window 64", 16, 4096, 12, 64, 64), ("full causal", 16, 4096, 12, 64, 0),
+                                                ("full causal", 1, 32768, 16, 128, 0)):
+        rows = frags * seq
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(3)
+        t = {}
+        for nm in ("q", "k", "v"):
+            x = torch.randn((rows, heads * d), generator=gen, device=dev) * 0.5
+            t[nm], t["s" + nm] = ops.quant_rows(x, "absmax", "e4m3", d)
+            del x
+        mask = ops.Mask.window([seq] * frags, window)
+        cfg = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.bfloat16)
+        att_out = torch.empty((rows, heads * d), dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((heads, rows), dtype=torch.float32, device=dev)
+        ws = torch.empty(1 << 16, dtype=torch.uint8, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ck = torch.randn((rows, heads * d), generator=gen, device=dev).bfloat16()
+        kv_a = torch.empty((rows, 4 * heads * d), dtype=torch.bfloat16, device=dev)
+        kv_b = torch.empty_like(kv_a)
+
+        def att(**kw):
+            return ops.att_fwd(cfg, t["q"], t["k"], t["v"], t["sk"], mask, 0.0, heads, qk_scale=t["sq"], v_scale=t["sv"], out=att_out, lse=lse,
+                               workspace=ws, status=status, **kw)
+
+        def two_launches():
+            att()
+            ops.kv_product(ck, att_out, heads, d, kv_mult=0.5, out=kv_a)
+
+        shape = (rows, heads * d, heads, d)
+        ms_att = timed(att)
+        ms_two = timed(two_launches)
+        ms_fused = timed(lambda: att(combiner_k=ck, kv_mult=0.5, kv=kv_b))
+        assert int(status.item()) == 0 and torch.equal(kv_a, kv_b)
+        out.append({"kernel": "tsa_att_fwd_kv e4m3 %s, %d x %d" % (name, frags, seq), "rows": rows, "dim": heads * d, "heads": heads, "head_dim": d,
+                    "ms": ms_fused, "ms_attention_alone": ms_att, "ms_attention_then_kv_product": ms_two, "same_bits": True})
+        del t, att_out, kv_a, kv_b, ck
     clocks = sampler.stop()
     first = out[0]
     print(json.dumps({

@@ -262,6 +262,24 @@ int tsa_kv_product(int inDtype, int outDtype, tsa_ptr2d k, tsa_ptr2d valLookup, 
 int tsa_kv_product_bwd(int inDtype, int gradDtype, tsa_ptr2d k, tsa_ptr2d valLookup, tsa_ptr2d dkv, tsa_ptr2d dK,
     tsa_ptr2d dValLookup, tsa_ptr2d dScale, int headCount, int headDim, int len, tsa_stream_t stream);
 
+/* tsa_att_fwd with the consumer fused into the kernel (the reference launches KVProduct right behind the attention,
+ * code/gpt/compute/gpt_cuda.cu:520-523): besides out and sumWeightLog the call writes
+ *   kv[t][head * 4 D + blk * D + z] = combinerK[t][head * D + (z ^ blk)] * out[t][head * D + z] * kvMult,  blk = 0 .. 3,
+ * bit for bit what tsa_kv_product(bf16, bf16) gives on the stored output.  The thread that rounds a row of the output to
+ * bf16 multiplies it with the row of combiner keys (prefetched into L2 while the block is computed) and stores the four
+ * products with streaming 32-byte stores, so the stand-alone kernel's launch and its re-read of the output go away.
+ * Measured on B200 the two calls it replaces are as fast or faster (the forward is bound by the instruction issue of
+ * the threads that would do this work, the stand-alone product by memory bandwidth, which it reaches): prefer them
+ * where speed decides.  combinerK bf16 [>= len][>= H*D], kv bf16 [>= len][>= 4*H*D],
+ * both 16-byte aligned; out dtype bf16, e4m3 values, head size 64 or 128 (otherwise TSA_UNSUPPORTED: call tsa_att_fwd
+ * and tsa_kv_product). */
+int tsa_att_fwd_kv(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    tsa_ptr2d out, tsa_ptr2d sumWeightLog, tsa_ptr2d combinerK, float kvMult, tsa_ptr2d kv, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream);
+
 /* ---- KV-cache decode -------------------------------------------------------------------------
  * Replaces NCPUInfer::TAttentionVecHistory / ComputeValLookup (code/gpt/train/cpu_infer.cpp:397-460),
  * batched over sequences.  Per sequence the cache is caller-owned device memory:

@@ -160,6 +160,39 @@ def test_fwd_extra_destinations_receive_the_same_rows(d, out_dtype, ragged):
                     out=views[0], out_copies=[views[1]])
 
 
+@pytest.mark.parametrize("d,window,slope", [(128, 128, 0.25), (64, 64, 0.0), (64, 0, 0.0)])
+def test_fwd_fused_consumer_equals_attention_then_kv_product(d, window, slope):
+    """tsa_att_fwd_kv (the forward with the consumer of its output fused in: KVProduct, code/gpt/compute/gpt_combiner.cuh:12-39)
+    gives the output of tsa_att_fwd and the combiner input of tsa_kv_product on that output, bit for bit; the combiner input
+    also equals the oracle's KVProduct of the same bf16 rows up to the bf16 rounding of the result; rows and columns around
+    kv stay untouched (ragged last fragment)."""
+    from tscale_b200 import ops
+    frag_lens, heads, kv_mult = [384, 200], 3, 0.375
+    out_ref, lse_ref, _, (g, mask, cfg, _, _, _) = _run_fwd(7, frag_lens, window, slope, heads, d, "e4m3", "e4m3", out_dtype=torch.bfloat16, scale=0.5)
+    rows, width = sum(frag_lens), heads * d
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    ck = torch.randn((rows, width), generator=gen).to(torch.bfloat16).to(_dev())
+    guard = torch.full((rows + 2, 4 * width + 16), -3.0, dtype=torch.bfloat16, device=_dev())
+    kv_view = guard[1:rows + 1, :4 * width]
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out, lse, kv = ops.att_fwd(cfg, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status,
+                               combiner_k=ck, kv_mult=kv_mult, kv=kv_view)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(util.to_np(out), out_ref) and np.array_equal(util.to_np(lse), lse_ref)
+    alone = ops.kv_product(ck, out, heads, d, kv_mult=kv_mult)
+    torch.cuda.synchronize()
+    assert torch.equal(kv.contiguous(), alone)
+    assert bool((guard[0] == -3.0).all()) and bool((guard[rows + 1] == -3.0).all()) and bool((guard[:, 4 * width:] == -3.0).all())
+    want = O.kv_product(ck.float().cpu().numpy(), out.float().cpu().numpy(), heads) * kv_mult
+    got = kv.float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 2.0 ** -8 * np.max(np.abs(want)) + 1e-30
+    # what the fused form does not cover is refused, not computed some other way
+    cfg32 = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.float32)
+    with pytest.raises(Exception):
+        ops.att_fwd(cfg32, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status, combiner_k=ck)
+
+
 def test_peer_scatter_copies_block_to_every_destination():
     """tsa_peer_scatter (one rank's part of the all-gather over peer memory, the library's own copy kernel): the rows of the
     source land in every destination, nothing else is touched; local buffers stand in for the peers'."""

@@ -78,7 +78,7 @@ EXPORTS = [
     "tsa_infer_workspace_bytes", "tsa_infer_step", "tsa_matmul_norm_rope_quant", "tsa_att_fwd_set_score_dump", "tsa_shard_range", "tsa_shard_rects", "tsa_status_from_word", "tsa_selftest_bounded_wait",
     "tsa_selftest_fwd_withhold_copy", "tsa_att_fwd_host", "tsa_att_fwd_host_staging_bytes",
     "tsa_bounds_check_hits", "tsa_selftest_bounds_check",
-    "tsa_att_fwd_to", "tsa_peer_scatter",
+    "tsa_att_fwd_to", "tsa_att_fwd_kv", "tsa_peer_scatter",
     "tsa_transpose_attention_device", "tsa_transpose_attention_device_workspace_bytes", "tsa_group_attention_device",
     "tsa_group_attention_device_workspace_bytes",
 ]
@@ -92,6 +92,8 @@ def _declare(lib):
                                 P, P, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
     lib.tsa_att_fwd_to.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, c_void_p, c_void_p, c_float,
                                    ctypes.POINTER(P), c_int, P, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
+    lib.tsa_att_fwd_kv.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, c_void_p, c_void_p, c_float,
+                                   P, P, P, c_float, P, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
     lib.tsa_peer_scatter.argtypes = [P, ctypes.POINTER(P), c_int, c_int, c_int, c_int, c_void_p]
     lib.tsa_att_fwd_host.argtypes = [ctypes.POINTER(AttCfg), c_void_p, P, P, P, P, P, P, c_void_p, c_void_p, c_float,
                                      P, P, P, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]

@@ -75,6 +75,11 @@ struct TFwdParams {
     P2D<char> OutCopy[TSA_MAX_OUT_COPIES]; // further destinations of the output rows (other GPUs' buffers among them)
     int OutCopies;
     int WideStores;   // every destination's rows are 32-byte aligned
+    // the consumer of the output, formed in the epilogue of kernels built with KV (null KvOut: none):
+    // kv[t][head * 4 D + blk * D + z] = KvK[t][head * D + (z ^ blk)] * out[t][head * D + z] * KvMult, all bf16
+    P2D<char> KvK, KvOut;
+    float KvMult;
+    int KvWide;       // rows of kv are 32-byte aligned
     P2D<float> Lse;
     const float *GlobalScale;
     float C;
@@ -253,7 +258,14 @@ __device__ __forceinline__ int ValueScaleExponent(float x)
 // half precision, gpt_att_fp16.cuh:121-318).
 // FORWARD: the kernel carries the warp that forwards output rows to two or more further destinations (a seventh warp;
 // built as its own kernel so that the usual launch keeps its 192 threads and register allocation)
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD = false>
+// KV: the epilogue also forms the consumer's input (the reference's KVProduct) from the row it has just rounded to bf16.
+// Measured against the two launches it replaces (attention, then the stand-alone product, which streams at 0.94 of the copy
+// bandwidth): equal on a full-causal layer of 16 x 4096 x 12 x 64 (0.941 against 0.938 ms), slower on the window-64 layer
+// (0.231 against 0.219 ms) and on 32768 x 16 x 128 (3.95 against 3.86 ms).  A kernel that carries this code runs its hot
+// loop 6-7 % slower even when none of the consumer's memory accesses execute, and the same holds for the two other forms
+// that were built: the products as a pass of their own that reads the stored row back from L2 (same register count as the
+// plain kernel; 0.290 / 0.949 / 3.99 ms) and a seventh warp that takes finished blocks from L2 (0.271 / 1.075 / 4.00 ms).
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD = false, bool KV = false>
 __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) FwdSm100Kernel(const __grid_constant__ CUtensorMap tmQ,
     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmV2,
     TFwdParams p)
@@ -852,6 +864,15 @@ __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) 
                 m = 0;
                 lacc2 = make_float2(0.0f, 0.0f);
                 tilesInItem = 0;
+                if (KV && rowOk) {
+                    // the row of combiner keys the epilogue will multiply with: on its way into L2 while the item is computed
+                    const char *kp = p.KvK.Row(row) + (size_t)head * D * 2;
+#pragma unroll
+                    for (int o = 0; o < D * 2; o += 128) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + o));
+                    }
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + D * 2 - 16));
+                }
                 if (HAS_VSCALE) {
                     // the loader stages sv_j * K with 1 / K = the power of two at or above the head's largest value scale,
                     // so the weights' e4m3 range is used whatever the scales' magnitude; O is in units of 1 / K
@@ -1181,6 +1202,25 @@ __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) 
             }
             if (flags & RF_LAST) {
                 // ---- epilogue of the item
+                // consumer fused into the epilogue: the combiner keys of 32 columns at a time, one step ahead of their use
+                uint32_t kcur[16];
+                const char *kRow = nullptr;
+                char *kvRow = nullptr;
+                auto loadKeys = [&](int col, uint32_t *dst) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(kRow + col * 2);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 x = __ldcs(src + i);
+                        dst[4 * i] = x.x, dst[4 * i + 1] = x.y, dst[4 * i + 2] = x.z, dst[4 * i + 3] = x.w;
+                    }
+                };
+                if (KV) {
+                    kRow = p.KvK.Row(rowOk ? row : 0) + (size_t)head * D * 2;
+                    kvRow = p.KvOut.Row(rowOk ? row : 0) + (size_t)head * 4 * D * 2;
+                    if (rowOk) {
+                        loadKeys(0, kcur);
+                    }
+                }
                 if (tilesInItem > 0) {
                     if (!wait(&misc.BarOFull, oCount & 1, kDevTimeoutMma)) {
                         break;
@@ -1218,6 +1258,10 @@ __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) 
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t o[32];
+                    uint32_t knext[16];
+                    if (KV && rowOk && c0 + 32 < D) {
+                        loadKeys(c0 + 32, knext);
+                    }
                     if (tilesInItem > 0) {
                         TmemLd32(tLane + TMEM_O_COL + c0, o);
                         TmemWaitLdRegs(o);
@@ -1254,7 +1298,45 @@ __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) 
                                     }
                                 }
                                 storeAll(oRow + (c0 + c) * 2, headOff + (c0 + c) * 2, w);
+                                if (KV) {
+                                    // kv[blk][z] = k[z ^ blk] * out[z] * kvMult for these 16 columns, out as it was just rounded to
+                                    // bf16 (so the result is that of the stand-alone kernel on the stored output, bit for bit);
+                                    // z ^ blk stays inside an aligned group of four columns
+                                    const uint32_t *kw = &kcur[c / 2];
+                                    float2 of[8], kf[8], ks[8];
+#pragma unroll
+                                    for (int k = 0; k < 8; ++k) {
+                                        of[k] = make_float2(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xffff0000u));
+                                        kf[k] = make_float2(__uint_as_float(kw[k] << 16), __uint_as_float(kw[k] & 0xffff0000u));
+                                        ks[k] = make_float2(kf[k].y, kf[k].x);
+                                    }
+                                    const float2 mult2 = make_float2(p.KvMult, p.KvMult);
+#pragma unroll
+                                    for (int blk = 0; blk < 4; ++blk) {
+                                        uint32_t rr[8];
+#pragma unroll
+                                        for (int k = 0; k < 8; ++k) {
+                                            const float2 kk = (blk & 1) ? ks[k ^ (blk >> 1)] : kf[k ^ (blk >> 1)];
+                                            const float2 pr = __fmul2_rn(__fmul2_rn(kk, of[k]), mult2);
+                                            const __nv_bfloat162 hh = __floats2bfloat162_rn(pr.x, pr.y);
+                                            rr[k] = *reinterpret_cast<const uint32_t *>(&hh);
+                                        }
+                                        char *dstp = kvRow + ((size_t)blk * D + c0 + c) * 2;
+                                        if (p.KvWide) {
+                                            StGlobal256Stream(dstp, rr);
+                                        } else {
+                                            __stcs(reinterpret_cast<uint4 *>(dstp), make_uint4(rr[0], rr[1], rr[2], rr[3]));
+                                            __stcs(reinterpret_cast<uint4 *>(dstp) + 1, make_uint4(rr[4], rr[5], rr[6], rr[7]));
+                                        }
+                                    }
+                                }
                             }
+                        }
+                    }
+                    if (KV) {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) {
+                            kcur[k] = knext[k];
                         }
                     }
                 }
@@ -1482,10 +1564,10 @@ void SetFwdScoreDump(const TFwdDump &d)
     g_dump = d;
 }
 
-template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD>
+template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8, bool FORWARD, bool KV = false>
 static int LaunchFwdT2(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
 {
-    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8, FORWARD>;
+    auto kern = FwdSm100Kernel<D, QK_I8, HAS_VSCALE, HAS_ALIBI, V_I8, FORWARD, KV>;
     int smemBytes = TFwdSmem<D, V_I8>::TOTAL;
     int dev = 0, smCount = 0;
     int rc = CheckCuda(cudaGetDevice(&dev), "cudaGetDevice");
@@ -1510,6 +1592,13 @@ template <int D, bool QK_I8, bool HAS_VSCALE, bool HAS_ALIBI, bool V_I8>
 static int LaunchFwdT(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mv2, const TFwdParams &fp, cudaStream_t stream)
 {
     // two or more further destinations: the kernel with the forwarding warp (e4m3 values only: the all-gather is a prefill feature)
+    if (fp.KvOut.Data != nullptr) {
+        // the consumer in the epilogue: its own kernel, so that the plain forward keeps its register allocation
+        if (V_I8 || fp.OutCopies > 1 || fp.OutDtype != TSA_BF16) {
+            return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_kv: e4m3 values, a bf16 output and at most one further destination");
+        }
+        return LaunchFwdT2<D, QK_I8, HAS_VSCALE, HAS_ALIBI, false, false, true>(mq, mk, mv, mv2, fp, stream);
+    }
     if (fp.OutCopies > 1) {
         if (V_I8) {
             return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_to: more than two destinations with int8 values");
@@ -1583,6 +1672,10 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
             fp.WideStores = 0;
         }
     }
+    fp.KvK = p.KvK;
+    fp.KvOut = p.KvOut;
+    fp.KvMult = p.KvMult;
+    fp.KvWide = ((((uintptr_t)p.KvOut.Data | (uintptr_t)p.KvOut.Stride) & 31) == 0) ? 1 : 0;
     fp.Lse = p.Lse;
     fp.GlobalScale = p.GlobalScale;
     fp.C = p.C;

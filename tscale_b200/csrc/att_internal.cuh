@@ -24,6 +24,9 @@ struct TGenParams {
     P2D<char> Out;
     P2D<char> OutCopy[TSA_MAX_OUT_COPIES]; // further destinations of the forward's output (same shape as Out; peer-GPU memory allowed)
     int OutCopies = 0;
+    // consumer fused into the forward (tsa_att_fwd_kv): combiner key rows bf16 [len][H*D], combiner input bf16 [len][H*4D]
+    P2D<char> KvK, KvOut;
+    float KvMult = 1.0f;
     P2D<float> Lse;
     P2D<char> DOut;
     P2D<float> DScale;

@@ -174,6 +174,15 @@ __device__ __forceinline__ void StGlobal256(void *p, const uint32_t *v)
                  : "memory");
 }
 
+// the same store with the streaming hint: data that is written once and read by a later kernel should not displace the
+// tiles this kernel keeps re-reading from L2
+__device__ __forceinline__ void StGlobal256Stream(void *p, const uint32_t *v)
+{
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+                 "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void TmemStN(uint32_t taddr, const uint32_t *r);
 template <>

@@ -167,7 +167,8 @@ static int AttFwdImpl(const tsa_att_cfg *cfg, const float *qvGlobalScale,
     tsa_ptr2d v, tsa_ptr2d vScale,
     const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
     tsa_ptr2d out, const tsa_ptr2d *copies, int copyCount, tsa_ptr2d sumWeightLog, int headCount, int lenAttTiles,
-    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream,
+    const tsa_ptr2d *combinerK = nullptr, float kvMult = 1.0f, const tsa_ptr2d *kv = nullptr)
 {
     TGenParams p;
     int rc = FillCommon("tsa_att_fwd", cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, headCount, lenAttTiles, &p);
@@ -199,6 +200,20 @@ static int AttFwdImpl(const tsa_att_cfg *cfg, const float *qvGlobalScale,
         p.OutCopy[k] = P2D<char>(copies[k]);
     }
     p.OutCopies = copyCount;
+    if (kv) {
+        const int D = cfg->head_dim_v;
+        TSA_REQUIRE(combinerK != nullptr, "tsa_att_fwd_kv: null combiner key argument");
+        if (!Sm100FwdSupports(cfg, qk, qv, v) || cfg->out_dtype != TSA_BF16 || cfg->v_dtype == TSA_I8) {
+            return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_kv needs the tensor-core forward (head size 64 or 128, aligned buffers), e4m3 values and a bf16 output");
+        }
+        TSA_REQUIRE(combinerK->data && combinerK->xsize >= headCount * D && combinerK->ysize >= p.Len &&
+            (uintptr_t)combinerK->data % 16 == 0 && combinerK->stride_bytes % 16 == 0, "tsa_att_fwd_kv: combiner keys missing, too small or not 16-byte aligned");
+        TSA_REQUIRE(kv->data && kv->xsize >= headCount * 4 * D && kv->ysize >= p.Len &&
+            (uintptr_t)kv->data % 16 == 0 && kv->stride_bytes % 16 == 0, "tsa_att_fwd_kv: kv missing, too small or not 16-byte aligned");
+        p.KvK = P2D<char>(*combinerK);
+        p.KvOut = P2D<char>(*kv);
+        p.KvMult = kvMult;
+    }
     if (copyCount > 0 && !Sm100FwdSupports(cfg, qk, qv, v)) {
         return Fail(TSA_UNSUPPORTED, "tsa_att_fwd_to: more than one destination needs the tensor-core forward (head size 64 or 128, aligned buffers)");
     }
@@ -232,6 +247,17 @@ extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_to(const tsa_a
     TSA_REQUIRE(outs != nullptr && outCount >= 1 && outCount <= TSA_MAX_OUT_COPIES + 1, "tsa_att_fwd_to: between 1 and %d destinations", TSA_MAX_OUT_COPIES + 1);
     return AttFwdImpl(cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, outs[0], outs + 1, outCount - 1,
         sumWeightLog, headCount, lenAttTiles, workspace, workspaceBytes, statusWord, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int tsa_att_fwd_kv(const tsa_att_cfg *cfg, const float *qvGlobalScale,
+    tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
+    tsa_ptr2d v, tsa_ptr2d vScale,
+    const tsa_span_group *attSpans, const int *attSpanPtr, float alibiSlope,
+    tsa_ptr2d out, tsa_ptr2d sumWeightLog, tsa_ptr2d combinerK, float kvMult, tsa_ptr2d kv, int headCount, int lenAttTiles,
+    void *workspace, size_t workspaceBytes, int *statusWord, tsa_stream_t stream)
+{
+    return AttFwdImpl(cfg, qvGlobalScale, qk, qv, qkScale, qvScale, v, vScale, attSpans, attSpanPtr, alibiSlope, out, nullptr, 0, sumWeightLog,
+        headCount, lenAttTiles, workspace, workspaceBytes, statusWord, stream, &combinerK, kvMult, &kv);
 }
 
 static TFwdDump g_hooks; // process-wide test hooks of the forward (score dump, failure-path self-test)

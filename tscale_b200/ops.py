@@ -207,10 +207,11 @@ def rope_norm_bwd(src, grad, rope, heads, head_dim, direction=1.0):
     return out
 
 
-def kv_product(k, val, heads, head_dim, kv_mult=1.0, out_dtype=None):
+def kv_product(k, val, heads, head_dim, kv_mult=1.0, out_dtype=None, out=None):
     """Combiner input [rows][H*D*4] from k and the attention output."""
-    out_dtype = k.dtype if out_dtype is None else out_dtype
-    out = torch.empty((k.shape[0], heads * head_dim * 4), dtype=out_dtype, device=k.device)
+    out_dtype = (k.dtype if out is None else out.dtype) if out_dtype is None else out_dtype
+    if out is None:
+        out = torch.empty((k.shape[0], heads * head_dim * 4), dtype=out_dtype, device=k.device)
     check(abi.lib().tsa_kv_product(_DT[k.dtype], _DT[out_dtype], p2d(k), p2d(val), kv_mult, p2d(out), heads, head_dim, k.shape[0], _stream()))
     return out
 
@@ -233,9 +234,11 @@ def make_cfg(qk_dtype, v_dtype, head_dim_qk, head_dim_v, out_dtype=torch.bfloat1
 
 
 def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale=None, global_scale=None,
-            out=None, lse=None, workspace=None, status=None, out_copies=None):
+            out=None, lse=None, workspace=None, status=None, out_copies=None, combiner_k=None, kv_mult=1.0, kv=None):
     """Forward.  Returns (out [len][H*Dv], sumWeightLog f32 [H][len]).  out_copies: further destinations of the output rows,
-    either tensors or (data_ptr, stride_bytes) pairs for buffers of other GPUs mapped into this process (tsa_att_fwd_to)."""
+    either tensors or (data_ptr, stride_bytes) pairs for buffers of other GPUs mapped into this process (tsa_att_fwd_to).
+    combiner_k (bf16 [len][H*D]): the kernel also forms the combiner input kv (bf16 [len][4*H*D], tsa_att_fwd_kv) and the
+    call returns (out, sumWeightLog, kv)."""
     L = abi.lib()
     dev = qk.device
     rows = qk.shape[0]
@@ -247,6 +250,16 @@ def att_fwd(cfg, qk, qv, v, qv_scale, mask, slope, heads, qk_scale=None, v_scale
     if workspace is None:
         workspace = torch.empty(max(1, L.tsa_att_fwd_workspace_bytes(ctypes.byref(cfg), heads, rows)), dtype=torch.uint8, device=dev)
     groups, gptr, _, _ = mask.dev(dev)
+    if combiner_k is not None:
+        if out_copies:
+            raise ValueError("att_fwd: out_copies and combiner_k exclude each other")
+        if kv is None:
+            kv = torch.empty((rows, 4 * heads * cfg.head_dim_v), dtype=torch.bfloat16, device=dev)
+        check(L.tsa_att_fwd_kv(ctypes.byref(cfg), _ptr(global_scale), p2d(qk), p2d(qv), p2d(qk_scale), p2d(qv_scale),
+                               p2d(v), p2d(v_scale), _ptr(groups), _ptr(gptr), slope, p2d(out), p2d(lse), p2d(combiner_k),
+                               kv_mult, p2d(kv), heads, mask.len_att_tiles, _ptr(workspace), workspace.numel(), _ptr(status),
+                               _stream()))
+        return out, lse, kv
     if out_copies:
         outs = (Ptr2D * (1 + len(out_copies)))()
         outs[0] = p2d(out)
