@@ -298,9 +298,13 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     f0, f1, h0, h1 = rects[0]
     nf, nh = f1 - f0, h1 - h0
     rows = nf * seq
-    # head slices of the rank's rectangle: four equal ones (slices shrinking towards the end, so that the last all-gather is
-    # small, were measured at N = 2: the exposed gather time stayed at 0.5 ms, it is not the last slice's gather that shows)
-    widths = [nh // 4] * 4 if nh % 4 == 0 else [nh]
+    # Head slices of the rank's rectangle.  With NCCL (or the copy kernel) four equal ones, so that the gather of a slice runs
+    # under the next slice's kernel (slices shrinking towards the end, so that the last all-gather is small, were measured at
+    # N = 2: the exposed gather time stayed at 0.5 ms, it is not the last slice's gather that shows).  One GPU, or the gather
+    # fused into the kernel: one launch for the whole rectangle, since every launch ends in a tail of long work items.
+    gather_mode = ("fused" if args.gather == "auto" else args.gather) if world > 1 else "none"
+    k_slices = args.slices if args.slices > 0 else (1 if gather_mode in ("none", "fused") else 4)
+    widths = [nh // k_slices] * k_slices if nh % k_slices == 0 else [nh]
     n_slices = len(widths)
     starts = [sum(widths[:i]) for i in range(n_slices)]
     cfg = ops.make_cfg(w["qk"], w["v"], d, d, out_dtype=torch.bfloat16)
@@ -327,7 +331,7 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     fused, scatter, symm_handle, peer_out, side = False, False, None, None, None
     if world > 1:
         # measured: fused is ahead at every N (two GPUs: 15.16 against 15.53 ms with NCCL; eight: 4.45 against 4.94 ms)
-        mode = args.gather if args.gather != "auto" else "fused"
+        mode = gather_mode
         if mode in ("fused", "scatter"):
             try:
                 assert len(set(widths)) == 1
@@ -339,6 +343,10 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                 side = torch.cuda.Stream(device=dev)
             except Exception as exc:  # noqa: BLE001 - any failure of the symmetric-memory set-up falls back to NCCL
                 sys.stderr.write("symmetric memory unavailable (%s): gathering with NCCL\n" % (exc,))
+                if args.slices <= 0 and nh % 4 == 0:
+                    widths = [nh // 4] * 4  # NCCL gathers overlap the following slices' kernels
+                    n_slices = len(widths)
+                    starts = [sum(widths[:i]) for i in range(n_slices)]
         if fused or scatter:
             # a rank's own block sits inside its gathered buffer: the kernel writes it there
             out_local = [gathered[s][rank] for s in range(n_slices)]
@@ -460,7 +468,9 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                               "NVLink) from the attention epilogue; one stream-ordered cross-rank barrier per step") if fused else (
                               "scatter: the library's copy kernel (tsa_peer_scatter, peer stores over NVLink into symmetric memory) pushes each "
                               "slice's block to the other ranks on a side stream under the next slice's attention; one cross-rank barrier per step")
-            gather["nccl_variant_ms_per_step"] = timed(nccl_step, n_probe)
+            if n_slices > 1:
+                # the same slices with an NCCL all-gather behind each (with one slice nothing would overlap: run --gather nccl)
+                gather["nccl_variant_ms_per_step"] = timed(nccl_step, n_probe)
         else:
             gather["mode"] = "per-slice NCCL all-gather behind each slice's kernel"
 
@@ -862,6 +872,8 @@ def main():
                     help="several GPUs: how every rank gets the whole output: 'fused' = the attention kernel stores its rows into every rank's "
                          "buffer itself, 'scatter' = the library's copy kernel pushes each slice's block to the peers under the next slice's "
                          "attention, 'nccl' = per-slice NCCL all-gathers; 'auto' = fused")
+    ap.add_argument("--slices", type=int, default=0,
+                    help="head slices (launches) per step of the default workload; 0 = one, or four when the gather is not fused")
     ap.add_argument("--frags", type=int, default=0, help="override the number of fragments (profiling on a small case)")
     ap.add_argument("--heads", type=int, default=0, help="override the number of heads (profiling on a small case)")
     args = ap.parse_args()

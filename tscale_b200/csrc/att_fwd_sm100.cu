@@ -60,6 +60,7 @@ enum { RF_FIRST = 1, RF_LAST = 2, RF_END = 4 };
 
 struct TFwdParams {
     int HeadCount;
+    int HeadGroup;    // heads whose work items are handed out together (1 .. HeadCount)
     int OutRows;      // rows of out that may be written
     int KeyRows;      // rows of K / V
     int LenAttTiles;  // number of 64-row span blocks
@@ -374,8 +375,16 @@ __global__ void __launch_bounds__(FORWARD ? FW_THREADS_FORWARD : FW_THREADS, 2) 
             if (!end && lane == 0) {
                 nextItem = atomicAdd(p.Counter, 1); // in flight while this item is set up
             }
-            const int qTile = end ? 0 : p.QTiles - 1 - item / p.HeadCount; // late (long) rows first
-            const int head = end ? 0 : item % p.HeadCount;
+            // Order of the work items: heads in groups of p.HeadGroup, inside a group late (long) rows first with the group's
+            // heads side by side.  The CTAs that run at the same time then read the keys and values of that many heads; the
+            // host sizes the group so that these stay L2-resident (with everything of every head in flight at once the
+            // four-fragment long-context batch ran 3.5 % slower, with groups smaller than needed shorter batches 2-8 % slower).
+            // The launch still ends on short items.
+            const int groupItems = p.QTiles * p.HeadGroup;
+            const int grp = item / groupItems, rem = item - grp * groupItems;
+            const int groupHeads = min(p.HeadGroup, p.HeadCount - grp * p.HeadGroup);
+            const int qTile = end ? 0 : p.QTiles - 1 - rem / groupHeads;
+            const int head = end ? 0 : grp * p.HeadGroup + rem % groupHeads;
             const int b0 = 2 * qTile;
             int p0 = 0, n0 = 0, p1 = 0, n1 = 0, nRounds = 0;
             int qSlot = qCount % Q_SLOTS;
@@ -1649,6 +1658,14 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     const size_t vrefBytes = VRefBytes(p.HeadCount);
     TFwdParams fp;
     fp.HeadCount = p.HeadCount;
+    {
+        // keys + values of one head (an upper bound of what the items of one head touch); groups of heads that keep about 128 MB
+        // in flight, the size of L2, and never fewer than four heads
+        const long long perHead = (long long)keyRows * D * (vI8 ? 3 : 2);
+        long long g = perHead > 0 ? (128ll << 20) / perHead : p.HeadCount;
+        g = g < 4 ? 4 : g;
+        fp.HeadGroup = (int)(g < p.HeadCount ? g : p.HeadCount);
+    }
     fp.OutRows = p.Len;
     fp.KeyRows = keyRows;
     fp.LenAttTiles = lenAttTiles;
