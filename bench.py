@@ -330,7 +330,8 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     # per-slice NCCL all-gather.
     fused, scatter, symm_handle, peer_out, side = False, False, None, None, None
     if world > 1:
-        # measured: fused is ahead at every N (two GPUs: 15.16 against 15.53 ms with NCCL; eight: 4.45 against 4.94 ms)
+        # measured: fused is ahead at every N (four launches per step, two GPUs: 15.16 against 15.53 ms with NCCL; eight: 4.45
+        # against 4.94 ms; as one launch per step 4.19 ms on eight)
         mode = gather_mode
         if mode in ("fused", "scatter"):
             try:
