@@ -193,6 +193,36 @@ def test_fwd_fused_consumer_equals_attention_then_kv_product(d, window, slope):
         ops.att_fwd(cfg32, g["q8"], g["k8"], g["v8"], g["sk"], mask, slope, heads, qk_scale=g["sq"], v_scale=g["sv"], status=status, combiner_k=ck)
 
 
+def test_fwd_head_groups_equal_single_head_calls():
+    """The forward hands its work items out in groups of heads sized by the key / value bytes of one head; with 98304 key rows
+    of 6 heads x 128 the groups are 5 + 1 heads (an incomplete last group).  Per-head work is independent, so the call over
+    all heads must equal six single-head calls on the head's columns bit for bit (inputs generated and quantised on the
+    device; the window-64 mask over 24 fragments of 4096 rows keeps it short)."""
+    from tscale_b200 import ops
+    heads, d, frag, nfrag, window = 6, 128, 4096, 24, 64
+    rows = frag * nfrag
+    gen = torch.Generator(device=_dev())
+    gen.manual_seed(21)
+    t = {}
+    for nm in ("q", "k", "v"):
+        x = torch.randn((rows, heads * d), generator=gen, device=_dev()) * 0.5
+        t[nm], t["s" + nm] = ops.quant_rows(x, "absmax", "e4m3", d)
+        del x
+    mask = ops.Mask.window([frag] * nfrag, window)
+    cfg = ops.make_cfg("e4m3", "e4m3", d, d, out_dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    out, lse = ops.att_fwd(cfg, t["q"], t["k"], t["v"], t["sk"], mask, 0.25, heads, qk_scale=t["sq"], v_scale=t["sv"], status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for h in range(heads):
+        cols = slice(h * d, (h + 1) * d)
+        o1, l1 = ops.att_fwd(cfg, t["q"][:, cols], t["k"][:, cols], t["v"][:, cols], t["sk"][h:h + 1], mask, 0.25, 1,
+                             qk_scale=t["sq"][h:h + 1], v_scale=t["sv"][h:h + 1], status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(o1, out[:, cols]) and torch.equal(l1[0], lse[h]), "head %d" % h
+
+
 def test_peer_scatter_copies_block_to_every_destination():
     """tsa_peer_scatter (one rank's part of the all-gather over peer memory, the library's own copy kernel): the rows of the
     source land in every destination, nothing else is touched; local buffers stand in for the peers'."""
