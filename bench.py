@@ -504,7 +504,7 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
     achieved = (flops / world) / (k_ms * 1e-3) / 1e12
     roofline = tensor_roofline(torch, dev, w, "FwdSm100Kernel<128> (full causal, e4m3 QK^T and PV), this rank's %d (fragment, head) units" % (nf * nh),
                                achieved, k_ms, flops / world, clocks)
-    roofline["timed"] = ("CUDA events around each slice's tsa_att_fwd call in the timed region (memset + V-scale maximum kernel of a few "
+    roofline["timed"] = ("CUDA events around each slice's tsa_att_fwd call in the timed region (V-scale maximum kernel of a few "
                          "microseconds + the attention kernel), summed per step")
     # DRAM bytes per step (this rank's launches together, like ms_per_launch): the committed ncu capture of one launch over 8
     # (fragment, head) units of this workload (profiles/fwd_sm100_e4m3_d128_longctx_1frag.md: 188.7 MB read + 39.2 MB written,
@@ -753,7 +753,7 @@ def run_layers(args, name, w, rank, world, local_rank, quick=False):
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     roofline = tensor_roofline(torch, dev, w, "FwdSm100Kernel<%d> (full-causal layer, %s QK^T, e4m3 PV)" % (d, w["qk"]),
                                achieved, dom_ms, dom_flops, clocks)
-    roofline["timed"] = "CUDA events around the layer's tsa_att_fwd call (memset + V-scale maximum kernel of a few microseconds + the attention kernel)"
+    roofline["timed"] = "CUDA events around the layer's tsa_att_fwd call (V-scale maximum kernel of a few microseconds + the attention kernel)"
     per_layer = []
     for i, it in enumerate(layers):
         ms = float(np.mean([a.elapsed_time(b) for a, b in layer_events[i]]))

@@ -1419,6 +1419,49 @@ __global__ void __launch_bounds__(256) VRefKernel(P2D<float> vScale, int keyRows
     }
 }
 
+// The same maximum with one CTA per head and no atomics, so that nothing has to be cleared first; the CTA of head 0 also
+// zeroes the forward's work-item counter: one launch in front of the attention kernel instead of a memset and a kernel.
+// Taken while a head's scale row is short enough for one CTA (VREF_ONE_CTA_ROWS).
+constexpr int VREF_ONE_CTA_ROWS = 1 << 18;
+__global__ void __launch_bounds__(1024) VRefHeadKernel(P2D<float> vScale, int keyRows, float *vRef, int *counter)
+{
+    __shared__ float part[32];
+    const int head = blockIdx.x, tid = threadIdx.x;
+    const float *rowp = vScale.Row(head);
+    float mx = 0;
+    if (((uintptr_t)rowp & 15) == 0) {
+        const float4 *row4 = reinterpret_cast<const float4 *>(rowp);
+        const int n4 = keyRows >> 2;
+#pragma unroll 4
+        for (int i = tid; i < n4; i += 1024) {
+            const float4 x = row4[i];
+            mx = fmaxf(fmaxf(mx, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
+        }
+        for (int t = (n4 << 2) + tid; t < keyRows; t += 1024) {
+            mx = fmaxf(mx, rowp[t]);
+        }
+    } else {
+#pragma unroll 8
+        for (int t = tid; t < keyRows; t += 1024) {
+            mx = fmaxf(mx, rowp[t]);
+        }
+    }
+    mx = WarpMax(mx);
+    if ((tid & 31) == 0) {
+        part[tid >> 5] = mx;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        mx = WarpMax(part[tid]);
+        if (tid == 0) {
+            vRef[head] = mx;
+            if (head == 0) {
+                *counter = 0;
+            }
+        }
+    }
+}
+
 // ---- raw int32 score tiles (parity hook for the kind::i8 accumulators) -------------------------
 struct TScoresMisc {
     uint64_t BarQ, BarMma;
@@ -1707,14 +1750,23 @@ int LaunchSm100Fwd(const tsa_att_cfg *cfg, const TGenParams &p, tsa_ptr2d qk, ts
     fp.DumpTile = g_dump.Tile;
     fp.WaitCycles = g_dump.WaitCycles > 0 ? g_dump.WaitCycles : WAIT_CYCLES;
     fp.WithholdTile = g_dump.WithholdTile;
-    // one clear covers the V-scale maxima and the counter behind them
-    rc = CheckCuda(cudaMemsetAsync(hasVs ? workspace : (void *)fp.Counter, 0, hasVs ? vrefBytes + 256 : 256, stream), "clearing the forward workspace");
-    if (rc != TSA_OK) {
-        return rc;
-    }
-    if (hasVs) {
-        dim3 vgrid((keyRows + VREF_CHUNK - 1) / VREF_CHUNK, p.HeadCount);
-        VRefKernel<<<vgrid, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
+    if (hasVs && keyRows <= VREF_ONE_CTA_ROWS) {
+        // one launch writes the per-head maxima and zeroes the counter
+        VRefHeadKernel<<<p.HeadCount, 1024, 0, stream>>>(p.VScale, keyRows, (float *)workspace, fp.Counter);
+        rc = CheckCuda(cudaGetLastError(), "value-scale maximum launch");
+        if (rc != TSA_OK) {
+            return rc;
+        }
+    } else {
+        // one clear covers the V-scale maxima and the counter behind them
+        rc = CheckCuda(cudaMemsetAsync(hasVs ? workspace : (void *)fp.Counter, 0, hasVs ? vrefBytes + 256 : 256, stream), "clearing the forward workspace");
+        if (rc != TSA_OK) {
+            return rc;
+        }
+        if (hasVs) {
+            dim3 vgrid((keyRows + VREF_CHUNK - 1) / VREF_CHUNK, p.HeadCount);
+            VRefKernel<<<vgrid, 256, 0, stream>>>(p.VScale, keyRows, (float *)workspace);
+        }
     }
     const bool i8 = cfg->qk_dtype == TSA_I8;
     const bool alibi = p.Slope != 0.0f;
