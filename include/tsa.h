@@ -93,7 +93,12 @@ const char *tsa_last_error(void);
  *   out           [len][H*Dv] of cfg->out_dtype; sumWeightLog f32 [H][len] (may be absent)
  * logit(i,j) = dot(qk_i, qv_j) * qkScale_i * qvScale_j * sqrt(1/Dqk) * 0.5/0.693147 * (*qvGlobalScale)
  *              - alibiSlope * (i - j);  softmax base 2 with an extra logit-0 / value-0 sink;
- * rows without keys give 0.  qvGlobalScale: device scalar, NULL = 1. */
+ * rows without keys give 0.  qvGlobalScale: device scalar, NULL = 1.
+ * Range of vScale on the tensor-core path: a weight is multiplied by vScale[key] / (the power of two at or above the head's
+ * largest vScale over all key rows of the call) before it is rounded to e4m3, so the row's result keeps its precision while
+ * the keys that carry its weight have value scales within a factor of 64 of that maximum (e4m3's normal range below 1), and
+ * loses it gradually beyond (per-row abs-max scales of normalised vectors are within a small factor of each other; the
+ * reference's kernel uses one constant value scale).  TSA_FLAG_FORCE_GENERIC keeps fp32 weights and has no such limit. */
 int tsa_att_fwd(const tsa_att_cfg *cfg, const float *qvGlobalScale,
     tsa_ptr2d qk, tsa_ptr2d qv, tsa_ptr2d qkScale, tsa_ptr2d qvScale,
     tsa_ptr2d v, tsa_ptr2d vScale,
