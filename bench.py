@@ -344,6 +344,11 @@ def run_longctx(args, name, w, rank, world, local_rank, quick=False):
                 side = torch.cuda.Stream(device=dev)
             except Exception as exc:  # noqa: BLE001 - any failure of the symmetric-memory set-up falls back to NCCL
                 sys.stderr.write("symmetric memory unavailable (%s): gathering with NCCL\n" % (exc,))
+            # every rank takes the same route: one rank without symmetric memory sends all of them to NCCL
+            agreed = torch.tensor([1 if (fused or scatter) else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:
+                fused, scatter, symm_handle, peer_out = False, False, None, None
                 if args.slices <= 0 and nh % 4 == 0:
                     widths = [nh // 4] * 4  # NCCL gathers overlap the following slices' kernels
                     n_slices = len(widths)
